@@ -1,0 +1,87 @@
+// Shared vocabulary of the kernel library: dtype codes, typed loads and
+// stores, the error channel, and warp/block reductions.
+//
+// Every exported launcher is `extern "C"`, takes raw device pointers, sizes
+// and a stream, validates its arguments on the host, and returns 0 or a
+// negative code after recording a message that `fb_last_error()` returns.
+// The reference validates every launch the same way before it reaches the
+// device (crates/forward/src/core/composites/standard_attn.rs:74-119).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define FB_API extern "C" __attribute__((visibility("default")))
+
+enum FbDtype : int { FB_F32 = 0, FB_BF16 = 1 };
+
+// Status word bits that kernels may set (never trap, never spin forever).
+enum FbStatus : int {
+    FB_STATUS_BAD_TOKEN = 1,      // embedding id outside the table
+    FB_STATUS_BAD_PAGE = 2,       // block table entry missing for a live key
+    FB_STATUS_WAIT_TIMEOUT = 4,   // a bounded barrier wait ran out
+};
+
+int fb_fail(int code, const char* fmt, ...);   // records the message, returns code
+int fb_check_launch(const char* what);          // cudaGetLastError -> fb_fail
+
+#define FB_REQUIRE(cond, ...)                                   \
+    do {                                                        \
+        if (!(cond)) return fb_fail(-1, __VA_ARGS__);           \
+    } while (0)
+
+// ---- typed access -----------------------------------------------------------
+__device__ __forceinline__ float fb_to_float(float v) { return v; }
+__device__ __forceinline__ float fb_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T fb_from_float(float v);
+template <> __device__ __forceinline__ float fb_from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 fb_from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// ---- reductions -------------------------------------------------------------
+__device__ __forceinline__ float fb_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float fb_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum; `scratch` holds at least 32 floats of shared memory.
+// Every thread of the block must call it; every thread gets the result.
+__device__ __forceinline__ float fb_block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = fb_warp_sum(v);
+    __syncthreads();                       // scratch may still be read from a previous call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : 0.0f;
+    r = fb_warp_sum(r);
+    return r;
+}
+__device__ __forceinline__ float fb_block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = fb_warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    r = fb_warp_max(r);
+    return r;
+}
+
+// Dispatch a dtype code to a template parameter.
+#define FB_DISPATCH_DTYPE(code, T, ...)                                   \
+    do {                                                                  \
+        if ((code) == FB_F32) { using T = float; __VA_ARGS__; }           \
+        else if ((code) == FB_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+        else return fb_fail(-1, "unknown dtype code %d", (int)(code));    \
+    } while (0)

@@ -1,0 +1,227 @@
+// Row-wise kernels between the matrix products: embedding gather, fused
+// residual add + RMSNorm, rotary tables, rotary + paged cache write, SiLU*mul.
+// All arithmetic is float32 whatever the storage type; the residual stream
+// itself is float32 in both engine modes.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding: x[t,:] = E[ids[t],:]  (crates/forward/src/core/composites/embed.rs:26-62)
+// ---------------------------------------------------------------------------
+template <typename TT>
+__global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ x, int H, int V, int* status) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0) atomicOr(status, FB_STATUS_BAD_TOKEN);
+        id = 0;
+    }
+    const TT* src = table + (size_t)id * H;
+    float* dst = x + (size_t)t * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = fb_to_float(src[c]);
+}
+
+FB_API int fb_embedding(const void* table, int table_dtype, const int* ids, float* x, int n, int H,
+                        int V, int* status, cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && H > 0 && V > 0, "embedding: bad sizes n=%d H=%d V=%d", n, H, V);
+    if (n == 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    FB_DISPATCH_DTYPE(table_dtype, TT,
+        embedding_kernel<TT><<<n, threads, 0, stream>>>((const TT*)table, ids, x, H, V, status));
+    return fb_check_launch("embedding");
+}
+
+// ---------------------------------------------------------------------------
+// Fused residual add + RMSNorm.
+//   r = rows ? rows[j] : j
+//   v = x[r] + sum_p delta[p][r]        (delta optional; n_partials slabs, slab stride given)
+//   if (!rows && delta) x[r] = v        (the stream is updated in place)
+//   out[j] = v * w / sqrt(mean(v^2) + eps)
+// crates/kernels-hip/src/kernels/rmsnorm_f16_add_residual.cu; rmsnorm_f16.cu:41-85.
+// The row lives in shared memory between the two passes.
+// ---------------------------------------------------------------------------
+template <typename TD, typename TW, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_partials,
+                                   size_t partial_stride, const TW* __restrict__ w,
+                                   TO* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    const int j = blockIdx.x;
+    const int r = rows ? rows[j] : j;
+    float* xr = x + (size_t)r * H;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = xr[c];
+        if (delta) {
+            for (int p = 0; p < n_partials; ++p)
+                v += fb_to_float(delta[(size_t)p * partial_stride + (size_t)r * H + c]);
+            if (!rows) xr[c] = v;
+        }
+        row[c] = v;
+        ss += v * v;
+    }
+    ss = fb_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)j * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x)
+        o[c] = fb_from_float<TO>(row[c] * fb_to_float(w[c]) * inv);
+}
+
+template <typename TD, typename TW, typename TO>
+static int launch_add_rmsnorm(float* x, const void* delta, int n_partials, size_t partial_stride,
+                              const void* w, void* out, const int* rows, int n_out, int H, float eps,
+                              cudaStream_t stream) {
+    const size_t smem = (size_t)H * sizeof(float);
+    auto kern = add_rmsnorm_kernel<TD, TW, TO>;
+    if (smem > 48 * 1024) {
+        if (smem > 220 * 1024) return fb_fail(-1, "add_rmsnorm: width %d does not fit in shared memory", H);
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    kern<<<n_out, threads, smem, stream>>>(x, (const TD*)delta, n_partials, partial_stride, (const TW*)w,
+                                           (TO*)out, rows, H, eps);
+    return fb_check_launch("add_rmsnorm");
+}
+
+FB_API int fb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_partials,
+                          long long partial_stride, const void* w, int w_dtype, void* out, int out_dtype,
+                          const int* rows, int n_out, int H, float eps, cudaStream_t stream) {
+    FB_REQUIRE(n_out >= 0 && H > 0, "add_rmsnorm: bad sizes n=%d H=%d", n_out, H);
+    FB_REQUIRE(eps > 0.0f, "add_rmsnorm: eps must be positive");
+    if (n_out == 0) return 0;
+    if (!delta) { delta_dtype = FB_F32; n_partials = 0; }
+    FB_DISPATCH_DTYPE(delta_dtype, TD, FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(out_dtype, TO,
+        return (launch_add_rmsnorm<TD, TW, TO>(x, delta, n_partials, (size_t)partial_stride, w, out, rows,
+                                               n_out, H, eps, stream)))));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Rotary tables for one step: cos/sin [n, half] of pos * inv_freq[i].
+// The angle is formed and reduced in double precision so that it is right to
+// float32 rounding at any position; the tables are float32.
+// Formula: crates/kernels-hip/src/kernels/rope_neox_partial_f16.cu:39-46.
+// ---------------------------------------------------------------------------
+__global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
+                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int n, int half) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n * half) return;
+    const int t = idx / half, i = idx - t * half;
+    double s, c;
+    sincos((double)positions[t] * inv_freq[i], &s, &c);
+    cos_t[idx] = (float)c;
+    sin_t[idx] = (float)s;
+}
+
+FB_API int fb_rope_table(const int* positions, const double* inv_freq, float* cos_t, float* sin_t, int n,
+                         int half, cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && half > 0, "rope_table: bad sizes n=%d half=%d", n, half);
+    if (n == 0) return 0;
+    const int total = n * half;
+    rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(positions, inv_freq, cos_t, sin_t, n, half);
+    return fb_check_launch("rope_table");
+}
+
+// ---------------------------------------------------------------------------
+// Rotary (split-half pairs (i, i+half)) on q in place and on k on its way into
+// the cache; v is copied into the cache.  One block per token.
+// Cache layout: [page][kv head][slot in page][head_dim]; the physical page of
+// logical position p of sequence s is block_table[s*table_stride + p/page_size].
+// crates/kernels-hip/src/kernels/rope_neox_partial_f16.cu:39-52 (rotation),
+// kv_append_f16_paged_prefill.cu (row placement).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ q, long q_stride, const T* __restrict__ k, long k_stride,
+                                     const T* __restrict__ v, long v_stride, const float* __restrict__ cos_t,
+                                     const float* __restrict__ sin_t, int half,
+                                     const int* __restrict__ positions, const int* __restrict__ row_seq,
+                                     const int* __restrict__ block_table, int table_stride,
+                                     T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size, int n_pages,
+                                     int nh, int nkv, int hd, int write_kv, int* status) {
+    const int t = blockIdx.x;
+    const int per_head = hd - half;                 // `half` rotated pairs + (hd - 2*half) untouched dims
+    const float* ct = cos_t ? cos_t + (size_t)t * half : nullptr;
+    const float* st = sin_t ? sin_t + (size_t)t * half : nullptr;
+
+    // q heads, in place
+    T* qt = q + (size_t)t * q_stride;
+    for (int idx = threadIdx.x; idx < nh * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx - h * half;
+        T* p = qt + (size_t)h * hd;
+        const float a = fb_to_float(p[i]), b = fb_to_float(p[i + half]);
+        const float c = ct[i], s = st[i];
+        p[i] = fb_from_float<T>(a * c - b * s);
+        p[i + half] = fb_from_float<T>(a * s + b * c);
+    }
+    if (!write_kv) return;
+
+    const int pos = positions[t];
+    const int page = block_table[(size_t)row_seq[t] * table_stride + pos / page_size];
+    if (page < 0 || page >= n_pages) {
+        if (threadIdx.x == 0) atomicOr(status, FB_STATUS_BAD_PAGE);
+        return;
+    }
+    const int slot = pos % page_size;
+    const T* kt = k + (size_t)t * k_stride;
+    const T* vt = v + (size_t)t * v_stride;
+    for (int idx = threadIdx.x; idx < nkv * per_head; idx += blockDim.x) {
+        const int h = idx / per_head, j = idx - h * per_head;
+        const T* src = kt + (size_t)h * hd;
+        T* dst = k_pool + (((size_t)page * nkv + h) * page_size + slot) * hd;
+        if (j < half) {
+            const float a = fb_to_float(src[j]), b = fb_to_float(src[j + half]);
+            const float c = ct[j], s = st[j];
+            dst[j] = fb_from_float<T>(a * c - b * s);
+            dst[j + half] = fb_from_float<T>(a * s + b * c);
+        } else {
+            dst[j + half] = src[j + half];
+        }
+    }
+    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+        const int h = idx / hd, d = idx - h * hd;
+        v_pool[(((size_t)page * nkv + h) * page_size + slot) * hd + d] = vt[(size_t)h * hd + d];
+    }
+}
+
+FB_API int fb_rope_kv_write(void* q, long long q_stride, const void* k, long long k_stride, const void* v,
+                            long long v_stride, int dtype, const float* cos_t, const float* sin_t, int half,
+                            const int* positions, const int* row_seq, const int* block_table,
+                            int table_stride, void* k_pool, void* v_pool, int page_size, int n_pages, int n,
+                            int nh, int nkv, int hd, int write_kv, int* status, cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && nh > 0 && nkv >= 0 && hd > 0, "rope_kv_write: bad sizes");
+    FB_REQUIRE(half >= 0 && 2 * half <= hd, "rope_kv_write: rotary width %d exceeds head size %d", 2 * half, hd);
+    FB_REQUIRE(half == 0 || (cos_t && sin_t), "rope_kv_write: rotary tables missing");
+    FB_REQUIRE(!write_kv || (page_size > 0 && n_pages > 0 && k_pool && v_pool && block_table),
+               "rope_kv_write: cache arguments missing");
+    if (n == 0) return 0;
+    FB_DISPATCH_DTYPE(dtype, T,
+        rope_kv_write_kernel<T><<<n, 128, 0, stream>>>((T*)q, q_stride, (const T*)k, k_stride, (const T*)v,
+            v_stride, cos_t, sin_t, half, positions, row_seq, block_table, table_stride, (T*)k_pool,
+            (T*)v_pool, page_size, n_pages, nh, nkv, hd, write_kv, status));
+    return fb_check_launch("rope_kv_write");
+}
+
+// ---------------------------------------------------------------------------
+// SiLU(gate) * up on a fused [n, 2I] buffer (gate in columns [0,I), up in [I,2I)).
+// crates/kernels-hip/src/kernels/swiglu_f32_to_f16.cu; activation.rs:107-118.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, long stride, T* __restrict__ out, int n, int I) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n * I) return;
+    const int r = (int)(idx / I), c = (int)(idx - (size_t)r * I);
+    const float g = fb_to_float(gu[(size_t)r * stride + c]);
+    const float u = fb_to_float(gu[(size_t)r * stride + I + c]);
+    out[idx] = fb_from_float<T>(g / (1.0f + expf(-g)) * u);
+}
+
+FB_API int fb_silu_mul(const void* gate_up, long long stride, void* out, int dtype, int n, int I,
+                       cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && I > 0 && stride >= 2LL * I, "silu_mul: bad sizes n=%d I=%d stride=%lld", n, I, stride);
+    if (n == 0) return 0;
+    const size_t total = (size_t)n * I;
+    FB_DISPATCH_DTYPE(dtype, T,
+        silu_mul_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const T*)gate_up, stride,
+                                                                                 (T*)out, n, I));
+    return fb_check_launch("silu_mul");
+}

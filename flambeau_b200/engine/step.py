@@ -1,0 +1,168 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the
+wanted places out.
+
+One step runs exactly the tokens it is given, as one batch, against the cache
+that earlier steps left: portions of prompts of any length beside single
+decoded tokens, in any mix.  The reference has three shapes of step (one
+prompt portion, N decode tokens, or exactly one portion plus decode tokens;
+crates/forward/src/runtime/mod.rs:188-258, ctx.rs:42-94); here a decoded token
+is just a portion of length one and any number of portions may share a step.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..cache.manager import CacheManager
+from .batch import BatchBuffers, BatchError, Entry, StepBatch
+from .runtime import Runtime, Workspace
+
+
+@dataclass
+class EngineOptions:
+    dtype: str = "bfloat16"            # 'bfloat16' (serving kernels) or 'float32' (true 32-bit everywhere)
+    page_size: int = 16                # tokens per cache page (crates/forward/src/core/scratch.rs:293)
+    cache_tokens: int = 4096           # tokens the page pool of each group can hold
+    max_requests: int = 8              # live requests (state slots, block-table rows)
+    max_step_tokens: int = 2048        # rows of one step
+    max_seq_len: Optional[int] = None  # longest request; default: the pool size or the model's position limit
+    device: str = "cuda:0"
+
+
+class StepContext:
+    """What parts see during one step."""
+
+    def __init__(self, engine, batch: StepBatch):
+        self.engine = engine
+        self.runtime = engine.runtime
+        self.batch = batch
+        self.n_tokens = batch.n_tokens
+        self.ws = engine.runtime.ws
+        self.shared: dict = {}              # per-step memo shared between layers (rotary tables, work lists)
+        self.normed = self.delta = None
+
+    def step_alloc(self, shape, dtype):
+        """Scratch that lives until the step ends (ctx.ws allocations end with their scope)."""
+        return self.engine.step_ws.alloc(shape, dtype)
+
+    def cache(self, call: int):
+        return self.engine.cache.view(call, self.batch.tables)
+
+    def logits(self, n_out: int, vocab: int):
+        return self.engine.logits_buffer(n_out, vocab)
+
+
+class Engine:
+    """A model, its cache and the step function."""
+
+    def __init__(self, model, options: EngineOptions):
+        self.model = model
+        self.options = options
+        self.runtime: Runtime = model.runtime
+        rt = self.runtime
+        limit = options.max_seq_len or min(options.cache_tokens, model.spec.max_positions or options.cache_tokens)
+        self.max_seq_len = int(limit)
+        self.cache = CacheManager(model.cache_plans(), max_tokens=options.cache_tokens, page_size=rt.page_size,
+                                  max_requests=options.max_requests, device=rt.device, dtype=rt.dtype,
+                                  max_seq_len=self.max_seq_len)
+        self.buffers = BatchBuffers(rt.device, options.max_step_tokens, options.max_requests, self.cache.n_groups,
+                                    self.cache.max_pages_per_request)
+        self.step_ws = Workspace(rt.device, 1 << 22)
+        self._logits = None
+        self._copied = torch.cuda.Event()
+        self._copy_pending = False
+        self.steps_run = 0
+        self.last_batch: Optional[StepBatch] = None
+
+    # ---- construction ----------------------------------------------------------
+    @classmethod
+    def from_folder(cls, folder, options: EngineOptions | None = None, **kw) -> "Engine":
+        from .. import models  # noqa: F401  (registers the built-in architectures)
+        from ..weights.loader import load_model
+        options = options or EngineOptions(**kw)
+        rt = Runtime(options.device, options.dtype, options.page_size)
+        return cls(load_model(folder, rt), options)
+
+    @classmethod
+    def from_config(cls, config, seed: int = 0, options: EngineOptions | None = None, **kw) -> "Engine":
+        """Random weights generated on the device (no model folder)."""
+        from .. import models  # noqa: F401
+        from ..config.registry import resolve
+        from ..models.decoder import DecoderModel
+        from ..weights.random_init import fill_random_on_device
+        options = options or EngineOptions(**kw)
+        rt = Runtime(options.device, options.dtype, options.page_size)
+        model = DecoderModel(resolve(config.architecture).build_spec(config), rt)
+        model.config = config
+        fill_random_on_device(model, seed)
+        return cls(model, options)
+
+    # ---- buffers -----------------------------------------------------------------
+    def logits_buffer(self, n_out: int, vocab: int) -> torch.Tensor:
+        if self._logits is None or self._logits.shape[0] < n_out or self._logits.shape[1] != vocab:
+            rows = max(n_out, self.options.max_requests)
+            self._logits = torch.empty((rows, vocab), dtype=torch.float32, device=self.runtime.device)
+        return self._logits[:n_out]
+
+    # ---- requests ----------------------------------------------------------------
+    def admit(self, request_id):
+        return self.cache.admit(request_id)
+
+    def finish(self, request_id) -> None:
+        self.cache.release(request_id)
+
+    def is_live(self, request_id) -> bool:
+        return request_id in self.cache.requests
+
+    # ---- the step ------------------------------------------------------------------
+    def step(self, entries: list, end=()) -> Optional[torch.Tensor]:
+        """Run `entries` (Entry or (request_id, tokens, want) tuples) as one batch.
+
+        Unknown request ids are admitted.  Returns float32 logits [wanted, vocab] on the device, in the
+        order of the entries and of each entry's `want` (None if nothing is wanted); the tensor is
+        overwritten by the next step.  Requests in `end` give back what they hold after the step.
+        Raises cache.pages.OutOfPages before anything runs if the pages do not suffice."""
+        entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
+        cache = self.cache
+        logits = None
+        if entries:
+            admitted = []
+            try:
+                for e in entries:
+                    if e.request_id not in cache.requests:
+                        cache.admit(e.request_id)
+                        admitted.append(e.request_id)
+                needs = [(e.request_id, len(e.tokens)) for e in entries]
+                if not cache.can_reserve(needs):
+                    from ..cache.pages import OutOfPages
+                    short = [sum(cache.pages_needed(r, k)[gi] for r, k in needs) for gi in range(cache.n_groups)]
+                    raise OutOfPages(max(short), min(cache.free_pages()), cache.groups[0].pool.n_pages)
+                for rid, k in needs:
+                    if cache.length(rid) + k > self.max_seq_len:
+                        raise BatchError(f"request {rid!r} would reach {cache.length(rid) + k} tokens; "
+                                         f"the engine was built for {self.max_seq_len} per request")
+                for rid, k in needs:
+                    cache.reserve(rid, k)
+            except Exception:
+                for rid in admitted:
+                    cache.release(rid)
+                raise
+            if self._copy_pending:
+                self._copied.synchronize()          # the staging buffers are free to be rewritten
+            batch = self.buffers.build(entries, cache, self.model.vocab_size)
+            self._copied.record()
+            self._copy_pending = True
+            self.runtime.ws.reset()
+            self.step_ws.reset()
+            ctx = StepContext(self, batch)
+            logits = self.model.forward(ctx)
+            for e in entries:
+                cache.commit(e.request_id, len(e.tokens))
+            self.last_batch = batch
+            self.steps_run += 1
+        for rid in end:
+            if rid in cache.requests:
+                cache.release(rid)
+        return logits

@@ -1,0 +1,76 @@
+"""Loads the compiled kernel library and declares the C signatures.
+
+There is no fallback: if the library cannot be built or loaded, `lib()` raises
+and nothing of the engine runs.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_double, c_float, c_int, c_longlong, c_void_p
+
+from .build import ensure_built
+
+P = c_void_p
+I = c_int
+L = c_longlong
+F = c_float
+STREAM = c_void_p
+
+_SIGNATURES = {
+    "fb_last_error": (c_char_p, []),
+    "fb_abi_version": (I, []),
+    # elementwise.cu
+    "fb_embedding": (I, [P, I, P, P, I, I, I, P, STREAM]),
+    "fb_add_rmsnorm": (I, [P, P, I, I, L, P, I, P, I, P, I, I, F, STREAM]),
+    "fb_rope_table": (I, [P, P, P, P, I, I, STREAM]),
+    "fb_rope_kv_write": (I, [P, L, P, L, P, L, I, P, P, I, P, P, P, I, P, P, I, I, I, I, I, I, I, P, STREAM]),
+    "fb_silu_mul": (I, [P, L, P, I, I, I, STREAM]),
+    # gemm_simt.cu
+    "fb_gemm_simt": (I, [P, I, L, P, I, L, P, I, L, I, I, I, STREAM]),
+    # attention_simt.cu
+    "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, I, I, I, I, I, F, P, STREAM]),
+    # sampling.cu
+    "fb_apply_penalties": (I, [P, L, I, P, P, P, P, P, P, I, STREAM]),
+    "fb_apply_logit_bias": (I, [P, L, I, P, P, P, I, STREAM]),
+    "fb_sample": (I, [P, L, I, I, P, P, P, P, P, P, STREAM]),
+}
+
+_LIB = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def declare(handle, signatures: dict) -> None:
+    for name, (res, args) in signatures.items():
+        try:
+            fn = getattr(handle, name)
+        except AttributeError:
+            raise KernelError(f"the kernel library has no symbol '{name}' (stale build?)") from None
+        fn.restype = res
+        fn.argtypes = args
+
+
+def lib():
+    """The loaded library (built on first use)."""
+    global _LIB
+    if _LIB is None:
+        path = ensure_built()
+        try:
+            handle = ctypes.CDLL(str(path))
+        except OSError as e:
+            raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+        declare(handle, _SIGNATURES)
+        _LIB = handle
+    return _LIB
+
+
+def library_path() -> str:
+    return str(ensure_built())
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = lib().fb_last_error().decode(errors="replace")
+        raise KernelError(f"{what}: {msg or 'error code %d' % code}")

@@ -1,0 +1,196 @@
+"""Tensor-level wrappers of the kernel launchers.
+
+Each wrapper checks devices, dtypes and strides, then launches on torch's
+current CUDA stream.  Constants (eps, theta-derived tables, head sizes, window,
+scale) arrive as arguments; nothing here knows a model.
+"""
+from __future__ import annotations
+
+import torch
+
+from .library import KernelError, check, lib
+
+_CODES = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not supported by the kernels (float32 or bfloat16)") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel arguments must live on the GPU; there is no CPU path")
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _rows(t: torch.Tensor) -> int:
+    """Row stride (elements) of a 2-d tensor whose rows are dense."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"expected a 2-d tensor with dense rows, got shape {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0)
+
+
+def _i32(t, what):
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{what} must be int32")
+
+
+# ---------------------------------------------------------------------------
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor, status: torch.Tensor) -> None:
+    _cuda(table, ids, x, status)
+    _i32(ids, "token ids")
+    V, H = table.shape
+    n = ids.numel()
+    if x.dtype != torch.float32 or x.shape[0] < n or x.shape[1] != H or not x.is_contiguous() \
+            or not table.is_contiguous():
+        raise KernelError("embedding: the stream must be contiguous float32 [n, width]")
+    check(lib().fb_embedding(table.data_ptr(), dtype_code(table), ids.data_ptr(), x.data_ptr(), n, H, V,
+                             status.data_ptr(), _stream()), "embedding")
+
+
+def add_rms_norm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                 rows=None, n_partials: int = 1, n_rows: int | None = None) -> None:
+    """out[j] = rmsnorm(x[r] + sum_p delta[p][r]) * weight, r = rows[j] or j; without `rows` the sum is
+    also written back to x.  `delta` is [n, H] or, with n_partials > 1, [n_partials, n, H]."""
+    _cuda(x, delta, weight, out, rows)
+    _i32(rows, "rows")
+    H = x.shape[1]
+    n_out = rows.numel() if rows is not None else (x.shape[0] if n_rows is None else n_rows)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or out.shape[-1] != H \
+            or weight.numel() != H or out.shape[0] < n_out:
+        raise KernelError("add_rms_norm: bad shapes")
+    stride = 0
+    if delta is not None:
+        if not delta.is_contiguous() or delta.shape[-1] != H:
+            raise KernelError("add_rms_norm: delta must be contiguous with the stream's width")
+        if n_partials > 1:
+            stride = delta.stride(0)
+    check(lib().fb_add_rmsnorm(x.data_ptr(), _ptr(delta), dtype_code(delta) if delta is not None else 0,
+                               n_partials, stride, weight.data_ptr(), dtype_code(weight), out.data_ptr(),
+                               dtype_code(out), _ptr(rows), n_out, H, float(eps), _stream()), "add_rms_norm")
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+    _cuda(positions, inv_freq, cos, sin)
+    _i32(positions, "positions")
+    n, half = positions.numel(), inv_freq.numel()
+    if inv_freq.dtype != torch.float64 or cos.dtype != torch.float32 or sin.dtype != torch.float32 \
+            or cos.numel() < n * half or sin.numel() < n * half:
+        raise KernelError("rope_table: bad arguments")
+    check(lib().fb_rope_table(positions.data_ptr(), inv_freq.data_ptr(), cos.data_ptr(), sin.data_ptr(), n, half,
+                              _stream()), "rope_table")
+
+
+def rope_kv_write(q, k, v, cos, sin, half: int, positions, row_seq, block_table, k_pool, v_pool,
+                  page_size: int, nh: int, nkv: int, hd: int, write_kv: bool, status) -> None:
+    """Rotate q in place; rotate k into the cache and copy v into the cache (when write_kv)."""
+    _cuda(q, k, v, cos, sin, positions, row_seq, block_table, k_pool, v_pool, status)
+    n = q.shape[0]
+    if q.shape[1] != nh * hd or (write_kv and (k.shape[1] != nkv * hd or v.shape[1] != nkv * hd)):
+        raise KernelError("rope_kv_write: q/k/v widths do not match the head counts")
+    if write_kv and (k.dtype != q.dtype or v.dtype != q.dtype or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype):
+        raise KernelError("rope_kv_write: q, k, v and the cache must share one dtype")
+    n_pages = k_pool.shape[0] if write_kv else 0
+    if write_kv and (tuple(k_pool.shape) != (n_pages, nkv, page_size, hd) or not k_pool.is_contiguous()
+                     or tuple(v_pool.shape) != tuple(k_pool.shape) or not v_pool.is_contiguous()):
+        raise KernelError("rope_kv_write: cache pools must be contiguous [pages, kv heads, page size, head size]")
+    check(lib().fb_rope_kv_write(
+        q.data_ptr(), _rows(q), _ptr(k), _rows(k) if k is not None else 0, _ptr(v),
+        _rows(v) if v is not None else 0, dtype_code(q), _ptr(cos), _ptr(sin), half, _ptr(positions),
+        _ptr(row_seq), _ptr(block_table), block_table.stride(0) if block_table is not None else 0,
+        _ptr(k_pool), _ptr(v_pool), page_size, n_pages, n, nh, nkv, hd, 1 if write_kv else 0,
+        status.data_ptr(), _stream()), "rope_kv_write")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    _cuda(gate_up, out)
+    n, two_i = gate_up.shape
+    I = two_i // 2
+    if out.dtype != gate_up.dtype or tuple(out.shape) != (n, I) or not out.is_contiguous():
+        raise KernelError("silu_mul: bad output")
+    check(lib().fb_silu_mul(gate_up.data_ptr(), _rows(gate_up), out.data_ptr(), dtype_code(out), n, I, _stream()),
+          "silu_mul")
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T, float32 accumulation on the CUDA cores."""
+    _cuda(a, w, out)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
+    check(lib().fb_gemm_simt(a.data_ptr(), dtype_code(a), _rows(a), w.data_ptr(), dtype_code(w), _rows(w),
+                             out.data_ptr(), dtype_code(out), _rows(out), M, N, K, _stream()), "gemm_simt")
+
+
+def paged_attention_simt(q, out, k_pool, v_pool, block_table, positions, row_seq, nh: int, nkv: int, hd: int,
+                         window: int, scale: float, status) -> None:
+    _cuda(q, out, k_pool, v_pool, block_table, positions, row_seq, status)
+    n = q.shape[0]
+    n_pages, pool_kv, page_size, pool_hd = k_pool.shape
+    if pool_kv != nkv or pool_hd != hd or q.shape[1] != nh * hd or out.shape[1] != nh * hd or out.shape[0] != n:
+        raise KernelError("attention: shapes do not match the head counts")
+    if not (q.dtype == out.dtype == k_pool.dtype == v_pool.dtype):
+        raise KernelError("attention: q, out and the cache must share one dtype")
+    if not k_pool.is_contiguous() or not v_pool.is_contiguous():
+        raise KernelError("attention: cache pools must be contiguous")
+    check(lib().fb_paged_attention_simt(
+        q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), dtype_code(q), k_pool.data_ptr(), v_pool.data_ptr(),
+        page_size, n_pages, block_table.data_ptr(), block_table.stride(0), positions.data_ptr(),
+        row_seq.data_ptr(), n, nh, nkv, hd, int(window), float(scale), status.data_ptr(), _stream()),
+        "paged_attention_simt")
+
+
+def apply_penalties(logits, rows, tokens, counts, repetition, presence, frequency) -> None:
+    _cuda(logits, rows, tokens, counts, repetition, presence, frequency)
+    check(lib().fb_apply_penalties(logits.data_ptr(), _rows(logits), logits.shape[1], rows.data_ptr(),
+                                   tokens.data_ptr(), counts.data_ptr(), repetition.data_ptr(),
+                                   presence.data_ptr(), frequency.data_ptr(), rows.numel(), _stream()),
+          "apply_penalties")
+
+
+def apply_logit_bias(logits, rows, tokens, bias) -> None:
+    _cuda(logits, rows, tokens, bias)
+    check(lib().fb_apply_logit_bias(logits.data_ptr(), _rows(logits), logits.shape[1], rows.data_ptr(),
+                                    tokens.data_ptr(), bias.data_ptr(), rows.numel(), _stream()),
+          "apply_logit_bias")
+
+
+def sample(logits, out, temperature=None, uniform=None, top_k=None, top_p=None, min_p=None, n=None) -> None:
+    """out[r] = argmax(logits[r]) where temperature[r] <= 0 (or no temperature given), else a draw."""
+    _cuda(logits, out, temperature, uniform, top_k, top_p, min_p)
+    if logits.dtype != torch.float32:
+        raise KernelError("sample: logits must be float32")
+    _i32(out, "sampled tokens")
+    _i32(top_k, "top_k")
+    n = logits.shape[0] if n is None else n
+    check(lib().fb_sample(logits.data_ptr(), _rows(logits), n, logits.shape[1], _ptr(temperature), _ptr(uniform),
+                          _ptr(top_k), _ptr(top_p), _ptr(min_p), out.data_ptr(), _stream()), "sample")
+
+
+# ---------------------------------------------------------------------------
+# choices between kernels of one family
+# ---------------------------------------------------------------------------
+
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ctx=None) -> None:
+    """out = a @ w^T with the kernel that fits the dtypes and the shape."""
+    gemm_simt(a, w, out)
+
+
+def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int, scale: float) -> None:
+    """Attention of every row of the step over its request's cached keys."""
+    b = ctx.batch
+    paged_attention_simt(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.positions, b.row_seq,
+                         nh, nkv, hd, window, scale, ctx.runtime.status)

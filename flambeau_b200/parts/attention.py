@@ -1,0 +1,89 @@
+"""Grouped-query attention over the paged cache."""
+from __future__ import annotations
+
+import math
+
+from ..kernels import ops
+from .base import KVRequirement, Mixer, TensorSpec
+from .linear import Linear, concat_rows
+from .spec import PartSpec, build_part, register_part
+
+
+class PagedAttention(Mixer):
+    """q, k, v = h Wq^T, h Wk^T, h Wv^T (no bias); position encoding on q and k
+    after the projection and before the cache write; every query at position p
+    attends to the cached keys [max(0, p-W+1), p] of its request (all of [0, p]
+    when window == 0) with scores scale * q.k; o = a Wo^T.
+    crates/forward/src/core/composites/standard_attn.rs:197-286 (projections),
+    :355-399 (rotary), :418-420 (scale), :1261-1302 (output projection).
+
+    Sizes are parameters: `num_heads * head_dim` need not equal `width`."""
+
+    def __init__(self, runtime=None, prefix="", *, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 window: int = 0, position: PartSpec | None = None, scale: float | None = None,
+                 init_std: float = 0.02):
+        super().__init__(runtime, prefix)
+        self.width, self.nh, self.nkv, self.hd = int(width), int(num_heads), int(num_kv_heads), int(head_dim)
+        if self.nh % self.nkv:
+            raise ValueError(f"{self.nh} query heads are not a multiple of {self.nkv} key/value heads")
+        self.window = int(window or 0)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.hd)
+        self.position = build_part(position, runtime) if position is not None else None
+        self.init_std = init_std
+        self.qw, self.kvw = self.nh * self.hd, self.nkv * self.hd
+        self.qkv = self.o = None
+
+    def children(self):
+        return [self.position] if self.position is not None else []
+
+    def cache_requirement(self):
+        return KVRequirement(self.nkv, self.hd, self.window)
+
+    def own_tensor_specs(self):
+        p, init = self.prefix, ("normal", self.init_std)
+        return {
+            p + "q_proj.weight": TensorSpec((self.qw, self.width), init=init),
+            p + "k_proj.weight": TensorSpec((self.kvw, self.width), init=init),
+            p + "v_proj.weight": TensorSpec((self.kvw, self.width), init=init),
+            p + "o_proj.weight": TensorSpec((self.width, self.qw), init=init),
+        }
+
+    def own_bind(self, tensors):
+        p = self.prefix
+        self.qkv = Linear(concat_rows([tensors[p + "q_proj.weight"], tensors[p + "k_proj.weight"],
+                                       tensors[p + "v_proj.weight"]]))
+        self.o = Linear(tensors[p + "o_proj.weight"])
+
+    def own_weights(self):
+        return [self.qkv.weight, self.o.weight]
+
+    def forward(self, ctx, h, out, call):
+        n = ctx.n_tokens
+        rt = self.runtime
+        cache = ctx.cache(call)
+        with ctx.ws.scope():
+            qkv = ctx.ws.alloc((n, self.qw + 2 * self.kvw), rt.dtype)
+            self.qkv(ctx, h, qkv)
+            q = qkv[:, :self.qw]
+            k = qkv[:, self.qw:self.qw + self.kvw]
+            v = qkv[:, self.qw + self.kvw:]
+            b = ctx.batch
+            pos = self.position
+            if pos is None or getattr(pos, "fused_with_cache_write", False):
+                cos, sin = pos.prepare(ctx) if pos is not None else (None, None)
+                half = pos.half if pos is not None else 0
+                ops.rope_kv_write(q, k, v, cos, sin, half, b.positions, b.row_seq, cache.block_table,
+                                  cache.k_pool, cache.v_pool, cache.page_size, self.nh, self.nkv, self.hd,
+                                  cache.writable, rt.status)
+            else:
+                pos.rotate(ctx, q, k if cache.writable else None)
+                if cache.writable:
+                    ops.rope_kv_write(q, k, v, None, None, 0, b.positions, b.row_seq, cache.block_table,
+                                      cache.k_pool, cache.v_pool, cache.page_size, self.nh, self.nkv, self.hd,
+                                      True, rt.status)
+            a = ctx.ws.alloc((n, self.qw), rt.dtype)
+            ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale)
+            self.o(ctx, a, out)
+
+
+register_part("mixer", "attention", PagedAttention)

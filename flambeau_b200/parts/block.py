@@ -1,0 +1,43 @@
+"""How a layer arranges its norms, mixer and feed-forward around the stream."""
+from __future__ import annotations
+
+from .base import Part
+from .spec import PartSpec, build_part, register_part
+
+
+class ResidualStream:
+    """The float32 stream x [n, width] plus the last part's output that has
+    not been added yet (`pending`): the next norm adds it while it normalises,
+    so the add costs no pass of its own."""
+
+    def __init__(self, x, pending=None):
+        self.x, self.pending = x, pending
+
+
+class PreNormBlock(Part):
+    """x = x + mixer(norm1(x)); x = x + feed_forward(norm2(x))
+    (crates/models/qwen35-v2/src/model.rs:25-42)."""
+    category = "block"
+
+    def __init__(self, runtime=None, prefix="", *, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
+                 feed_forward_norm: PartSpec):
+        super().__init__(runtime, prefix)
+        self.mixer = build_part(mixer, runtime)
+        self.feed_forward = build_part(feed_forward, runtime)
+        self.mixer_norm = build_part(mixer_norm, runtime)
+        self.feed_forward_norm = build_part(feed_forward_norm, runtime)
+
+    def children(self):
+        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+
+    def forward(self, ctx, stream: ResidualStream, call) -> None:
+        h, delta = ctx.normed, ctx.delta
+        self.mixer_norm.add_norm(ctx, stream.x, stream.pending, h)
+        self.mixer.forward(ctx, h, delta, call)
+        stream.pending = delta
+        self.feed_forward_norm.add_norm(ctx, stream.x, stream.pending, h)
+        self.feed_forward.forward(ctx, h, delta)
+        stream.pending = delta
+
+
+register_part("block", "pre_norm", PreNormBlock)

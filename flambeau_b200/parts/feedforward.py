@@ -1,0 +1,49 @@
+"""SiLU-gated dense feed-forward."""
+from __future__ import annotations
+
+from ..kernels import ops
+from .base import FeedForward, TensorSpec
+from .linear import Linear, concat_rows
+from .spec import register_part
+
+
+class GatedMLP(FeedForward):
+    """d = (silu(h Wg^T) * (h Wu^T)) Wd^T, no bias, no routing
+    (crates/forward/src/core/composites/dense_ffn.rs:116-186).  Gate and up
+    weights are stacked at load so one product yields both."""
+
+    def __init__(self, runtime=None, prefix="", *, width: int, inner: int, activation: str = "silu",
+                 init_std: float = 0.02):
+        super().__init__(runtime, prefix)
+        if activation != "silu":
+            raise ValueError(f"gated feed-forward: activation '{activation}' is not implemented (silu)")
+        self.width, self.inner, self.init_std = int(width), int(inner), init_std
+        self.gate_up = self.down = None
+
+    def own_tensor_specs(self):
+        p, init = self.prefix, ("normal", self.init_std)
+        return {
+            p + "gate_proj.weight": TensorSpec((self.inner, self.width), init=init),
+            p + "up_proj.weight": TensorSpec((self.inner, self.width), init=init),
+            p + "down_proj.weight": TensorSpec((self.width, self.inner), init=init),
+        }
+
+    def own_bind(self, tensors):
+        p = self.prefix
+        self.gate_up = Linear(concat_rows([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]]))
+        self.down = Linear(tensors[p + "down_proj.weight"])
+
+    def own_weights(self):
+        return [self.gate_up.weight, self.down.weight]
+
+    def forward(self, ctx, h, out):
+        n = ctx.n_tokens
+        with ctx.ws.scope():
+            gu = ctx.ws.alloc((n, 2 * self.inner), self.runtime.dtype)
+            self.gate_up(ctx, h, gu)
+            a = ctx.ws.alloc((n, self.inner), self.runtime.dtype)
+            ops.silu_mul(gu, a)
+            self.down(ctx, a, out)
+
+
+register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -1,0 +1,27 @@
+"""A bias-free linear map y = a W^T with W stored [outputs, inputs]
+(crates/forward/src/loader/shard.rs:81-83)."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor):
+        if weight.dim() != 2:
+            raise ValueError("a linear weight is 2-d [outputs, inputs]")
+        self.weight = weight
+        self.out_features, self.in_features = weight.shape
+
+    def __call__(self, ctx, a: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        ops.linear(a, self.weight, out, ctx)
+        return out
+
+
+def concat_rows(tensors) -> torch.Tensor:
+    """Stack weights that share their input so one product serves them all."""
+    dts = {t.dtype for t in tensors}
+    if len(dts) != 1:
+        raise ValueError(f"fused weights must share a dtype, got {dts}")
+    return torch.cat(list(tensors), dim=0).contiguous()

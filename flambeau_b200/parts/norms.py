@@ -1,0 +1,33 @@
+"""RMSNorm with the residual add fused in front of it."""
+from __future__ import annotations
+
+from ..kernels import ops
+from .base import Norm, TensorSpec
+from .spec import register_part
+
+
+class RMSNorm(Norm):
+    """y = v * w / sqrt(mean(v^2) + eps) with v = x + delta; plain weight, no 1+w
+    (crates/kernels-hip/src/kernels/rmsnorm_f16.cu:41-85).  The sum, the mean
+    and the product are float32; the stream x stays float32."""
+
+    def __init__(self, runtime=None, prefix="", *, width: int, eps: float, init=("one_plus_normal", 0.02)):
+        super().__init__(runtime, prefix)
+        self.width, self.eps, self.init = int(width), float(eps), tuple(init)
+        self.weight = None
+
+    def own_tensor_specs(self):
+        return {self.prefix + "weight": TensorSpec((self.width,), init=self.init)}
+
+    def own_bind(self, tensors):
+        self.weight = tensors[self.prefix + "weight"]
+
+    def own_weights(self):
+        return [self.weight]
+
+    def add_norm(self, ctx, x, delta, out, rows=None, n_partials: int = 1):
+        ops.add_rms_norm(x, delta, self.weight, self.eps, out, rows=rows, n_partials=n_partials,
+                         n_rows=ctx.n_tokens)
+
+
+register_part("norm", "rmsnorm", RMSNorm)

@@ -1,0 +1,82 @@
+"""Replay on the GPU against the plain implementation: every request whole, with the last 32 tokens one by
+one, in portions of changing size, and mixed with other requests on a pool so small that pages are used
+again; in 32-bit and in bfloat16, on both tiny configurations."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_mistral as pm
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 23, 40, 70, 33, 18, 64], "B": [1, 7, 31, 64, 47, 12, 80]}
+
+
+@pytest.fixture(scope="module", params=[(c, d) for c in ("A", "B") for d in ("float32", "bfloat16")],
+                ids=lambda p: f"{p[0]}-{p[1]}")
+def case(request, tmp_path_factory):
+    name, dtype = request.param
+    cfg = tiny.CONFIGS[name]
+    folder = tiny.make_folder(tmp_path_factory.mktemp(f"model{name}{dtype}"), cfg, seed=11 if name == "A" else 23,
+                              dtype=dtype)
+    requests = tiny.random_requests(cfg, LENGTHS[name], seed=5)
+    pcfg, W = pm.read_model_folder(folder)
+    want = {rid: pm.forward_logits(pcfg, W, toks) for rid, toks in requests.items()}
+    return dict(name=name, dtype=dtype, cfg=cfg, folder=folder, requests=requests, want=want)
+
+
+def run(case, schedule, tmp_path, slack_tokens=0):
+    from flambeau_b200.engine.step import Engine, EngineOptions
+    from flambeau_b200.engine.trace import replay
+    tokens = schedule.max_live_tokens(case["requests"]) + slack_tokens
+    engine = Engine.from_folder(case["folder"], EngineOptions(
+        dtype=case["dtype"], cache_tokens=tokens, max_requests=4, max_step_tokens=max(tokens, 128),
+        max_seq_len=max(tokens, 128)))
+    replay(engine, schedule.lines(), tmp_path)
+    engine.cache.check_invariants()
+    assert not engine.cache.requests, "requests left live after the trace"
+    assert all(g.pool.n_free == g.pool.n_pages for g in engine.cache.groups), "pages lost"
+    got = tiny.read_rows(tmp_path, schedule, case["cfg"]["vocab_size"])
+    return tiny.compare_rows(got, case["want"], tiny.TOL[case["dtype"]], f"{case['name']} {case['dtype']}")
+
+
+def test_whole(case, tmp_path):
+    run(case, tiny.schedule_whole(case["requests"]), tmp_path)
+
+
+def test_last_32_one_by_one(case, tmp_path):
+    run(case, tiny.schedule_tail(case["requests"], 32), tmp_path)
+
+
+def test_portions_of_changing_size(case, tmp_path):
+    run(case, tiny.schedule_portions(case["requests"]), tmp_path)
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_mixed_with_page_reuse(case, tmp_path, seed):
+    sched = tiny.schedule_mixed(case["requests"], seed=seed)
+    total_pages = sum(-(-len(t) // 16) for t in case["requests"].values())
+    pool_pages = sched.max_live_tokens(case["requests"]) // 16
+    assert pool_pages < total_pages, "the pool must be smaller than what all requests need, so pages are reused"
+    run(case, sched, tmp_path)
+
+
+def test_trace_run_program(case, tmp_path):
+    """The program itself, in a process of its own."""
+    sched = tiny.schedule_mixed(case["requests"], seed=9)
+    exe = Path(__file__).resolve().parent.parent / "bin" / "trace_run"
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, str(exe), "--model", str(case["folder"]), "--dtype", case["dtype"], "--out", str(out),
+         "--max-tokens", str(sched.max_live_tokens(case["requests"]))],
+        input="\n".join(sched.lines()) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    done = [ln for ln in proc.stdout.splitlines() if ln.startswith("done ")]
+    assert done == [f"done {i}" for i in range(len(sched.steps))]
+    got = tiny.read_rows(out, sched, case["cfg"]["vocab_size"])
+    tiny.compare_rows(got, case["want"], tiny.TOL[case["dtype"]], "trace_run")
