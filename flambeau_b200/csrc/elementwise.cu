@@ -130,9 +130,10 @@ FB_API int fb_rope_table(const int* positions, const double* inv_freq, float* co
 // crates/kernels-hip/src/kernels/rope_neox_partial_f16.cu:39-52 (rotation),
 // kv_append_f16_paged_prefill.cu (row placement).
 // ---------------------------------------------------------------------------
-template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ q, long q_stride, const T* __restrict__ k, long k_stride,
-                                     const T* __restrict__ v, long v_stride, const float* __restrict__ cos_t,
+template <typename TI, typename T>
+__global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stride, T* __restrict__ q_out,
+                                     long q_out_stride, const TI* __restrict__ k, long k_stride,
+                                     const TI* __restrict__ v, long v_stride, const float* __restrict__ cos_t,
                                      const float* __restrict__ sin_t, int half,
                                      const int* __restrict__ positions, const int* __restrict__ row_seq,
                                      const int* __restrict__ block_table, int table_stride,
@@ -143,15 +144,21 @@ __global__ void rope_kv_write_kernel(T* __restrict__ q, long q_stride, const T* 
     const float* ct = cos_t ? cos_t + (size_t)t * half : nullptr;
     const float* st = sin_t ? sin_t + (size_t)t * half : nullptr;
 
-    // q heads, in place
-    T* qt = q + (size_t)t * q_stride;
-    for (int idx = threadIdx.x; idx < nh * half; idx += blockDim.x) {
-        const int h = idx / half, i = idx - h * half;
-        T* p = qt + (size_t)h * hd;
-        const float a = fb_to_float(p[i]), b = fb_to_float(p[i + half]);
-        const float c = ct[i], s = st[i];
-        p[i] = fb_from_float<T>(a * c - b * s);
-        p[i + half] = fb_from_float<T>(a * s + b * c);
+    // q heads (q_out may be q_in itself: a thread reads both halves of its pair before it writes them)
+    const TI* qi = q_in + (size_t)t * q_in_stride;
+    T* qo = q_out + (size_t)t * q_out_stride;
+    for (int idx = threadIdx.x; idx < nh * per_head; idx += blockDim.x) {
+        const int h = idx / per_head, j = idx - h * per_head;
+        const TI* src = qi + (size_t)h * hd;
+        T* dst = qo + (size_t)h * hd;
+        if (j < half) {
+            const float a = fb_to_float(src[j]), b = fb_to_float(src[j + half]);
+            const float c = ct[j], s = st[j];
+            dst[j] = fb_from_float<T>(a * c - b * s);
+            dst[j + half] = fb_from_float<T>(a * s + b * c);
+        } else {
+            dst[j + half] = fb_from_float<T>(fb_to_float(src[j + half]));
+        }
     }
     if (!write_kv) return;
 
@@ -162,11 +169,11 @@ __global__ void rope_kv_write_kernel(T* __restrict__ q, long q_stride, const T* 
         return;
     }
     const int slot = pos % page_size;
-    const T* kt = k + (size_t)t * k_stride;
-    const T* vt = v + (size_t)t * v_stride;
+    const TI* kt = k + (size_t)t * k_stride;
+    const TI* vt = v + (size_t)t * v_stride;
     for (int idx = threadIdx.x; idx < nkv * per_head; idx += blockDim.x) {
         const int h = idx / per_head, j = idx - h * per_head;
-        const T* src = kt + (size_t)h * hd;
+        const TI* src = kt + (size_t)h * hd;
         T* dst = k_pool + (((size_t)page * nkv + h) * page_size + slot) * hd;
         if (j < half) {
             const float a = fb_to_float(src[j]), b = fb_to_float(src[j + half]);
@@ -174,17 +181,21 @@ __global__ void rope_kv_write_kernel(T* __restrict__ q, long q_stride, const T* 
             dst[j] = fb_from_float<T>(a * c - b * s);
             dst[j + half] = fb_from_float<T>(a * s + b * c);
         } else {
-            dst[j + half] = src[j + half];
+            dst[j + half] = fb_from_float<T>(fb_to_float(src[j + half]));
         }
     }
     for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
         const int h = idx / hd, d = idx - h * hd;
-        v_pool[(((size_t)page * nkv + h) * page_size + slot) * hd + d] = vt[(size_t)h * hd + d];
+        v_pool[(((size_t)page * nkv + h) * page_size + slot) * hd + d] =
+            fb_from_float<T>(fb_to_float(vt[(size_t)h * hd + d]));
     }
 }
 
-FB_API int fb_rope_kv_write(void* q, long long q_stride, const void* k, long long k_stride, const void* v,
-                            long long v_stride, int dtype, const float* cos_t, const float* sin_t, int half,
+// q_in/k/v have dtype `in_dtype` (the projection's output, float32 in both engine modes so that q and k are
+// rounded once, after the rotation); q_out and the cache have dtype `out_dtype`.
+FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, void* q_out, long long q_out_stride,
+                            const void* k, long long k_stride, const void* v, long long v_stride, int in_dtype,
+                            int out_dtype, const float* cos_t, const float* sin_t, int half,
                             const int* positions, const int* row_seq, const int* block_table,
                             int table_stride, void* k_pool, void* v_pool, int page_size, int n_pages, int n,
                             int nh, int nkv, int hd, int write_kv, int* status, cudaStream_t stream) {
@@ -193,11 +204,12 @@ FB_API int fb_rope_kv_write(void* q, long long q_stride, const void* k, long lon
     FB_REQUIRE(half == 0 || (cos_t && sin_t), "rope_kv_write: rotary tables missing");
     FB_REQUIRE(!write_kv || (page_size > 0 && n_pages > 0 && k_pool && v_pool && block_table),
                "rope_kv_write: cache arguments missing");
+    FB_REQUIRE(q_in != q_out || in_dtype == out_dtype, "rope_kv_write: in-place rotation needs one dtype");
     if (n == 0) return 0;
-    FB_DISPATCH_DTYPE(dtype, T,
-        rope_kv_write_kernel<T><<<n, 128, 0, stream>>>((T*)q, q_stride, (const T*)k, k_stride, (const T*)v,
-            v_stride, cos_t, sin_t, half, positions, row_seq, block_table, table_stride, (T*)k_pool,
-            (T*)v_pool, page_size, n_pages, nh, nkv, hd, write_kv, status));
+    FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
+        (rope_kv_write_kernel<TI, T><<<n, 128, 0, stream>>>((const TI*)q_in, q_in_stride, (T*)q_out, q_out_stride,
+            (const TI*)k, k_stride, (const TI*)v, v_stride, cos_t, sin_t, half, positions, row_seq, block_table,
+            table_stride, (T*)k_pool, (T*)v_pool, page_size, n_pages, nh, nkv, hd, write_kv, status))));
     return fb_check_launch("rope_kv_write");
 }
 

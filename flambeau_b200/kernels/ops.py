@@ -93,25 +93,29 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tenso
                               _stream()), "rope_table")
 
 
-def rope_kv_write(q, k, v, cos, sin, half: int, positions, row_seq, block_table, k_pool, v_pool,
+def rope_kv_write(q_in, q_out, k, v, cos, sin, half: int, positions, row_seq, block_table, k_pool, v_pool,
                   page_size: int, nh: int, nkv: int, hd: int, write_kv: bool, status) -> None:
-    """Rotate q in place; rotate k into the cache and copy v into the cache (when write_kv)."""
-    _cuda(q, k, v, cos, sin, positions, row_seq, block_table, k_pool, v_pool, status)
-    n = q.shape[0]
-    if q.shape[1] != nh * hd or (write_kv and (k.shape[1] != nkv * hd or v.shape[1] != nkv * hd)):
-        raise KernelError("rope_kv_write: q/k/v widths do not match the head counts")
-    if write_kv and (k.dtype != q.dtype or v.dtype != q.dtype or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype):
-        raise KernelError("rope_kv_write: q, k, v and the cache must share one dtype")
+    """q_out = rotate(q_in) (q_out may be q_in); with write_kv, rotate k into the cache and copy v into it.
+    q_in, k, v share one dtype (the projection's output); q_out and the cache share one dtype."""
+    _cuda(q_in, q_out, k, v, cos, sin, positions, row_seq, block_table, k_pool, v_pool, status)
+    n = q_in.shape[0]
+    if q_in.shape[1] != nh * hd or q_out.shape[1] != nh * hd or q_out.shape[0] != n:
+        raise KernelError("rope_kv_write: q widths do not match the head counts")
+    if write_kv:
+        if k.shape[1] != nkv * hd or v.shape[1] != nkv * hd:
+            raise KernelError("rope_kv_write: k/v widths do not match the head counts")
+        if k.dtype != q_in.dtype or v.dtype != q_in.dtype or k_pool.dtype != q_out.dtype or v_pool.dtype != q_out.dtype:
+            raise KernelError("rope_kv_write: inputs must share one dtype; q_out and the cache another")
     n_pages = k_pool.shape[0] if write_kv else 0
     if write_kv and (tuple(k_pool.shape) != (n_pages, nkv, page_size, hd) or not k_pool.is_contiguous()
                      or tuple(v_pool.shape) != tuple(k_pool.shape) or not v_pool.is_contiguous()):
         raise KernelError("rope_kv_write: cache pools must be contiguous [pages, kv heads, page size, head size]")
     check(lib().fb_rope_kv_write(
-        q.data_ptr(), _rows(q), _ptr(k), _rows(k) if k is not None else 0, _ptr(v),
-        _rows(v) if v is not None else 0, dtype_code(q), _ptr(cos), _ptr(sin), half, _ptr(positions),
-        _ptr(row_seq), _ptr(block_table), block_table.stride(0) if block_table is not None else 0,
-        _ptr(k_pool), _ptr(v_pool), page_size, n_pages, n, nh, nkv, hd, 1 if write_kv else 0,
-        status.data_ptr(), _stream()), "rope_kv_write")
+        q_in.data_ptr(), _rows(q_in), q_out.data_ptr(), _rows(q_out), _ptr(k), _rows(k) if k is not None else 0,
+        _ptr(v), _rows(v) if v is not None else 0, dtype_code(q_in), dtype_code(q_out), _ptr(cos), _ptr(sin), half,
+        _ptr(positions), _ptr(row_seq), _ptr(block_table),
+        block_table.stride(0) if block_table is not None else 0, _ptr(k_pool), _ptr(v_pool), page_size, n_pages,
+        n, nh, nkv if write_kv else 0, hd, 1 if write_kv else 0, status.data_ptr(), _stream()), "rope_kv_write")
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:

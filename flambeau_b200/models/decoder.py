@@ -67,7 +67,7 @@ class DecoderModel:
         n = b.n_tokens
         x = ctx.step_alloc((n, self.hidden_size), torch.float32)
         ctx.normed = ctx.step_alloc((n, self.hidden_size), rt.dtype)
-        ctx.delta = ctx.step_alloc((n, self.hidden_size), rt.dtype)
+        ctx.delta = ctx.step_alloc((n, self.hidden_size), torch.float32)   # mixer / feed-forward outputs stay float32 until added
         self.embedding.forward(ctx, b.token_ids[:n], x)
         stream = ResidualStream(x)
         for ci, call in enumerate(self.order):

@@ -3,6 +3,8 @@ from __future__ import annotations
 
 import math
 
+import torch
+
 from ..kernels import ops
 from .base import KVRequirement, Mixer, TensorSpec
 from .linear import Linear, concat_rows
@@ -62,25 +64,26 @@ class PagedAttention(Mixer):
         rt = self.runtime
         cache = ctx.cache(call)
         with ctx.ws.scope():
-            qkv = ctx.ws.alloc((n, self.qw + 2 * self.kvw), rt.dtype)
+            # the projection stays float32 until after the rotation, so q and k are rounded once
+            qkv = ctx.ws.alloc((n, self.qw + 2 * self.kvw), torch.float32)
             self.qkv(ctx, h, qkv)
-            q = qkv[:, :self.qw]
+            q_in = qkv[:, :self.qw]
             k = qkv[:, self.qw:self.qw + self.kvw]
             v = qkv[:, self.qw + self.kvw:]
+            q = ctx.ws.alloc((n, self.qw), rt.dtype)
             b = ctx.batch
             pos = self.position
             if pos is None or getattr(pos, "fused_with_cache_write", False):
                 cos, sin = pos.prepare(ctx) if pos is not None else (None, None)
                 half = pos.half if pos is not None else 0
-                ops.rope_kv_write(q, k, v, cos, sin, half, b.positions, b.row_seq, cache.block_table,
+                ops.rope_kv_write(q_in, q, k, v, cos, sin, half, b.positions, b.row_seq, cache.block_table,
                                   cache.k_pool, cache.v_pool, cache.page_size, self.nh, self.nkv, self.hd,
                                   cache.writable, rt.status)
             else:
-                pos.rotate(ctx, q, k if cache.writable else None)
-                if cache.writable:
-                    ops.rope_kv_write(q, k, v, None, None, 0, b.positions, b.row_seq, cache.block_table,
-                                      cache.k_pool, cache.v_pool, cache.page_size, self.nh, self.nkv, self.hd,
-                                      True, rt.status)
+                pos.rotate(ctx, q_in, k if cache.writable else None)
+                ops.rope_kv_write(q_in, q, k, v, None, None, 0, b.positions, b.row_seq, cache.block_table,
+                                  cache.k_pool, cache.v_pool, cache.page_size, self.nh, self.nkv, self.hd,
+                                  cache.writable, rt.status)
             a = ctx.ws.alloc((n, self.qw), rt.dtype)
             ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale)
             self.o(ctx, a, out)

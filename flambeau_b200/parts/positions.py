@@ -53,7 +53,7 @@ class RotaryHalf(PositionEncoding):
             if t is None:
                 continue
             heads = t.shape[1] // self.head_dim
-            ops.rope_kv_write(t, None, None, cos, sin, self.half, None, None, None, None, None, 0,
+            ops.rope_kv_write(t, t, None, None, cos, sin, self.half, None, None, None, None, None, 0,
                               heads, 0, self.head_dim, False, self.runtime.status)
 
 

@@ -179,5 +179,6 @@ def compare_rows(got: dict, want: dict, tol: float, what: str) -> float:
             assert np.isfinite(err), f"{what}: non-finite logits for request {rid} position {p}"
             if err > worst:
                 worst, worst_at = err, (rid, p)
+    print(f"[compare] {what}: worst error {worst:.3e} of the logit scale at {worst_at} (tolerance {tol:.0e})")
     assert worst <= tol, f"{what}: error {worst:.3e} of the logit scale at {worst_at} exceeds {tol:.0e}"
     return worst
