@@ -1,0 +1,1 @@
+from .params import SamplingParams, uniform_for  # noqa: F401

@@ -1,0 +1,148 @@
+"""The page pool and the cache manager on the CPU: no page lost, held twice or freed twice, under random
+orders of requests; windowed release; fixed-size state slots."""
+import random
+
+import pytest
+import torch
+
+from flambeau_b200.cache.manager import CacheManager, CallPlan
+from flambeau_b200.cache.pages import OutOfPages, PageError, PagePool
+from flambeau_b200.parts.base import KVRequirement, StateRequirement
+
+
+def test_pool_is_fifo_and_all_or_nothing():
+    pool = PagePool(4)
+    a = pool.take(3)
+    assert a == [0, 1, 2] and pool.n_free == 1
+    with pytest.raises(OutOfPages):
+        pool.take(2)
+    assert pool.n_free == 1                      # nothing was taken
+    pool.give_back([1])
+    assert pool.take(2) == [3, 1]                # reused in the order of return
+    with pytest.raises(PageError):
+        pool.give_back([0, 0])                   # freed twice
+    with pytest.raises(PageError):
+        pool.give_back([7])
+
+
+def manager(window=0, tokens=256, layers=2, max_requests=4, state=False, max_seq_len=None):
+    plans = [CallPlan(kv=KVRequirement(2, 16, window), state=StateRequirement((3,)) if state else None)
+             for _ in range(layers)]
+    return CacheManager(plans, max_tokens=tokens, page_size=16, max_requests=max_requests, device="cpu",
+                        dtype=torch.float32, max_seq_len=max_seq_len or tokens)
+
+
+def test_groups_follow_requirements():
+    plans = [CallPlan(kv=KVRequirement(2, 16, 0)), CallPlan(kv=KVRequirement(2, 16, 8)),
+             CallPlan(kv=KVRequirement(2, 16, 0)), CallPlan(kv=None, state=StateRequirement((5,))),
+             CallPlan(kv=KVRequirement(2, 16, 0), cache_from=0)]
+    cm = CacheManager(plans, max_tokens=64, page_size=16, max_requests=2, device="cpu", dtype=torch.float32)
+    assert cm.n_groups == 2
+    assert cm.group_of_call[0] == cm.group_of_call[2] == cm.group_of_call[4] != cm.group_of_call[1]
+    assert 3 not in cm.group_of_call and cm.state[3].shape == (2, 5)
+    v = cm.view(4, [None, None])
+    assert not v.writable and v.k_pool is cm.groups[cm.group_of_call[0]].k[0]
+    assert cm.view(2, [None, None]).writable
+    with pytest.raises(ValueError):
+        CacheManager([CallPlan(kv=None), CallPlan(kv=KVRequirement(1, 8), cache_from=0)], max_tokens=64,
+                     page_size=16, max_requests=1, device="cpu", dtype=torch.float32)
+
+
+def test_reserve_is_all_or_nothing_and_release_returns_everything():
+    cm = manager(tokens=64)                      # 4 pages
+    cm.admit("a")
+    cm.reserve("a", 40)                          # 3 pages
+    cm.commit("a", 40)
+    cm.admit("b")
+    assert not cm.can_reserve([("b", 17)])
+    with pytest.raises(OutOfPages):
+        cm.reserve("b", 17)
+    assert cm.free_pages() == [1]
+    cm.reserve("b", 16)
+    cm.commit("b", 16)
+    cm.check_invariants()
+    cm.release("a")
+    cm.release("b")
+    assert cm.free_pages() == [4] and not cm.requests
+    with pytest.raises(KeyError):
+        cm.release("a")
+
+
+def test_window_gives_pages_back_as_they_die():
+    cm = manager(window=16, tokens=64, max_seq_len=128)
+    cm.admit("a")
+    held = []
+    for _ in range(10):                          # 100 tokens through a 4-page pool
+        cm.reserve("a", 10)
+        cm.commit("a", 10)
+        cm.check_invariants()
+        held.append(4 - cm.free_pages()[0])
+    assert max(held) <= 3
+    rec = cm.requests["a"]
+    first_live = rec.length - 16 + 1
+    for j, p in enumerate(rec.pages[0]):
+        assert (p < 0) == ((j + 1) * 16 <= first_live), "exactly the pages wholly below the window are given back"
+    cm.release("a")
+    assert cm.free_pages() == [4]
+
+
+def test_commit_beyond_reservation_is_an_error():
+    cm = manager()
+    cm.admit("a")
+    cm.reserve("a", 5)
+    with pytest.raises(PageError):
+        cm.commit("a", 6)
+
+
+def test_state_slots_are_zeroed_on_admission_and_reused():
+    cm = manager(state=True, max_requests=2)
+    a = cm.admit("a")
+    cm.state[0][a.slot] += 5.0
+    b = cm.admit("b")
+    assert a.slot != b.slot
+    with pytest.raises(PageError):
+        cm.admit("c")
+    cm.release("a")
+    c = cm.admit("c")
+    assert c.slot == a.slot and float(cm.state[0][c.slot].abs().sum()) == 0.0
+    assert cm.state_bytes_per_request() == 2 * 3 * 4
+
+
+@pytest.mark.parametrize("window", [0, 16, 40])
+@pytest.mark.parametrize("seed", range(5))
+def test_random_orders_never_lose_or_double_a_page(window, seed):
+    rng = random.Random(seed)
+    cm = manager(window=window, tokens=192, max_requests=4)
+    live, next_id = {}, 0
+    for _ in range(400):
+        r = rng.random()
+        if r < 0.25 and cm.has_slot():
+            cm.admit(next_id)
+            live[next_id] = 0
+            next_id += 1
+        elif r < 0.85 and live:
+            rid = rng.choice(list(live))
+            k = rng.choice([1, 1, 1, 2, 5, 17, 33])
+            if cm.can_reserve([(rid, k)]) and cm.length(rid) + k <= 192:
+                before = cm.free_pages()
+                cm.reserve(rid, k)
+                cm.commit(rid, k)
+                live[rid] += k
+                assert cm.length(rid) == live[rid]
+                if window == 0:
+                    assert before[0] - cm.free_pages()[0] == -(-live[rid] // 16) - -(-(live[rid] - k) // 16)
+            else:
+                free = cm.free_pages()
+                if not cm.can_reserve([(rid, k)]):
+                    with pytest.raises(OutOfPages):
+                        cm.reserve(rid, k)
+                    assert cm.free_pages() == free
+        elif live:
+            rid = rng.choice(list(live))
+            cm.release(rid)
+            del live[rid]
+        cm.check_invariants()
+        held = sum(sum(1 for p in rec.pages[0] if p >= 0) for rec in cm.requests.values())
+        assert held + cm.free_pages()[0] == cm.groups[0].pool.n_pages
+    cm.release_all()
+    assert cm.free_pages() == [12]

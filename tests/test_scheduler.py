@@ -1,0 +1,153 @@
+"""The scheduler's decisions on the CPU, with an executor that keeps the cache books but computes nothing."""
+import pytest
+import torch
+
+from flambeau_b200.cache.manager import CacheManager, CallPlan
+from flambeau_b200.engine.scheduler import Scheduler
+from flambeau_b200.parts.base import KVRequirement
+from flambeau_b200.sampling.params import SamplingParams
+
+
+class BookkeepingExecutor:
+    """Does what Engine.step does to the cache (admit, reserve all-or-nothing, commit) and returns token ids
+    that encode who was sampled when, so that tests can follow the order of events."""
+
+    def __init__(self, tokens=256, window=0, max_requests=4, page_size=16):
+        self.cache = CacheManager([CallPlan(kv=KVRequirement(1, 8, window))], max_tokens=tokens, page_size=page_size,
+                                  max_requests=max_requests, device="cpu", dtype=torch.float32, max_seq_len=4096)
+        self.log = []
+
+    def run(self, entries, sampled):
+        for e in entries:
+            if e.request_id not in self.cache.requests:
+                self.cache.admit(e.request_id)
+        assert self.cache.can_reserve([(e.request_id, len(e.tokens)) for e in entries]), "planned step does not fit"
+        for e in entries:
+            self.cache.reserve(e.request_id, len(e.tokens))
+        for e in entries:
+            self.cache.commit(e.request_id, len(e.tokens))
+        self.cache.check_invariants()
+        self.log.append([(e.request_id, len(e.tokens), list(e.want)) for e in entries])
+        want_ids = [e.request_id for e in entries if e.want]
+        assert want_ids == [r.request_id for r in sampled]
+        return [100 + len(r.generated) for r in sampled]
+
+    def finish(self, request_id):
+        self.cache.release(request_id)
+
+
+def test_prompt_is_cut_under_the_budget_and_decodes_come_first():
+    ex = BookkeepingExecutor()
+    s = Scheduler(ex, token_budget=16, prefill_chunk=10, max_running=4)
+    s.add("a", list(range(25)), SamplingParams(max_tokens=3))
+    s.step()
+    assert ex.log[-1] == [("a", 10, [])]                        # chunk limit
+    s.add("b", list(range(30)), SamplingParams(max_tokens=2))
+    s.step()
+    assert ex.log[-1] == [("a", 10, []), ("b", 6, [])]          # budget 16 = 10 + 6, arrival order
+    s.step()
+    assert ex.log[-1] == [("a", 5, [4]), ("b", 10, [])]         # a's prompt ends: its last row is wanted
+    s.step()
+    assert ex.log[-1] == [("a", 1, [0]), ("b", 10, [])]         # a decodes beside b's portion
+    s.step()
+    assert ex.log[-1] == [("a", 1, [0]), ("b", 4, [3])]
+    done = s.run()
+    assert [r.request_id for r in done] == ["a", "b"]
+    assert done[0].generated == [100, 101, 102] and done[0].finish_reason == "length"
+    assert done[1].generated == [100, 101]
+    assert not ex.cache.requests and ex.cache.free_pages() == [16]
+
+
+def test_positions_first_generated_token_is_fed_at_prompt_length():
+    ex = BookkeepingExecutor()
+    s = Scheduler(ex, token_budget=64, prefill_chunk=64)
+    r = s.add("a", [1, 2, 3, 4, 5], SamplingParams(max_tokens=4))
+    s.step()
+    assert ex.cache.length("a") == 5 and r.generated == [100]
+    s.step()
+    assert ex.cache.length("a") == 6                            # the token sampled from position 4 sits at 5
+
+
+def test_stop_token_and_max_tokens_zero():
+    ex = BookkeepingExecutor()
+    s = Scheduler(ex)
+    a = s.add("a", [1, 2], SamplingParams(max_tokens=10, stop_token_ids=(101,)))
+    b = s.add("b", [1, 2], SamplingParams(max_tokens=10, stop_token_ids=(101,), ignore_eos=True))
+    c = s.add("c", [1], SamplingParams(max_tokens=0))
+    s.run()
+    assert a.generated == [100, 101] and a.finish_reason == "stop"
+    assert len(b.generated) == 10 and b.finish_reason == "length"
+    assert c.generated == [] and c.finish_reason == "length"
+    with pytest.raises(ValueError):
+        s.add("d", [])
+
+
+def test_admission_waits_for_a_slot_and_for_pages():
+    ex = BookkeepingExecutor(tokens=64, max_requests=2)        # 4 pages, 2 slots
+    s = Scheduler(ex, token_budget=64, prefill_chunk=64, max_running=4)
+    for name in "abc":
+        s.add(name, list(range(20)), SamplingParams(max_tokens=2))
+    s.step()
+    assert [e[0] for e in ex.log[-1]] == ["a", "b"]             # two slots; c waits
+    assert [r.request_id for r in s.waiting] == ["c"]
+    s.run()
+    assert sorted(r.request_id for r in s.finished) == ["a", "b", "c"]
+    assert all(len(r.generated) == 2 for r in s.finished)
+    assert ex.cache.free_pages() == [4]
+
+
+def test_out_of_pages_preempts_the_youngest_and_resumes_it():
+    ex = BookkeepingExecutor(tokens=64, max_requests=4)         # 4 pages of 16
+    s = Scheduler(ex, token_budget=64, prefill_chunk=64, max_running=4)
+    a = s.add("a", list(range(30)), SamplingParams(max_tokens=20))   # will need 4 pages alone (50 tokens)
+    b = s.add("b", list(range(14)), SamplingParams(max_tokens=40))
+    preempted = []
+    while not s.idle:
+        before = len(s.finished)
+        plan_preempted = len([r for r in (a, b) if r.preemptions])
+        s.step()
+        ex.cache.check_invariants()
+    assert b.preemptions >= 1 and a.preemptions == 0, "the younger request gives way"
+    assert a.finish_reason == "length" and len(a.generated) == 20
+    assert b.finish_reason == "length" and len(b.generated) == 40
+    # a preempted request is fed again from position 0 with prompt + generated so far
+    refeeds = [e for step in ex.log for e in step if e[0] == "b" and e[1] > 1]
+    assert len(refeeds) >= 2 and refeeds[-1][1] > 14
+    assert ex.cache.free_pages() == [4] and not ex.cache.requests
+
+
+def test_a_request_that_cannot_fit_alone_ends_with_capacity():
+    ex = BookkeepingExecutor(tokens=32)                         # 2 pages
+    s = Scheduler(ex, token_budget=64, prefill_chunk=64)
+    a = s.add("a", list(range(20)), SamplingParams(max_tokens=30))
+    b = s.add("b", list(range(5)), SamplingParams(max_tokens=3))
+    s.run()
+    assert a.finish_reason == "capacity" and 0 < len(a.generated) < 30
+    assert b.finish_reason == "length" and len(b.generated) == 3
+    assert ex.cache.free_pages() == [2]
+
+
+def test_window_lets_a_long_request_run_in_a_small_pool():
+    ex = BookkeepingExecutor(tokens=64, window=16)             # 4 pages, but only ~2 stay live per request
+    s = Scheduler(ex, token_budget=8, prefill_chunk=8)
+    a = s.add("a", list(range(40)), SamplingParams(max_tokens=100))
+    s.run()
+    assert a.finish_reason == "length" and len(a.generated) == 100 and a.preemptions == 0
+    assert ex.cache.free_pages() == [4]
+
+
+def test_random_load_never_breaks_the_books():
+    import random
+    rng = random.Random(3)
+    ex = BookkeepingExecutor(tokens=160, max_requests=4)
+    s = Scheduler(ex, token_budget=24, prefill_chunk=16, max_running=4)
+    reqs = [s.add(i, list(range(rng.randint(1, 60))), SamplingParams(max_tokens=rng.randint(1, 40)))
+            for i in range(12)]
+    steps = 0
+    while not s.idle:
+        s.step()
+        steps += 1
+        assert steps < 5000
+        assert sum(n for _, n, _ in ex.log[-1]) <= 24 if ex.log else True
+    assert all(r.finish_reason == "length" and len(r.generated) == r.params.max_tokens for r in reqs)
+    assert ex.cache.free_pages() == [10] and not ex.cache.requests
