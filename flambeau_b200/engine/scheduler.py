@@ -46,6 +46,15 @@ class Request:
     def tokens(self) -> list:
         return self.prompt + self.generated
 
+    def span(self, a: int, b: int) -> list:
+        """tokens[a:b] of prompt + generated without building the whole list."""
+        p = len(self.prompt)
+        if b <= p:
+            return self.prompt[a:b]
+        if a >= p:
+            return self.generated[a - p:b - p]
+        return self.prompt[a:] + self.generated[:b - p]
+
     @property
     def remaining(self) -> int:
         return len(self.prompt) + len(self.generated) - self.fed
@@ -145,7 +154,7 @@ class Scheduler:
         for r in decoders[:budget]:
             for gi, k in enumerate(cache.pages_needed(r.request_id, 1)):
                 free[gi] -= k
-            plan.entries.append(Entry(r.request_id, [r.tokens[-1]], [0]))
+            plan.entries.append(Entry(r.request_id, [r.generated[-1]], [0]))
             plan.sampled.append(r)
             budget -= 1
 
@@ -162,7 +171,7 @@ class Scheduler:
 
         def take(r: Request, k: int) -> None:
             nonlocal budget
-            toks = r.tokens[r.fed:r.fed + k]
+            toks = r.span(r.fed, r.fed + k)
             last = r.fed + k == len(r.prompt) + len(r.generated)
             if r.request_id in cache.requests:
                 need = cache.pages_needed(r.request_id, k)

@@ -70,7 +70,11 @@ def library_path() -> str:
     return str(ensure_built())
 
 
+LAUNCHES = [0]          # launcher calls that reached the device queue (each is at least one kernel launch)
+
+
 def check(code: int, what: str) -> None:
+    LAUNCHES[0] += 1
     if code != 0:
         msg = lib().fb_last_error().decode(errors="replace")
         raise KernelError(f"{what}: {msg or 'error code %d' % code}")
