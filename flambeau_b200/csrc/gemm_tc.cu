@@ -1,0 +1,424 @@
+// out[M,N] = X[M,K] * W[N,K]^T in bfloat16 on the 5th-generation tensor cores.
+//
+// The weight is the 128-row operand of tcgen05.mma and the tokens are its N
+// dimension ("swap-AB"): one CTA owns 128 output features x BN tokens, with
+// BN in {16, 32, 64, 128, 256} chosen from the number of rows, so a decode step of a few
+// tokens streams the weights at full width instead of padding the token side
+// to 128.  Both operands are K-major in shared memory, staged by TMA with the
+// 128-byte swizzle, 64 elements of K per stage; the float32 accumulator
+// lives in tensor memory and is read back with tcgen05.ld by four epilogue
+// warps whose lanes are the output features, so that a warp stores 32
+// consecutive features of one token.
+//
+// Warps: 0 = TMA producer, 1 = tensor-memory owner and MMA issuer, 2..5 = epilogue.
+// Split-K: grid.z CTAs share one output tile; each writes its float32 partial
+// to scratch, and the CTA that arrives last (an atomic counter per tile, no
+// waiting) adds the partials in split order and writes the result, so the sum
+// does not depend on the order of arrival.
+//
+// Every wait on an mbarrier is bounded in time: when it runs out the kernel
+// sets FB_STATUS_WAIT_TIMEOUT in the status word, leaves its loops, frees its
+// tensor memory and returns.
+//
+// The reference multiplies with scalar-FMA tiles of 64 outputs x 8 rows
+// (crates/kernels-hip/src/kernels/mmq_f16_tile.cu:32-107); the weight layout
+// (rows = outputs) is the same.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128;          // output features per CTA (UMMA M)
+constexpr int BK = 64;           // K elements per stage: 128 bytes, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// Waits until the phase with the given parity has completed, or gives up after WAIT_LIMIT_NS.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            atomicOr(status, FB_STATUS_WAIT_TIMEOUT);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t pred = 0;
+    asm volatile(
+        "{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\t"
+        "elect.sync rx|px, %1;\n\t"
+        "selp.u32 %0, 1, 0, px;\n\t}"
+        : "=r"(pred) : "r"(0xFFFFFFFFu));
+    return pred;
+}
+
+// Shared-memory matrix descriptor: K-major tile of rows x 64 bf16, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address, bits [0,14)
+    d |= (uint64_t)1 << 16;                                // leading byte offset (unused with this swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset, bits [32,46)
+    d |= (uint64_t)1 << 46;                                // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                                // layout: 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN> struct TileCfg {
+    static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
+    static constexpr int STAGES = BN == 16 ? 6 : BN == 32 ? 5 : BN == 64 ? 4 : BN == 128 ? 3 : 4;
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int BN, typename TO>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               TO* __restrict__ out, long ldo, float* __restrict__ partials, int* __restrict__ tile_counters,
+               int M, int N, int K, int splits, int* status) {
+    using Cfg = TileCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+    // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * Cfg::STAGES + 1);
+    int* last_flag = (int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BM;              // first output feature of the tile
+    const int m0 = blockIdx.y * BN;              // first token of the tile
+    const int split = blockIdx.z;
+    const int kb_total = (K + BK - 1) / BK;
+    const int kb_begin = (int)((long)split * kb_total / splits);
+    const int kb_end = (int)((long)(split + 1) * kb_total / splits);
+    const int n_kb = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[Cfg::STAGES + s]), 1);
+        }
+        mbar_init(smem_u32(&bars[2 * Cfg::STAGES]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (elect_one()) {
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % Cfg::STAGES;
+                const uint32_t round = (uint32_t)(i / Cfg::STAGES);
+                if (!mbar_wait(smem_u32(&bars[Cfg::STAGES + s]), (round & 1u) ^ 1u, status)) break;
+                const uint32_t full = smem_u32(&bars[s]);
+                mbar_expect_tx(full, (uint32_t)Cfg::STAGE_BYTES);
+                uint8_t* stage = smem + (size_t)s * Cfg::STAGE_BYTES;
+                const int k0 = (kb_begin + i) * BK;
+                tma_load_2d(smem_u32(stage), &map_w, full, k0, n0);
+                tma_load_2d(smem_u32(stage + BM * BK * 2), &map_x, full, k0, m0);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (elect_one()) {
+            constexpr uint32_t idesc = umma_idesc(BN);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % Cfg::STAGES;
+                const uint32_t round = (uint32_t)(i / Cfg::STAGES);
+                ok = mbar_wait(smem_u32(&bars[s]), round & 1u, status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint8_t* stage = smem + (size_t)s * Cfg::STAGE_BYTES;
+                const uint64_t da = umma_desc(smem_u32(stage));
+                const uint64_t db = umma_desc(smem_u32(stage + BM * BK * 2));
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // 16 elements of K = 32 bytes further along the swizzled row
+                    umma_bf16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
+                              (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&bars[Cfg::STAGES + s]));      // frees the stage when the MMAs have read it
+            }
+            umma_commit(smem_u32(&bars[2 * Cfg::STAGES]));          // accumulator complete
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: warps 2..5, lane quarter = warp % 4 ----------------
+        const int quarter = warp & 3;
+        const int row_local = quarter * 32 + lane;                  // output feature within the tile
+        const int n = n0 + row_local;
+        const bool got = mbar_wait(smem_u32(&bars[2 * Cfg::STAGES]), 0u, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        if (splits == 1) {
+            if (got && n_kb > 0) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    if (m0 + c >= M) break;
+                    float v[16];
+                    tmem_ld16(taddr + (uint32_t)c, v);
+                    if (n < N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (m0 + c + j < M) out[(size_t)(m0 + c + j) * ldo + n] = fb_from_float<TO>(v[j]);
+                    }
+                }
+            }
+        } else {
+            const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+            float* mine = partials + ((size_t)tile_id * splits + split) * (size_t)(BN * BM);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (m0 + c >= M) break;
+                float v[16];
+                if (got && n_kb > 0) {
+                    tmem_ld16(taddr + (uint32_t)c, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) mine[(size_t)(c + j) * BM + row_local] = v[j];
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (warp == 2 && lane == 0) {
+                const int arrived = atomicAdd(&tile_counters[tile_id], 1);
+                *last_flag = (arrived == splits - 1) ? 1 : 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*last_flag) {
+                __threadfence();
+                const float* base = partials + (size_t)tile_id * splits * (size_t)(BN * BM);
+#pragma unroll 1
+                for (int c = 0; c < BN && m0 + c < M; ++c) {
+                    float acc = 0.0f;
+                    for (int s = 0; s < splits; ++s)
+                        acc += __ldcg(base + ((size_t)s * BN + c) * BM + row_local);
+                    if (n < N) out[(size_t)(m0 + c) * ldo + n] = fb_from_float<TO>(acc);
+                }
+                if (warp == 2 && lane == 0) tile_counters[tile_id] = 0;      // ready for the next launch
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side: tensor maps
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long rows, cols, ld; int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows;
+        h = h * 1000003u ^ (size_t)k.cols;
+        h = h * 1000003u ^ (size_t)k.ld;
+        return h * 1000003u ^ (size_t)k.box_rows;
+    }
+};
+
+// A [rows, cols] bf16 matrix with row stride ld (elements), fetched in boxes of box_rows x 64.
+int make_map(CUtensorMap* out, const void* ptr, long rows, long cols, long ld, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    const MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fb_fail(-3, "gemm_tc: the driver does not provide cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fb_fail(-3, "gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+int pick_splits(int tiles, int kb_total, int slots, int max_splits) {
+    // time ~ waves * (k-blocks per CTA + fixed cost of a CTA, in k-blocks)
+    int best = 1;
+    double best_cost = 1e30;
+    for (int s = 1; s <= max_splits && s <= kb_total; ++s) {
+        const int waves = (tiles * s + slots - 1) / slots;
+        const double cost = waves * ((double)((kb_total + s - 1) / s) + 3.0) + (s > 1 ? 1.0 : 0.0);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
+    }
+    return best;
+}
+
+template <int BN, typename TO>
+int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo, float* partials,
+              long partial_floats, int* counters, int n_counters, int M, int N, int K, int force_splits,
+              int* status, cudaStream_t stream) {
+    using Cfg = TileCfg<BN>;
+    const int tiles_n = (N + BM - 1) / BM, tiles_m = (M + BN - 1) / BN;
+    const int tiles = tiles_n * tiles_m;
+    const int kb_total = (K + BK - 1) / BK;
+    const int per_sm = Cfg::SMEM_BYTES <= 113 * 1024 ? 2 : 1;
+    int splits = force_splits > 0 ? force_splits : pick_splits(tiles, kb_total, 148 * per_sm, 16);
+    if (splits > kb_total) splits = kb_total;
+    while (splits > 1 && ((long)tiles * splits * BN * BM > partial_floats || tiles > n_counters)) --splits;
+    if (tiles_m > 65535 || splits > 65535) return fb_fail(-1, "gemm_tc: too many tiles (M=%d)", M);
+    auto kern = gemm_tc_kernel<BN, TO>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return fb_fail(-2, "gemm_tc: cannot reserve %d bytes of shared memory: %s",
+                                             Cfg::SMEM_BYTES, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(tiles_n, tiles_m, splits);
+    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, mx, (TO*)out, ldo, partials, counters, M, N, K,
+                                                          splits, status);
+    return fb_check_launch("gemm_tc");
+}
+
+}  // namespace
+
+// X [M,K] and W [N,K] are bfloat16 with row strides lda, ldw (elements); out is float32 or bfloat16.
+// `partials` (float32 scratch) and `counters` (int32, zero before the first call; the kernel leaves them zero)
+// serve split-K.  Shapes the TMA path cannot take are refused with an error, never computed wrongly.
+FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw, void* out, int o_dtype,
+                      long long ldo, int M, int N, int K, float* partials, long long partial_floats,
+                      int* counters, int n_counters, int force_splits, int* status, cudaStream_t stream) {
+    FB_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
+    FB_REQUIRE(lda >= K && ldw >= K && ldo >= N, "gemm_tc: a row stride is shorter than its row");
+    FB_REQUIRE(lda % 8 == 0 && ldw % 8 == 0, "gemm_tc: row strides must be multiples of 8 elements (16 bytes)");
+    FB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
+    FB_REQUIRE(partials && counters && n_counters > 0, "gemm_tc: split-K scratch missing");
+    if (M == 0) return 0;
+    const int BN = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, W, N, K, (long)ldw, BM);
+    if (rc) return rc;
+    rc = make_map(&mx, X, M, K, (long)lda, BN);
+    if (rc) return rc;
+#define FB_TC_CASE(BN_)                                                                                         \
+    case BN_:                                                                                                   \
+        if (o_dtype == FB_F32)                                                                                  \
+            return launch_tc<BN_, float>(mw, mx, out, (long)ldo, partials, (long)partial_floats, counters,      \
+                                         n_counters, M, N, K, force_splits, status, stream);                    \
+        else if (o_dtype == FB_BF16)                                                                            \
+            return launch_tc<BN_, __nv_bfloat16>(mw, mx, out, (long)ldo, partials, (long)partial_floats,        \
+                                                 counters, n_counters, M, N, K, force_splits, status, stream);  \
+        break;
+    switch (BN) {
+        FB_TC_CASE(16)
+        FB_TC_CASE(32)
+        FB_TC_CASE(64)
+        FB_TC_CASE(128)
+        FB_TC_CASE(256)
+    }
+#undef FB_TC_CASE
+    return fb_fail(-1, "gemm_tc: unknown output dtype code %d", o_dtype);
+}

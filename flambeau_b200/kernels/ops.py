@@ -188,9 +188,53 @@ def sample(logits, out, temperature=None, uniform=None, top_k=None, top_p=None, 
 # choices between kernels of one family
 # ---------------------------------------------------------------------------
 
+class _SplitScratch:
+    """Float32 partial tiles and per-tile arrival counters of the split-K tensor-core product, per device.
+    Kernels of one stream run in order, so one buffer serves every product of the step."""
+    PARTIAL_FLOATS = 16 << 20
+    COUNTERS = 8192
+    _by_device: dict = {}
+
+    @classmethod
+    def get(cls, device):
+        hit = cls._by_device.get(device)
+        if hit is None:
+            hit = (torch.empty(cls.PARTIAL_FLOATS, dtype=torch.float32, device=device),
+                   torch.zeros(cls.COUNTERS, dtype=torch.int32, device=device))
+            cls._by_device[device] = hit
+        return hit
+
+
+def tc_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether the tcgen05 product takes these operands: bfloat16, 16-byte aligned, row strides of 8 elements."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in _CODES
+            and a.dim() == 2 and w.dim() == 2 and a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor, splits: int = 0) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T on the tensor cores (bfloat16 operands, float32 accumulation).
+    splits = 0 lets the launcher choose the split of K."""
+    _cuda(a, w, out, status)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc: operands must be bfloat16")
+    partials, counters = _SplitScratch.get(a.device)
+    check(lib().fb_gemm_tc(a.data_ptr(), _rows(a), w.data_ptr(), _rows(w), out.data_ptr(), dtype_code(out),
+                           _rows(out), M, N, K, partials.data_ptr(), partials.numel(), counters.data_ptr(),
+                           counters.numel(), int(splits), status.data_ptr(), _stream()), "gemm_tc")
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ctx=None) -> None:
-    """out = a @ w^T with the kernel that fits the dtypes and the shape."""
-    gemm_simt(a, w, out)
+    """out = a @ w^T with the kernel that fits the dtypes and the shape: the tcgen05 kernel for bfloat16
+    operands it can fetch by TMA, the float32-FMA kernel for everything else (all of the 32-bit mode)."""
+    if ctx is not None and tc_supported(a, w, out):
+        gemm_tc(a, w, out, ctx.runtime.status)
+    else:
+        gemm_simt(a, w, out)
 
 
 def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int, scale: float) -> None:

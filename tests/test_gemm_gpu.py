@@ -1,0 +1,88 @@
+"""The matrix-product kernels alone against torch's float32/float64 product, at sizes other than the engine's."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(got, want):
+    return float((got.double() - want).abs().max() / want.abs().max())
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 130, 96), (17, 64, 160), (70, 321, 64), (300, 257, 100), (5, 1000, 24)])
+@pytest.mark.parametrize("dt", ["fff", "bbf", "bbb", "bff"])
+def test_simt_product(M, N, K, dt):
+    from flambeau_b200.kernels import ops
+    t = {"f": torch.float32, "b": torch.bfloat16}
+    g = torch.Generator(device="cuda").manual_seed(M * 1000 + N)
+    a = torch.randn(M, K, device="cuda", generator=g).to(t[dt[0]])
+    w = torch.randn(N, K, device="cuda", generator=g).to(t[dt[1]])
+    wide = torch.zeros(M, N + 3, device="cuda", dtype=t[dt[2]])
+    out = wide[:, :N]                                    # a strided output
+    ops.gemm_simt(a, w, out)
+    want = a.double() @ w.double().T
+    tol = 1e-5 if dt[2] == "f" else 8e-3
+    assert rel_err(out, want) < tol
+    assert float(wide[:, N:].abs().max()) == 0.0
+
+
+SHAPES_TC = [
+    (1, 128, 64), (8, 256, 512), (8, 6144, 4096), (16, 384, 1024), (17, 130, 72), (33, 4096, 4096),
+    (64, 1000, 264), (65, 257, 8), (128, 512, 2048), (200, 320, 96), (256, 1024, 1024), (300, 200, 136),
+    (515, 4096, 1024), (2048, 1024, 4096),
+]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES_TC)
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("splits", [0, 1, 3])
+def test_tensor_core_product(M, N, K, out_dtype, splits):
+    from flambeau_b200.kernels import ops
+    if splits > (K + 63) // 64:
+        pytest.skip("more splits than 64-wide blocks of K")
+    g = torch.Generator(device="cuda").manual_seed(M + 7 * N + 13 * K)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", generator=g).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=out_dtype)
+    assert ops.tc_supported(a, w, out)
+    ops.gemm_tc(a, w, out, status, splits=splits)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded wait inside the kernel ran out"
+    want = a.double() @ w.double().T
+    assert torch.isfinite(out).all()
+    tol = 2e-5 if out_dtype == torch.float32 else 8e-3
+    assert rel_err(out, want) < tol
+    # twice in a row: the split-K counters must have been left at zero
+    out2 = torch.empty_like(out)
+    ops.gemm_tc(a, w, out2, status, splits=splits)
+    assert torch.equal(out, out2), "the product is not reproducible"
+
+
+def test_tensor_core_product_on_strided_views():
+    from flambeau_b200.kernels import ops
+    g = torch.Generator(device="cuda").manual_seed(3)
+    big_a = torch.randn(40, 200, device="cuda", generator=g).to(torch.bfloat16)
+    big_w = torch.randn(300, 200, device="cuda", generator=g).to(torch.bfloat16)
+    a, w = big_a[:, 8:136], big_w[:, 64:192]               # 16-byte aligned column offsets, K = 128
+    wide = torch.zeros(40, 304, device="cuda", dtype=torch.float32)
+    out = wide[:, :300]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert ops.tc_supported(a, w, out)
+    ops.gemm_tc(a, w, out, status)
+    assert rel_err(out, a.double() @ w.double().T) < 2e-5
+    assert float(wide[:, 300:].abs().max()) == 0.0 and int(status.item()) == 0
+
+
+def test_shapes_the_tma_path_cannot_take_are_refused():
+    from flambeau_b200.kernels import ops
+    from flambeau_b200.kernels.library import KernelError
+    a = torch.zeros(4, 20, device="cuda", dtype=torch.bfloat16)    # row stride 20 elements = 40 bytes
+    w = torch.zeros(8, 20, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros(4, 8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert not ops.tc_supported(a, w, out)
+    with pytest.raises(KernelError):
+        ops.gemm_tc(a, w, out, status)
+    with pytest.raises(KernelError):
+        ops.gemm_tc(a.float(), w, out, status)
