@@ -1,0 +1,485 @@
+// Paged causal (sliding-window) attention for bfloat16 on the tensor cores
+// (mma.sync m16n8k16, float32 accumulation and softmax), one kernel in two
+// arrangements:
+//
+//   LONG  (prompt portions): a CTA owns one key/value head and a tile of up to 64
+//         query rows = (64 / G) tokens x the G query heads that share the head, so
+//         every K/V tile is read once for the whole group.  Its four warps split
+//         the rows; each walks all visible key tiles with an online softmax.
+//   SHORT (decoded tokens and portions of a few tokens, rows = tokens x G <= 16):
+//         a CTA owns one (sequence, key/value head, chunk of keys).  Its four warps
+//         share the 16 rows and split every 64-key tile; their partial (m, l, o)
+//         are merged in shared memory and written to scratch, and a second kernel
+//         merges the chunks ("split-K").
+//
+// Keys and values come through the block table in tiles of 64 keys with
+// cp.async, double-buffered; a key outside [t0, p] of every row of the CTA is
+// not read at all (its slot in shared memory is zero-filled), so pages that the
+// cache manager has taken back are never touched.  Softmax runs in base 2 with
+// scale*log2(e) folded into the scores.  Head sizes are padded with zeros to
+// HD_MAX in shared memory, so any head size that is a multiple of 8 runs.
+//
+// Formulas: crates/kernels-hip/src/kernels/attention_prefill_flash_tile_f16.cu:73-213
+// (tile + online softmax), attention_decode_f16_splitk.cu:215-256 (merge of chunks).
+#include "common.cuh"
+
+namespace {
+
+constexpr int KT = 64;             // keys per tile
+constexpr int ATT_THREADS = 128;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const uint32_t d = smem_addr(dst);
+    const int bytes = valid ? 16 : 0;              // 0 source bytes: the 16 destination bytes become zero
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct AttnArgs {
+    const __nv_bfloat16* q; long q_stride;
+    __nv_bfloat16* out; long out_stride;
+    const __nv_bfloat16* k_pool; const __nv_bfloat16* v_pool;
+    int page_size, n_pages;
+    const int* block_table; int table_stride;
+    const int* seq_q_start; const int* seq_q_len; const int* seq_pos_start;
+    int nh, nkv, hd, window;
+    float scale_log2e;
+    float* part_o; float* part_ml;     // SHORT: [seq][kv head][chunk][16 rows][HD_MAX] and [..][16][2]
+    int chunk_keys, max_chunks;        // SHORT: keys per chunk, chunk slots per (seq, kv head)
+    int short_rows;                    // sequences with q_len * G <= short_rows belong to the SHORT arrangement
+    int* status;
+};
+
+// The keys a group of consecutive query tokens [first, last] of a sequence can see, and where tiles start.
+struct KeyRange { int t_lo, t_hi, tile_lo; };
+__device__ __forceinline__ KeyRange key_range(int p_first, int p_last, int window) {
+    KeyRange r;
+    r.t_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+    r.t_hi = p_last;
+    r.tile_lo = (r.t_lo / KT) * KT;
+    return r;
+}
+
+template <int HD_MAX, bool SHORT>
+__global__ void __launch_bounds__(ATT_THREADS)
+attention_mma_kernel(const AttnArgs a) {
+    constexpr int LDS = HD_MAX + 8;                 // row stride in shared memory: 16 bytes of padding
+    constexpr int NKS = HD_MAX / 16;                // k-steps of Q K^T
+    constexpr int NDB = HD_MAX / 8;                 // n-blocks of P V
+    constexpr int ROWS = SHORT ? 16 : 64;           // query rows per CTA
+    constexpr int WARP_KEYS = SHORT ? 16 : KT;      // keys of a tile that one warp scores
+    constexpr int NSB = WARP_KEYS / 8;              // n-blocks of S per warp
+    constexpr bool Q_IN_REGS = HD_MAX <= 128;
+
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [ROWS][LDS]
+    __nv_bfloat16* Ks = Qs + ROWS * LDS;                                        // [2][KT][LDS]
+    __nv_bfloat16* Vs = Ks + 2 * KT * LDS;                                      // [2][KT][LDS]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq = blockIdx.z, kvh = blockIdx.y;
+    const int G = a.nh / a.nkv;
+    const int q_len = a.seq_q_len[seq], q_start = a.seq_q_start[seq], pos0 = a.seq_pos_start[seq];
+    const bool is_short = q_len * G <= a.short_rows;
+    int tok0, ntok;
+    if (SHORT) {
+        if (!is_short) return;
+        tok0 = 0;
+        ntok = q_len;
+    } else {
+        if (is_short) return;
+        const int TQ = 64 / G;
+        tok0 = blockIdx.x * TQ;
+        if (tok0 >= q_len) return;
+        ntok = min(TQ, q_len - tok0);
+    }
+    const int rows_valid = ntok * G;
+    const KeyRange kr = key_range(pos0 + tok0, pos0 + tok0 + ntok - 1, a.window);
+    int k_begin = kr.tile_lo, k_end = kr.t_hi + 1;
+    if (SHORT) {
+        k_begin = kr.tile_lo + blockIdx.x * a.chunk_keys;
+        if (k_begin > kr.t_hi) return;
+        k_end = min(k_end, k_begin + a.chunk_keys);
+    }
+    const int n_tiles = (k_end - k_begin + KT - 1) / KT;
+    const int hd = a.hd, hd_chunks = hd / 8;
+    const int* table = a.block_table + (size_t)seq * a.table_stride;
+
+    // ---- stage Q (zero-padded) and clear the padding of the K/V buffers ----
+    for (int idx = tid; idx < ROWS * (HD_MAX / 8); idx += ATT_THREADS) {
+        const int r = idx / (HD_MAX / 8), c = idx - r * (HD_MAX / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows_valid && c < hd_chunks) {
+            const int token = q_start + tok0 + r / G, head = kvh * G + r % G;
+            v = *reinterpret_cast<const uint4*>(a.q + (size_t)token * a.q_stride + (size_t)head * hd + c * 8);
+        }
+        *reinterpret_cast<uint4*>(Qs + r * LDS + c * 8) = v;
+    }
+    if (hd < HD_MAX) {
+        const int pad_chunks = HD_MAX / 8 - hd_chunks;
+        for (int idx = tid; idx < 2 * KT * pad_chunks; idx += ATT_THREADS) {
+            const int r = idx / pad_chunks, c = hd_chunks + idx - r * pad_chunks;
+            *reinterpret_cast<uint4*>(Ks + r * LDS + c * 8) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(Vs + r * LDS + c * 8) = make_uint4(0, 0, 0, 0);
+        }
+    }
+
+    auto load_tile = [&](int buf, int tile_start) {
+        __nv_bfloat16* kd = Ks + buf * KT * LDS;
+        __nv_bfloat16* vd = Vs + buf * KT * LDS;
+        for (int idx = tid; idx < KT * hd_chunks; idx += ATT_THREADS) {
+            const int r = idx / hd_chunks, c = idx - r * hd_chunks;
+            const int t = tile_start + r;
+            bool valid = t >= kr.t_lo && t < k_end;
+            size_t off = 0;
+            if (valid) {
+                const int page = table[t / a.page_size];
+                if (page < 0 || page >= a.n_pages) {
+                    atomicOr(a.status, FB_STATUS_BAD_PAGE);
+                    valid = false;
+                } else {
+                    off = (((size_t)page * a.nkv + kvh) * a.page_size + (t % a.page_size)) * hd + c * 8;
+                }
+            }
+            cp_async16(kd + r * LDS + c * 8, a.k_pool + off, valid);
+            cp_async16(vd + r * LDS + c * 8, a.v_pool + off, valid);
+        }
+        cp_async_commit();
+    };
+
+    load_tile(0, k_begin);
+    __syncthreads();                                  // Q is staged
+
+    const int row_base = SHORT ? 0 : warp * 16;       // first row of this warp within the CTA
+    const int key0 = SHORT ? warp * 16 : 0;           // first key of this warp within a tile
+    uint32_t qf[Q_IN_REGS ? NKS : 1][4];
+    if (Q_IN_REGS) {
+#pragma unroll
+        for (int ks = 0; ks < NKS; ++ks)
+            ldmatrix_x4(qf[ks], Qs + (row_base + (lane & 15)) * LDS + ks * 16 + 8 * (lane >> 4));
+    }
+    // per-thread rows: r0 = row_base + lane/4 and r0 + 8
+    int p_row[2], t0_row[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = row_base + (lane >> 2) + 8 * h;
+        if (r < rows_valid) {
+            p_row[h] = pos0 + tok0 + r / G;
+            t0_row[h] = (a.window > 0 && p_row[h] - a.window + 1 > 0) ? p_row[h] - a.window + 1 : 0;
+        } else {
+            p_row[h] = -1;                            // sees nothing
+            t0_row[h] = 0;
+        }
+    }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o[NDB][4];
+#pragma unroll
+    for (int d = 0; d < NDB; ++d)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[d][e] = 0.0f;
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int buf = it & 1;
+        const int tile_start = k_begin + it * KT;
+        if (it + 1 < n_tiles) {
+            load_tile(buf ^ 1, tile_start + KT);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const __nv_bfloat16* kt = Ks + buf * KT * LDS;
+        const __nv_bfloat16* vt = Vs + buf * KT * LDS;
+
+        // ---- S = Q K^T for this warp's rows and keys ----
+        float s[NSB][4];
+#pragma unroll
+        for (int nb = 0; nb < NSB; ++nb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nb][e] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < NKS; ks += 2) {
+            uint32_t qa[4], qb[4];
+            if (Q_IN_REGS) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { qa[e] = qf[ks][e]; qb[e] = qf[ks + 1][e]; }
+            } else {
+                ldmatrix_x4(qa, Qs + (row_base + (lane & 15)) * LDS + ks * 16 + 8 * (lane >> 4));
+                ldmatrix_x4(qb, Qs + (row_base + (lane & 15)) * LDS + (ks + 1) * 16 + 8 * (lane >> 4));
+            }
+#pragma unroll
+            for (int nb = 0; nb < NSB; ++nb) {
+                uint32_t b[4];     // (b0,b1): dims ks*16..+15, (b2,b3): dims (ks+1)*16..+15, keys nb*8..+7
+                ldmatrix_x4(b, kt + (key0 + nb * 8 + (lane & 7)) * LDS + ks * 16 + 8 * (lane >> 3));
+                mma_bf16(s[nb], qa, b[0], b[1]);
+                mma_bf16(s[nb], qb, b[2], b[3]);
+            }
+        }
+        // ---- scale, mask, online softmax ----
+        float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nb = 0; nb < NSB; ++nb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const int t = tile_start + key0 + nb * 8 + 2 * (lane & 3) + (e & 1);
+                const bool ok = t >= t0_row[h] && t <= p_row[h] && t < k_end;
+                const float v = ok ? s[nb][e] * a.scale_log2e : -INFINITY;
+                s[nb][e] = v;
+                tile_max[h] = fmaxf(tile_max[h], v);
+            }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float tm = tile_max[h];
+            tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
+            tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
+            const float m_new = fmaxf(m_run[h], tm);
+            const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;     // a row that has seen nothing yet
+            corr[h] = exp2f(m_run[h] - m_use);
+            m_run[h] = m_new;
+            float sum = 0.0f;
+#pragma unroll
+            for (int nb = 0; nb < NSB; ++nb) {
+                const float p0 = exp2f(s[nb][2 * h] - m_use), p1 = exp2f(s[nb][2 * h + 1] - m_use);
+                s[nb][2 * h] = p0;
+                s[nb][2 * h + 1] = p1;
+                sum += p0 + p1;
+            }
+            l_run[h] = l_run[h] * corr[h] + sum;
+        }
+#pragma unroll
+        for (int d = 0; d < NDB; ++d) {
+            o[d][0] *= corr[0]; o[d][1] *= corr[0];
+            o[d][2] *= corr[1]; o[d][3] *= corr[1];
+        }
+        // ---- O += P V ----
+#pragma unroll
+        for (int kk = 0; kk < WARP_KEYS / 16; ++kk) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int d = 0; d < NDB; d += 2) {
+                uint32_t b[4];     // (b0,b1): dims d*8..+7, (b2,b3): dims (d+1)*8..+7, keys kk*16..+15
+                ldmatrix_x4_trans(b, vt + (key0 + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + d * 8 +
+                                         8 * (lane >> 4));
+                mma_bf16(o[d], pa, b[0], b[1]);
+                mma_bf16(o[d + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncthreads();                              // the buffer may be refilled by the next iteration's load
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+
+    if (!SHORT) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = row_base + (lane >> 2) + 8 * h;
+            if (r >= rows_valid) continue;
+            const float inv = l_run[h] > 0.0f ? 1.0f / l_run[h] : 0.0f;
+            const int token = q_start + tok0 + r / G, head = kvh * G + r % G;
+            __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd;
+#pragma unroll
+            for (int d = 0; d < NDB; ++d) {
+                const int col = d * 8 + 2 * (lane & 3);
+                if (col < hd)
+                    *reinterpret_cast<__nv_bfloat162*>(dst + col) =
+                        __floats2bfloat162_rn(o[d][2 * h] * inv, o[d][2 * h + 1] * inv);
+            }
+        }
+        return;
+    }
+
+    // ---- SHORT: merge the four warps (they saw different keys of the same rows), write one partial ----
+    float* so = reinterpret_cast<float*>(Ks);         // [4 warps][16][HD_MAX] floats; K/V buffers are free now
+    float* sml = so + 4 * 16 * HD_MAX;                // [4 warps][16][2]
+    static_assert(4 * 16 * HD_MAX * 4 + 4 * 16 * 2 * 4 <= 4 * KT * (HD_MAX + 8) * 2, "merge buffer fits in K/V");
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = (lane >> 2) + 8 * h;
+#pragma unroll
+        for (int d = 0; d < NDB; ++d) {
+            const int col = d * 8 + 2 * (lane & 3);
+            so[(warp * 16 + r) * HD_MAX + col] = o[d][2 * h];
+            so[(warp * 16 + r) * HD_MAX + col + 1] = o[d][2 * h + 1];
+        }
+        if ((lane & 3) == 0) {
+            sml[(warp * 16 + r) * 2] = m_run[h];
+            sml[(warp * 16 + r) * 2 + 1] = l_run[h];
+        }
+    }
+    __syncthreads();
+    const size_t slot = ((size_t)seq * a.nkv + kvh) * a.max_chunks + blockIdx.x;
+    float* po = a.part_o + slot * 16 * HD_MAX;
+    float* pml = a.part_ml + slot * 16 * 2;
+    for (int idx = tid; idx < 16 * HD_MAX; idx += ATT_THREADS) {
+        const int r = idx / HD_MAX, c = idx - r * HD_MAX;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, sml[(w * 16 + r) * 2]);
+        float acc = 0.0f, l = 0.0f;
+        if (m > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float wgt = exp2f(sml[(w * 16 + r) * 2] - m);
+                acc += wgt * so[(w * 16 + r) * HD_MAX + c];
+                l += wgt * sml[(w * 16 + r) * 2 + 1];
+            }
+        }
+        po[idx] = acc;
+        if (c == 0) { pml[r * 2] = m; pml[r * 2 + 1] = l; }
+    }
+}
+
+// Merges the chunks of the SHORT arrangement: out = sum_c 2^(m_c - m) o_c / sum_c 2^(m_c - m) l_c.
+template <int HD_MAX>
+__global__ void __launch_bounds__(ATT_THREADS)
+attention_merge_kernel(const AttnArgs a) {
+    const int seq = blockIdx.y, kvh = blockIdx.x;
+    const int G = a.nh / a.nkv;
+    const int q_len = a.seq_q_len[seq], q_start = a.seq_q_start[seq], pos0 = a.seq_pos_start[seq];
+    if (q_len * G > a.short_rows) return;
+    const KeyRange kr = key_range(pos0, pos0 + q_len - 1, a.window);
+    const int n_chunks = (kr.t_hi - kr.tile_lo) / a.chunk_keys + 1;
+    const size_t slot0 = ((size_t)seq * a.nkv + kvh) * a.max_chunks;
+    const int rows = q_len * G, hd = a.hd;
+    for (int idx = threadIdx.x; idx < rows * hd; idx += ATT_THREADS) {
+        const int r = idx / hd, c = idx - r * hd;
+        float m = -INFINITY;
+        for (int ch = 0; ch < n_chunks; ++ch) m = fmaxf(m, a.part_ml[((slot0 + ch) * 16 + r) * 2]);
+        float acc = 0.0f, l = 0.0f;
+        if (m > -INFINITY) {
+            for (int ch = 0; ch < n_chunks; ++ch) {
+                const float wgt = exp2f(a.part_ml[((slot0 + ch) * 16 + r) * 2] - m);
+                acc += wgt * a.part_o[((slot0 + ch) * 16 + r) * HD_MAX + c];
+                l += wgt * a.part_ml[((slot0 + ch) * 16 + r) * 2 + 1];
+            }
+        }
+        const int token = q_start + r / G, head = kvh * G + r % G;
+        a.out[(size_t)token * a.out_stride + (size_t)head * hd + c] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    }
+}
+
+template <int HD_MAX>
+int launch_attention_mma(const AttnArgs& a, int n_seqs, int max_q_len, int max_kv_len, int any_short, int any_long,
+                         long scratch_floats, cudaStream_t stream) {
+    constexpr int LDS = HD_MAX + 8;
+    const int G = a.nh / a.nkv;
+    if (any_long) {
+        const int TQ = 64 / G;
+        const int q_tiles = (max_q_len + TQ - 1) / TQ;
+        const size_t smem = (size_t)(64 + 4 * KT) * LDS * 2;
+        auto kern = attention_mma_kernel<HD_MAX, false>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        dim3 grid(q_tiles, a.nkv, n_seqs);
+        kern<<<grid, ATT_THREADS, smem, stream>>>(a);
+        int rc = fb_check_launch("attention_mma (long)");
+        if (rc) return rc;
+    }
+    if (any_short) {
+        const size_t smem = (size_t)(16 + 4 * KT) * LDS * 2;
+        auto kern = attention_mma_kernel<HD_MAX, true>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        dim3 grid(a.max_chunks, a.nkv, n_seqs);
+        kern<<<grid, ATT_THREADS, smem, stream>>>(a);
+        int rc = fb_check_launch("attention_mma (short)");
+        if (rc) return rc;
+        attention_merge_kernel<HD_MAX><<<dim3(a.nkv, n_seqs), ATT_THREADS, 0, stream>>>(a);
+        rc = fb_check_launch("attention_merge");
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+}  // namespace
+
+// q, out: bfloat16 [rows, heads*hd]; pools bfloat16 [pages][kv heads][page size][hd].
+// seq_*: per sequence of the step (device int32).  max_q_len / max_kv_len / any_short / any_long come from the
+// host's copy of the step descriptor.  `scratch` holds the partials of the SHORT arrangement.
+FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, long long out_stride,
+                                  const void* k_pool, const void* v_pool, int page_size, int n_pages,
+                                  const int* block_table, int table_stride, const int* seq_q_start,
+                                  const int* seq_q_len, const int* seq_pos_start, int n_seqs, int max_q_len,
+                                  int max_kv_len, int any_short, int any_long, int nh, int nkv, int hd, int window,
+                                  float scale, float* scratch, long long scratch_floats, int* status,
+                                  cudaStream_t stream) {
+    FB_REQUIRE(n_seqs >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention_mma: bad sizes");
+    FB_REQUIRE(nh % nkv == 0, "attention_mma: %d query heads are not a multiple of %d key/value heads", nh, nkv);
+    FB_REQUIRE(hd % 8 == 0 && hd <= 256, "attention_mma: head size %d must be a multiple of 8 and at most 256", hd);
+    const int G = nh / nkv;
+    FB_REQUIRE(G <= 64, "attention_mma: %d query heads per key/value head exceed 64", G);
+    FB_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0, "attention_mma: q rows must be 16-byte aligned");
+    FB_REQUIRE(out_stride % 2 == 0 && ((uintptr_t)out & 3) == 0, "attention_mma: out rows must be 4-byte aligned");
+    FB_REQUIRE(page_size > 0 && n_pages > 0 && window >= 0, "attention_mma: bad cache geometry");
+    if (n_seqs == 0) return 0;
+    const int HD_MAX = hd <= 32 ? 32 : hd <= 64 ? 64 : hd <= 128 ? 128 : 256;
+    AttnArgs a;
+    a.q = (const __nv_bfloat16*)q; a.q_stride = (long)q_stride;
+    a.out = (__nv_bfloat16*)out; a.out_stride = (long)out_stride;
+    a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
+    a.page_size = page_size; a.n_pages = n_pages;
+    a.block_table = block_table; a.table_stride = table_stride;
+    a.seq_q_start = seq_q_start; a.seq_q_len = seq_q_len; a.seq_pos_start = seq_pos_start;
+    a.nh = nh; a.nkv = nkv; a.hd = hd; a.window = window;
+    a.scale_log2e = scale * 1.4426950408889634f;
+    a.status = status;
+    a.short_rows = G <= 16 ? 16 : 0;               // with more than 16 heads per group even one token is "long"
+    if (a.short_rows == 0) { any_long = any_long || any_short; any_short = 0; }
+    // chunking of the SHORT arrangement: enough CTAs to fill the GPU, chunks a multiple of the tile
+    int span = max_kv_len;
+    if (window > 0 && window + max_q_len < span) span = window + max_q_len;
+    span += KT;                                     // tile alignment of the first key
+    const int pairs = n_seqs * nkv;
+    int want_chunks = (4 * 148 + pairs - 1) / pairs;
+    if (want_chunks < 1) want_chunks = 1;
+    int chunk_keys = ((span + want_chunks - 1) / want_chunks + KT - 1) / KT * KT;
+    if (chunk_keys < 2 * KT) chunk_keys = 2 * KT;
+    int max_chunks = (span + chunk_keys - 1) / chunk_keys;
+    const long per_slot = 16L * HD_MAX + 32;
+    while ((long)pairs * max_chunks * per_slot > scratch_floats && chunk_keys < (1 << 24)) {
+        chunk_keys *= 2;
+        max_chunks = (span + chunk_keys - 1) / chunk_keys;
+    }
+    FB_REQUIRE(!any_short || (long)pairs * max_chunks * per_slot <= scratch_floats,
+               "attention_mma: the scratch buffer is too small for %d sequences", n_seqs);
+    a.chunk_keys = chunk_keys; a.max_chunks = max_chunks;
+    a.part_o = scratch;
+    a.part_ml = scratch + (size_t)pairs * max_chunks * 16 * HD_MAX;
+    switch (HD_MAX) {
+        case 32: return launch_attention_mma<32>(a, n_seqs, max_q_len, max_kv_len, any_short, any_long, scratch_floats, stream);
+        case 64: return launch_attention_mma<64>(a, n_seqs, max_q_len, max_kv_len, any_short, any_long, scratch_floats, stream);
+        case 128: return launch_attention_mma<128>(a, n_seqs, max_q_len, max_kv_len, any_short, any_long, scratch_floats, stream);
+        default: return launch_attention_mma<256>(a, n_seqs, max_q_len, max_kv_len, any_short, any_long, scratch_floats, stream);
+    }
+}

@@ -237,8 +237,57 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ctx=None) -> Non
         gemm_simt(a, w, out)
 
 
+class _AttentionScratch:
+    """Float32 partial outputs of the split-key attention arrangement, per device."""
+    FLOATS = 8 << 20
+    _by_device: dict = {}
+
+    @classmethod
+    def get(cls, device):
+        hit = cls._by_device.get(device)
+        if hit is None:
+            hit = cls._by_device[device] = torch.empty(cls.FLOATS, dtype=torch.float32, device=device)
+        return hit
+
+
+def mma_attention_supported(q: torch.Tensor, nh: int, nkv: int, hd: int) -> bool:
+    return (q.dtype == torch.bfloat16 and hd % 8 == 0 and hd <= 256 and nh % nkv == 0 and nh // nkv <= 64
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+
+
+def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, n_seqs: int,
+                        max_q_len: int, max_kv_len: int, any_short: bool, any_long: bool, nh: int, nkv: int,
+                        hd: int, window: int, scale: float, status) -> None:
+    """bfloat16 attention on the tensor cores over the paged cache; sequences are described per entry of the
+    step (first row, rows, first position).  any_short / any_long say whether the step holds sequences with
+    rows * (nh/nkv) <= 16 / > 16, which run in different arrangements of the kernel."""
+    _cuda(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, status)
+    n_pages, pool_kv, page_size, pool_hd = k_pool.shape
+    if pool_kv != nkv or pool_hd != hd or q.shape[1] != nh * hd or out.shape[1] != nh * hd:
+        raise KernelError("attention: shapes do not match the head counts")
+    if not (q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16):
+        raise KernelError("attention_mma: q, out and the cache must be bfloat16")
+    if not k_pool.is_contiguous() or not v_pool.is_contiguous():
+        raise KernelError("attention: cache pools must be contiguous")
+    scratch = _AttentionScratch.get(q.device)
+    check(lib().fb_paged_attention_mma(
+        q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), k_pool.data_ptr(), v_pool.data_ptr(), page_size, n_pages,
+        block_table.data_ptr(), block_table.stride(0), seq_q_start.data_ptr(), seq_q_len.data_ptr(),
+        seq_pos_start.data_ptr(), n_seqs, max_q_len, max_kv_len, 1 if any_short else 0, 1 if any_long else 0,
+        nh, nkv, hd, int(window), float(scale), scratch.data_ptr(), scratch.numel(), status.data_ptr(), _stream()),
+        "paged_attention_mma")
+
+
 def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int, scale: float) -> None:
-    """Attention of every row of the step over its request's cached keys."""
+    """Attention of every row of the step over its request's cached keys: the tensor-core kernel for bfloat16
+    and head sizes it takes, the float32 CUDA-core kernel otherwise (all of the 32-bit mode)."""
     b = ctx.batch
-    paged_attention_simt(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.positions, b.row_seq,
-                         nh, nkv, hd, window, scale, ctx.runtime.status)
+    if mma_attention_supported(q, nh, nkv, hd):
+        G = nh // nkv
+        short = [ql * G <= 16 for ql in b.seq_q_len]
+        paged_attention_mma(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.seq_q_start_d, b.seq_q_len_d,
+                            b.seq_pos_start_d, b.n_seqs, b.max_q_len, b.max_kv_len, any(short), not all(short),
+                            nh, nkv, hd, window, scale, ctx.runtime.status)
+    else:
+        paged_attention_simt(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.positions, b.row_seq,
+                             nh, nkv, hd, window, scale, ctx.runtime.status)

@@ -1,0 +1,164 @@
+"""The attention kernels alone against a plain softmax over gathered keys, at sizes other than the engine's:
+float32 CUDA-core kernel and bfloat16 tensor-core kernel; grouped heads 1:1, 2:1, 4:1, 8:1; head sizes from 16
+to 256; windows; pages in random order, pages of the prefix taken back; portions beside decoded tokens in one
+call; and single keys that stand out at the edge of a page, of a window and of a chunk."""
+import math
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+class Scene:
+    """A set of sequences with keys/values scattered over a paged pool, plus this step's queries."""
+
+    def __init__(self, seqs, nh, nkv, hd, window, dtype, page_size=16, seed=0, spread=1.0, extra_pages=7):
+        # seqs: list of (cached tokens before the step, new tokens in the step)
+        g = torch.Generator().manual_seed(seed)
+        rnd = random.Random(seed)
+        self.nh, self.nkv, self.hd, self.window, self.dtype, self.ps = nh, nkv, hd, window, dtype, page_size
+        self.seqs = seqs
+        total_pages = sum(-(-(a + b) // page_size) for a, b in seqs) + extra_pages
+        ids = list(range(total_pages))
+        rnd.shuffle(ids)
+        max_pages = max(-(-(a + b) // page_size) for a, b in seqs) + 2
+        self.k_pool = torch.full((total_pages, nkv, page_size, hd), float("nan"))   # unwritten slots are poison
+        self.v_pool = torch.full((total_pages, nkv, page_size, hd), float("nan"))
+        self.table = torch.full((len(seqs), max_pages), -1, dtype=torch.int32)
+        self.k, self.v, self.q = [], [], []
+        rows = []
+        for s, (cached, new) in enumerate(seqs):
+            T = cached + new
+            k = torch.randn(T, nkv, hd, generator=g) * spread
+            v = torch.randn(T, nkv, hd, generator=g)
+            q = torch.randn(new, nh, hd, generator=g) * spread
+            k, v, q = (t.to(dtype).float() for t in (k, v, q))          # values exactly representable in dtype
+            self.k.append(k); self.v.append(v); self.q.append(q)
+            first_live = max(0, cached - window + 1) if window else 0   # what the cache manager keeps
+            for j in range(-(-T // page_size)):
+                if (j + 1) * page_size <= first_live:
+                    continue                                            # page given back: table stays -1
+                pid = ids.pop()
+                self.table[s, j] = pid
+                lo, hi = j * page_size, min(T, (j + 1) * page_size)
+                self.k_pool[pid, :, :hi - lo] = k[lo:hi].transpose(0, 1)
+                self.v_pool[pid, :, :hi - lo] = v[lo:hi].transpose(0, 1)
+            rows += [(s, cached + i) for i in range(new)]
+        self.rows = rows
+        self.positions = torch.tensor([p for _, p in rows], dtype=torch.int32)
+        self.row_seq = torch.tensor([s for s, _ in rows], dtype=torch.int32)
+        self.q_flat = torch.cat(self.q).reshape(len(rows), nh * hd)
+        starts, acc = [], 0
+        for _, new in seqs:
+            starts.append(acc)
+            acc += new
+        self.seq_q_start = torch.tensor(starts, dtype=torch.int32)
+        self.seq_q_len = torch.tensor([n for _, n in seqs], dtype=torch.int32)
+        self.seq_pos_start = torch.tensor([c for c, _ in seqs], dtype=torch.int32)
+
+    def reference(self, scale):
+        out = torch.zeros(len(self.rows), self.nh, self.hd, dtype=torch.float64)
+        G = self.nh // self.nkv
+        i = 0
+        for s, (cached, new) in enumerate(self.seqs):
+            k, v, q = self.k[s].double(), self.v[s].double(), self.q[s].double()
+            for j in range(new):
+                p = cached + j
+                t0 = max(0, p - self.window + 1) if self.window else 0
+                for h in range(self.nh):
+                    sc = scale * (k[t0:p + 1, h // G] @ q[j, h])
+                    w = torch.softmax(sc, dim=0)
+                    out[i, h] = w @ v[t0:p + 1, h // G]
+                i += 1
+        return out.reshape(len(self.rows), self.nh * self.hd)
+
+    def run(self, kernel, scale):
+        from flambeau_b200.kernels import ops
+        dev = "cuda"
+        q = self.q_flat.to(dev, self.dtype)
+        out = torch.full_like(q, float("nan"))
+        kp, vp = self.k_pool.to(dev, self.dtype), self.v_pool.to(dev, self.dtype)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        table = self.table.to(dev)
+        if kernel == "simt":
+            ops.paged_attention_simt(q, out, kp, vp, table, self.positions.to(dev), self.row_seq.to(dev),
+                                     self.nh, self.nkv, self.hd, self.window, scale, status)
+        else:
+            G = self.nh // self.nkv
+            short = [n * G <= 16 for _, n in self.seqs]
+            assert ops.mma_attention_supported(q, self.nh, self.nkv, self.hd)
+            ops.paged_attention_mma(q, out, kp, vp, table, self.seq_q_start.to(dev), self.seq_q_len.to(dev),
+                                    self.seq_pos_start.to(dev), len(self.seqs), max(n for _, n in self.seqs),
+                                    max(c + n for c, n in self.seqs), any(short), not all(short), self.nh, self.nkv,
+                                    self.hd, self.window, scale, status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0, "the kernel flagged a fault (missing page or timed-out wait)"
+        return out.float().cpu()
+
+
+def check(scene, kernel, tol=None):
+    scale = 1.0 / math.sqrt(scene.hd)
+    got, want = scene.run(kernel, scale), scene.reference(scale)
+    assert torch.isfinite(got).all(), "poison from an unwritten or released slot reached the output"
+    tol = tol if tol is not None else (2e-5 if scene.dtype == torch.float32 else 1.2e-2)
+    err = float((got.double() - want).abs().max() / want.abs().max())
+    assert err < tol, f"{kernel}: error {err:.3e}"
+
+
+KERNELS = [("simt", torch.float32), ("simt", torch.bfloat16), ("mma", torch.bfloat16)]
+GEOMETRY = [(4, 4, 16), (4, 2, 24), (8, 2, 64), (8, 1, 80), (32, 8, 128), (6, 3, 40), (2, 1, 256), (16, 2, 32)]
+
+
+@pytest.mark.parametrize("kernel,dtype", KERNELS)
+@pytest.mark.parametrize("nh,nkv,hd", GEOMETRY)
+@pytest.mark.parametrize("window", [0, 24])
+def test_portions_beside_decoded_tokens(kernel, dtype, nh, nkv, hd, window):
+    seqs = [(0, 37), (50, 1), (3, 2), (129, 1), (17, 70), (0, 1), (64, 3), (200, 1)]
+    check(Scene(seqs, nh, nkv, hd, window, dtype, seed=nh * 100 + hd + window), kernel)
+
+
+@pytest.mark.parametrize("kernel,dtype", KERNELS)
+@pytest.mark.parametrize("page_size", [8, 16, 64])
+def test_long_context_many_chunks(kernel, dtype, page_size):
+    # long enough that the split-key arrangement uses many chunks, and that a portion spans many key tiles
+    seqs = [(3000, 1), (777, 1), (1500, 130), (4095, 2)]
+    check(Scene(seqs, 8, 2, 64, 0, dtype, page_size=page_size, seed=page_size), kernel)
+    check(Scene(seqs, 8, 2, 64, 1000, dtype, page_size=page_size, seed=page_size + 1), kernel)
+
+
+@pytest.mark.parametrize("kernel,dtype", KERNELS)
+@pytest.mark.parametrize("where", ["page_edge_low", "page_edge_high", "window_first", "just_outside_window",
+                                   "first_key", "self", "chunk_edge"])
+def test_one_key_stands_out(kernel, dtype, where):
+    """Scale one key so that its score dominates: the output must be that key's value (or must not be, when the
+    key lies just outside the window).  A kernel that drops or adds a key at an edge fails by a wide margin."""
+    window, cached, nh, nkv, hd = 100, 700, 4, 2, 32
+    p = cached                       # the single query's position
+    target = {"page_edge_low": 640, "page_edge_high": 655, "window_first": p - window + 1,
+              "just_outside_window": p - window, "first_key": 0, "self": p, "chunk_edge": 639}[where]
+    if where == "first_key":
+        window = 0
+    sc = Scene([(cached, 1), (40, 1)], nh, nkv, hd, window, dtype, seed=5, spread=0.3)
+    for h in range(nkv):
+        qh = sc.q[0][0, h * (nh // nkv)]
+        sc.k[0][target, h] = (qh / qh.norm() * 40.0).to(dtype).float()      # score ~ 40*|q|/sqrt(hd) >> others
+    # rewrite the pool with the planted key
+    j, slot = target // 16, target % 16
+    pid = int(sc.table[0, j])
+    if pid >= 0:
+        sc.k_pool[pid, :, slot] = sc.k[0][target]
+    scale = 1.0 / math.sqrt(hd)
+    got = sc.run(kernel, scale).reshape(-1, nh, hd)
+    want = sc.reference(scale).reshape(-1, nh, hd)
+    tol = 2e-5 if dtype == torch.float32 else 1.2e-2
+    assert float((got.double() - want).abs().max() / want.abs().max()) < tol
+    planted = sc.v[0][target]                                               # [nkv, hd]
+    head0 = got[0, 0]
+    closeness = float((head0 - planted[0]).abs().max())
+    if where == "just_outside_window":
+        assert closeness > 0.3, "a key outside the window was attended to"
+    elif where != "self" or True:
+        # heads whose query the key was built from see (almost) only that key
+        assert closeness < 0.05, "the key that dominates was lost"
