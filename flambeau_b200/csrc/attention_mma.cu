@@ -28,6 +28,12 @@ namespace {
 constexpr int KT = 64;             // keys per tile
 constexpr int ATT_THREADS = 128;
 
+// The split-key arrangement streams the cache once and is bound by memory: three tiles (two in flight) per
+// CTA; the long arrangement reuses each tile for 64 rows and keeps two.
+__host__ __device__ constexpr int attn_stages(int hd_max, bool short_rows) {
+    return short_rows ? (hd_max <= 128 ? 3 : 2) : 2;
+}
+
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -94,11 +100,12 @@ attention_mma_kernel(const AttnArgs a) {
     constexpr int WARP_KEYS = SHORT ? 16 : KT;      // keys of a tile that one warp scores
     constexpr int NSB = WARP_KEYS / 8;              // n-blocks of S per warp
     constexpr bool Q_IN_REGS = HD_MAX <= 128;
+    constexpr int NST = attn_stages(HD_MAX, SHORT);    // K/V tiles in shared memory (NST - 1 in flight)
 
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [ROWS][LDS]
-    __nv_bfloat16* Ks = Qs + ROWS * LDS;                                        // [2][KT][LDS]
-    __nv_bfloat16* Vs = Ks + 2 * KT * LDS;                                      // [2][KT][LDS]
+    __nv_bfloat16* Ks = Qs + ROWS * LDS;                                        // [NST][KT][LDS]
+    __nv_bfloat16* Vs = Ks + NST * KT * LDS;                                    // [NST][KT][LDS]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.z, kvh = blockIdx.y;
@@ -141,7 +148,7 @@ attention_mma_kernel(const AttnArgs a) {
     }
     if (hd < HD_MAX) {
         const int pad_chunks = HD_MAX / 8 - hd_chunks;
-        for (int idx = tid; idx < 2 * KT * pad_chunks; idx += ATT_THREADS) {
+        for (int idx = tid; idx < NST * KT * pad_chunks; idx += ATT_THREADS) {
             const int r = idx / pad_chunks, c = hd_chunks + idx - r * pad_chunks;
             *reinterpret_cast<uint4*>(Ks + r * LDS + c * 8) = make_uint4(0, 0, 0, 0);
             *reinterpret_cast<uint4*>(Vs + r * LDS + c * 8) = make_uint4(0, 0, 0, 0);
@@ -171,7 +178,12 @@ attention_mma_kernel(const AttnArgs a) {
         cp_async_commit();
     };
 
-    load_tile(0, k_begin);
+    // prologue: NST - 1 tiles in flight (empty groups keep the group count uniform)
+#pragma unroll
+    for (int st = 0; st < NST - 1; ++st) {
+        if (st < n_tiles) load_tile(st, k_begin + st * KT);
+        else cp_async_commit();
+    }
     __syncthreads();                                  // Q is staged
 
     const int row_base = SHORT ? 0 : warp * 16;       // first row of this warp within the CTA
@@ -203,15 +215,13 @@ attention_mma_kernel(const AttnArgs a) {
         for (int e = 0; e < 4; ++e) o[d][e] = 0.0f;
 
     for (int it = 0; it < n_tiles; ++it) {
-        const int buf = it & 1;
+        const int buf = it % NST;
         const int tile_start = k_begin + it * KT;
-        if (it + 1 < n_tiles) {
-            load_tile(buf ^ 1, tile_start + KT);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        // tile `it` is complete when at most NST - 2 younger groups are pending
+        cp_async_wait<NST - 2>();
+        __syncthreads();                              // tile `it` visible to all; tile it-1's buffer is free
+        if (it + NST - 1 < n_tiles) load_tile((it + NST - 1) % NST, tile_start + (NST - 1) * KT);
+        else cp_async_commit();
         const __nv_bfloat16* kt = Ks + buf * KT * LDS;
         const __nv_bfloat16* vt = Vs + buf * KT * LDS;
 
@@ -294,8 +304,9 @@ attention_mma_kernel(const AttnArgs a) {
                 mma_bf16(o[d + 1], pa, b[2], b[3]);
             }
         }
-        __syncthreads();                              // the buffer may be refilled by the next iteration's load
     }
+    cp_async_wait<0>();
+    __syncthreads();                                  // every warp is done with the tiles
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
@@ -324,7 +335,7 @@ attention_mma_kernel(const AttnArgs a) {
     // ---- SHORT: merge the four warps (they saw different keys of the same rows), write one partial ----
     float* so = reinterpret_cast<float*>(Ks);         // [4 warps][16][HD_MAX] floats; K/V buffers are free now
     float* sml = so + 4 * 16 * HD_MAX;                // [4 warps][16][2]
-    static_assert(4 * 16 * HD_MAX * 4 + 4 * 16 * 2 * 4 <= 4 * KT * (HD_MAX + 8) * 2, "merge buffer fits in K/V");
+    static_assert(4 * 16 * HD_MAX * 4 + 4 * 16 * 2 * 4 <= 2 * NST * KT * (HD_MAX + 8) * 2, "merge buffer fits in K/V");
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = (lane >> 2) + 8 * h;
@@ -363,10 +374,12 @@ attention_mma_kernel(const AttnArgs a) {
 }
 
 // Merges the chunks of the SHORT arrangement: out = sum_c 2^(m_c - m) o_c / sum_c 2^(m_c - m) l_c.
+// One warp per row: lanes first share the chunks (weights), then the head dimensions (sums).
 template <int HD_MAX>
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_merge_kernel(const AttnArgs a) {
     const int seq = blockIdx.y, kvh = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = a.nh / a.nkv;
     const int q_len = a.seq_q_len[seq], q_start = a.seq_q_start[seq], pos0 = a.seq_pos_start[seq];
     if (q_len * G > a.short_rows) return;
@@ -374,20 +387,40 @@ attention_merge_kernel(const AttnArgs a) {
     const int n_chunks = (kr.t_hi - kr.tile_lo) / a.chunk_keys + 1;
     const size_t slot0 = ((size_t)seq * a.nkv + kvh) * a.max_chunks;
     const int rows = q_len * G, hd = a.hd;
-    for (int idx = threadIdx.x; idx < rows * hd; idx += ATT_THREADS) {
-        const int r = idx / hd, c = idx - r * hd;
+    for (int r = warp; r < rows; r += ATT_THREADS / 32) {
         float m = -INFINITY;
-        for (int ch = 0; ch < n_chunks; ++ch) m = fmaxf(m, a.part_ml[((slot0 + ch) * 16 + r) * 2]);
-        float acc = 0.0f, l = 0.0f;
+        for (int ch = lane; ch < n_chunks; ch += 32) m = fmaxf(m, a.part_ml[((slot0 + ch) * 16 + r) * 2]);
+        m = fb_warp_max(m);
+        float l = 0.0f;
+        float acc[HD_MAX / 32];
+#pragma unroll
+        for (int i = 0; i < HD_MAX / 32; ++i) acc[i] = 0.0f;
         if (m > -INFINITY) {
-            for (int ch = 0; ch < n_chunks; ++ch) {
-                const float wgt = exp2f(a.part_ml[((slot0 + ch) * 16 + r) * 2] - m);
-                acc += wgt * a.part_o[((slot0 + ch) * 16 + r) * HD_MAX + c];
-                l += wgt * a.part_ml[((slot0 + ch) * 16 + r) * 2 + 1];
+            for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+                const int mine = c0 + lane;
+                float wgt = 0.0f;
+                if (mine < n_chunks) {
+                    wgt = exp2f(a.part_ml[((slot0 + mine) * 16 + r) * 2] - m);
+                    l += wgt * a.part_ml[((slot0 + mine) * 16 + r) * 2 + 1];
+                }
+                const int cnt = min(32, n_chunks - c0);
+                for (int j = 0; j < cnt; ++j) {
+                    const float wj = __shfl_sync(0xffffffffu, wgt, j);
+                    const float* po = a.part_o + ((slot0 + c0 + j) * 16 + r) * HD_MAX;
+#pragma unroll
+                    for (int i = 0; i < HD_MAX / 32; ++i) acc[i] = fmaf(wj, po[lane + 32 * i], acc[i]);
+                }
             }
         }
+        l = fb_warp_sum(l);
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         const int token = q_start + r / G, head = kvh * G + r % G;
-        a.out[(size_t)token * a.out_stride + (size_t)head * hd + c] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd;
+#pragma unroll
+        for (int i = 0; i < HD_MAX / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < hd) dst[d] = __float2bfloat16_rn(acc[i] * inv);
+        }
     }
 }
 
@@ -399,18 +432,26 @@ int launch_attention_mma(const AttnArgs& a, int n_seqs, int max_q_len, int max_k
     if (any_long) {
         const int TQ = 64 / G;
         const int q_tiles = (max_q_len + TQ - 1) / TQ;
-        const size_t smem = (size_t)(64 + 4 * KT) * LDS * 2;
+        const size_t smem = (size_t)(64 + 2 * attn_stages(HD_MAX, false) * KT) * LDS * 2;
         auto kern = attention_mma_kernel<HD_MAX, false>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        static bool configured = false;
+        if (!configured && smem > 48 * 1024) {
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            configured = true;
+        }
         dim3 grid(q_tiles, a.nkv, n_seqs);
         kern<<<grid, ATT_THREADS, smem, stream>>>(a);
         int rc = fb_check_launch("attention_mma (long)");
         if (rc) return rc;
     }
     if (any_short) {
-        const size_t smem = (size_t)(16 + 4 * KT) * LDS * 2;
+        const size_t smem = (size_t)(16 + 2 * attn_stages(HD_MAX, true) * KT) * LDS * 2;
         auto kern = attention_mma_kernel<HD_MAX, true>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        static bool configured = false;
+        if (!configured && smem > 48 * 1024) {
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            configured = true;
+        }
         dim3 grid(a.max_chunks, a.nkv, n_seqs);
         kern<<<grid, ATT_THREADS, smem, stream>>>(a);
         int rc = fb_check_launch("attention_mma (short)");
@@ -461,10 +502,20 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     if (window > 0 && window + max_q_len < span) span = window + max_q_len;
     span += KT;                                     // tile alignment of the first key
     const int pairs = n_seqs * nkv;
-    int want_chunks = (4 * 148 + pairs - 1) / pairs;
-    if (want_chunks < 1) want_chunks = 1;
-    int chunk_keys = ((span + want_chunks - 1) / want_chunks + KT - 1) / KT * KT;
-    if (chunk_keys < 2 * KT) chunk_keys = 2 * KT;
+    const int total_tiles = (span + KT - 1) / KT;
+    const size_t short_smem = (size_t)(16 + 2 * attn_stages(HD_MAX, true) * KT) * (HD_MAX + 8) * 2;
+    const int per_sm = (int)(227 * 1024 / (short_smem + 1024)) > 4 ? 4 : (int)(227 * 1024 / (short_smem + 1024));
+    const int slots = 148 * (per_sm < 1 ? 1 : per_sm);
+    int want_chunks = 1;
+    double best_cost = 1e30;
+    for (int c = 1; c <= total_tiles && c <= 256; ++c) {
+        // time ~ waves * (tiles per chunk + the fixed cost of a CTA, counted in tiles)
+        const int tiles_per_chunk = (total_tiles + c - 1) / c;
+        const long ctas = (long)pairs * ((total_tiles + tiles_per_chunk - 1) / tiles_per_chunk);
+        const double cost = (double)((ctas + slots - 1) / slots) * (tiles_per_chunk + 3.0);
+        if (cost < best_cost - 1e-9) { best_cost = cost; want_chunks = c; }
+    }
+    int chunk_keys = ((total_tiles + want_chunks - 1) / want_chunks) * KT;
     int max_chunks = (span + chunk_keys - 1) / chunk_keys;
     const long per_slot = 16L * HD_MAX + 32;
     while ((long)pairs * max_chunks * per_slot > scratch_floats && chunk_keys < (1 << 24)) {

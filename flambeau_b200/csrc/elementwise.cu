@@ -67,10 +67,102 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
         o[c] = fb_from_float<TO>(row[c] * fb_to_float(w[c]) * inv);
 }
 
+// Fast path: width a multiple of 4 and at most 4 * VPT * blockDim: every thread keeps its part of the row in
+// registers and issues all of its loads before the first use, so a row costs one round trip to memory.
+template <typename T> struct Vec4 {};
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename TD, typename TW, typename TO, int VPT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_partials,
+                                       size_t partial_stride, const TW* __restrict__ w, TO* __restrict__ out,
+                                       const int* __restrict__ rows, int H, float eps) {
+    __shared__ float red[32];
+    const int j = blockIdx.x;
+    const int r = rows ? rows[j] : j;
+    float* xr = x + (size_t)r * H;
+    const int nvec = H >> 2;
+    float4 v[VPT], wv[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nvec) {
+            v[i] = Vec4<float>::load(xr + 4 * c);
+            wv[i] = Vec4<TW>::load(w + 4 * c);
+        } else {
+            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            wv[i] = v[i];
+        }
+    }
+    if (delta) {
+        for (int p = 0; p < n_partials; ++p) {
+            const TD* dp = delta + (size_t)p * partial_stride + (size_t)r * H;
+            float4 d[VPT];
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int c = threadIdx.x + i * blockDim.x;
+                d[i] = c < nvec ? Vec4<TD>::load(dp + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) { v[i].x += d[i].x; v[i].y += d[i].y; v[i].z += d[i].z; v[i].w += d[i].w; }
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    if (delta && !rows) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            if (c < nvec) Vec4<float>::store(xr + 4 * c, v[i]);
+        }
+    }
+    ss = fb_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)j * H;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nvec)
+            Vec4<TO>::store(o + 4 * c, make_float4(v[i].x * wv[i].x * inv, v[i].y * wv[i].y * inv,
+                                                   v[i].z * wv[i].z * inv, v[i].w * wv[i].w * inv));
+    }
+}
+
 template <typename TD, typename TW, typename TO>
 static int launch_add_rmsnorm(float* x, const void* delta, int n_partials, size_t partial_stride,
                               const void* w, void* out, const int* rows, int n_out, int H, float eps,
                               cudaStream_t stream) {
+    const bool aligned = H % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+                         ((uintptr_t)out % 16 == 0) && (!delta || ((uintptr_t)delta % 16 == 0 && partial_stride % 4 == 0));
+    if (aligned && H <= 16384) {
+        const int nvec = H / 4;
+        int threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
+        const int vpt = (nvec + threads - 1) / threads;
+#define FB_NORM_VEC(V)                                                                                        \
+        add_rmsnorm_vec_kernel<TD, TW, TO, V><<<n_out, threads, 0, stream>>>(x, (const TD*)delta, n_partials,  \
+            partial_stride, (const TW*)w, (TO*)out, rows, H, eps)
+        if (vpt == 1) FB_NORM_VEC(1); else if (vpt == 2) FB_NORM_VEC(2); else FB_NORM_VEC(4);
+#undef FB_NORM_VEC
+        return fb_check_launch("add_rmsnorm");
+    }
     const size_t smem = (size_t)H * sizeof(float);
     auto kern = add_rmsnorm_kernel<TD, TW, TO>;
     if (smem > 48 * 1024) {
@@ -139,29 +231,30 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stri
                                      const int* __restrict__ block_table, int table_stride,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size, int n_pages,
                                      int nh, int nkv, int hd, int write_kv, int* status) {
-    const int t = blockIdx.x;
+    // grid (tokens, nh + nkv): blocks y < nh rotate one query head; the others rotate one key head into the
+    // cache and copy the value head beside it.
+    const int t = blockIdx.x, hy = blockIdx.y;
     const int per_head = hd - half;                 // `half` rotated pairs + (hd - 2*half) untouched dims
     const float* ct = cos_t ? cos_t + (size_t)t * half : nullptr;
     const float* st = sin_t ? sin_t + (size_t)t * half : nullptr;
-
-    // q heads (q_out may be q_in itself: a thread reads both halves of its pair before it writes them)
-    const TI* qi = q_in + (size_t)t * q_in_stride;
-    T* qo = q_out + (size_t)t * q_out_stride;
-    for (int idx = threadIdx.x; idx < nh * per_head; idx += blockDim.x) {
-        const int h = idx / per_head, j = idx - h * per_head;
-        const TI* src = qi + (size_t)h * hd;
-        T* dst = qo + (size_t)h * hd;
-        if (j < half) {
-            const float a = fb_to_float(src[j]), b = fb_to_float(src[j + half]);
-            const float c = ct[j], s = st[j];
-            dst[j] = fb_from_float<T>(a * c - b * s);
-            dst[j + half] = fb_from_float<T>(a * s + b * c);
-        } else {
-            dst[j + half] = fb_from_float<T>(fb_to_float(src[j + half]));
+    if (hy < nh) {
+        // q_out may be q_in itself: a thread reads both halves of its pair before it writes them
+        const TI* src = q_in + (size_t)t * q_in_stride + (size_t)hy * hd;
+        T* dst = q_out + (size_t)t * q_out_stride + (size_t)hy * hd;
+        for (int j = threadIdx.x; j < per_head; j += blockDim.x) {
+            if (j < half) {
+                const float a = fb_to_float(src[j]), b = fb_to_float(src[j + half]);
+                const float c = ct[j], s = st[j];
+                dst[j] = fb_from_float<T>(a * c - b * s);
+                dst[j + half] = fb_from_float<T>(a * s + b * c);
+            } else {
+                dst[j + half] = fb_from_float<T>(fb_to_float(src[j + half]));
+            }
         }
+        return;
     }
     if (!write_kv) return;
-
+    const int h = hy - nh;
     const int pos = positions[t];
     const int page = block_table[(size_t)row_seq[t] * table_stride + pos / page_size];
     if (page < 0 || page >= n_pages) {
@@ -169,26 +262,22 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stri
         return;
     }
     const int slot = pos % page_size;
-    const TI* kt = k + (size_t)t * k_stride;
-    const TI* vt = v + (size_t)t * v_stride;
-    for (int idx = threadIdx.x; idx < nkv * per_head; idx += blockDim.x) {
-        const int h = idx / per_head, j = idx - h * per_head;
-        const TI* src = kt + (size_t)h * hd;
-        T* dst = k_pool + (((size_t)page * nkv + h) * page_size + slot) * hd;
+    const TI* ksrc = k + (size_t)t * k_stride + (size_t)h * hd;
+    const TI* vsrc = v + (size_t)t * v_stride + (size_t)h * hd;
+    const size_t base = (((size_t)page * nkv + h) * page_size + slot) * hd;
+    T* kdst = k_pool + base;
+    T* vdst = v_pool + base;
+    for (int j = threadIdx.x; j < per_head; j += blockDim.x) {
         if (j < half) {
-            const float a = fb_to_float(src[j]), b = fb_to_float(src[j + half]);
+            const float a = fb_to_float(ksrc[j]), b = fb_to_float(ksrc[j + half]);
             const float c = ct[j], s = st[j];
-            dst[j] = fb_from_float<T>(a * c - b * s);
-            dst[j + half] = fb_from_float<T>(a * s + b * c);
+            kdst[j] = fb_from_float<T>(a * c - b * s);
+            kdst[j + half] = fb_from_float<T>(a * s + b * c);
         } else {
-            dst[j + half] = fb_from_float<T>(fb_to_float(src[j + half]));
+            kdst[j + half] = fb_from_float<T>(fb_to_float(ksrc[j + half]));
         }
     }
-    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
-        const int h = idx / hd, d = idx - h * hd;
-        v_pool[(((size_t)page * nkv + h) * page_size + slot) * hd + d] =
-            fb_from_float<T>(fb_to_float(vt[(size_t)h * hd + d]));
-    }
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) vdst[d] = fb_from_float<T>(fb_to_float(vsrc[d]));
 }
 
 // q_in/k/v have dtype `in_dtype` (the projection's output, float32 in both engine modes so that q and k are
@@ -206,8 +295,9 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, void* q_out
                "rope_kv_write: cache arguments missing");
     FB_REQUIRE(q_in != q_out || in_dtype == out_dtype, "rope_kv_write: in-place rotation needs one dtype");
     if (n == 0) return 0;
+    FB_REQUIRE(nh + nkv <= 65535, "rope_kv_write: too many heads");
     FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
-        (rope_kv_write_kernel<TI, T><<<n, 128, 0, stream>>>((const TI*)q_in, q_in_stride, (T*)q_out, q_out_stride,
+        (rope_kv_write_kernel<TI, T><<<dim3(n, nh + (write_kv ? nkv : 0)), hd >= 128 ? 64 : 32, 0, stream>>>((const TI*)q_in, q_in_stride, (T*)q_out, q_out_stride,
             (const TI*)k, k_stride, (const TI*)v, v_stride, cos_t, sin_t, half, positions, row_seq, block_table,
             table_stride, (T*)k_pool, (T*)v_pool, page_size, n_pages, nh, nkv, hd, write_kv, status))));
     return fb_check_launch("rope_kv_write");
@@ -227,10 +317,32 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, long stride, T* __rest
     out[idx] = fb_from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// Four elements per thread (I and the row stride multiples of 4, 16-byte aligned rows for float / 8-byte for bf16).
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, long stride, T* __restrict__ out, int n, int I) {
+    const int nvec = I >> 2;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n * nvec) return;
+    const int r = (int)(idx / nvec), c = (int)(idx - (size_t)r * nvec);
+    const float4 g = Vec4<T>::load(gu + (size_t)r * stride + 4 * c);
+    const float4 u = Vec4<T>::load(gu + (size_t)r * stride + I + 4 * c);
+    Vec4<T>::store(out + (size_t)r * I + 4 * c,
+                   make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
+                               g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
+}
+
 FB_API int fb_silu_mul(const void* gate_up, long long stride, void* out, int dtype, int n, int I,
                        cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && I > 0 && stride >= 2LL * I, "silu_mul: bad sizes n=%d I=%d stride=%lld", n, I, stride);
     if (n == 0) return 0;
+    const bool vec = I % 4 == 0 && stride % 4 == 0 && (uintptr_t)gate_up % 16 == 0 && (uintptr_t)out % 16 == 0;
+    if (vec) {
+        const size_t total = (size_t)n * (I / 4);
+        FB_DISPATCH_DTYPE(dtype, T,
+            silu_mul_vec_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const T*)gate_up, stride,
+                                                                                         (T*)out, n, I));
+        return fb_check_launch("silu_mul");
+    }
     const size_t total = (size_t)n * I;
     FB_DISPATCH_DTYPE(dtype, T,
         silu_mul_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const T*)gate_up, stride,

@@ -150,8 +150,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     int* last_flag = (int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BM;              // first output feature of the tile
-    const int m0 = blockIdx.y * BN;              // first token of the tile
+    // token tiles vary fastest, so the CTAs that share a weight tile run together and it is read from DRAM once
+    const int n0 = blockIdx.y * BM;              // first output feature of the tile
+    const int m0 = blockIdx.x * BN;              // first token of the tile
     const int split = blockIdx.z;
     const int kb_total = (K + BK - 1) / BK;
     const int kb_begin = (int)((long)split * kb_total / splits);
@@ -368,7 +369,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
     int splits = force_splits > 0 ? force_splits : pick_splits(tiles, kb_total, 148 * per_sm, 16);
     if (splits > kb_total) splits = kb_total;
     while (splits > 1 && ((long)tiles * splits * BN * BM > partial_floats || tiles > n_counters)) --splits;
-    if (tiles_m > 65535 || splits > 65535) return fb_fail(-1, "gemm_tc: too many tiles (M=%d)", M);
+    if (tiles_n > 65535 || splits > 65535) return fb_fail(-1, "gemm_tc: too many tiles (N=%d)", N);
     auto kern = gemm_tc_kernel<BN, TO>;
     static bool configured = false;
     if (!configured) {
@@ -377,7 +378,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
                                              Cfg::SMEM_BYTES, cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(tiles_n, tiles_m, splits);
+    dim3 grid(tiles_m, tiles_n, splits);
     kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, mx, (TO*)out, ldo, partials, counters, M, N, K,
                                                           splits, status);
     return fb_check_launch("gemm_tc");

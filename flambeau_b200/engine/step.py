@@ -16,6 +16,7 @@ from typing import Optional
 import torch
 
 from ..cache.manager import CacheManager
+from ..kernels import library
 from .batch import BatchBuffers, BatchError, Entry, StepBatch
 from .runtime import Runtime, Workspace
 
@@ -29,6 +30,7 @@ class EngineOptions:
     max_step_tokens: int = 2048        # rows of one step
     max_seq_len: Optional[int] = None  # longest request; default: the pool size or the model's position limit
     device: str = "cuda:0"
+    cuda_graphs: bool = True           # replay steps of single decoded tokens from a captured CUDA graph
 
 
 class StepContext:
@@ -75,6 +77,8 @@ class Engine:
         self._copy_pending = False
         self.steps_run = 0
         self.last_batch: Optional[StepBatch] = None
+        self._graphs: dict = {}            # step shape -> captured graph (or the count of eager runs so far)
+        self.graph_replays = 0
 
     # ---- construction ----------------------------------------------------------
     @classmethod
@@ -105,6 +109,63 @@ class Engine:
             rows = max(n_out, self.options.max_requests)
             self._logits = torch.empty((rows, vocab), dtype=torch.float32, device=self.runtime.device)
         return self._logits[:n_out]
+
+    # ---- running a packed batch: eagerly, or by replaying a captured graph -----------------------------
+    def _forward(self, batch: StepBatch):
+        self.runtime.ws.reset()
+        self.step_ws.reset()
+        return self.model.forward(StepContext(self, batch))
+
+    def _graph_key(self, batch: StepBatch):
+        """Steps of single decoded tokens repeat with the same shape; everything that differs between them
+        (tokens, positions, block tables, wanted rows) lives in the descriptor buffers, whose addresses are
+        fixed.  The key holds what is baked into kernel arguments: the number of sequences and wanted rows,
+        and the bucket of the longest context (it sets the split of the attention's key range)."""
+        if not self.options.cuda_graphs or batch.max_q_len != 1:
+            return None
+        if batch.n_out not in (0, batch.n_seqs):
+            return None
+        bucket = 1 << max(8, (batch.max_kv_len - 1).bit_length())
+        return (batch.n_seqs, batch.n_out, bucket)
+
+    def _run(self, batch: StepBatch):
+        key = self._graph_key(batch)
+        if key is None:
+            return self._forward(batch)
+        entry = self._graphs.get(key, 0)
+        if isinstance(entry, int):
+            if entry < 1:                               # first time: run eagerly (lazy allocations, attributes)
+                self._graphs[key] = entry + 1
+                return self._forward(batch)
+            entry = self._capture(batch, key)
+        graph, logits, _keep, n_kernels = entry
+        graph.replay()
+        library.LAUNCHES[0] += n_kernels                # the launches the graph replays
+        self.graph_replays += 1
+        return logits
+
+    def _capture(self, batch: StepBatch, key):
+        rt = self.runtime
+        # kernels size their key-range split from max_kv_len: capture with the bucket's upper end
+        real = batch.max_kv_len
+        batch.max_kv_len = key[2]
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        launches_before = library.LAUNCHES[0]
+        rt.ws.frozen = self.step_ws.frozen = True
+        try:
+            with torch.cuda.graph(graph):
+                logits = self._forward(batch)
+        finally:
+            rt.ws.frozen = self.step_ws.frozen = False
+            batch.max_kv_len = real
+        # the graph holds raw addresses: keep the buffers it wrote into and read from alive with it
+        keep = (rt.ws.buffer, self.step_ws.buffer, self._logits)
+        n_kernels = library.LAUNCHES[0] - launches_before
+        library.LAUNCHES[0] = launches_before           # capturing launched nothing
+        entry = (graph, logits, keep, n_kernels)
+        self._graphs[key] = entry
+        return entry
 
     # ---- requests ----------------------------------------------------------------
     def admit(self, request_id):
@@ -154,10 +215,7 @@ class Engine:
             batch = self.buffers.build(entries, cache, self.model.vocab_size)
             self._copied.record()
             self._copy_pending = True
-            self.runtime.ws.reset()
-            self.step_ws.reset()
-            ctx = StepContext(self, batch)
-            logits = self.model.forward(ctx)
+            logits = self._run(batch)
             for e in entries:
                 cache.commit(e.request_id, len(e.tokens))
             self.last_batch = batch
