@@ -21,7 +21,7 @@
 //
 // Formulas: crates/kernels-hip/src/kernels/attention_prefill_flash_tile_f16.cu:73-213
 // (tile + online softmax), attention_decode_f16_splitk.cu:215-256 (merge of chunks).
-#include "common.cuh"
+#include "async_copy.cuh"
 
 namespace {
 
@@ -34,17 +34,7 @@ __host__ __device__ constexpr int attn_stages(int hd_max, bool short_rows) {
     return short_rows ? (hd_max <= 128 ? 3 : 2) : 2;
 }
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
-    const uint32_t d = smem_addr(dst);
-    const int bytes = valid ? 16 : 0;              // 0 source bytes: the 16 destination bytes become zero
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return smem_u32(p); }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -106,6 +96,8 @@ attention_mma_kernel(const AttnArgs a) {
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [ROWS][LDS]
     __nv_bfloat16* Ks = Qs + ROWS * LDS;                                        // [NST][KT][LDS]
     __nv_bfloat16* Vs = Ks + NST * KT * LDS;                                    // [NST][KT][LDS]
+    uint64_t* full = reinterpret_cast<uint64_t*>(Vs + NST * KT * LDS);          // [NST] tile-complete barriers
+    int* bail = reinterpret_cast<int*>(full + NST);                             // a bounded wait ran out
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.z, kvh = blockIdx.y;
@@ -136,6 +128,11 @@ attention_mma_kernel(const AttnArgs a) {
     const int hd = a.hd, hd_chunks = hd / 8;
     const int* table = a.block_table + (size_t)seq * a.table_stride;
 
+    if (tid == 0) {
+        for (int st = 0; st < NST; ++st) mbar_init(smem_u32(&full[st]), ATT_THREADS);
+        *bail = 0;
+        mbar_fence_init();
+    }
     // ---- stage Q (zero-padded) and clear the padding of the K/V buffers ----
     for (int idx = tid; idx < ROWS * (HD_MAX / 8); idx += ATT_THREADS) {
         const int r = idx / (HD_MAX / 8), c = idx - r * (HD_MAX / 8);
@@ -155,36 +152,41 @@ attention_mma_kernel(const AttnArgs a) {
         }
     }
 
+    __syncthreads();                                  // barriers initialised, Q staged, padding cleared
+
+    // One row of 64 keys (threads 0..63) or 64 values (threads 64..127) per thread and tile: a single bulk copy
+    // of the row's hd*2 bytes, counted on the tile's barrier.  A row that no query of this CTA may see (before
+    // the window, past the last position, or in another chunk) is not read: its slot is filled with zeros.
     auto load_tile = [&](int buf, int tile_start) {
-        __nv_bfloat16* kd = Ks + buf * KT * LDS;
-        __nv_bfloat16* vd = Vs + buf * KT * LDS;
-        for (int idx = tid; idx < KT * hd_chunks; idx += ATT_THREADS) {
-            const int r = idx / hd_chunks, c = idx - r * hd_chunks;
-            const int t = tile_start + r;
-            bool valid = t >= kr.t_lo && t < k_end;
-            size_t off = 0;
-            if (valid) {
-                const int page = table[t / a.page_size];
-                if (page < 0 || page >= a.n_pages) {
-                    atomicOr(a.status, FB_STATUS_BAD_PAGE);
-                    valid = false;
-                } else {
-                    off = (((size_t)page * a.nkv + kvh) * a.page_size + (t % a.page_size)) * hd + c * 8;
-                }
+        const int r = tid & (KT - 1);
+        const bool is_v = tid >= KT;
+        const int t = tile_start + r;
+        __nv_bfloat16* dst = (is_v ? Vs : Ks) + (buf * KT + r) * LDS;
+        const uint32_t bar = smem_u32(&full[buf]);
+        bool valid = t >= kr.t_lo && t < k_end;
+        if (valid) {
+            const int page = table[t / a.page_size];
+            if (page < 0 || page >= a.n_pages) {
+                atomicOr(a.status, FB_STATUS_BAD_PAGE);
+                valid = false;
+            } else {
+                const size_t off = (((size_t)page * a.nkv + kvh) * a.page_size + (t % a.page_size)) * hd;
+                mbar_expect_tx(bar, (uint32_t)(hd * 2));
+                bulk_copy_g2s(smem_u32(dst), (is_v ? a.v_pool : a.k_pool) + off, (uint32_t)(hd * 2), bar);
             }
-            cp_async16(kd + r * LDS + c * 8, a.k_pool + off, valid);
-            cp_async16(vd + r * LDS + c * 8, a.v_pool + off, valid);
         }
-        cp_async_commit();
+        if (!valid) {
+            for (int c = 0; c < hd_chunks; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
+            // order these generic stores before a later bulk copy into the same row
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(bar);
+        }
     };
 
-    // prologue: NST - 1 tiles in flight (empty groups keep the group count uniform)
+    // prologue: NST - 1 tiles in flight
 #pragma unroll
-    for (int st = 0; st < NST - 1; ++st) {
+    for (int st = 0; st < NST - 1; ++st)
         if (st < n_tiles) load_tile(st, k_begin + st * KT);
-        else cp_async_commit();
-    }
-    __syncthreads();                                  // Q is staged
 
     const int row_base = SHORT ? 0 : warp * 16;       // first row of this warp within the CTA
     const int key0 = SHORT ? warp * 16 : 0;           // first key of this warp within a tile
@@ -217,11 +219,10 @@ attention_mma_kernel(const AttnArgs a) {
     for (int it = 0; it < n_tiles; ++it) {
         const int buf = it % NST;
         const int tile_start = k_begin + it * KT;
-        // tile `it` is complete when at most NST - 2 younger groups are pending
-        cp_async_wait<NST - 2>();
-        __syncthreads();                              // tile `it` visible to all; tile it-1's buffer is free
+        if (!mbar_wait(smem_u32(&full[buf]), (uint32_t)(it / NST) & 1u, a.status)) *bail = 1;
+        __syncthreads();                              // every thread is past tile it-1: its buffer is free
+        if (*bail) break;
         if (it + NST - 1 < n_tiles) load_tile((it + NST - 1) % NST, tile_start + (NST - 1) * KT);
-        else cp_async_commit();
         const __nv_bfloat16* kt = Ks + buf * KT * LDS;
         const __nv_bfloat16* vt = Vs + buf * KT * LDS;
 
@@ -305,7 +306,6 @@ attention_mma_kernel(const AttnArgs a) {
             }
         }
     }
-    cp_async_wait<0>();
     __syncthreads();                                  // every warp is done with the tiles
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -432,7 +432,7 @@ int launch_attention_mma(const AttnArgs& a, int n_seqs, int max_q_len, int max_k
     if (any_long) {
         const int TQ = 64 / G;
         const int q_tiles = (max_q_len + TQ - 1) / TQ;
-        const size_t smem = (size_t)(64 + 2 * attn_stages(HD_MAX, false) * KT) * LDS * 2;
+        const size_t smem = (size_t)(64 + 2 * attn_stages(HD_MAX, false) * KT) * LDS * 2 + 64;
         auto kern = attention_mma_kernel<HD_MAX, false>;
         static bool configured = false;
         if (!configured && smem > 48 * 1024) {
@@ -445,7 +445,7 @@ int launch_attention_mma(const AttnArgs& a, int n_seqs, int max_q_len, int max_k
         if (rc) return rc;
     }
     if (any_short) {
-        const size_t smem = (size_t)(16 + 2 * attn_stages(HD_MAX, true) * KT) * LDS * 2;
+        const size_t smem = (size_t)(16 + 2 * attn_stages(HD_MAX, true) * KT) * LDS * 2 + 64;
         auto kern = attention_mma_kernel<HD_MAX, true>;
         static bool configured = false;
         if (!configured && smem > 48 * 1024) {

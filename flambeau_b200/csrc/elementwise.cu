@@ -222,8 +222,17 @@ FB_API int fb_rope_table(const int* positions, const double* inv_freq, float* co
 // crates/kernels-hip/src/kernels/rope_neox_partial_f16.cu:39-52 (rotation),
 // kv_append_f16_paged_prefill.cu (row placement).
 // ---------------------------------------------------------------------------
+// Element j of a row that is stored as `n_partials` slabs `partial_stride` elements apart (split-K shares).
+template <typename TI>
+__device__ __forceinline__ float slab_sum(const TI* __restrict__ row, int j, int n_partials, long partial_stride) {
+    float acc = fb_to_float(row[j]);
+    for (int p = 1; p < n_partials; ++p) acc += fb_to_float(row[(size_t)p * partial_stride + j]);
+    return acc;
+}
+
 template <typename TI, typename T>
-__global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stride, T* __restrict__ q_out,
+__global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stride, int n_partials,
+                                     long partial_stride, T* __restrict__ q_out,
                                      long q_out_stride, const TI* __restrict__ k, long k_stride,
                                      const TI* __restrict__ v, long v_stride, const float* __restrict__ cos_t,
                                      const float* __restrict__ sin_t, int half,
@@ -243,12 +252,12 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stri
         T* dst = q_out + (size_t)t * q_out_stride + (size_t)hy * hd;
         for (int j = threadIdx.x; j < per_head; j += blockDim.x) {
             if (j < half) {
-                const float a = fb_to_float(src[j]), b = fb_to_float(src[j + half]);
+                const float a = slab_sum(src, j, n_partials, partial_stride), b = slab_sum(src, j + half, n_partials, partial_stride);
                 const float c = ct[j], s = st[j];
                 dst[j] = fb_from_float<T>(a * c - b * s);
                 dst[j + half] = fb_from_float<T>(a * s + b * c);
             } else {
-                dst[j + half] = fb_from_float<T>(fb_to_float(src[j + half]));
+                dst[j + half] = fb_from_float<T>(slab_sum(src, j + half, n_partials, partial_stride));
             }
         }
         return;
@@ -269,20 +278,22 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stri
     T* vdst = v_pool + base;
     for (int j = threadIdx.x; j < per_head; j += blockDim.x) {
         if (j < half) {
-            const float a = fb_to_float(ksrc[j]), b = fb_to_float(ksrc[j + half]);
+            const float a = slab_sum(ksrc, j, n_partials, partial_stride), b = slab_sum(ksrc, j + half, n_partials, partial_stride);
             const float c = ct[j], s = st[j];
             kdst[j] = fb_from_float<T>(a * c - b * s);
             kdst[j + half] = fb_from_float<T>(a * s + b * c);
         } else {
-            kdst[j + half] = fb_from_float<T>(fb_to_float(ksrc[j + half]));
+            kdst[j + half] = fb_from_float<T>(slab_sum(ksrc, j + half, n_partials, partial_stride));
         }
     }
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) vdst[d] = fb_from_float<T>(fb_to_float(vsrc[d]));
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) vdst[d] = fb_from_float<T>(slab_sum(vsrc, d, n_partials, partial_stride));
 }
 
 // q_in/k/v have dtype `in_dtype` (the projection's output, float32 in both engine modes so that q and k are
-// rounded once, after the rotation); q_out and the cache have dtype `out_dtype`.
-FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, void* q_out, long long q_out_stride,
+// rounded once, after the rotation); q_out and the cache have dtype `out_dtype`.  The inputs may be split-K
+// shares: `n_partials` slabs `partial_stride` elements apart, which are added here.
+FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, int n_partials, long long partial_stride,
+                            void* q_out, long long q_out_stride,
                             const void* k, long long k_stride, const void* v, long long v_stride, int in_dtype,
                             int out_dtype, const float* cos_t, const float* sin_t, int half,
                             const int* positions, const int* row_seq, const int* block_table,
@@ -293,11 +304,13 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, void* q_out
     FB_REQUIRE(half == 0 || (cos_t && sin_t), "rope_kv_write: rotary tables missing");
     FB_REQUIRE(!write_kv || (page_size > 0 && n_pages > 0 && k_pool && v_pool && block_table),
                "rope_kv_write: cache arguments missing");
-    FB_REQUIRE(q_in != q_out || in_dtype == out_dtype, "rope_kv_write: in-place rotation needs one dtype");
+    FB_REQUIRE(q_in != q_out || (in_dtype == out_dtype && n_partials <= 1),
+               "rope_kv_write: in-place rotation needs one dtype and one slab");
+    if (n_partials < 1) n_partials = 1;
     if (n == 0) return 0;
     FB_REQUIRE(nh + nkv <= 65535, "rope_kv_write: too many heads");
     FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
-        (rope_kv_write_kernel<TI, T><<<dim3(n, nh + (write_kv ? nkv : 0)), hd >= 128 ? 64 : 32, 0, stream>>>((const TI*)q_in, q_in_stride, (T*)q_out, q_out_stride,
+        (rope_kv_write_kernel<TI, T><<<dim3(n, nh + (write_kv ? nkv : 0)), hd >= 128 ? 64 : 32, 0, stream>>>((const TI*)q_in, q_in_stride, n_partials, (long)partial_stride, (T*)q_out, q_out_stride,
             (const TI*)k, k_stride, (const TI*)v, v_stride, cos_t, sin_t, half, positions, row_seq, block_table,
             table_stride, (T*)k_pool, (T*)v_pool, page_size, n_pages, nh, nkv, hd, write_kv, status))));
     return fb_check_launch("rope_kv_write");
@@ -307,45 +320,58 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, void* q_out
 // SiLU(gate) * up on a fused [n, 2I] buffer (gate in columns [0,I), up in [I,2I)).
 // crates/kernels-hip/src/kernels/swiglu_f32_to_f16.cu; activation.rs:107-118.
 // ---------------------------------------------------------------------------
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, long stride, T* __restrict__ out, int n, int I) {
+template <typename TI, typename T>
+__global__ void silu_mul_kernel(const TI* __restrict__ gu, long stride, int n_partials, long partial_stride,
+                                T* __restrict__ out, int n, int I) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n * I) return;
     const int r = (int)(idx / I), c = (int)(idx - (size_t)r * I);
-    const float g = fb_to_float(gu[(size_t)r * stride + c]);
-    const float u = fb_to_float(gu[(size_t)r * stride + I + c]);
+    const TI* row = gu + (size_t)r * stride;
+    const float g = slab_sum(row, c, n_partials, partial_stride);
+    const float u = slab_sum(row, I + c, n_partials, partial_stride);
     out[idx] = fb_from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
-// Four elements per thread (I and the row stride multiples of 4, 16-byte aligned rows for float / 8-byte for bf16).
-template <typename T>
-__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, long stride, T* __restrict__ out, int n, int I) {
+// Four elements per thread (I and the strides multiples of 4, 16-byte aligned rows for float / 8-byte for bf16).
+template <typename TI, typename T>
+__global__ void silu_mul_vec_kernel(const TI* __restrict__ gu, long stride, int n_partials, long partial_stride,
+                                    T* __restrict__ out, int n, int I) {
     const int nvec = I >> 2;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n * nvec) return;
     const int r = (int)(idx / nvec), c = (int)(idx - (size_t)r * nvec);
-    const float4 g = Vec4<T>::load(gu + (size_t)r * stride + 4 * c);
-    const float4 u = Vec4<T>::load(gu + (size_t)r * stride + I + 4 * c);
+    const TI* row = gu + (size_t)r * stride;
+    float4 g = Vec4<TI>::load(row + 4 * c), u = Vec4<TI>::load(row + I + 4 * c);
+    for (int p = 1; p < n_partials; ++p) {
+        const float4 g2 = Vec4<TI>::load(row + (size_t)p * partial_stride + 4 * c);
+        const float4 u2 = Vec4<TI>::load(row + (size_t)p * partial_stride + I + 4 * c);
+        g.x += g2.x; g.y += g2.y; g.z += g2.z; g.w += g2.w;
+        u.x += u2.x; u.y += u2.y; u.z += u2.z; u.w += u2.w;
+    }
     Vec4<T>::store(out + (size_t)r * I + 4 * c,
                    make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
                                g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
 }
 
-FB_API int fb_silu_mul(const void* gate_up, long long stride, void* out, int dtype, int n, int I,
-                       cudaStream_t stream) {
+// gate_up has dtype in_dtype and may be split-K shares (n_partials slabs partial_stride elements apart);
+// out has dtype out_dtype.
+FB_API int fb_silu_mul(const void* gate_up, long long stride, int in_dtype, int n_partials,
+                       long long partial_stride, void* out, int out_dtype, int n, int I, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && I > 0 && stride >= 2LL * I, "silu_mul: bad sizes n=%d I=%d stride=%lld", n, I, stride);
     if (n == 0) return 0;
-    const bool vec = I % 4 == 0 && stride % 4 == 0 && (uintptr_t)gate_up % 16 == 0 && (uintptr_t)out % 16 == 0;
+    if (n_partials < 1) n_partials = 1;
+    const bool vec = I % 4 == 0 && stride % 4 == 0 && partial_stride % 4 == 0 && (uintptr_t)gate_up % 16 == 0 &&
+                     (uintptr_t)out % 16 == 0;
     if (vec) {
         const size_t total = (size_t)n * (I / 4);
-        FB_DISPATCH_DTYPE(dtype, T,
-            silu_mul_vec_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const T*)gate_up, stride,
-                                                                                         (T*)out, n, I));
+        FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
+            (silu_mul_vec_kernel<TI, T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+                (const TI*)gate_up, stride, n_partials, (long)partial_stride, (T*)out, n, I))));
         return fb_check_launch("silu_mul");
     }
     const size_t total = (size_t)n * I;
-    FB_DISPATCH_DTYPE(dtype, T,
-        silu_mul_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const T*)gate_up, stride,
-                                                                                 (T*)out, n, I));
+    FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
+        (silu_mul_kernel<TI, T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+            (const TI*)gate_up, stride, n_partials, (long)partial_stride, (T*)out, n, I))));
     return fb_check_launch("silu_mul");
 }

@@ -23,7 +23,7 @@
 // The reference multiplies with scalar-FMA tiles of 64 outputs x 8 rows
 // (crates/kernels-hip/src/kernels/mmq_f16_tile.cu:32-107); the weight layout
 // (rows = outputs) is the same.
-#include "common.cuh"
+#include "async_copy.cuh"
 
 #include <cuda.h>
 #include <mutex>
@@ -35,60 +35,10 @@ constexpr int BM = 128;          // output features per CTA (UMMA M)
 constexpr int BK = 64;           // K elements per stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok;
-}
-// Waits until the phase with the given parity has completed, or gives up after WAIT_LIMIT_NS.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 256; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (global_ns() - t0 > WAIT_LIMIT_NS) {
-            atomicOr(status, FB_STATUS_WAIT_TIMEOUT);
-            return false;
-        }
-    }
-}
-
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-
-__device__ __forceinline__ uint32_t elect_one() {
-    uint32_t pred = 0;
-    asm volatile(
-        "{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\t"
-        "elect.sync rx|px, %1;\n\t"
-        "selp.u32 %0, 1, 0, px;\n\t}"
-        : "=r"(pred) : "r"(0xFFFFFFFFu));
-    return pred;
 }
 
 // Shared-memory matrix descriptor: K-major tile of rows x 64 bf16, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -139,8 +89,8 @@ template <int BN> struct TileCfg {
 template <int BN, typename TO>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               TO* __restrict__ out, long ldo, float* __restrict__ partials, int* __restrict__ tile_counters,
-               int M, int N, int K, int splits, int* status) {
+               TO* __restrict__ out, long ldo, long slab_stride, float* __restrict__ partials,
+               int* __restrict__ tile_counters, int M, int N, int K, int splits, int* status) {
     using Cfg = TileCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -165,7 +115,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             mbar_init(smem_u32(&bars[Cfg::STAGES + s]), 1);
         }
         mbar_init(smem_u32(&bars[2 * Cfg::STAGES]), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_fence_init();
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -226,17 +176,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const bool got = mbar_wait(smem_u32(&bars[2 * Cfg::STAGES]), 0u, status);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        if (splits == 1) {
-            if (got && n_kb > 0) {
+        if (splits == 1 || slab_stride > 0) {
+            // the whole sum, or this split's share of it written to its own slab (the consumer adds the slabs)
+            TO* dst = out + (size_t)split * (size_t)slab_stride;
+            if (got) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     if (m0 + c >= M) break;
                     float v[16];
-                    tmem_ld16(taddr + (uint32_t)c, v);
+                    if (n_kb > 0) {
+                        tmem_ld16(taddr + (uint32_t)c, v);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                    }
                     if (n < N) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            if (m0 + c + j < M) out[(size_t)(m0 + c + j) * ldo + n] = fb_from_float<TO>(v[j]);
+                            if (m0 + c + j < M) dst[(size_t)(m0 + c + j) * ldo + n] = fb_from_float<TO>(v[j]);
                     }
                 }
             }
@@ -267,11 +224,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 __threadfence();
                 const float* base = partials + (size_t)tile_id * splits * (size_t)(BN * BM);
 #pragma unroll 1
-                for (int c = 0; c < BN && m0 + c < M; ++c) {
-                    float acc = 0.0f;
-                    for (int s = 0; s < splits; ++s)
-                        acc += __ldcg(base + ((size_t)s * BN + c) * BM + row_local);
-                    if (n < N) out[(size_t)(m0 + c) * ldo + n] = fb_from_float<TO>(acc);
+                for (int c = 0; c < BN && m0 + c < M; c += 4) {
+                    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    for (int s = 0; s < splits; ++s) {
+                        float v[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) v[j] = __ldcg(base + ((size_t)s * BN + c + j) * BM + row_local);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) acc[j] += v[j];
+                    }
+                    if (n < N) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (m0 + c + j < M) out[(size_t)(m0 + c + j) * ldo + n] = fb_from_float<TO>(acc[j]);
+                    }
                 }
                 if (warp == 2 && lane == 0) tile_counters[tile_id] = 0;      // ready for the next launch
             }
@@ -358,9 +324,9 @@ int pick_splits(int tiles, int kb_total, int slots, int max_splits) {
 }
 
 template <int BN, typename TO>
-int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo, float* partials,
-              long partial_floats, int* counters, int n_counters, int M, int N, int K, int force_splits,
-              int* status, cudaStream_t stream) {
+int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo, long slab_stride, int max_slabs,
+              int* splits_used, float* partials, long partial_floats, int* counters, int n_counters, int M, int N,
+              int K, int force_splits, int* status, cudaStream_t stream) {
     using Cfg = TileCfg<BN>;
     const int tiles_n = (N + BM - 1) / BM, tiles_m = (M + BN - 1) / BN;
     const int tiles = tiles_n * tiles_m;
@@ -368,7 +334,12 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
     const int per_sm = Cfg::SMEM_BYTES <= 113 * 1024 ? 2 : 1;
     int splits = force_splits > 0 ? force_splits : pick_splits(tiles, kb_total, 148 * per_sm, 16);
     if (splits > kb_total) splits = kb_total;
-    while (splits > 1 && ((long)tiles * splits * BN * BM > partial_floats || tiles > n_counters)) --splits;
+    if (slab_stride > 0) {
+        if (splits > max_slabs) splits = max_slabs;
+    } else {
+        while (splits > 1 && ((long)tiles * splits * BN * BM > partial_floats || tiles > n_counters)) --splits;
+    }
+    if (splits_used) *splits_used = splits;
     if (tiles_n > 65535 || splits > 65535) return fb_fail(-1, "gemm_tc: too many tiles (N=%d)", N);
     auto kern = gemm_tc_kernel<BN, TO>;
     static bool configured = false;
@@ -379,24 +350,31 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
         configured = true;
     }
     dim3 grid(tiles_m, tiles_n, splits);
-    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, mx, (TO*)out, ldo, partials, counters, M, N, K,
-                                                          splits, status);
+    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, mx, (TO*)out, ldo, slab_stride, partials, counters, M,
+                                                          N, K, splits, status);
     return fb_check_launch("gemm_tc");
 }
 
 }  // namespace
 
 // X [M,K] and W [N,K] are bfloat16 with row strides lda, ldw (elements); out is float32 or bfloat16.
-// `partials` (float32 scratch) and `counters` (int32, zero before the first call; the kernel leaves them zero)
-// serve split-K.  Shapes the TMA path cannot take are refused with an error, never computed wrongly.
+// Split-K has two forms.  With slab_stride == 0 the splits meet in `partials` (float32 scratch) and the CTA that
+// arrives last at `counters` (int32, zero before the first call; the kernel leaves them zero) writes the sum.
+// With slab_stride > 0 (float32 out only) split s writes its share to out + s * slab_stride and the caller's
+// next kernel adds the `*splits_used` slabs (at most max_slabs), which costs no second pass here.
+// Shapes the TMA path cannot take are refused with an error, never computed wrongly.
 FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw, void* out, int o_dtype,
-                      long long ldo, int M, int N, int K, float* partials, long long partial_floats,
-                      int* counters, int n_counters, int force_splits, int* status, cudaStream_t stream) {
+                      long long ldo, long long slab_stride, int max_slabs, int* splits_used, int M, int N, int K,
+                      float* partials, long long partial_floats, int* counters, int n_counters, int force_splits,
+                      int* status, cudaStream_t stream) {
     FB_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     FB_REQUIRE(lda >= K && ldw >= K && ldo >= N, "gemm_tc: a row stride is shorter than its row");
     FB_REQUIRE(lda % 8 == 0 && ldw % 8 == 0, "gemm_tc: row strides must be multiples of 8 elements (16 bytes)");
     FB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
     FB_REQUIRE(partials && counters && n_counters > 0, "gemm_tc: split-K scratch missing");
+    FB_REQUIRE(slab_stride == 0 || (o_dtype == FB_F32 && max_slabs >= 1 && slab_stride >= (long long)M * ldo),
+               "gemm_tc: slabs must be float32, at least one, and not overlap");
+    if (splits_used) *splits_used = 1;
     if (M == 0) return 0;
     const int BN = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     CUtensorMap mw, mx;
@@ -407,11 +385,13 @@ FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw
 #define FB_TC_CASE(BN_)                                                                                         \
     case BN_:                                                                                                   \
         if (o_dtype == FB_F32)                                                                                  \
-            return launch_tc<BN_, float>(mw, mx, out, (long)ldo, partials, (long)partial_floats, counters,      \
-                                         n_counters, M, N, K, force_splits, status, stream);                    \
+            return launch_tc<BN_, float>(mw, mx, out, (long)ldo, (long)slab_stride, max_slabs, splits_used,     \
+                                         partials, (long)partial_floats, counters, n_counters, M, N, K,         \
+                                         force_splits, status, stream);                                         \
         else if (o_dtype == FB_BF16)                                                                            \
-            return launch_tc<BN_, __nv_bfloat16>(mw, mx, out, (long)ldo, partials, (long)partial_floats,        \
-                                                 counters, n_counters, M, N, K, force_splits, status, stream);  \
+            return launch_tc<BN_, __nv_bfloat16>(mw, mx, out, (long)ldo, 0, 1, splits_used, partials,           \
+                                                 (long)partial_floats, counters, n_counters, M, N, K,           \
+                                                 force_splits, status, stream);                                 \
         break;
     switch (BN) {
         FB_TC_CASE(16)

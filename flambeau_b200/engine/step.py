@@ -43,7 +43,9 @@ class StepContext:
         self.n_tokens = batch.n_tokens
         self.ws = engine.runtime.ws
         self.shared: dict = {}              # per-step memo shared between layers (rotary tables, work lists)
-        self.normed = self.delta = None
+        self.normed = self.delta = self.delta_slabs = None
+        self.max_slabs = 1                  # how many split-K slabs a product may leave for the next kernel to add
+        self.pending_slabs = 1
 
     def step_alloc(self, shape, dtype):
         """Scratch that lives until the step ends (ctx.ws allocations end with their scope)."""

@@ -23,12 +23,12 @@ _SIGNATURES = {
     "fb_embedding": (I, [P, I, P, P, I, I, I, P, STREAM]),
     "fb_add_rmsnorm": (I, [P, P, I, I, L, P, I, P, I, P, I, I, F, STREAM]),
     "fb_rope_table": (I, [P, P, P, P, I, I, STREAM]),
-    "fb_rope_kv_write": (I, [P, L, P, L, P, L, P, L, I, I, P, P, I, P, P, P, I, P, P, I, I, I, I, I, I, I, P, STREAM]),
-    "fb_silu_mul": (I, [P, L, P, I, I, I, STREAM]),
+    "fb_rope_kv_write": (I, [P, L, I, L, P, L, P, L, P, L, I, I, P, P, I, P, P, P, I, P, P, I, I, I, I, I, I, I, P, STREAM]),
+    "fb_silu_mul": (I, [P, L, I, I, L, P, I, I, I, STREAM]),
     # gemm_simt.cu
     "fb_gemm_simt": (I, [P, I, L, P, I, L, P, I, L, I, I, I, STREAM]),
     # gemm_tc.cu
-    "fb_gemm_tc": (I, [P, L, P, L, P, I, L, I, I, I, P, L, P, I, I, P, STREAM]),
+    "fb_gemm_tc": (I, [P, L, P, L, P, I, L, L, I, P, I, I, I, P, L, P, I, I, P, STREAM]),
     # attention_simt.cu
     "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, I, I, I, I, I, F, P, STREAM]),
     # attention_mma.cu

@@ -6,6 +6,8 @@ scale) arrive as arguments; nothing here knows a model.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from .library import KernelError, check, lib
@@ -61,9 +63,10 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor, status: t
 
 
 def add_rms_norm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: torch.Tensor,
-                 rows=None, n_partials: int = 1, n_rows: int | None = None) -> None:
-    """out[j] = rmsnorm(x[r] + sum_p delta[p][r]) * weight, r = rows[j] or j; without `rows` the sum is
-    also written back to x.  `delta` is [n, H] or, with n_partials > 1, [n_partials, n, H]."""
+                 rows=None, n_partials: int = 1, n_rows: int | None = None, partial_stride: int = 0) -> None:
+    """out[j] = rmsnorm(x[r] + sum_p delta_p[r]) * weight, r = rows[j] or j; without `rows` the sum is
+    also written back to x.  `delta` is [n, H]; with n_partials > 1 it is the first of that many slabs
+    `partial_stride` elements apart."""
     _cuda(x, delta, weight, out, rows)
     _i32(rows, "rows")
     H = x.shape[1]
@@ -76,7 +79,9 @@ def add_rms_norm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: 
         if not delta.is_contiguous() or delta.shape[-1] != H:
             raise KernelError("add_rms_norm: delta must be contiguous with the stream's width")
         if n_partials > 1:
-            stride = delta.stride(0)
+            stride = int(partial_stride)
+            if stride <= 0:
+                raise KernelError("add_rms_norm: several slabs need their stride")
     check(lib().fb_add_rmsnorm(x.data_ptr(), _ptr(delta), dtype_code(delta) if delta is not None else 0,
                                n_partials, stride, weight.data_ptr(), dtype_code(weight), out.data_ptr(),
                                dtype_code(out), _ptr(rows), n_out, H, float(eps), _stream()), "add_rms_norm")
@@ -94,9 +99,11 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tenso
 
 
 def rope_kv_write(q_in, q_out, k, v, cos, sin, half: int, positions, row_seq, block_table, k_pool, v_pool,
-                  page_size: int, nh: int, nkv: int, hd: int, write_kv: bool, status) -> None:
+                  page_size: int, nh: int, nkv: int, hd: int, write_kv: bool, status, n_partials: int = 1,
+                  partial_stride: int = 0) -> None:
     """q_out = rotate(q_in) (q_out may be q_in); with write_kv, rotate k into the cache and copy v into it.
-    q_in, k, v share one dtype (the projection's output); q_out and the cache share one dtype."""
+    q_in, k, v share one dtype (the projection's output); q_out and the cache share one dtype.  With
+    n_partials > 1 the inputs are split-K shares `partial_stride` elements apart and are added first."""
     _cuda(q_in, q_out, k, v, cos, sin, positions, row_seq, block_table, k_pool, v_pool, status)
     n = q_in.shape[0]
     if q_in.shape[1] != nh * hd or q_out.shape[1] != nh * hd or q_out.shape[0] != n:
@@ -111,21 +118,24 @@ def rope_kv_write(q_in, q_out, k, v, cos, sin, half: int, positions, row_seq, bl
                      or tuple(v_pool.shape) != tuple(k_pool.shape) or not v_pool.is_contiguous()):
         raise KernelError("rope_kv_write: cache pools must be contiguous [pages, kv heads, page size, head size]")
     check(lib().fb_rope_kv_write(
-        q_in.data_ptr(), _rows(q_in), q_out.data_ptr(), _rows(q_out), _ptr(k), _rows(k) if k is not None else 0,
+        q_in.data_ptr(), _rows(q_in), int(n_partials), int(partial_stride), q_out.data_ptr(), _rows(q_out), _ptr(k),
+        _rows(k) if k is not None else 0,
         _ptr(v), _rows(v) if v is not None else 0, dtype_code(q_in), dtype_code(q_out), _ptr(cos), _ptr(sin), half,
         _ptr(positions), _ptr(row_seq), _ptr(block_table),
         block_table.stride(0) if block_table is not None else 0, _ptr(k_pool), _ptr(v_pool), page_size, n_pages,
         n, nh, nkv if write_kv else 0, hd, 1 if write_kv else 0, status.data_ptr(), _stream()), "rope_kv_write")
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, n_partials: int = 1, partial_stride: int = 0) -> None:
+    """out = silu(gate) * up for gate_up = [gate | up] rows; with n_partials > 1, gate_up is the first of that
+    many split-K shares `partial_stride` elements apart, which are added first."""
     _cuda(gate_up, out)
     n, two_i = gate_up.shape
     I = two_i // 2
-    if out.dtype != gate_up.dtype or tuple(out.shape) != (n, I) or not out.is_contiguous():
+    if tuple(out.shape) != (n, I) or not out.is_contiguous():
         raise KernelError("silu_mul: bad output")
-    check(lib().fb_silu_mul(gate_up.data_ptr(), _rows(gate_up), out.data_ptr(), dtype_code(out), n, I, _stream()),
-          "silu_mul")
+    check(lib().fb_silu_mul(gate_up.data_ptr(), _rows(gate_up), dtype_code(gate_up), int(n_partials),
+                            int(partial_stride), out.data_ptr(), dtype_code(out), n, I, _stream()), "silu_mul")
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -212,9 +222,15 @@ def tc_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor, splits: int = 0) -> None:
+_SPLITS_USED = ctypes.c_int(1)
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor, splits: int = 0,
+            slabs: torch.Tensor | None = None) -> int:
     """out[M,N] = a[M,K] @ w[N,K]^T on the tensor cores (bfloat16 operands, float32 accumulation).
-    splits = 0 lets the launcher choose the split of K."""
+    splits = 0 lets the launcher choose the split of K.  With `slabs` (float32 [P, M, N], out = slabs[0]) each
+    split writes its share into its own slab and the count of slabs to add is returned; otherwise the kernel
+    adds the shares itself and 1 is returned."""
     _cuda(a, w, out, status)
     M, K = a.shape
     N = w.shape[0]
@@ -222,10 +238,27 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.T
         raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tc: operands must be bfloat16")
+    slab_stride = max_slabs = 0
+    if slabs is not None:
+        if slabs.dtype != torch.float32 or slabs.dim() != 3 or slabs.data_ptr() != out.data_ptr():
+            raise KernelError("gemm_tc: slabs must be float32 [P, M, N] with out = slabs[0]")
+        slab_stride, max_slabs = slabs.stride(0), slabs.shape[0]
     partials, counters = _SplitScratch.get(a.device)
     check(lib().fb_gemm_tc(a.data_ptr(), _rows(a), w.data_ptr(), _rows(w), out.data_ptr(), dtype_code(out),
-                           _rows(out), M, N, K, partials.data_ptr(), partials.numel(), counters.data_ptr(),
-                           counters.numel(), int(splits), status.data_ptr(), _stream()), "gemm_tc")
+                           _rows(out), slab_stride, max_slabs, ctypes.byref(_SPLITS_USED), M, N, K,
+                           partials.data_ptr(), partials.numel(), counters.data_ptr(), counters.numel(),
+                           int(splits), status.data_ptr(), _stream()), "gemm_tc")
+    return _SPLITS_USED.value if slabs is not None else 1
+
+
+def linear_slabs(a: torch.Tensor, w: torch.Tensor, slabs: torch.Tensor, ctx) -> int:
+    """slabs[0] + ... + slabs[k-1] = a @ w^T; returns k.  The tensor-core kernel leaves the split-K shares for the
+    next kernel to add; every other path writes the whole product into slabs[0]."""
+    out = slabs[0]
+    if slabs.shape[0] > 1 and tc_supported(a, w, out):
+        return gemm_tc(a, w, out, ctx.runtime.status, slabs=slabs)
+    linear(a, w, out, ctx)
+    return 1
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ctx=None) -> None:

@@ -67,7 +67,12 @@ class DecoderModel:
         n = b.n_tokens
         x = ctx.step_alloc((n, self.hidden_size), torch.float32)
         ctx.normed = ctx.step_alloc((n, self.hidden_size), rt.dtype)
-        ctx.delta = ctx.step_alloc((n, self.hidden_size), torch.float32)   # mixer / feed-forward outputs stay float32 until added
+        # mixer / feed-forward outputs stay float32 until they are added; for steps of few rows (decoding) they
+        # may arrive as split-K shares in up to ctx.max_slabs slabs, which the next norm adds
+        ctx.max_slabs = 16 if n <= 16 else (8 if n <= 64 else 1)
+        ctx.delta_slabs = ctx.step_alloc((ctx.max_slabs, n, self.hidden_size), torch.float32)
+        ctx.delta = ctx.delta_slabs[0]
+        ctx.pending_slabs = 1
         self.embedding.forward(ctx, b.token_ids[:n], x)
         stream = ResidualStream(x)
         for ci, call in enumerate(self.order):
@@ -75,7 +80,8 @@ class DecoderModel:
         if b.n_out == 0:
             return None
         h = ctx.step_alloc((b.n_out, self.hidden_size), rt.dtype)
-        self.final_norm.add_norm(ctx, stream.x, stream.pending, h, rows=b.out_rows[:b.n_out])
+        self.final_norm.add_norm(ctx, stream.x, stream.pending, h, rows=b.out_rows[:b.n_out],
+                                 n_partials=stream.pending_slabs)
         logits = ctx.logits(b.n_out, self.vocab_size)
         self.head.forward(ctx, h, logits)
         return logits

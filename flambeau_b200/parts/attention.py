@@ -65,20 +65,25 @@ class PagedAttention(Mixer):
         cache = ctx.cache(call)
         with ctx.ws.scope():
             # the projection stays float32 until after the rotation, so q and k are rounded once
-            qkv = ctx.ws.alloc((n, self.qw + 2 * self.kvw), torch.float32)
-            self.qkv(ctx, h, qkv)
+            pos = self.position
+            fused = pos is None or getattr(pos, "fused_with_cache_write", False)
+            # the fused rotary kernel adds split-K shares of the projection itself; a position encoding with a
+            # rotate() of its own gets whole rows
+            qkv_slabs = ctx.ws.alloc((ctx.max_slabs if fused else 1, n, self.qw + 2 * self.kvw), torch.float32)
+            parts = self.qkv.slabs(ctx, h, qkv_slabs)
+            stride = qkv_slabs.stride(0)
+            qkv = qkv_slabs[0]
             q_in = qkv[:, :self.qw]
             k = qkv[:, self.qw:self.qw + self.kvw]
             v = qkv[:, self.qw + self.kvw:]
             q = ctx.ws.alloc((n, self.qw), rt.dtype)
             b = ctx.batch
-            pos = self.position
-            if pos is None or getattr(pos, "fused_with_cache_write", False):
+            if fused:
                 cos, sin = pos.prepare(ctx) if pos is not None else (None, None)
                 half = pos.half if pos is not None else 0
                 ops.rope_kv_write(q_in, q, k, v, cos, sin, half, b.positions, b.row_seq, cache.block_table,
                                   cache.k_pool, cache.v_pool, cache.page_size, self.nh, self.nkv, self.hd,
-                                  cache.writable, rt.status)
+                                  cache.writable, rt.status, n_partials=parts, partial_stride=stride)
             else:
                 pos.rotate(ctx, q_in, k if cache.writable else None)
                 ops.rope_kv_write(q_in, q, k, v, None, None, 0, b.positions, b.row_seq, cache.block_table,
@@ -86,7 +91,7 @@ class PagedAttention(Mixer):
                                   cache.writable, rt.status)
             a = ctx.ws.alloc((n, self.qw), rt.dtype)
             ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale)
-            self.o(ctx, a, out)
+            ctx.pending_slabs = self.o.slabs(ctx, a, ctx.delta_slabs)
 
 
 register_part("mixer", "attention", PagedAttention)

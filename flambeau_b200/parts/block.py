@@ -8,10 +8,12 @@ from .spec import PartSpec, build_part, register_part
 class ResidualStream:
     """The float32 stream x [n, width] plus the last part's output that has
     not been added yet (`pending`): the next norm adds it while it normalises,
-    so the add costs no pass of its own."""
+    so the add costs no pass of its own.  `pending_slabs` > 1 says that the
+    output is a sum of that many float32 slabs (split-K shares of the part's last
+    product, ctx.delta_slabs[0..k)), which the norm adds as well."""
 
-    def __init__(self, x, pending=None):
-        self.x, self.pending = x, pending
+    def __init__(self, x, pending=None, pending_slabs: int = 1):
+        self.x, self.pending, self.pending_slabs = x, pending, pending_slabs
 
 
 class PreNormBlock(Part):
@@ -32,12 +34,14 @@ class PreNormBlock(Part):
 
     def forward(self, ctx, stream: ResidualStream, call) -> None:
         h, delta = ctx.normed, ctx.delta
-        self.mixer_norm.add_norm(ctx, stream.x, stream.pending, h)
+        self.mixer_norm.add_norm(ctx, stream.x, stream.pending, h, n_partials=stream.pending_slabs)
+        ctx.pending_slabs = 1                 # a part that leaves split-K shares in ctx.delta_slabs says how many
         self.mixer.forward(ctx, h, delta, call)
-        stream.pending = delta
-        self.feed_forward_norm.add_norm(ctx, stream.x, stream.pending, h)
+        stream.pending, stream.pending_slabs = delta, ctx.pending_slabs
+        self.feed_forward_norm.add_norm(ctx, stream.x, stream.pending, h, n_partials=stream.pending_slabs)
+        ctx.pending_slabs = 1
         self.feed_forward.forward(ctx, h, delta)
-        stream.pending = delta
+        stream.pending, stream.pending_slabs = delta, ctx.pending_slabs
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -1,6 +1,8 @@
 """SiLU-gated dense feed-forward."""
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
 from .base import FeedForward, TensorSpec
 from .linear import Linear, concat_rows
@@ -39,11 +41,16 @@ class GatedMLP(FeedForward):
     def forward(self, ctx, h, out):
         n = ctx.n_tokens
         with ctx.ws.scope():
-            gu = ctx.ws.alloc((n, 2 * self.inner), self.runtime.dtype)
-            self.gate_up(ctx, h, gu)
             a = ctx.ws.alloc((n, self.inner), self.runtime.dtype)
-            ops.silu_mul(gu, a)
-            self.down(ctx, a, out)
+            if ctx.max_slabs > 1:
+                gu = ctx.ws.alloc((ctx.max_slabs, n, 2 * self.inner), torch.float32)
+                parts = self.gate_up.slabs(ctx, h, gu)
+                ops.silu_mul(gu[0], a, n_partials=parts, partial_stride=gu.stride(0))
+            else:
+                gu = ctx.ws.alloc((n, 2 * self.inner), self.runtime.dtype)
+                self.gate_up(ctx, h, gu)
+                ops.silu_mul(gu, a)
+            ctx.pending_slabs = self.down.slabs(ctx, a, ctx.delta_slabs)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -18,6 +18,10 @@ class Linear:
         ops.linear(a, self.weight, out, ctx)
         return out
 
+    def slabs(self, ctx, a: torch.Tensor, slabs: torch.Tensor) -> int:
+        """The product as a sum of float32 slabs (split-K shares that the next kernel adds); returns how many."""
+        return ops.linear_slabs(a, self.weight, slabs, ctx)
+
 
 def concat_rows(tensors) -> torch.Tensor:
     """Stack weights that share their input so one product serves them all."""
