@@ -65,10 +65,11 @@ class CacheGroup:
         self.page_size = page_size
         self.pool = PagePool(n_pages)
         shape = (n_pages, req.kv_heads, page_size, req.head_dim)
-        # uninitialised on purpose (the reference leaves its pools so too, scratch.rs:546-573):
-        # a key is always written before any query can see it.
-        self.k = {c: torch.empty(shape, dtype=dtype, device=device) for c in owners}
-        self.v = {c: torch.empty(shape, dtype=dtype, device=device) for c in owners}
+        # Zeroed once (the reference leaves its pools uninitialised, scratch.rs:546-573).  A key is always
+        # written before any query can see it, but the tensor-core attention fetches whole pages, masked slots
+        # included, and a masked probability of 0 times a stray NaN would still be NaN.
+        self.k = {c: torch.zeros(shape, dtype=dtype, device=device) for c in owners}
+        self.v = {c: torch.zeros(shape, dtype=dtype, device=device) for c in owners}
 
     def bytes_per_token(self) -> int:
         any_pool = next(iter(self.k.values()))

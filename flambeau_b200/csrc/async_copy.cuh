@@ -60,6 +60,14 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
+// One box of a 2-d tensor map (x = innermost coordinate in elements, a multiple of 8 for 16-bit types) from
+// global to shared memory; completion is counted on the mbarrier.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
 __device__ __forceinline__ uint32_t elect_one() {
     uint32_t pred = 0;
     asm volatile(

@@ -22,6 +22,7 @@
 // Formulas: crates/kernels-hip/src/kernels/attention_prefill_flash_tile_f16.cu:73-213
 // (tile + online softmax), attention_decode_f16_splitk.cu:215-256 (merge of chunks).
 #include "async_copy.cuh"
+#include "tensor_map.cuh"
 
 namespace {
 
@@ -56,6 +57,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 struct AttnArgs {
+    CUtensorMap map_k, map_v;          // TMA mode: the pools as [pages * kv heads * page size, hd] matrices
     const __nv_bfloat16* q; long q_stride;
     __nv_bfloat16* out; long out_stride;
     const __nv_bfloat16* k_pool; const __nv_bfloat16* v_pool;
@@ -80,10 +82,21 @@ __device__ __forceinline__ KeyRange key_range(int p_first, int p_last, int windo
     return r;
 }
 
-template <int HD_MAX, bool SHORT>
+// Where element (row, dim) of a K/V tile lives in shared memory (dim a multiple of 8).
+//   padded:  rows of HD_MAX + 8 elements (the per-row bulk copies land here);
+//   swizzled (TMA mode): HD_MAX / 64 column blocks of [64 rows][128 bytes], the 16-byte chunks of a row
+//   XOR-ed with (row & 7), which is how a tensor-map copy with the 128-byte swizzle stores a box.
+template <int HD_MAX, bool TMA>
+__device__ __forceinline__ const __nv_bfloat16* tile_at(const __nv_bfloat16* tile, int row, int dim) {
+    if (TMA) return tile + (dim >> 6) * (KT * 64) + row * 64 + ((((dim & 63) >> 3) ^ (row & 7)) << 3);
+    return tile + row * (HD_MAX + 8) + dim;
+}
+
+template <int HD_MAX, bool SHORT, bool TMA>
 __global__ void __launch_bounds__(ATT_THREADS)
-attention_mma_kernel(const AttnArgs a) {
-    constexpr int LDS = HD_MAX + 8;                 // row stride in shared memory: 16 bytes of padding
+attention_mma_kernel(const __grid_constant__ AttnArgs a) {
+    constexpr int LDS = HD_MAX + 8;                 // row stride of Q (and of K/V when padded): 16 bytes of padding
+    constexpr int TILE_ELEMS = TMA ? KT * HD_MAX : KT * LDS;
     constexpr int NKS = HD_MAX / 16;                // k-steps of Q K^T
     constexpr int NDB = HD_MAX / 8;                 // n-blocks of P V
     constexpr int ROWS = SHORT ? 16 : 64;           // query rows per CTA
@@ -92,11 +105,14 @@ attention_mma_kernel(const AttnArgs a) {
     constexpr bool Q_IN_REGS = HD_MAX <= 128;
     constexpr int NST = attn_stages(HD_MAX, SHORT);    // K/V tiles in shared memory (NST - 1 in flight)
 
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [ROWS][LDS]
-    __nv_bfloat16* Ks = Qs + ROWS * LDS;                                        // [NST][KT][LDS]
-    __nv_bfloat16* Vs = Ks + NST * KT * LDS;                                    // [NST][KT][LDS]
-    uint64_t* full = reinterpret_cast<uint64_t*>(Vs + NST * KT * LDS);          // [NST] tile-complete barriers
+    // Q first; the K/V tiles start on a 1024-byte boundary (the swizzle pattern of TMA mode needs it)
+    const uint32_t smem_base = smem_u32(smem_raw);
+    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(
+        smem_raw + (((smem_base + ROWS * LDS * 2 + 1023u) & ~1023u) - smem_base));
+    __nv_bfloat16* Vs = Ks + NST * TILE_ELEMS;                                  // [NST] tiles each
+    uint64_t* full = reinterpret_cast<uint64_t*>(Vs + NST * TILE_ELEMS);        // [NST] tile-complete barriers
     int* bail = reinterpret_cast<int*>(full + NST);                             // a bounded wait ran out
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -127,9 +143,13 @@ attention_mma_kernel(const AttnArgs a) {
     const int n_tiles = (k_end - k_begin + KT - 1) / KT;
     const int hd = a.hd, hd_chunks = hd / 8;
     const int* table = a.block_table + (size_t)seq * a.table_stride;
+    // TMA mode: one copy per (K or V, page of the tile, 64-column block), issued by thread number = op number
+    const int pages_per_tile = TMA ? KT / a.page_size : 1;
+    const int col_blocks = TMA ? hd / 64 : 1;
+    const int tma_ops = 2 * pages_per_tile * col_blocks;
 
     if (tid == 0) {
-        for (int st = 0; st < NST; ++st) mbar_init(smem_u32(&full[st]), ATT_THREADS);
+        for (int st = 0; st < NST; ++st) mbar_init(smem_u32(&full[st]), TMA ? tma_ops : ATT_THREADS);
         *bail = 0;
         mbar_fence_init();
     }
@@ -143,7 +163,12 @@ attention_mma_kernel(const AttnArgs a) {
         }
         *reinterpret_cast<uint4*>(Qs + r * LDS + c * 8) = v;
     }
-    if (hd < HD_MAX) {
+    if (TMA) {
+        // pages that no query can see are not fetched; clear the tiles once so that what stays there is finite
+        for (int idx = tid; idx < 2 * NST * TILE_ELEMS / 8; idx += ATT_THREADS)
+            *reinterpret_cast<uint4*>(Ks + idx * 8) = make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    } else if (hd < HD_MAX) {
         const int pad_chunks = HD_MAX / 8 - hd_chunks;
         for (int idx = tid; idx < NST * KT * pad_chunks; idx += ATT_THREADS) {
             const int r = idx / pad_chunks, c = hd_chunks + idx - r * pad_chunks;
@@ -158,10 +183,33 @@ attention_mma_kernel(const AttnArgs a) {
     // of the row's hd*2 bytes, counted on the tile's barrier.  A row that no query of this CTA may see (before
     // the window, past the last position, or in another chunk) is not read: its slot is filled with zeros.
     auto load_tile = [&](int buf, int tile_start) {
+        if constexpr (TMA) {
+            if (tid >= tma_ops) return;
+            const bool is_v = tid & 1;
+            const int rest = tid >> 1;
+            const int cb = rest % col_blocks, pj = rest / col_blocks;
+            const int t_first = tile_start + pj * a.page_size;
+            const uint32_t bar = smem_u32(&full[buf]);
+            bool valid = t_first + a.page_size > kr.t_lo && t_first < k_end;
+            if (valid) {
+                const int page = table[t_first / a.page_size];
+                if (page < 0 || page >= a.n_pages) {
+                    atomicOr(a.status, FB_STATUS_BAD_PAGE);
+                    valid = false;
+                } else {
+                    __nv_bfloat16* dst = (is_v ? Vs : Ks) + buf * TILE_ELEMS + cb * (KT * 64) + pj * a.page_size * 64;
+                    mbar_expect_tx(bar, (uint32_t)(a.page_size * 128));
+                    tma_load_2d(smem_u32(dst), is_v ? &a.map_v : &a.map_k, bar, cb * 64,
+                                (page * a.nkv + kvh) * a.page_size);
+                }
+            }
+            if (!valid) mbar_arrive(bar);
+            return;
+        }
         const int r = tid & (KT - 1);
         const bool is_v = tid >= KT;
         const int t = tile_start + r;
-        __nv_bfloat16* dst = (is_v ? Vs : Ks) + (buf * KT + r) * LDS;
+        __nv_bfloat16* dst = (is_v ? Vs : Ks) + buf * TILE_ELEMS + r * LDS;
         const uint32_t bar = smem_u32(&full[buf]);
         bool valid = t >= kr.t_lo && t < k_end;
         if (valid) {
@@ -223,8 +271,24 @@ attention_mma_kernel(const AttnArgs a) {
         __syncthreads();                              // every thread is past tile it-1: its buffer is free
         if (*bail) break;
         if (it + NST - 1 < n_tiles) load_tile((it + NST - 1) % NST, tile_start + (NST - 1) * KT);
-        const __nv_bfloat16* kt = Ks + buf * KT * LDS;
-        const __nv_bfloat16* vt = Vs + buf * KT * LDS;
+        if constexpr (TMA) {
+            // Whole pages arrive, the slots behind the last position included, and what a page holds there was
+            // never written by this request.  Scores of such keys are masked by assignment, but their values
+            // would be multiplied by a probability of 0, and 0 * NaN is NaN: clear those value rows.
+            if (tile_start + KT > kr.t_hi + 1) {
+                const int first_dead = kr.t_hi + 1 - tile_start;            // >= 0 because tile_start <= t_hi
+                __nv_bfloat16* vz = Vs + buf * TILE_ELEMS;
+                const int chunks = (KT - first_dead) * 8;                    // 16-byte chunks per 64-column block
+                for (int idx = tid; idx < chunks * (HD_MAX / 64); idx += ATT_THREADS) {
+                    const int cb = idx / chunks, rest = idx - cb * chunks;
+                    *reinterpret_cast<uint4*>(vz + cb * (KT * 64) + (first_dead + rest / 8) * 64 + (rest & 7) * 8) =
+                        make_uint4(0, 0, 0, 0);
+                }
+                __syncthreads();
+            }
+        }
+        const __nv_bfloat16* kt = Ks + buf * TILE_ELEMS;
+        const __nv_bfloat16* vt = Vs + buf * TILE_ELEMS;
 
         // ---- S = Q K^T for this warp's rows and keys ----
         float s[NSB][4];
@@ -245,7 +309,7 @@ attention_mma_kernel(const AttnArgs a) {
 #pragma unroll
             for (int nb = 0; nb < NSB; ++nb) {
                 uint32_t b[4];     // (b0,b1): dims ks*16..+15, (b2,b3): dims (ks+1)*16..+15, keys nb*8..+7
-                ldmatrix_x4(b, kt + (key0 + nb * 8 + (lane & 7)) * LDS + ks * 16 + 8 * (lane >> 3));
+                ldmatrix_x4(b, tile_at<HD_MAX, TMA>(kt, key0 + nb * 8 + (lane & 7), ks * 16 + 8 * (lane >> 3)));
                 mma_bf16(s[nb], qa, b[0], b[1]);
                 mma_bf16(s[nb], qb, b[2], b[3]);
             }
@@ -299,8 +363,8 @@ attention_mma_kernel(const AttnArgs a) {
 #pragma unroll
             for (int d = 0; d < NDB; d += 2) {
                 uint32_t b[4];     // (b0,b1): dims d*8..+7, (b2,b3): dims (d+1)*8..+7, keys kk*16..+15
-                ldmatrix_x4_trans(b, vt + (key0 + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + d * 8 +
-                                         8 * (lane >> 4));
+                ldmatrix_x4_trans(b, tile_at<HD_MAX, TMA>(vt, key0 + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1),
+                                                          d * 8 + 8 * (lane >> 4)));
                 mma_bf16(o[d], pa, b[0], b[1]);
                 mma_bf16(o[d + 1], pa, b[2], b[3]);
             }
@@ -335,7 +399,7 @@ attention_mma_kernel(const AttnArgs a) {
     // ---- SHORT: merge the four warps (they saw different keys of the same rows), write one partial ----
     float* so = reinterpret_cast<float*>(Ks);         // [4 warps][16][HD_MAX] floats; K/V buffers are free now
     float* sml = so + 4 * 16 * HD_MAX;                // [4 warps][16][2]
-    static_assert(4 * 16 * HD_MAX * 4 + 4 * 16 * 2 * 4 <= 2 * NST * KT * (HD_MAX + 8) * 2, "merge buffer fits in K/V");
+    static_assert(4 * 16 * HD_MAX * 4 + 4 * 16 * 2 * 4 <= 2 * NST * KT * HD_MAX * 2, "merge buffer fits in K/V");
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = (lane >> 2) + 8 * h;
@@ -424,37 +488,51 @@ attention_merge_kernel(const AttnArgs a) {
     }
 }
 
+__host__ __device__ constexpr size_t attn_smem_bytes(int hd_max, bool short_rows, bool tma) {
+    return (size_t)(short_rows ? 16 : 64) * (hd_max + 8) * 2 + 1024 /* tile alignment */ +
+           (size_t)2 * attn_stages(hd_max, short_rows) * KT * (tma ? hd_max : hd_max + 8) * 2 + 64 /* barriers */;
+}
+
+template <int HD_MAX, bool SHORT, bool TMA>
+int launch_one(const AttnArgs& a, dim3 grid, const char* what, cudaStream_t stream) {
+    constexpr size_t smem = attn_smem_bytes(HD_MAX, SHORT, TMA);
+    auto kern = attention_mma_kernel<HD_MAX, SHORT, TMA>;
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fb_fail(-2, "%s: cannot reserve %d bytes of shared memory: %s", what, (int)smem,
+                                             cudaGetErrorString(e));
+        configured = true;
+    }
+    kern<<<grid, ATT_THREADS, smem, stream>>>(a);
+    return fb_check_launch(what);
+}
+
 template <int HD_MAX>
-int launch_attention_mma(const AttnArgs& a, int n_seqs, int max_q_len, int max_kv_len, int any_short, int any_long,
-                         long scratch_floats, cudaStream_t stream) {
-    constexpr int LDS = HD_MAX + 8;
+int launch_attention_mma(const AttnArgs& a, bool tma, int n_seqs, int max_q_len, int any_short, int any_long,
+                         cudaStream_t stream) {
     const int G = a.nh / a.nkv;
     if (any_long) {
         const int TQ = 64 / G;
-        const int q_tiles = (max_q_len + TQ - 1) / TQ;
-        const size_t smem = (size_t)(64 + 2 * attn_stages(HD_MAX, false) * KT) * LDS * 2 + 64;
-        auto kern = attention_mma_kernel<HD_MAX, false>;
-        static bool configured = false;
-        if (!configured && smem > 48 * 1024) {
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            configured = true;
+        const dim3 grid((max_q_len + TQ - 1) / TQ, a.nkv, n_seqs);
+        int rc;
+        if constexpr (HD_MAX >= 64) {
+            rc = tma ? launch_one<HD_MAX, false, true>(a, grid, "attention_mma (long)", stream)
+                     : launch_one<HD_MAX, false, false>(a, grid, "attention_mma (long)", stream);
+        } else {
+            rc = launch_one<HD_MAX, false, false>(a, grid, "attention_mma (long)", stream);
         }
-        dim3 grid(q_tiles, a.nkv, n_seqs);
-        kern<<<grid, ATT_THREADS, smem, stream>>>(a);
-        int rc = fb_check_launch("attention_mma (long)");
         if (rc) return rc;
     }
     if (any_short) {
-        const size_t smem = (size_t)(16 + 2 * attn_stages(HD_MAX, true) * KT) * LDS * 2 + 64;
-        auto kern = attention_mma_kernel<HD_MAX, true>;
-        static bool configured = false;
-        if (!configured && smem > 48 * 1024) {
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            configured = true;
+        const dim3 grid(a.max_chunks, a.nkv, n_seqs);
+        int rc;
+        if constexpr (HD_MAX >= 64) {
+            rc = tma ? launch_one<HD_MAX, true, true>(a, grid, "attention_mma (short)", stream)
+                     : launch_one<HD_MAX, true, false>(a, grid, "attention_mma (short)", stream);
+        } else {
+            rc = launch_one<HD_MAX, true, false>(a, grid, "attention_mma (short)", stream);
         }
-        dim3 grid(a.max_chunks, a.nkv, n_seqs);
-        kern<<<grid, ATT_THREADS, smem, stream>>>(a);
-        int rc = fb_check_launch("attention_mma (short)");
         if (rc) return rc;
         attention_merge_kernel<HD_MAX><<<dim3(a.nkv, n_seqs), ATT_THREADS, 0, stream>>>(a);
         rc = fb_check_launch("attention_merge");
@@ -503,7 +581,17 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     span += KT;                                     // tile alignment of the first key
     const int pairs = n_seqs * nkv;
     const int total_tiles = (span + KT - 1) / KT;
-    const size_t short_smem = (size_t)(16 + 2 * attn_stages(HD_MAX, true) * KT) * (HD_MAX + 8) * 2;
+    // whole pages fetched by tensor-map copies when a 64-key tile is a whole number of pages and the head a whole
+    // number of 64-column blocks; single rows by bulk copies otherwise
+    const bool tma = hd % 64 == 0 && page_size >= 8 && page_size <= KT && KT % page_size == 0;
+    if (tma) {
+        const long pool_rows = (long)n_pages * nkv * page_size;
+        int rc = fb_tensor_map_bf16(&a.map_k, k_pool, pool_rows, hd, hd, 64, page_size);
+        if (rc) return rc;
+        rc = fb_tensor_map_bf16(&a.map_v, v_pool, pool_rows, hd, hd, 64, page_size);
+        if (rc) return rc;
+    }
+    const size_t short_smem = attn_smem_bytes(HD_MAX, true, tma);
     const int per_sm = (int)(227 * 1024 / (short_smem + 1024)) > 4 ? 4 : (int)(227 * 1024 / (short_smem + 1024));
     const int slots = 148 * (per_sm < 1 ? 1 : per_sm);
     int want_chunks = 1;
@@ -528,9 +616,9 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     a.part_o = scratch;
     a.part_ml = scratch + (size_t)pairs * max_chunks * 16 * HD_MAX;
     switch (HD_MAX) {
-        case 32: return launch_attention_mma<32>(a, n_seqs, max_q_len, max_kv_len, any_short, any_long, scratch_floats, stream);
-        case 64: return launch_attention_mma<64>(a, n_seqs, max_q_len, max_kv_len, any_short, any_long, scratch_floats, stream);
-        case 128: return launch_attention_mma<128>(a, n_seqs, max_q_len, max_kv_len, any_short, any_long, scratch_floats, stream);
-        default: return launch_attention_mma<256>(a, n_seqs, max_q_len, max_kv_len, any_short, any_long, scratch_floats, stream);
+        case 32: return launch_attention_mma<32>(a, tma, n_seqs, max_q_len, any_short, any_long, stream);
+        case 64: return launch_attention_mma<64>(a, tma, n_seqs, max_q_len, any_short, any_long, stream);
+        case 128: return launch_attention_mma<128>(a, tma, n_seqs, max_q_len, any_short, any_long, stream);
+        default: return launch_attention_mma<256>(a, tma, n_seqs, max_q_len, any_short, any_long, stream);
     }
 }

@@ -112,16 +112,25 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restri
         }
     }
     if (delta) {
-        for (int p = 0; p < n_partials; ++p) {
-            const TD* dp = delta + (size_t)p * partial_stride + (size_t)r * H;
-            float4 d[VPT];
+        // the slabs are independent loads: issue them four slabs at a time, add in slab order
+        for (int p0 = 0; p0 < n_partials; p0 += 4) {
+            float4 d[4][VPT];
 #pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                const int c = threadIdx.x + i * blockDim.x;
-                d[i] = c < nvec ? Vec4<TD>::load(dp + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int q = 0; q < 4; ++q) {
+                const TD* dp = delta + (size_t)(p0 + q) * partial_stride + (size_t)r * H;
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const int c = threadIdx.x + i * blockDim.x;
+                    d[q][i] = (p0 + q < n_partials && c < nvec) ? Vec4<TD>::load(dp + 4 * c)
+                                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
             }
 #pragma unroll
-            for (int i = 0; i < VPT; ++i) { v[i].x += d[i].x; v[i].y += d[i].y; v[i].z += d[i].z; v[i].w += d[i].w; }
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    v[i].x += d[q][i].x; v[i].y += d[q][i].y; v[i].z += d[q][i].z; v[i].w += d[q][i].w;
+                }
         }
     }
     float ss = 0.0f;
@@ -226,7 +235,15 @@ FB_API int fb_rope_table(const int* positions, const double* inv_freq, float* co
 template <typename TI>
 __device__ __forceinline__ float slab_sum(const TI* __restrict__ row, int j, int n_partials, long partial_stride) {
     float acc = fb_to_float(row[j]);
-    for (int p = 1; p < n_partials; ++p) acc += fb_to_float(row[(size_t)p * partial_stride + j]);
+    int p = 1;
+    for (; p + 3 < n_partials; p += 4) {              // four independent loads in flight, added in slab order
+        const float a0 = fb_to_float(row[(size_t)p * partial_stride + j]);
+        const float a1 = fb_to_float(row[(size_t)(p + 1) * partial_stride + j]);
+        const float a2 = fb_to_float(row[(size_t)(p + 2) * partial_stride + j]);
+        const float a3 = fb_to_float(row[(size_t)(p + 3) * partial_stride + j]);
+        acc = (((acc + a0) + a1) + a2) + a3;
+    }
+    for (; p < n_partials; ++p) acc += fb_to_float(row[(size_t)p * partial_stride + j]);
     return acc;
 }
 
@@ -342,6 +359,7 @@ __global__ void silu_mul_vec_kernel(const TI* __restrict__ gu, long stride, int 
     const int r = (int)(idx / nvec), c = (int)(idx - (size_t)r * nvec);
     const TI* row = gu + (size_t)r * stride;
     float4 g = Vec4<TI>::load(row + 4 * c), u = Vec4<TI>::load(row + I + 4 * c);
+#pragma unroll 4
     for (int p = 1; p < n_partials; ++p) {
         const float4 g2 = Vec4<TI>::load(row + (size_t)p * partial_stride + 4 * c);
         const float4 u2 = Vec4<TI>::load(row + (size_t)p * partial_stride + I + 4 * c);

@@ -25,9 +25,7 @@
 // (rows = outputs) is the same.
 #include "async_copy.cuh"
 
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
+#include "tensor_map.cuh"
 
 namespace {
 
@@ -35,12 +33,6 @@ constexpr int BM = 128;          // output features per CTA (UMMA M)
 constexpr int BK = 64;           // K elements per stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-
 // Shared-memory matrix descriptor: K-major tile of rows x 64 bf16, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -255,62 +247,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // ---------------------------------------------------------------------------
 // host side: tensor maps
 // ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; long rows, cols, ld; int box_rows;
-    bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
-    }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        size_t h = (size_t)k.ptr;
-        h = h * 1000003u ^ (size_t)k.rows;
-        h = h * 1000003u ^ (size_t)k.cols;
-        h = h * 1000003u ^ (size_t)k.ld;
-        return h * 1000003u ^ (size_t)k.box_rows;
-    }
-};
-
-// A [rows, cols] bf16 matrix with row stride ld (elements), fetched in boxes of box_rows x 64.
-int make_map(CUtensorMap* out, const void* ptr, long rows, long cols, long ld, int box_rows) {
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    static std::mutex mu;
-    const MapKey key{ptr, rows, cols, ld, box_rows};
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return 0; }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return fb_fail(-3, "gemm_tc: the driver does not provide cuTensorMapEncodeTiled");
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fb_fail(-3, "gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
-    if (cache.size() > 8192) cache.clear();
-    cache.emplace(key, *out);
-    return 0;
-}
-
 int pick_splits(int tiles, int kb_total, int slots, int max_splits) {
     // time ~ waves * (k-blocks per CTA + fixed cost of a CTA, in k-blocks)
     int best = 1;
@@ -378,9 +314,9 @@ FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw
     if (M == 0) return 0;
     const int BN = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     CUtensorMap mw, mx;
-    int rc = make_map(&mw, W, N, K, (long)ldw, BM);
+    int rc = fb_tensor_map_bf16(&mw, W, N, K, (long)ldw, BK, BM);
     if (rc) return rc;
-    rc = make_map(&mx, X, M, K, (long)lda, BN);
+    rc = fb_tensor_map_bf16(&mx, X, M, K, (long)lda, BK, BN);
     if (rc) return rc;
 #define FB_TC_CASE(BN_)                                                                                         \
     case BN_:                                                                                                   \
