@@ -95,6 +95,8 @@ __device__ __forceinline__ const __nv_bfloat16* tile_at(const __nv_bfloat16* til
 template <int HD_MAX, bool SHORT, bool TMA>
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_mma_kernel(const __grid_constant__ AttnArgs a) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     constexpr int LDS = HD_MAX + 8;                 // row stride of Q (and of K/V when padded): 16 bytes of padding
     constexpr int TILE_ELEMS = TMA ? KT * HD_MAX : KT * LDS;
     constexpr int NKS = HD_MAX / 16;                // k-steps of Q K^T
@@ -442,6 +444,8 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
 template <int HD_MAX>
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_merge_kernel(const AttnArgs a) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     const int seq = blockIdx.y, kvh = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = a.nh / a.nkv;
@@ -468,11 +472,22 @@ attention_merge_kernel(const AttnArgs a) {
                     l += wgt * a.part_ml[((slot0 + mine) * 16 + r) * 2 + 1];
                 }
                 const int cnt = min(32, n_chunks - c0);
-                for (int j = 0; j < cnt; ++j) {
-                    const float wj = __shfl_sync(0xffffffffu, wgt, j);
-                    const float* po = a.part_o + ((slot0 + c0 + j) * 16 + r) * HD_MAX;
+                for (int j0 = 0; j0 < cnt; j0 += 8) {
+                    // eight chunks' loads in flight, added in chunk order
+                    float v[8][HD_MAX / 32];
 #pragma unroll
-                    for (int i = 0; i < HD_MAX / 32; ++i) acc[i] = fmaf(wj, po[lane + 32 * i], acc[i]);
+                    for (int u = 0; u < 8; ++u) {
+                        const int j = j0 + u < cnt ? j0 + u : cnt - 1;
+                        const float* po = a.part_o + ((slot0 + c0 + j) * 16 + r) * HD_MAX;
+#pragma unroll
+                        for (int i = 0; i < HD_MAX / 32; ++i) v[u][i] = po[lane + 32 * i];
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const float wj = j0 + u < cnt ? __shfl_sync(0xffffffffu, wgt, (j0 + u) & 31) : 0.0f;
+#pragma unroll
+                        for (int i = 0; i < HD_MAX / 32; ++i) acc[i] = fmaf(wj, v[u][i], acc[i]);
+                    }
                 }
             }
         }
@@ -504,7 +519,7 @@ int launch_one(const AttnArgs& a, dim3 grid, const char* what, cudaStream_t stre
                                              cudaGetErrorString(e));
         configured = true;
     }
-    kern<<<grid, ATT_THREADS, smem, stream>>>(a);
+    fb_launch((kern), grid, ATT_THREADS, smem, stream, a);
     return fb_check_launch(what);
 }
 
@@ -534,7 +549,7 @@ int launch_attention_mma(const AttnArgs& a, bool tma, int n_seqs, int max_q_len,
             rc = launch_one<HD_MAX, true, false>(a, grid, "attention_mma (short)", stream);
         }
         if (rc) return rc;
-        attention_merge_kernel<HD_MAX><<<dim3(a.nkv, n_seqs), ATT_THREADS, 0, stream>>>(a);
+        fb_launch((attention_merge_kernel<HD_MAX>), dim3(a.nkv, n_seqs), ATT_THREADS, 0, stream, a);
         rc = fb_check_launch("attention_merge");
         if (rc) return rc;
     }
@@ -600,7 +615,7 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
         // time ~ waves * (tiles per chunk + the fixed cost of a CTA, counted in tiles)
         const int tiles_per_chunk = (total_tiles + c - 1) / c;
         const long ctas = (long)pairs * ((total_tiles + tiles_per_chunk - 1) / tiles_per_chunk);
-        const double cost = (double)((ctas + slots - 1) / slots) * (tiles_per_chunk + 3.0);
+        const double cost = (double)((ctas + slots - 1) / slots) * (tiles_per_chunk + 6.0) + 0.05 * c;
         if (cost < best_cost - 1e-9) { best_cost = cost; want_chunks = c; }
     }
     int chunk_keys = ((total_tiles + want_chunks - 1) / want_chunks) * KT;

@@ -20,6 +20,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
                             int n_pages, const int* __restrict__ block_table, int table_stride,
                             const int* __restrict__ positions, const int* __restrict__ row_seq, int n, int nh,
                             int nkv, int hd, int window, float scale, int* status) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     extern __shared__ float q_sh[];                    // [4 warps][hd]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long item = (long)blockIdx.x * 4 + warp;
@@ -100,7 +102,7 @@ static int launch_attention_simt(const void* q, long q_stride, void* out, long o
                                  int nkv, int hd, int window, float scale, int* status, cudaStream_t stream) {
     const long items = (long)n * nh;
     const unsigned blocks = (unsigned)((items + 3) / 4);
-    paged_attention_simt_kernel<T, NDR><<<blocks, 128, 4 * hd * sizeof(float), stream>>>(
+    fb_launch((paged_attention_simt_kernel<T, NDR>), blocks, 128, 4 * hd * sizeof(float), stream, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, page_size, n_pages,
         block_table, table_stride, positions, row_seq, n, nh, nkv, hd, window, scale, status);
     return fb_check_launch("paged_attention_simt");

@@ -31,6 +31,38 @@ int fb_check_launch(const char* what);          // cudaGetLastError -> fb_fail
         if (!(cond)) return fb_fail(-1, __VA_ARGS__);           \
     } while (0)
 
+// ---- launches ---------------------------------------------------------------
+// Kernels of a step run back to back on one stream.  With programmatic dependent launch the next kernel of the
+// stream may be scheduled while this one is still draining: every kernel begins with fb_pdl_launch_dependents()
+// (which lets the kernel after it start being placed once all of this kernel's blocks have begun) and calls
+// fb_pdl_wait() before its first read of what the kernel before it produced and before its first global write.
+// fb_pdl_wait() returns once all earlier kernels of the stream have completed and their writes are visible, so
+// the order of results is that of ordinary stream launches; only launch latency and prologues overlap.
+extern int g_fb_pdl;        // 1: launch with the programmatic-serialization attribute; 0: plain launches
+
+__device__ __forceinline__ void fb_pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void fb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline void fb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                      Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (g_fb_pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);     // an error shows in fb_check_launch()
+}
+
 // ---- typed access -----------------------------------------------------------
 __device__ __forceinline__ float fb_to_float(float v) { return v; }
 __device__ __forceinline__ float fb_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

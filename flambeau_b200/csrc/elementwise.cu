@@ -10,6 +10,8 @@
 template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ x, int H, int V, int* status) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= V) {
@@ -27,7 +29,7 @@ FB_API int fb_embedding(const void* table, int table_dtype, const int* ids, floa
     if (n == 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     FB_DISPATCH_DTYPE(table_dtype, TT,
-        embedding_kernel<TT><<<n, threads, 0, stream>>>((const TT*)table, ids, x, H, V, status));
+        fb_launch((embedding_kernel<TT>), n, threads, 0, stream, (const TT*)table, ids, x, H, V, status));
     return fb_check_launch("embedding");
 }
 
@@ -44,6 +46,8 @@ template <typename TD, typename TW, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_partials,
                                    size_t partial_stride, const TW* __restrict__ w,
                                    TO* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     extern __shared__ float row[];
     __shared__ float red[32];
     const int j = blockIdx.x;
@@ -94,6 +98,8 @@ template <typename TD, typename TW, typename TO, int VPT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_partials,
                                        size_t partial_stride, const TW* __restrict__ w, TO* __restrict__ out,
                                        const int* __restrict__ rows, int H, float eps) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     __shared__ float red[32];
     const int j = blockIdx.x;
     const int r = rows ? rows[j] : j;
@@ -166,7 +172,7 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_partials, size_
         int threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
         const int vpt = (nvec + threads - 1) / threads;
 #define FB_NORM_VEC(V)                                                                                        \
-        add_rmsnorm_vec_kernel<TD, TW, TO, V><<<n_out, threads, 0, stream>>>(x, (const TD*)delta, n_partials,  \
+        fb_launch((add_rmsnorm_vec_kernel<TD, TW, TO, V>), n_out, threads, 0, stream, x, (const TD*)delta, n_partials,  \
             partial_stride, (const TW*)w, (TO*)out, rows, H, eps)
         if (vpt == 1) FB_NORM_VEC(1); else if (vpt == 2) FB_NORM_VEC(2); else FB_NORM_VEC(4);
 #undef FB_NORM_VEC
@@ -179,7 +185,7 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_partials, size_
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    kern<<<n_out, threads, smem, stream>>>(x, (const TD*)delta, n_partials, partial_stride, (const TW*)w,
+    fb_launch((kern), n_out, threads, smem, stream, x, (const TD*)delta, n_partials, partial_stride, (const TW*)w,
                                            (TO*)out, rows, H, eps);
     return fb_check_launch("add_rmsnorm");
 }
@@ -205,6 +211,8 @@ FB_API int fb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_pa
 // ---------------------------------------------------------------------------
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
                                   float* __restrict__ cos_t, float* __restrict__ sin_t, int n, int half) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n * half) return;
     const int t = idx / half, i = idx - t * half;
@@ -219,7 +227,7 @@ FB_API int fb_rope_table(const int* positions, const double* inv_freq, float* co
     FB_REQUIRE(n >= 0 && half > 0, "rope_table: bad sizes n=%d half=%d", n, half);
     if (n == 0) return 0;
     const int total = n * half;
-    rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(positions, inv_freq, cos_t, sin_t, n, half);
+    fb_launch((rope_table_kernel), (total + 255) / 256, 256, 0, stream, positions, inv_freq, cos_t, sin_t, n, half);
     return fb_check_launch("rope_table");
 }
 
@@ -257,6 +265,8 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stri
                                      const int* __restrict__ block_table, int table_stride,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size, int n_pages,
                                      int nh, int nkv, int hd, int write_kv, int* status) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     // grid (tokens, nh + nkv): blocks y < nh rotate one query head; the others rotate one key head into the
     // cache and copy the value head beside it.
     const int t = blockIdx.x, hy = blockIdx.y;
@@ -327,7 +337,7 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, int n_parti
     if (n == 0) return 0;
     FB_REQUIRE(nh + nkv <= 65535, "rope_kv_write: too many heads");
     FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
-        (rope_kv_write_kernel<TI, T><<<dim3(n, nh + (write_kv ? nkv : 0)), hd >= 128 ? 64 : 32, 0, stream>>>((const TI*)q_in, q_in_stride, n_partials, (long)partial_stride, (T*)q_out, q_out_stride,
+        (fb_launch((rope_kv_write_kernel<TI, T>), dim3(n, nh + (write_kv ? nkv : 0)), hd >= 128 ? 64 : 32, 0, stream, (const TI*)q_in, q_in_stride, n_partials, (long)partial_stride, (T*)q_out, q_out_stride,
             (const TI*)k, k_stride, (const TI*)v, v_stride, cos_t, sin_t, half, positions, row_seq, block_table,
             table_stride, (T*)k_pool, (T*)v_pool, page_size, n_pages, nh, nkv, hd, write_kv, status))));
     return fb_check_launch("rope_kv_write");
@@ -340,6 +350,8 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, int n_parti
 template <typename TI, typename T>
 __global__ void silu_mul_kernel(const TI* __restrict__ gu, long stride, int n_partials, long partial_stride,
                                 T* __restrict__ out, int n, int I) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n * I) return;
     const int r = (int)(idx / I), c = (int)(idx - (size_t)r * I);
@@ -353,6 +365,8 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, long stride, int n_pa
 template <typename TI, typename T>
 __global__ void silu_mul_vec_kernel(const TI* __restrict__ gu, long stride, int n_partials, long partial_stride,
                                     T* __restrict__ out, int n, int I) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     const int nvec = I >> 2;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n * nvec) return;
@@ -383,13 +397,13 @@ FB_API int fb_silu_mul(const void* gate_up, long long stride, int in_dtype, int 
     if (vec) {
         const size_t total = (size_t)n * (I / 4);
         FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
-            (silu_mul_vec_kernel<TI, T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+            (fb_launch((silu_mul_vec_kernel<TI, T>), (unsigned)((total + 255) / 256), 256, 0, stream, 
                 (const TI*)gate_up, stride, n_partials, (long)partial_stride, (T*)out, n, I))));
         return fb_check_launch("silu_mul");
     }
     const size_t total = (size_t)n * I;
     FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
-        (silu_mul_kernel<TI, T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+        (fb_launch((silu_mul_kernel<TI, T>), (unsigned)((total + 255) / 256), 256, 0, stream, 
             (const TI*)gate_up, stride, n_partials, (long)partial_stride, (T*)out, n, I))));
     return fb_check_launch("silu_mul");
 }

@@ -6,6 +6,11 @@
 
 static thread_local char g_last_error[1024] = "";
 
+int g_fb_pdl = 1;
+
+// Switches programmatic dependent launch on (1, the default) or off (0) for all later launches.
+FB_API void fb_set_pdl(int on) { g_fb_pdl = on ? 1 : 0; }
+
 int fb_fail(int code, const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);

@@ -13,6 +13,8 @@ template <typename TA, typename TW, typename TO, int BM, int BN, int BK, int TM,
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W, long ldw,
                  TO* __restrict__ out, long ldo, int M, int N, int K) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     constexpr int THREADS = (BM / TM) * (BN / TN);
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
@@ -71,17 +73,17 @@ static int launch_gemm_simt(const void* A, long lda, const void* W, long ldw, vo
     if (M >= 256 && N >= 128) {
         constexpr int BM = 128, BN = 128, BK = 8, TM = 8, TN = 8;
         dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-        gemm_simt_kernel<TA, TW, TO, BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, stream>>>(
+        fb_launch((gemm_simt_kernel<TA, TW, TO, BM, BN, BK, TM, TN>), grid, (BM / TM) * (BN / TN), 0, stream, 
             (const TA*)A, lda, (const TW*)W, ldw, (TO*)out, ldo, M, N, K);
     } else if (M > 16) {
         constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
         dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-        gemm_simt_kernel<TA, TW, TO, BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, stream>>>(
+        fb_launch((gemm_simt_kernel<TA, TW, TO, BM, BN, BK, TM, TN>), grid, (BM / TM) * (BN / TN), 0, stream, 
             (const TA*)A, lda, (const TW*)W, ldw, (TO*)out, ldo, M, N, K);
     } else {
         constexpr int BM = 16, BN = 64, BK = 32, TM = 2, TN = 2;
         dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-        gemm_simt_kernel<TA, TW, TO, BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, stream>>>(
+        fb_launch((gemm_simt_kernel<TA, TW, TO, BM, BN, BK, TM, TN>), grid, (BM / TM) * (BN / TN), 0, stream, 
             (const TA*)A, lda, (const TW*)W, ldw, (TO*)out, ldo, M, N, K);
     }
     return fb_check_launch("gemm_simt");

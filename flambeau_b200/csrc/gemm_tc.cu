@@ -91,6 +91,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * Cfg::STAGES + 1);
     int* last_flag = (int*)(tmem_slot + 1);
 
+    fb_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // token tiles vary fastest, so the CTAs that share a weight tile run together and it is read from DRAM once
     const int n0 = blockIdx.y * BM;              // first output feature of the tile
@@ -122,7 +123,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (elect_one()) {
-            for (int i = 0; i < n_kb; ++i) {
+            // The weights do not depend on the kernel before this one: their first tiles are requested while
+            // that kernel may still be running; the activations are requested after the dependency wait.
+            const int pre = n_kb < Cfg::STAGES ? n_kb : Cfg::STAGES;
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t full = smem_u32(&bars[i]);
+                mbar_expect_tx(full, (uint32_t)Cfg::STAGE_BYTES);
+                tma_load_2d(smem_u32(smem + (size_t)i * Cfg::STAGE_BYTES), &map_w, full, (kb_begin + i) * BK, n0);
+            }
+            fb_pdl_wait();
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(smem_u32(smem + (size_t)i * Cfg::STAGE_BYTES + BM * BK * 2), &map_x, smem_u32(&bars[i]),
+                            (kb_begin + i) * BK, m0);
+            for (int i = pre; i < n_kb; ++i) {
                 const int s = i % Cfg::STAGES;
                 const uint32_t round = (uint32_t)(i / Cfg::STAGES);
                 if (!mbar_wait(smem_u32(&bars[Cfg::STAGES + s]), (round & 1u) ^ 1u, status)) break;
@@ -162,6 +175,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         __syncwarp();
     } else {
         // ---------------- epilogue: warps 2..5, lane quarter = warp % 4 ----------------
+        fb_pdl_wait();                                              // before any global write of this kernel
         const int quarter = warp & 3;
         const int row_local = quarter * 32 + lane;                  // output feature within the tile
         const int n = n0 + row_local;
@@ -286,7 +300,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
         configured = true;
     }
     dim3 grid(tiles_m, tiles_n, splits);
-    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, mx, (TO*)out, ldo, slab_stride, partials, counters, M,
+    fb_launch((kern), grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, partials, counters, M,
                                                           N, K, splits, status);
     return fb_check_launch("gemm_tc");
 }

@@ -20,6 +20,8 @@ __global__ void penalties_kernel(float* __restrict__ logits, long stride, int V,
                                  const int* __restrict__ tokens, const int* __restrict__ counts,
                                  const float* __restrict__ repetition, const float* __restrict__ presence,
                                  const float* __restrict__ frequency, int n_pairs) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_pairs) return;
     const int r = rows[i], tok = tokens[i];
@@ -37,7 +39,7 @@ FB_API int fb_apply_penalties(float* logits, long long stride, int V, const int*
                               const int* counts, const float* repetition, const float* presence,
                               const float* frequency, int n_pairs, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
-    penalties_kernel<<<(n_pairs + 255) / 256, 256, 0, stream>>>(logits, (long)stride, V, rows, tokens, counts,
+    fb_launch((penalties_kernel), (n_pairs + 255) / 256, 256, 0, stream, logits, (long)stride, V, rows, tokens, counts,
                                                                repetition, presence, frequency, n_pairs);
     return fb_check_launch("apply_penalties");
 }
@@ -45,6 +47,8 @@ FB_API int fb_apply_penalties(float* logits, long long stride, int V, const int*
 // (row, token, bias) triples: logits[row][tok] += bias.  Pairs must be unique.
 __global__ void logit_bias_kernel(float* __restrict__ logits, long stride, int V, const int* __restrict__ rows,
                                   const int* __restrict__ tokens, const float* __restrict__ bias, int n) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int tok = tokens[i];
@@ -55,7 +59,7 @@ __global__ void logit_bias_kernel(float* __restrict__ logits, long stride, int V
 FB_API int fb_apply_logit_bias(float* logits, long long stride, int V, const int* rows, const int* tokens,
                                const float* bias, int n, cudaStream_t stream) {
     if (n <= 0) return 0;
-    logit_bias_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, (long)stride, V, rows, tokens, bias, n);
+    fb_launch((logit_bias_kernel), (n + 255) / 256, 256, 0, stream, logits, (long)stride, V, rows, tokens, bias, n);
     return fb_check_launch("apply_logit_bias");
 }
 
@@ -112,6 +116,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long stride, int V, const float* __restrict__ temperature,
               const float* __restrict__ uniform, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ min_p, int* __restrict__ out) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
     __shared__ SampleShared sh;
     const int row = blockIdx.x;
     const float* l = logits + (size_t)row * stride;
@@ -218,7 +224,7 @@ FB_API int fb_sample(const float* logits, long long stride, int n, int V, const 
     FB_REQUIRE(n >= 0 && V > 0 && stride >= V, "sample: bad sizes n=%d V=%d", n, V);
     FB_REQUIRE(!temperature || uniform, "sample: a temperature needs uniform numbers");
     if (n == 0) return 0;
-    sample_kernel<<<n, SAMPLE_THREADS, 0, stream>>>(logits, (long)stride, V, temperature, uniform, top_k, top_p,
+    fb_launch((sample_kernel), n, SAMPLE_THREADS, 0, stream, logits, (long)stride, V, temperature, uniform, top_k, top_p,
                                                     min_p, out);
     return fb_check_launch("sample");
 }

@@ -6,6 +6,7 @@ and nothing of the engine runs.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p, c_double, c_float, c_int, c_longlong, c_void_p
 
 from .build import ensure_built
@@ -19,6 +20,7 @@ STREAM = c_void_p
 _SIGNATURES = {
     "fb_last_error": (c_char_p, []),
     "fb_abi_version": (I, []),
+    "fb_set_pdl": (None, [I]),
     # elementwise.cu
     "fb_embedding": (I, [P, I, P, P, I, I, I, P, STREAM]),
     "fb_add_rmsnorm": (I, [P, P, I, I, L, P, I, P, I, P, I, I, F, STREAM]),
@@ -66,6 +68,8 @@ def lib():
         except OSError as e:
             raise KernelError(f"cannot load the kernel library {path}: {e}") from None
         declare(handle, _SIGNATURES)
+        if os.environ.get("FLAMBEAU_PDL", "1") == "0":
+            handle.fb_set_pdl(0)                # plain stream-ordered launches (for debugging and A/B timing)
         _LIB = handle
     return _LIB
 
