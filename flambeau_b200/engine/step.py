@@ -47,6 +47,20 @@ class StepContext:
         self.max_slabs = 1                  # how many split-K slabs a product may leave for the next kernel to add
         self.pending_slabs = 1
 
+    def open_stream(self, width: int):
+        """Allocate what the blocks of a step share: the float32 residual stream (returned), the buffer for
+        normalised rows (ctx.normed) and the float32 output of mixers and feed-forwards (ctx.delta).  For steps
+        of few rows (decoding) a part's last product may leave its split-K shares in up to ctx.max_slabs slabs
+        (ctx.delta_slabs, ctx.delta being the first), which the next norm adds."""
+        n = self.n_tokens
+        x = self.step_alloc((n, width), torch.float32)
+        self.normed = self.step_alloc((n, width), self.runtime.dtype)
+        self.max_slabs = 16 if n <= 16 else (8 if n <= 64 else 1)
+        self.delta_slabs = self.step_alloc((self.max_slabs, n, width), torch.float32)
+        self.delta = self.delta_slabs[0]
+        self.pending_slabs = 1
+        return x
+
     def step_alloc(self, shape, dtype):
         """Scratch that lives until the step ends (ctx.ws allocations end with their scope)."""
         return self.engine.step_ws.alloc(shape, dtype)
@@ -80,6 +94,7 @@ class Engine:
         self.steps_run = 0
         self.last_batch: Optional[StepBatch] = None
         self._graphs: dict = {}            # step shape -> captured graph (or the count of eager runs so far)
+        self.use_graphs = bool(options.cuda_graphs) and model.graph_safe()
         self.graph_replays = 0
 
     # ---- construction ----------------------------------------------------------
@@ -123,7 +138,7 @@ class Engine:
         (tokens, positions, block tables, wanted rows) lives in the descriptor buffers, whose addresses are
         fixed.  The key holds what is baked into kernel arguments: the number of sequences and wanted rows,
         and the bucket of the longest context (it sets the split of the attention's key range)."""
-        if not self.options.cuda_graphs or batch.max_q_len != 1:
+        if not self.use_graphs or batch.max_q_len != 1:
             return None
         if batch.n_out not in (0, batch.n_seqs):
             return None
@@ -139,7 +154,14 @@ class Engine:
             if entry < 1:                               # first time: run eagerly (lazy allocations, attributes)
                 self._graphs[key] = entry + 1
                 return self._forward(batch)
-            entry = self._capture(batch, key)
+            try:
+                entry = self._capture(batch, key)
+            except Exception as exc:                    # a part that cannot be captured after all: run eagerly
+                import warnings
+                warnings.warn(f"CUDA graph capture failed ({exc}); steps run eagerly from now on")
+                self.use_graphs = False
+                torch.cuda.synchronize()
+                return self._forward(batch)
         graph, logits, _keep, n_kernels = entry
         graph.replay()
         library.LAUNCHES[0] += n_kernels                # the launches the graph replays

@@ -44,6 +44,9 @@ class DecoderModel:
         for p in self.parts():
             p.bind(tensors)
 
+    def graph_safe(self) -> bool:
+        return all(p.all_graph_safe() for p in self.parts())
+
     def step_weight_bytes(self) -> int:
         """Bytes of weights one step reads: every layer call's weights once, the final norm and the head."""
         total = self.final_norm.weight_bytes() + self.head.weight_bytes()
@@ -65,14 +68,7 @@ class DecoderModel:
         """Runs the rows of ctx.batch; returns float32 logits [n_out, vocab] (None when nothing is wanted)."""
         rt, b = self.runtime, ctx.batch
         n = b.n_tokens
-        x = ctx.step_alloc((n, self.hidden_size), torch.float32)
-        ctx.normed = ctx.step_alloc((n, self.hidden_size), rt.dtype)
-        # mixer / feed-forward outputs stay float32 until they are added; for steps of few rows (decoding) they
-        # may arrive as split-K shares in up to ctx.max_slabs slabs, which the next norm adds
-        ctx.max_slabs = 16 if n <= 16 else (8 if n <= 64 else 1)
-        ctx.delta_slabs = ctx.step_alloc((ctx.max_slabs, n, self.hidden_size), torch.float32)
-        ctx.delta = ctx.delta_slabs[0]
-        ctx.pending_slabs = 1
+        x = ctx.open_stream(self.hidden_size)
         self.embedding.forward(ctx, b.token_ids[:n], x)
         stream = ResidualStream(x)
         for ci, call in enumerate(self.order):

@@ -20,6 +20,7 @@ class PagedAttention(Mixer):
     :355-399 (rotary), :418-420 (scale), :1261-1302 (output projection).
 
     Sizes are parameters: `num_heads * head_dim` need not equal `width`."""
+    graph_safe = True
 
     def __init__(self, runtime=None, prefix="", *, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  window: int = 0, position: PartSpec | None = None, scale: float | None = None,

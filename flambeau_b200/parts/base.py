@@ -51,6 +51,10 @@ class StateRequirement:
 
 class Part:
     category = "part"
+    # A part whose work in a step is kernels on the current stream with arguments that depend only on the step's
+    # shape may be captured in a CUDA graph and replayed.  A part that reads the batch on the host, copies from
+    # host memory or allocates must leave this False; the engine then runs steps with it eagerly.
+    graph_safe = False
 
     def __init__(self, runtime=None, prefix: str = ""):
         self.runtime = runtime
@@ -86,6 +90,9 @@ class Part:
 
     def own_weights(self) -> list:
         return []
+
+    def all_graph_safe(self) -> bool:
+        return bool(self.graph_safe) and all(c.all_graph_safe() for c in self.children())
 
 
 class Mixer(Part):

@@ -19,6 +19,7 @@ class ResidualStream:
 class PreNormBlock(Part):
     """x = x + mixer(norm1(x)); x = x + feed_forward(norm2(x))
     (crates/models/qwen35-v2/src/model.rs:25-42)."""
+    graph_safe = True
     category = "block"
 
     def __init__(self, runtime=None, prefix="", *, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,

@@ -9,6 +9,7 @@ from .spec import register_part
 
 class TokenEmbedding(Part):
     """x[t,:] = E[token[t],:], no scale (crates/forward/src/core/composites/embed.rs:26-62)."""
+    graph_safe = True
     category = "embedding"
 
     def __init__(self, runtime=None, prefix="", *, vocab: int, width: int, init_std: float = 0.02):
@@ -33,6 +34,7 @@ class LMHead(Part):
     """logits = h W^T in float32, for the wanted rows only; a tied head reuses
     the embedding table (crates/forward/src/core/composites/output_head.rs:90-132;
     crates/models/qwen35-v2/src/loader.rs:219-223)."""
+    graph_safe = True
     category = "head"
 
     def __init__(self, runtime=None, prefix="", *, vocab: int, width: int, tied_to: str | None = None,

@@ -13,6 +13,7 @@ class GatedMLP(FeedForward):
     """d = (silu(h Wg^T) * (h Wu^T)) Wd^T, no bias, no routing
     (crates/forward/src/core/composites/dense_ffn.rs:116-186).  Gate and up
     weights are stacked at load so one product yields both."""
+    graph_safe = True
 
     def __init__(self, runtime=None, prefix="", *, width: int, inner: int, activation: str = "silu",
                  init_std: float = 0.02):

@@ -10,6 +10,7 @@ class RMSNorm(Norm):
     """y = v * w / sqrt(mean(v^2) + eps) with v = x + delta; plain weight, no 1+w
     (crates/kernels-hip/src/kernels/rmsnorm_f16.cu:41-85).  The sum, the mean
     and the product are float32; the stream x stays float32."""
+    graph_safe = True
 
     def __init__(self, runtime=None, prefix="", *, width: int, eps: float, init=("one_plus_normal", 0.02)):
         super().__init__(runtime, prefix)

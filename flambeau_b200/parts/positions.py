@@ -14,6 +14,7 @@ class RotaryHalf(PositionEncoding):
     rope_neox_partial_f16.cu:39-52).  `rotary_dim` < head_dim leaves the tail
     of the head untouched.  The cos/sin tables of a step are computed once and
     shared by every layer that uses equal parameters."""
+    graph_safe = True
 
     fused_with_cache_write = True      # the attention mixer may hand the tables to its fused kernel
 

@@ -1,0 +1,137 @@
+"""Generation through the Python entry point and the command line, long decoding, and the first tokens of a
+sequence, against the plain implementation."""
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_mistral as pm
+import tiny
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module", params=[("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("B", "bfloat16")],
+                ids=lambda p: f"{p[0]}-{p[1]}")
+def model(request, tmp_path_factory):
+    name, dtype = request.param
+    cfg = tiny.CONFIGS[name]
+    folder = tiny.make_folder(tmp_path_factory.mktemp(f"gen{name}{dtype}"), cfg, seed=31, dtype=dtype,
+                              sharp=0.2 if dtype == "float32" else 0.1)
+    pcfg, W = pm.read_model_folder(folder)
+    return dict(name=name, dtype=dtype, cfg=cfg, folder=folder, pcfg=pcfg, W=W)
+
+
+def check_greedy(model, prompts, outs, n_new):
+    """Each generated token must be the plain implementation's argmax given what came before it (in bfloat16:
+    within the tolerance of the best logit, since near-ties may fall either way)."""
+    for prompt, out in zip(prompts, outs):
+        assert len(out) == n_new
+        toks = list(prompt)
+        for t in out:
+            logits = pm.forward_logits(model["pcfg"], model["W"], toks)[-1]
+            if model["dtype"] == "float32":
+                assert t == pm.argmax_lowest(logits), "greedy token differs from the plain implementation"
+            else:
+                gap = float(logits.max() - logits[t]) / float(logits.abs().max())
+                assert gap <= 2 * tiny.TOL["bfloat16"], f"token {t} is {gap:.3f} of the scale below the best logit"
+            toks.append(t)
+
+
+def test_greedy_generation_matches(model):
+    from flambeau_b200 import generate
+    lengths = [5, 23, 40] if model["name"] == "A" else [1, 7, 31, 64]
+    prompts = list(tiny.random_requests(model["cfg"], lengths, seed=8).values())
+    outs = generate(model["folder"], prompts, max_tokens=8, temperature=0.0, dtype=model["dtype"],
+                    prefill_chunk_tokens=8, prefill_ubatch=24, inflight_slots=4)
+    check_greedy(model, prompts, outs, 8)
+
+
+def test_generation_under_page_pressure_gives_the_same_tokens(model):
+    """So few pages that requests are preempted and fed again: the tokens must not change."""
+    from flambeau_b200.engine.generate import Generator
+    from flambeau_b200.engine.step import Engine, EngineOptions
+    from flambeau_b200.sampling.params import SamplingParams
+    if model["dtype"] != "float32":
+        pytest.skip("token-for-token equality is a float32 property")
+    prompts = list(tiny.random_requests(model["cfg"], [20, 33, 18, 27], seed=9).values())
+    params = SamplingParams(max_tokens=30)
+    roomy = Engine.from_folder(model["folder"], EngineOptions(dtype="float32", cache_tokens=512, max_requests=4,
+                                                              max_step_tokens=64, max_seq_len=128))
+    want = Generator(roomy, prefill_chunk_tokens=16).generate(prompts, params)
+    tight = Engine.from_folder(model["folder"], EngineOptions(dtype="float32", cache_tokens=112, max_requests=4,
+                                                              max_step_tokens=64, max_seq_len=128))
+    gen = Generator(tight, prefill_chunk_tokens=16)
+    got = gen.generate(prompts, params)
+    assert got == want
+    sched = gen.last_scheduler
+    if model["cfg"]["sliding_window"] is None:
+        assert sum(r.preemptions for r in sched.finished) > 0, "the pool was meant to be too small"
+    assert all(r.finish_reason == "length" for r in sched.finished)
+    tight.cache.check_invariants()
+    assert not tight.cache.requests
+
+
+def test_temperature_sampling_is_seeded_and_independent_of_the_batch(model):
+    from flambeau_b200 import generate
+    prompts = list(tiny.random_requests(model["cfg"], [6, 19, 11], seed=10).values())
+    kw = dict(max_tokens=6, temperature=0.8, seed=5, dtype=model["dtype"], prefill_chunk_tokens=8)
+    a = generate(model["folder"], prompts, **kw)
+    b = generate(model["folder"], prompts, **kw)
+    assert a == b, "same seed, same tokens"
+    c = generate(model["folder"], prompts, **{**kw, "seed": 6})
+    assert c != a
+    if model["dtype"] == "float32":
+        alone = generate(model["folder"], [prompts[1]], **{**kw, "seed": 6})      # request 1 of seed 5 draws with 5+1
+        assert alone[0] == a[1], "a request's draws do not depend on what shares its batches"
+    d = generate(model["folder"], prompts, **{**kw, "top_k": 1})
+    g = generate(model["folder"], prompts, **{**kw, "temperature": 0.0})
+    assert d == g, "top_k = 1 is greedy"
+
+
+def test_long_decoding_and_first_tokens(model, tmp_path):
+    """One token a step from the very first token on, for far longer than the window and several pages."""
+    from flambeau_b200.engine.step import Engine, EngineOptions
+    from flambeau_b200.engine.trace import replay
+    reqs = tiny.random_requests(model["cfg"], [150], seed=12)
+    sched = tiny.schedule_tail(reqs, tail=149)                    # position 0 alone, then 149 single tokens
+    engine = Engine.from_folder(model["folder"], EngineOptions(dtype=model["dtype"], cache_tokens=192, max_requests=2,
+                                                               max_step_tokens=16, max_seq_len=192))
+    replay(engine, sched.lines(), tmp_path)
+    assert engine.graph_replays > 100, "single-token steps are replayed from a captured graph"
+    want = {rid: pm.forward_logits(model["pcfg"], model["W"], toks) for rid, toks in reqs.items()}
+    got = tiny.read_rows(tmp_path, sched, model["cfg"]["vocab_size"])
+    tiny.compare_rows(got, want, tiny.TOL[model["dtype"]], f"long decode {model['name']} {model['dtype']}")
+
+
+def test_command_line_infer(model):
+    prompts = list(tiny.random_requests(model["cfg"], [9, 4], seed=13).values())
+    cmd = [sys.executable, str(ROOT / "bin" / "flambeau"), "infer", "--model", str(model["folder"]), "--max-tokens", "5",
+           "--dtype", model["dtype"]]
+    for p in prompts:
+        cmd += ["--prompt", ",".join(map(str, p))]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    outs = [[int(t) for t in line.split(",")] for line in proc.stdout.strip().splitlines()]
+    check_greedy(model, prompts, outs, 5)
+
+
+def test_errors_are_raised_before_anything_runs(model):
+    from flambeau_b200.cache.pages import OutOfPages
+    from flambeau_b200.engine.batch import BatchError
+    from flambeau_b200.engine.step import Engine, EngineOptions
+    e = Engine.from_folder(model["folder"], EngineOptions(dtype=model["dtype"], cache_tokens=32, max_requests=2,
+                                                          max_step_tokens=64, max_seq_len=64))
+    with pytest.raises(OutOfPages):
+        e.step([("a", list(range(40)), [])])
+    assert not e.cache.requests and e.cache.free_pages() == [2]
+    with pytest.raises(BatchError):
+        e.step([("a", [model["cfg"]["vocab_size"]], [0])])
+    with pytest.raises(BatchError):
+        e.step([("a", [1, 2], [2])])
+    logits = e.step([("a", [1, 2, 3], [2])], end=["a"])
+    assert logits.shape == (1, model["cfg"]["vocab_size"]) and torch.isfinite(logits).all()
+    assert not e.cache.requests

@@ -1,0 +1,248 @@
+"""The row-wise kernels and the sampler alone against plain torch float64 formulas, at sizes other than the
+engine's (widths that are no power of two, odd row counts, every dtype combination the engine can meet)."""
+import math
+
+import pytest
+import torch
+
+import plain_mistral as pm
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DT = {"f": torch.float32, "b": torch.bfloat16}
+
+
+def close(got, want, tol):
+    err = float((got.double().cpu() - want.double().cpu()).abs().max())
+    scale = float(want.double().abs().max()) or 1.0
+    assert err / scale < tol, f"error {err / scale:.3e} of scale"
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("V,H,dt", [(11, 7, "f"), (300, 96, "b"), (1000, 4100, "b")])
+def test_embedding(V, H, dt):
+    from flambeau_b200.kernels import ops
+    table = torch.randn(V, H, device=DEV).to(DT[dt])
+    ids = torch.randint(0, V, (13,), dtype=torch.int32, device=DEV)
+    x = torch.full((13, H), float("nan"), device=DEV)
+    st = status()
+    ops.embedding(table, ids, x, st)
+    assert torch.equal(x, table[ids.long()].float()) and int(st.item()) == 0
+    bad = ids.clone()
+    bad[3] = V
+    ops.embedding(table, bad, x, st)
+    assert int(st.item()) == 1, "an id outside the table must be flagged"
+
+
+@pytest.mark.parametrize("H", [8, 100, 96, 4096, 5120, 6000, 20000])
+@pytest.mark.parametrize("dd,wd,od", ["fff", "fbb", "ffb", "bbb"])
+def test_add_rms_norm(H, dd, wd, od):
+    from flambeau_b200.kernels import ops
+    n, eps = 5, 1e-5
+    x = torch.randn(n, H, device=DEV)
+    delta = (torch.randn(n, H, device=DEV) * 0.5).to(DT[dd])
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).to(DT[wd])
+    out = torch.empty(n, H, device=DEV, dtype=DT[od])
+    x0 = x.clone()
+    ops.add_rms_norm(x, delta, w, eps, out)
+    v = x0.double() + delta.double()
+    close(x, v, 1e-6)                                             # the stream holds the sum
+    close(out, pm.rms_norm(v, w.double(), eps), 2e-6 if od == "f" else 6e-3)
+    # without a delta the stream is untouched
+    x1 = x.clone()
+    ops.add_rms_norm(x, None, w, eps, out)
+    assert torch.equal(x, x1)
+    close(out, pm.rms_norm(x1.double(), w.double(), eps), 2e-6 if od == "f" else 6e-3)
+
+
+def test_add_rms_norm_rows_and_slabs():
+    from flambeau_b200.kernels import ops
+    n, H, eps, P = 9, 200, 1e-6, 7
+    x = torch.randn(n, H, device=DEV)
+    slabs = torch.randn(P, n, H, device=DEV)
+    w = torch.randn(H, device=DEV)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, H, device=DEV)
+    x0 = x.clone()
+    ops.add_rms_norm(x, slabs[0], w, eps, out, rows=rows, n_partials=5, partial_stride=slabs.stride(0))
+    assert torch.equal(x, x0), "with a row list the stream is read only"
+    v = (x0.double() + slabs[:5].double().sum(0))[rows.long()]
+    close(out, pm.rms_norm(v, w.double(), eps), 3e-6)
+    out_all = torch.empty(n, H, device=DEV)
+    ops.add_rms_norm(x, slabs[0], w, eps, out_all, n_partials=P, partial_stride=slabs.stride(0))
+    close(x, x0.double() + slabs.double().sum(0), 2e-6)
+
+
+@pytest.mark.parametrize("half,theta", [(8, 1e4), (12, 1e6), (64, 1e4)])
+def test_rope_table_is_right_at_far_positions(half, theta):
+    from flambeau_b200.kernels import ops
+    pos = torch.tensor([0, 1, 17, 4095, 8191, 131071, 1000003], dtype=torch.int32, device=DEV)
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / (2 * half))
+    cos = torch.empty(len(pos), half, device=DEV)
+    sin = torch.empty(len(pos), half, device=DEV)
+    ops.rope_table(pos, inv.to(DEV), cos, sin)
+    ang = pos.double().cpu()[:, None] * inv[None, :]
+    assert float((cos.cpu().double() - torch.cos(ang)).abs().max()) < 1e-6
+    assert float((sin.cpu().double() - torch.sin(ang)).abs().max()) < 1e-6
+
+
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (8, 1, 24, 24), (3, 3, 40, 16), (32, 8, 128, 128)])
+@pytest.mark.parametrize("dt_in,dt_out,slabs", [("f", "f", 1), ("f", "b", 1), ("f", "b", 6), ("b", "b", 1)])
+def test_rope_and_cache_write(nh, nkv, hd, rot, dt_in, dt_out, slabs):
+    from flambeau_b200.kernels import ops
+    n, ps, n_pages, theta = 11, 8, 9, 1e4
+    half = rot // 2
+    g = torch.Generator(device=DEV).manual_seed(nh + hd)
+    width = (nh + 2 * nkv) * hd
+    parts = (torch.randn(slabs, n, width, device=DEV, generator=g)).to(DT[dt_in])
+    whole = parts.double().sum(0)
+    positions = torch.tensor([3, 4, 5, 6, 7, 8, 40, 0, 1, 2, 63], dtype=torch.int32, device=DEV)
+    row_seq = torch.tensor([0] * 6 + [1] + [2] * 3 + [1], dtype=torch.int32, device=DEV)
+    table = torch.full((3, 8), -1, dtype=torch.int32, device=DEV)
+    table[0, 0], table[0, 1] = 5, 2
+    table[1, 5], table[1, 7] = 0, 7
+    table[2, 0] = 3
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / rot)
+    cos = torch.empty(n, half, device=DEV)
+    sin = torch.empty(n, half, device=DEV)
+    ops.rope_table(positions, inv.to(DEV), cos, sin)
+    kp = torch.zeros(n_pages, nkv, ps, hd, device=DEV, dtype=DT[dt_out])
+    vp = torch.zeros_like(kp)
+    q_out = torch.empty(n, nh * hd, device=DEV, dtype=DT[dt_out])
+    st = status()
+    qkv = parts[0]
+    ops.rope_kv_write(qkv[:, :nh * hd], q_out, qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:], cos, sin,
+                      half, positions, row_seq, table, kp, vp, ps, nh, nkv, hd, True, st,
+                      n_partials=slabs, partial_stride=parts.stride(0))
+    assert int(st.item()) == 0
+    q = whole[:, :nh * hd].reshape(n, nh, hd)
+    k = whole[:, nh * hd:(nh + nkv) * hd].reshape(n, nkv, hd)
+    v = whole[:, (nh + nkv) * hd:].reshape(n, nkv, hd)
+    tol = 2e-6 if dt_out == "f" else 5e-3
+    close(q_out.reshape(n, nh, hd), pm.rope_split_half(q.cpu(), positions.cpu(), theta, rot), tol)
+    k_rot = pm.rope_split_half(k.cpu(), positions.cpu(), theta, rot)
+    for r in range(n):
+        p, s = int(positions[r]), int(row_seq[r])
+        page = int(table[s, p // ps])
+        close(kp[page, :, p % ps], k_rot[r], tol)
+        close(vp[page, :, p % ps], v[r].cpu(), tol)
+    written = sum(1 for _ in range(n))
+    assert int((kp.float().abs().sum(dim=(1, 3)) > 0).sum()) == written, "only the rows of the step are written"
+
+
+def test_cache_write_flags_a_missing_page():
+    from flambeau_b200.kernels import ops
+    qkv = torch.randn(2, 4 * 16, device=DEV)
+    q_out = torch.empty(2, 2 * 16, device=DEV)
+    kp = torch.zeros(2, 1, 8, 16, device=DEV)
+    table = torch.full((1, 4), -1, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    st = status()
+    ops.rope_kv_write(qkv[:, :32], q_out, qkv[:, 32:48], qkv[:, 48:], None, None, 0, pos, torch.zeros_like(pos), table,
+                      kp, torch.zeros_like(kp), 8, 2, 1, 16, True, st)
+    assert int(st.item()) == 2
+
+
+@pytest.mark.parametrize("n,I", [(1, 7), (5, 160), (3, 14336), (2, 1002)])
+@pytest.mark.parametrize("di,do,slabs", [("f", "f", 1), ("b", "b", 1), ("f", "b", 5), ("f", "b", 9)])
+def test_silu_mul(n, I, di, do, slabs):
+    from flambeau_b200.kernels import ops
+    parts = torch.randn(slabs, n, 2 * I, device=DEV).to(DT[di])
+    out = torch.empty(n, I, device=DEV, dtype=DT[do])
+    ops.silu_mul(parts[0], out, n_partials=slabs, partial_stride=parts.stride(0))
+    gu = parts.double().sum(0)
+    g, u = gu[:, :I], gu[:, I:]
+    close(out, g / (1 + torch.exp(-g)) * u, 3e-6 if do == "f" else 6e-3)
+
+
+# ---- sampler -------------------------------------------------------------------------------------------------
+
+def test_argmax_takes_the_lowest_index_of_a_tie():
+    from flambeau_b200.kernels import ops
+    V = 70001
+    logits = torch.randn(4, V, device=DEV)
+    logits[0, 123] = logits[0, 60000] = 50.0
+    logits[1, :] = 1.0
+    logits[2, V - 1] = 99.0
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out)
+    want = [pm.argmax_lowest(r) for r in logits.cpu()]
+    assert out.tolist() == want and want[0] == 123 and want[1] == 0 and want[2] == V - 1
+
+
+@pytest.mark.parametrize("V", [320, 32000, 131072 + 5])
+def test_temperature_draw_is_the_inverse_cdf(V):
+    from flambeau_b200.kernels import ops
+    n = 16
+    g = torch.Generator(device=DEV).manual_seed(V)
+    logits = torch.randn(n, V, device=DEV, generator=g) * 3
+    temp = torch.tensor([0.0, 0.5, 0.8, 1.0, 1.5, 0.3, 2.0, 1.0] * 2, device=DEV)
+    u = torch.tensor([0.0, 0.999, 0.5, 0.25, 0.75, 0.1, 0.9, 0.33] * 2, device=DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out, temperature=temp, uniform=u)
+    for r in range(n):
+        row = logits[r].cpu()
+        if float(temp[r]) <= 0:
+            assert int(out[r]) == pm.argmax_lowest(row)
+            continue
+        p = pm.softmax_temperature(row, float(temp[r]))
+        cdf = torch.cumsum(p, 0)
+        tok = int(out[r])
+        lo = float(cdf[tok - 1]) if tok else 0.0
+        # float32 sums on the device: the drawn token's CDF interval must hold u within a small slack
+        assert lo - 1e-4 <= float(u[r]) <= float(cdf[tok]) + 1e-4, f"row {r}: token {tok} does not hold u"
+
+
+def test_filters_keep_the_reference_support():
+    from flambeau_b200.kernels import ops
+    V, n = 5000, 6
+    g = torch.Generator(device=DEV).manual_seed(1)
+    logits = torch.randn(n, V, device=DEV, generator=g) * 2.5
+    cfgs = [dict(top_k=5), dict(top_p=0.6), dict(min_p=0.2), dict(top_k=50, top_p=0.9), dict(top_k=3, min_p=0.5),
+            dict(top_p=0.3, min_p=0.05)]
+    T = 0.9
+    for trial in range(40):
+        u = torch.rand(n, device=DEV, generator=g)
+        out = torch.empty(n, dtype=torch.int32, device=DEV)
+        ops.sample(logits, out, temperature=torch.full((n,), T, device=DEV), uniform=u,
+                   top_k=torch.tensor([c.get("top_k", 0) for c in cfgs], dtype=torch.int32, device=DEV),
+                   top_p=torch.tensor([c.get("top_p", 0.0) for c in cfgs], device=DEV),
+                   min_p=torch.tensor([c.get("min_p", 0.0) for c in cfgs], device=DEV))
+        for r, c in enumerate(cfgs):
+            probs = pm.softmax_temperature(logits[r].cpu(), T)
+            support = set(pm.filtered_support(probs, **c))
+            assert int(out[r]) in support, f"{c}: token {int(out[r])} is outside the kept set of {len(support)}"
+    # a draw with u close to 0 returns the lowest kept index, close to 1 the highest
+    probs = pm.softmax_temperature(logits[0].cpu(), T)
+    support = sorted(pm.filtered_support(probs, top_k=5))
+    for uval, want in ((0.0, support[0]), (0.99999, support[-1])):
+        out = torch.empty(1, dtype=torch.int32, device=DEV)
+        ops.sample(logits[:1], out, temperature=torch.tensor([T], device=DEV), uniform=torch.tensor([uval], device=DEV),
+                   top_k=torch.tensor([5], dtype=torch.int32, device=DEV), top_p=torch.zeros(1, device=DEV),
+                   min_p=torch.zeros(1, device=DEV))
+        assert int(out[0]) == want
+
+
+def test_penalties_and_bias():
+    from flambeau_b200.kernels import ops
+    V = 100
+    logits = torch.randn(2, V, device=DEV)
+    before = logits.clone().cpu()
+    history = [[3, 3, 7, 99], [5]]
+    rows, toks, cnts = [], [], []
+    for r, h in enumerate(history):
+        for t in sorted(set(h)):
+            rows.append(r); toks.append(t); cnts.append(h.count(t))
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    f32 = lambda v: torch.tensor(v, dtype=torch.float32, device=DEV)
+    ops.apply_penalties(logits, i32(rows), i32(toks), i32(cnts), f32([1.3, 1.0]), f32([0.4, 0.0]), f32([0.1, 0.7]))
+    want0 = pm.apply_penalties(before[0], history[0], repetition=1.3, presence=0.4, frequency=0.1)
+    want1 = pm.apply_penalties(before[1], history[1], repetition=1.0, presence=0.0, frequency=0.7)
+    close(logits[0], want0, 1e-6)
+    close(logits[1], want1, 1e-6)
+    ops.apply_logit_bias(logits, i32([0, 1]), i32([10, 20]), f32([5.0, -2.0]))
+    assert math.isclose(float(logits[0, 10]), float(want0[10]) + 5.0, rel_tol=1e-6)
+    assert math.isclose(float(logits[1, 20]), float(want1[20]) - 2.0, rel_tol=1e-6)
