@@ -27,6 +27,8 @@
 
 #include "tensor_map.cuh"
 
+#include <mutex>
+
 namespace {
 
 constexpr int BM = 128;          // output features per CTA (UMMA M)
@@ -352,4 +354,87 @@ FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw
     }
 #undef FB_TC_CASE
     return fb_fail(-1, "gemm_tc: unknown output dtype code %d", o_dtype);
+}
+
+// ---------------------------------------------------------------------------
+// The product for callers that must not allocate (declared and described in no_alloc.h; no counterpart in the
+// reference).  Same kernel and launcher as fb_gemm_tc in its meet-in-scratch form; the scratch is this array.
+// ---------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// Partial tiles (float32) followed by one arrival counter per output tile.  Held by every GPU that loads the
+// library until the process exits.  In host code this name is only a handle for cudaGetSymbolAddress: it is not
+// a device address and must never be passed to a kernel.
+static __device__ __align__(256) unsigned char fb_noalloc_scratch[FB_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+void* g_noalloc_base[NOALLOC_MAX_DEVICES] = {};      // device address of the array, per device ordinal
+std::mutex g_noalloc_mu;
+
+// Once per device, with that device current: the array's device address.
+int noalloc_scratch(unsigned char** base) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fb_fail(-2, "gemm_tc_noalloc: cudaGetDevice failed: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES)
+        return fb_fail(-1, "gemm_tc_noalloc: device ordinal %d is outside [0, %d)", dev, NOALLOC_MAX_DEVICES);
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_base[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, fb_noalloc_scratch);
+        if (e != cudaSuccess || !p)
+            return fb_fail(-2, "gemm_tc_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev,
+                           cudaGetErrorString(e));
+        g_noalloc_base[dev] = p;
+    }
+    *base = (unsigned char*)g_noalloc_base[dev];
+    return 0;
+}
+}  // namespace
+
+int fb_gemm_tc_noalloc(const void* X, long long lda, const void* W, long long ldw, void* out, int o_dtype,
+                       long long ldo, int M, int N, int K, int* status, cudaStream_t stream) {
+    FB_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc_noalloc: bad sizes M=%d N=%d K=%d", M, N, K);
+    FB_REQUIRE(M <= FB_NOALLOC_MAX_ROWS, "gemm_tc_noalloc: %d rows exceed the maximum of %d", M, FB_NOALLOC_MAX_ROWS);
+    const int tiles_n = (N + BM - 1) / BM;
+    FB_REQUIRE(tiles_n <= FB_NOALLOC_MAX_TILES, "gemm_tc_noalloc: %d output features exceed the maximum of %d", N,
+               FB_NOALLOC_MAX_TILES * BM);
+    FB_REQUIRE(lda >= K && ldw >= K && ldo >= N, "gemm_tc_noalloc: a row stride is shorter than its row");
+    FB_REQUIRE(lda % 8 == 0 && ldw % 8 == 0, "gemm_tc_noalloc: row strides must be multiples of 8 elements");
+    FB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tc_noalloc: operands must be 16-byte aligned");
+    FB_REQUIRE(status != nullptr, "gemm_tc_noalloc: the status word is missing");
+    if (M == 0) return 0;
+    unsigned char* base = nullptr;
+    int rc = noalloc_scratch(&base);
+    if (rc) return rc;
+    float* partials = (float*)base;
+    int* counters = (int*)(base + FB_NOALLOC_PARTIAL_BYTES);
+    // the array keeps the last call's contents: the counters must start at zero (stream-ordered, no allocation)
+    cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)FB_NOALLOC_MAX_TILES * sizeof(int), stream);
+    if (e != cudaSuccess) return fb_fail(-2, "gemm_tc_noalloc: clearing the counters failed: %s", cudaGetErrorString(e));
+    const int BN = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+    CUtensorMap mw, mx;
+    rc = fb_tensor_map_bf16_uncached(&mw, W, N, K, (long)ldw, BK, BM);
+    if (rc) return rc;
+    rc = fb_tensor_map_bf16_uncached(&mx, X, M, K, (long)lda, BK, BN);
+    if (rc) return rc;
+    const long partial_floats = (long)(FB_NOALLOC_PARTIAL_BYTES / sizeof(float));
+#define FB_NA_CASE(BN_)                                                                                          \
+    case BN_:                                                                                                    \
+        if (o_dtype == FB_F32)                                                                                   \
+            return launch_tc<BN_, float>(mw, mx, out, (long)ldo, 0, 1, nullptr, partials, partial_floats,        \
+                                         counters, FB_NOALLOC_MAX_TILES, M, N, K, 0, status, stream);            \
+        else if (o_dtype == FB_BF16)                                                                             \
+            return launch_tc<BN_, __nv_bfloat16>(mw, mx, out, (long)ldo, 0, 1, nullptr, partials,                \
+                                                 partial_floats, counters, FB_NOALLOC_MAX_TILES, M, N, K, 0,     \
+                                                 status, stream);                                                \
+        break;
+    switch (BN) {
+        FB_NA_CASE(16)
+        FB_NA_CASE(32)
+        FB_NA_CASE(64)
+    }
+#undef FB_NA_CASE
+    return fb_fail(-1, "gemm_tc_noalloc: unknown output dtype code %d", o_dtype);
 }

@@ -69,3 +69,22 @@ int fb_tensor_map_bf16(CUtensorMap* out, const void* ptr, long rows, long cols, 
     cache.emplace(key, *out);
     return 0;
 }
+
+// The same encoding without the cache: nothing is kept and no host memory is taken, for callers that must not
+// allocate.  (The encoder writes the 128-byte map into *out and touches nothing else.)
+int fb_tensor_map_bf16_uncached(CUtensorMap* out, const void* ptr, long rows, long cols, long ld, int box_cols,
+                                int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fb_fail(-3, "tensor map: the driver does not provide cuTensorMapEncodeTiled");
+    if (box_cols * 2 != 128 || box_rows < 1 || box_rows > 256)
+        return fb_fail(-3, "tensor map: box of %d x %d elements is not supported", box_rows, box_cols);
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fb_fail(-3, "tensor map: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}

@@ -6,3 +6,7 @@
 // A [rows, cols] bfloat16 matrix with row stride `ld` elements, fetched in boxes of box_rows x box_cols elements
 // with the 128-byte swizzle (box_cols * 2 bytes must be 128).  Returns 0, or a negative code after fb_fail().
 int fb_tensor_map_bf16(CUtensorMap* out, const void* ptr, long rows, long cols, long ld, int box_cols, int box_rows);
+
+// As above, but nothing is cached and no host memory is taken.
+int fb_tensor_map_bf16_uncached(CUtensorMap* out, const void* ptr, long rows, long cols, long ld, int box_cols,
+                                int box_rows);
