@@ -76,40 +76,61 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 template <int BN> struct TileCfg {
     static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
     static constexpr int STAGES = BN == 16 ? 6 : BN == 32 ? 5 : BN == 64 ? 4 : BN == 128 ? 3 : 4;
-    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int ACC_COLS = BN < 32 ? 32 : BN;      // tensor-memory columns of one accumulator
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;          // two accumulators: the epilogue of one unit of work
+                                                            // overlaps the products of the next
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
+// One unit of work: output tile (m_tile, n_tile) and one share `split` of its K range.  Token tiles vary
+// fastest, so CTAs that run together share weight tiles through L2; shares of K vary slowest.
+struct Unit { int m0, n0, split, kb_begin, n_kb, tile_id; };
+__device__ __forceinline__ Unit unit_of(int u, int tiles_m, int tiles_n, int splits, int kb_total) {
+    Unit w;
+    const int mt = u % tiles_m;
+    const int r = u / tiles_m;
+    const int nt = r % tiles_n;
+    w.split = r / tiles_n;
+    w.m0 = mt;                                   // scaled by the caller (BN is a template parameter there)
+    w.n0 = nt * BM;
+    w.tile_id = nt * tiles_m + mt;
+    w.kb_begin = (int)((long)w.split * kb_total / splits);
+    w.n_kb = (int)((long)(w.split + 1) * kb_total / splits) - w.kb_begin;
+    return w;
+}
+
+// Persistent: the grid is at most one or two CTAs per SM; CTA c takes units c, c + grid, c + 2*grid, ...
+// The TMA pipeline runs on across units, and the accumulator alternates between two regions of tensor memory.
 template <int BN, typename TO>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                TO* __restrict__ out, long ldo, long slab_stride, float* __restrict__ partials,
-               int* __restrict__ tile_counters, int M, int N, int K, int splits, int* status) {
+               int* __restrict__ tile_counters, int M, int N, int K, int splits, int tiles_m, int tiles_n,
+               int n_units, int* status) {
     using Cfg = TileCfg<BN>;
+    constexpr int S = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
-    // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * Cfg::STAGES + 1);
+    uint64_t* bars = (uint64_t*)(smem + S * Cfg::STAGE_BYTES);
+    // bars[0..S): stage full, [S..2S): stage empty, [2S..2S+2): accumulator full, [2S+2..2S+4): accumulator empty
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 4);
     int* last_flag = (int*)(tmem_slot + 1);
+    int* bail = last_flag + 1;                   // a bounded wait ran out somewhere in this CTA
 
     fb_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // token tiles vary fastest, so the CTAs that share a weight tile run together and it is read from DRAM once
-    const int n0 = blockIdx.y * BM;              // first output feature of the tile
-    const int m0 = blockIdx.x * BN;              // first token of the tile
-    const int split = blockIdx.z;
     const int kb_total = (K + BK - 1) / BK;
-    const int kb_begin = (int)((long)split * kb_total / splits);
-    const int kb_end = (int)((long)(split + 1) * kb_total / splits);
-    const int n_kb = kb_end - kb_begin;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::STAGES; ++s) {
+        for (int s = 0; s < S; ++s) {
             mbar_init(smem_u32(&bars[s]), 1);
-            mbar_init(smem_u32(&bars[Cfg::STAGES + s]), 1);
+            mbar_init(smem_u32(&bars[S + s]), 1);
         }
-        mbar_init(smem_u32(&bars[2 * Cfg::STAGES]), 1);
+        mbar_init(smem_u32(&bars[2 * S]), 1);
+        mbar_init(smem_u32(&bars[2 * S + 1]), 1);
+        mbar_init(smem_u32(&bars[2 * S + 2]), 128);
+        mbar_init(smem_u32(&bars[2 * S + 3]), 128);
+        *bail = 0;
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -125,54 +146,80 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (elect_one()) {
-            // The weights do not depend on the kernel before this one: their first tiles are requested while
-            // that kernel may still be running; the activations are requested after the dependency wait.
-            const int pre = n_kb < Cfg::STAGES ? n_kb : Cfg::STAGES;
-            for (int i = 0; i < pre; ++i) {
-                const uint32_t full = smem_u32(&bars[i]);
-                mbar_expect_tx(full, (uint32_t)Cfg::STAGE_BYTES);
-                tma_load_2d(smem_u32(smem + (size_t)i * Cfg::STAGE_BYTES), &map_w, full, (kb_begin + i) * BK, n0);
+            uint32_t it = 0;                     // stages issued so far, over all units
+            bool first = true;
+            for (int u = blockIdx.x; u < n_units && !*(volatile int*)bail; u += gridDim.x) {
+                const Unit w = unit_of(u, tiles_m, tiles_n, splits, kb_total);
+                const int m0 = w.m0 * BN;
+                int i = 0;
+                if (first) {
+                    // The weights do not depend on the kernel before this one: the first tiles are requested
+                    // while that kernel may still be running; the activations follow the dependency wait.
+                    first = false;
+                    const int pre = w.n_kb < S ? w.n_kb : S;
+                    for (int j = 0; j < pre; ++j) {
+                        const uint32_t full = smem_u32(&bars[j]);
+                        mbar_expect_tx(full, (uint32_t)Cfg::STAGE_BYTES);
+                        tma_load_2d(smem_u32(smem + (size_t)j * Cfg::STAGE_BYTES), &map_w, full,
+                                    (w.kb_begin + j) * BK, w.n0);
+                    }
+                    fb_pdl_wait();
+                    for (int j = 0; j < pre; ++j)
+                        tma_load_2d(smem_u32(smem + (size_t)j * Cfg::STAGE_BYTES + BM * BK * 2), &map_x,
+                                    smem_u32(&bars[j]), (w.kb_begin + j) * BK, m0);
+                    i = pre;
+                    it = (uint32_t)pre;
+                }
+                for (; i < w.n_kb; ++i, ++it) {
+                    const int s = (int)(it % S);
+                    const uint32_t round = it / S;
+                    if (!mbar_wait(smem_u32(&bars[S + s]), (round & 1u) ^ 1u, status)) { *bail = 1; break; }
+                    const uint32_t full = smem_u32(&bars[s]);
+                    mbar_expect_tx(full, (uint32_t)Cfg::STAGE_BYTES);
+                    uint8_t* stage = smem + (size_t)s * Cfg::STAGE_BYTES;
+                    const int k0 = (w.kb_begin + i) * BK;
+                    tma_load_2d(smem_u32(stage), &map_w, full, k0, w.n0);
+                    tma_load_2d(smem_u32(stage + BM * BK * 2), &map_x, full, k0, m0);
+                }
             }
-            fb_pdl_wait();
-            for (int i = 0; i < pre; ++i)
-                tma_load_2d(smem_u32(smem + (size_t)i * Cfg::STAGE_BYTES + BM * BK * 2), &map_x, smem_u32(&bars[i]),
-                            (kb_begin + i) * BK, m0);
-            for (int i = pre; i < n_kb; ++i) {
-                const int s = i % Cfg::STAGES;
-                const uint32_t round = (uint32_t)(i / Cfg::STAGES);
-                if (!mbar_wait(smem_u32(&bars[Cfg::STAGES + s]), (round & 1u) ^ 1u, status)) break;
-                const uint32_t full = smem_u32(&bars[s]);
-                mbar_expect_tx(full, (uint32_t)Cfg::STAGE_BYTES);
-                uint8_t* stage = smem + (size_t)s * Cfg::STAGE_BYTES;
-                const int k0 = (kb_begin + i) * BK;
-                tma_load_2d(smem_u32(stage), &map_w, full, k0, n0);
-                tma_load_2d(smem_u32(stage + BM * BK * 2), &map_x, full, k0, m0);
-            }
+            if (first) fb_pdl_wait();
         }
         __syncwarp();
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (elect_one()) {
             constexpr uint32_t idesc = umma_idesc(BN);
-            bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % Cfg::STAGES;
-                const uint32_t round = (uint32_t)(i / Cfg::STAGES);
-                ok = mbar_wait(smem_u32(&bars[s]), round & 1u, status);
-                if (!ok) break;
+            uint32_t it = 0;
+            int j = 0;                           // units done by this CTA
+            for (int u = blockIdx.x; u < n_units && !*(volatile int*)bail; u += gridDim.x, ++j) {
+                const Unit w = unit_of(u, tiles_m, tiles_n, splits, kb_total);
+                const int b = j & 1;
+                const uint32_t use = (uint32_t)(j >> 1);
+                // the epilogue must have drained this accumulator (two units ago)
+                if (!mbar_wait(smem_u32(&bars[2 * S + 2 + b]), (use & 1u) ^ 1u, status)) { *bail = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint8_t* stage = smem + (size_t)s * Cfg::STAGE_BYTES;
-                const uint64_t da = umma_desc(smem_u32(stage));
-                const uint64_t db = umma_desc(smem_u32(stage + BM * BK * 2));
+                const uint32_t d_tmem = tmem_base + (uint32_t)(b * Cfg::ACC_COLS);
+                bool ok = true;
+                for (int i = 0; i < w.n_kb; ++i, ++it) {
+                    const int s = (int)(it % S);
+                    const uint32_t round = it / S;
+                    ok = mbar_wait(smem_u32(&bars[s]), round & 1u, status);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    uint8_t* stage = smem + (size_t)s * Cfg::STAGE_BYTES;
+                    const uint64_t da = umma_desc(smem_u32(stage));
+                    const uint64_t db = umma_desc(smem_u32(stage + BM * BK * 2));
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // 16 elements of K = 32 bytes further along the swizzled row
-                    umma_bf16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
-                              (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // 16 elements of K = 32 bytes further along the swizzled row
+                        umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
+                                  (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&bars[S + s]));            // frees the stage when the MMAs have read it
                 }
-                umma_commit(smem_u32(&bars[Cfg::STAGES + s]));      // frees the stage when the MMAs have read it
+                if (!ok) { *bail = 1; break; }
+                umma_commit(smem_u32(&bars[2 * S + b]));            // accumulator complete
             }
-            umma_commit(smem_u32(&bars[2 * Cfg::STAGES]));          // accumulator complete
         }
         __syncwarp();
     } else {
@@ -180,78 +227,91 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         fb_pdl_wait();                                              // before any global write of this kernel
         const int quarter = warp & 3;
         const int row_local = quarter * 32 + lane;                  // output feature within the tile
-        const int n = n0 + row_local;
-        const bool got = mbar_wait(smem_u32(&bars[2 * Cfg::STAGES]), 0u, status);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        if (splits == 1 || slab_stride > 0) {
-            // the whole sum, or this split's share of it written to its own slab (the consumer adds the slabs)
-            TO* dst = out + (size_t)split * (size_t)slab_stride;
-            if (got) {
+        int j = 0;
+        for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
+            const Unit w = unit_of(u, tiles_m, tiles_n, splits, kb_total);
+            const int m0 = w.m0 * BN, n0 = w.n0, split = w.split, n_kb = w.n_kb;
+            const int n = n0 + row_local;
+            const int b = j & 1;
+            const uint32_t use = (uint32_t)(j >> 1);
+            const bool got = !*(volatile int*)bail && mbar_wait(smem_u32(&bars[2 * S + b]), use & 1u, status);
+            if (!got) *bail = 1;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * Cfg::ACC_COLS);
+            if (splits == 1 || slab_stride > 0) {
+                // the whole sum, or this split's share of it written to its own slab (the consumer adds the slabs)
+                TO* dst = out + (size_t)split * (size_t)slab_stride;
+                if (got) {
+#pragma unroll 1
+                    for (int c = 0; c < BN; c += 16) {
+                        if (m0 + c >= M) break;
+                        float v[16];
+                        if (n_kb > 0) {
+                            tmem_ld16(taddr + (uint32_t)c, v);
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < 16; ++q) v[q] = 0.0f;
+                        }
+                        if (n < N) {
+#pragma unroll
+                            for (int q = 0; q < 16; ++q)
+                                if (m0 + c + q < M) dst[(size_t)(m0 + c + q) * ldo + n] = fb_from_float<TO>(v[q]);
+                        }
+                    }
+                }
+            } else {
+                const int tile_id = w.tile_id;
+                float* mine = partials + ((size_t)tile_id * splits + split) * (size_t)(BN * BM);
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     if (m0 + c >= M) break;
                     float v[16];
-                    if (n_kb > 0) {
+                    if (got && n_kb > 0) {
                         tmem_ld16(taddr + (uint32_t)c, v);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                        for (int q = 0; q < 16; ++q) v[q] = 0.0f;
                     }
-                    if (n < N) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (m0 + c + j < M) dst[(size_t)(m0 + c + j) * ldo + n] = fb_from_float<TO>(v[j]);
-                    }
+                    for (int q = 0; q < 16; ++q) mine[(size_t)(c + q) * BM + row_local] = v[q];
                 }
-            }
-        } else {
-            const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-            float* mine = partials + ((size_t)tile_id * splits + split) * (size_t)(BN * BM);
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                if (m0 + c >= M) break;
-                float v[16];
-                if (got && n_kb > 0) {
-                    tmem_ld16(taddr + (uint32_t)c, v);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) mine[(size_t)(c + j) * BM + row_local] = v[j];
-            }
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (warp == 2 && lane == 0) {
-                const int arrived = atomicAdd(&tile_counters[tile_id], 1);
-                *last_flag = (arrived == splits - 1) ? 1 : 0;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (*last_flag) {
                 __threadfence();
-                const float* base = partials + (size_t)tile_id * splits * (size_t)(BN * BM);
-#pragma unroll 1
-                for (int c = 0; c < BN && m0 + c < M; c += 4) {
-                    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    for (int s = 0; s < splits; ++s) {
-                        float v[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) v[j] = __ldcg(base + ((size_t)s * BN + c + j) * BM + row_local);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) acc[j] += v[j];
-                    }
-                    if (n < N) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (m0 + c + j < M) out[(size_t)(m0 + c + j) * ldo + n] = fb_from_float<TO>(acc[j]);
-                    }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    const int arrived = atomicAdd(&tile_counters[tile_id], 1);
+                    *last_flag = (arrived == splits - 1) ? 1 : 0;
                 }
-                if (warp == 2 && lane == 0) tile_counters[tile_id] = 0;      // ready for the next launch
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*last_flag) {
+                    __threadfence();
+                    const float* base = partials + (size_t)tile_id * splits * (size_t)(BN * BM);
+#pragma unroll 1
+                    for (int c = 0; c < BN && m0 + c < M; c += 4) {
+                        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        for (int s = 0; s < splits; ++s) {
+                            float v[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) v[q] = __ldcg(base + ((size_t)s * BN + c + q) * BM + row_local);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) acc[q] += v[q];
+                        }
+                        if (n < N) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                if (m0 + c + q < M) out[(size_t)(m0 + c + q) * ldo + n] = fb_from_float<TO>(acc[q]);
+                        }
+                    }
+                    if (warp == 2 && lane == 0) tile_counters[tile_id] = 0;  // ready for the next launch
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");                // last_flag may be rewritten
             }
+            // this accumulator may be overwritten now
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(smem_u32(&bars[2 * S + 2 + b]));
+            if (*(volatile int*)bail) break;
         }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -260,16 +320,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 }
 
-// ---------------------------------------------------------------------------
-// host side: tensor maps
-// ---------------------------------------------------------------------------
-int pick_splits(int tiles, int kb_total, int slots, int max_splits) {
-    // time ~ waves * (k-blocks per CTA + fixed cost of a CTA, in k-blocks)
+// How many shares of K per output tile.  CTA c of a grid of `grid` takes units c, c + grid, ...; a unit costs its
+// k-blocks plus a little for switching accumulators; every share beyond the first costs the traffic of one more
+// copy of the output (written here, read by whoever adds the shares), counted in k-block times.
+int pick_splits(int tiles, int kb_total, int slots, int max_splits, double share_cost_kb) {
     int best = 1;
     double best_cost = 1e30;
     for (int s = 1; s <= max_splits && s <= kb_total; ++s) {
-        const int waves = (tiles * s + slots - 1) / slots;
-        const double cost = waves * ((double)((kb_total + s - 1) / s) + 3.0) + (s > 1 ? 1.0 : 0.0);
+        const long units = (long)tiles * s;
+        const long grid = units < slots ? units : slots;
+        const long rounds = (units + grid - 1) / grid;
+        const double cost = rounds * ((double)((kb_total + s - 1) / s) + 0.5) + (s - 1) * share_cost_kb;
         if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
     }
     return best;
@@ -284,7 +345,14 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
     const int tiles = tiles_n * tiles_m;
     const int kb_total = (K + BK - 1) / BK;
     const int per_sm = Cfg::SMEM_BYTES <= 113 * 1024 ? 2 : 1;
-    int splits = force_splits > 0 ? force_splits : pick_splits(tiles, kb_total, 148 * per_sm, 16);
+    const int slots = 148 * per_sm;
+    // One more share = one more float32 copy of the output, written and read once at about HBM speed.  A k-block
+    // of one CTA takes its stage bytes at the CTA's part of that speed when the weights stream from DRAM (few
+    // rows), or its flops at an SM's tensor rate when the tile is large enough to be bound by them.
+    const double kb_seconds = BN <= 64 ? (double)Cfg::STAGE_BYTES / (6.0e12 / slots)
+                                       : 2.0 * BM * BN * BK / 9.0e12;
+    const double share_cost_kb = ((double)M * N * 8.0 / 6.0e12) / kb_seconds;
+    int splits = force_splits > 0 ? force_splits : pick_splits(tiles, kb_total, slots, 16, share_cost_kb);
     if (splits > kb_total) splits = kb_total;
     if (slab_stride > 0) {
         if (splits > max_slabs) splits = max_slabs;
@@ -292,7 +360,8 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
         while (splits > 1 && ((long)tiles * splits * BN * BM > partial_floats || tiles > n_counters)) --splits;
     }
     if (splits_used) *splits_used = splits;
-    if (tiles_n > 65535 || splits > 65535) return fb_fail(-1, "gemm_tc: too many tiles (N=%d)", N);
+    const long n_units = (long)tiles * splits;
+    if (n_units > 2000000000L) return fb_fail(-1, "gemm_tc: too many tiles (M=%d N=%d)", M, N);
     auto kern = gemm_tc_kernel<BN, TO>;
     static bool configured = false;
     if (!configured) {
@@ -301,9 +370,9 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
                                              Cfg::SMEM_BYTES, cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(tiles_m, tiles_n, splits);
-    fb_launch((kern), grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, partials, counters, M,
-                                                          N, K, splits, status);
+    const int grid = (int)(n_units < slots ? n_units : slots);
+    fb_launch((kern), grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, partials,
+              counters, M, N, K, splits, tiles_m, tiles_n, (int)n_units, status);
     return fb_check_launch("gemm_tc");
 }
 

@@ -49,13 +49,14 @@ class StepContext:
 
     def open_stream(self, width: int):
         """Allocate what the blocks of a step share: the float32 residual stream (returned), the buffer for
-        normalised rows (ctx.normed) and the float32 output of mixers and feed-forwards (ctx.delta).  For steps
-        of few rows (decoding) a part's last product may leave its split-K shares in up to ctx.max_slabs slabs
-        (ctx.delta_slabs, ctx.delta being the first), which the next norm adds."""
+        normalised rows (ctx.normed) and the float32 output of mixers and feed-forwards (ctx.delta).  A part's
+        last product may leave its split-K shares in up to ctx.max_slabs slabs (ctx.delta_slabs, ctx.delta being
+        the first), which the next norm adds: many for steps of few rows (decoding), where the split fills the
+        GPU, a few for long portions, where it balances the last wave of a deep product."""
         n = self.n_tokens
         x = self.step_alloc((n, width), torch.float32)
         self.normed = self.step_alloc((n, width), self.runtime.dtype)
-        self.max_slabs = 16 if n <= 16 else (8 if n <= 64 else 1)
+        self.max_slabs = 16 if n <= 16 else (8 if n <= 64 else 4)
         self.delta_slabs = self.step_alloc((self.max_slabs, n, width), torch.float32)
         self.delta = self.delta_slabs[0]
         self.pending_slabs = 1

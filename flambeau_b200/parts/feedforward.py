@@ -43,7 +43,7 @@ class GatedMLP(FeedForward):
         n = ctx.n_tokens
         with ctx.ws.scope():
             a = ctx.ws.alloc((n, self.inner), self.runtime.dtype)
-            if ctx.max_slabs > 1:
+            if n <= 64:                   # few rows: float32 split-K shares, added by the activation kernel
                 gu = ctx.ws.alloc((ctx.max_slabs, n, 2 * self.inner), torch.float32)
                 parts = self.gate_up.slabs(ctx, h, gu)
                 ops.silu_mul(gu[0], a, n_partials=parts, partial_stride=gu.stride(0))
