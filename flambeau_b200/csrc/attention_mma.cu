@@ -2,9 +2,9 @@
 // (mma.sync m16n8k16, float32 accumulation and softmax), one kernel in two
 // arrangements:
 //
-//   LONG  (prompt portions): a CTA owns one key/value head and a tile of up to 64
-//         query rows = (64 / G) tokens x the G query heads that share the head, so
-//         every K/V tile is read once for the whole group.  Its four warps split
+//   LONG  (prompt portions): a CTA owns one key/value head and a tile of up to 128
+//         query rows = (128 / G) tokens x the G query heads that share the head, so
+//         every K/V tile is read once for the whole group.  Its eight warps split
 //         the rows; each walks all visible key tiles with an online softmax.
 //   SHORT (decoded tokens and portions of a few tokens, rows = tokens x G <= 16):
 //         a CTA owns one (sequence, key/value head, chunk of keys).  Its four warps
@@ -13,7 +13,7 @@
 //         merges the chunks ("split-K").
 //
 // Keys and values come through the block table in tiles of 64 keys with
-// cp.async, double-buffered; a key outside [t0, p] of every row of the CTA is
+// bulk copies through a 2-3 stage pipeline; a key outside [t0, p] of every row of the CTA is
 // not read at all (its slot in shared memory is zero-filled), so pages that the
 // cache manager has taken back are never touched.  Softmax runs in base 2 with
 // scale*log2(e) folded into the scores.  Head sizes are padded with zeros to
@@ -27,12 +27,12 @@
 namespace {
 
 constexpr int KT = 64;             // keys per tile
-constexpr int ATT_THREADS = 128;
+constexpr int ATT_THREADS = 128;   // SHORT arrangement and the merge kernel
+constexpr int LONG_THREADS = 256;  // LONG arrangement: eight warps of 16 query rows
 
-// The split-key arrangement streams the cache once and is bound by memory: three tiles (two in flight) per
-// CTA; the long arrangement reuses each tile for 64 rows and keeps two.
+// Three K/V tiles in shared memory (two in flight) where the head size leaves room for them.
 __host__ __device__ constexpr int attn_stages(int hd_max, bool short_rows) {
-    return short_rows ? (hd_max <= 128 ? 3 : 2) : 2;
+    return hd_max <= 128 ? 3 : 2;
 }
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return smem_u32(p); }
@@ -93,15 +93,16 @@ __device__ __forceinline__ const __nv_bfloat16* tile_at(const __nv_bfloat16* til
 }
 
 template <int HD_MAX, bool SHORT, bool TMA>
-__global__ void __launch_bounds__(ATT_THREADS)
+__global__ void __launch_bounds__(SHORT ? ATT_THREADS : LONG_THREADS)
 attention_mma_kernel(const __grid_constant__ AttnArgs a) {
+    constexpr int NT = SHORT ? ATT_THREADS : LONG_THREADS;
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     constexpr int LDS = HD_MAX + 8;                 // row stride of Q (and of K/V when padded): 16 bytes of padding
     constexpr int TILE_ELEMS = TMA ? KT * HD_MAX : KT * LDS;
     constexpr int NKS = HD_MAX / 16;                // k-steps of Q K^T
     constexpr int NDB = HD_MAX / 8;                 // n-blocks of P V
-    constexpr int ROWS = SHORT ? 16 : 64;           // query rows per CTA
+    constexpr int ROWS = SHORT ? 16 : 128;          // query rows per CTA
     constexpr int WARP_KEYS = SHORT ? 16 : KT;      // keys of a tile that one warp scores
     constexpr int NSB = WARP_KEYS / 8;              // n-blocks of S per warp
     constexpr bool Q_IN_REGS = HD_MAX <= 128;
@@ -129,8 +130,8 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
         ntok = q_len;
     } else {
         if (is_short) return;
-        const int TQ = 64 / G;
-        tok0 = blockIdx.x * TQ;
+        const int TQ = ROWS / G;
+        tok0 = (gridDim.x - 1 - blockIdx.x) * TQ;       // later tiles see more keys: start them first
         if (tok0 >= q_len) return;
         ntok = min(TQ, q_len - tok0);
     }
@@ -151,12 +152,12 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     const int tma_ops = 2 * pages_per_tile * col_blocks;
 
     if (tid == 0) {
-        for (int st = 0; st < NST; ++st) mbar_init(smem_u32(&full[st]), TMA ? tma_ops : ATT_THREADS);
+        for (int st = 0; st < NST; ++st) mbar_init(smem_u32(&full[st]), TMA ? tma_ops : 2 * KT);
         *bail = 0;
         mbar_fence_init();
     }
     // ---- stage Q (zero-padded) and clear the padding of the K/V buffers ----
-    for (int idx = tid; idx < ROWS * (HD_MAX / 8); idx += ATT_THREADS) {
+    for (int idx = tid; idx < ROWS * (HD_MAX / 8); idx += NT) {
         const int r = idx / (HD_MAX / 8), c = idx - r * (HD_MAX / 8);
         uint4 v = make_uint4(0, 0, 0, 0);
         if (r < rows_valid && c < hd_chunks) {
@@ -167,12 +168,12 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     }
     if (TMA) {
         // pages that no query can see are not fetched; clear the tiles once so that what stays there is finite
-        for (int idx = tid; idx < 2 * NST * TILE_ELEMS / 8; idx += ATT_THREADS)
+        for (int idx = tid; idx < 2 * NST * TILE_ELEMS / 8; idx += NT)
             *reinterpret_cast<uint4*>(Ks + idx * 8) = make_uint4(0, 0, 0, 0);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     } else if (hd < HD_MAX) {
         const int pad_chunks = HD_MAX / 8 - hd_chunks;
-        for (int idx = tid; idx < NST * KT * pad_chunks; idx += ATT_THREADS) {
+        for (int idx = tid; idx < NST * KT * pad_chunks; idx += NT) {
             const int r = idx / pad_chunks, c = hd_chunks + idx - r * pad_chunks;
             *reinterpret_cast<uint4*>(Ks + r * LDS + c * 8) = make_uint4(0, 0, 0, 0);
             *reinterpret_cast<uint4*>(Vs + r * LDS + c * 8) = make_uint4(0, 0, 0, 0);
@@ -208,6 +209,7 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
             if (!valid) mbar_arrive(bar);
             return;
         }
+        if (tid >= 2 * KT) return;
         const int r = tid & (KT - 1);
         const bool is_v = tid >= KT;
         const int t = tile_start + r;
@@ -281,7 +283,7 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
                 const int first_dead = kr.t_hi + 1 - tile_start;            // >= 0 because tile_start <= t_hi
                 __nv_bfloat16* vz = Vs + buf * TILE_ELEMS;
                 const int chunks = (KT - first_dead) * 8;                    // 16-byte chunks per 64-column block
-                for (int idx = tid; idx < chunks * (HD_MAX / 64); idx += ATT_THREADS) {
+                for (int idx = tid; idx < chunks * (HD_MAX / 64); idx += NT) {
                     const int cb = idx / chunks, rest = idx - cb * chunks;
                     *reinterpret_cast<uint4*>(vz + cb * (KT * 64) + (first_dead + rest / 8) * 64 + (rest & 7) * 8) =
                         make_uint4(0, 0, 0, 0);
@@ -401,7 +403,7 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     // ---- SHORT: merge the four warps (they saw different keys of the same rows), write one partial ----
     float* so = reinterpret_cast<float*>(Ks);         // [4 warps][16][HD_MAX] floats; K/V buffers are free now
     float* sml = so + 4 * 16 * HD_MAX;                // [4 warps][16][2]
-    static_assert(4 * 16 * HD_MAX * 4 + 4 * 16 * 2 * 4 <= 2 * NST * KT * HD_MAX * 2, "merge buffer fits in K/V");
+    static_assert(!SHORT || 4 * 16 * HD_MAX * 4 + 4 * 16 * 2 * 4 <= 2 * NST * KT * HD_MAX * 2, "merge buffer fits in K/V");
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = (lane >> 2) + 8 * h;
@@ -420,7 +422,7 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     const size_t slot = ((size_t)seq * a.nkv + kvh) * a.max_chunks + blockIdx.x;
     float* po = a.part_o + slot * 16 * HD_MAX;
     float* pml = a.part_ml + slot * 16 * 2;
-    for (int idx = tid; idx < 16 * HD_MAX; idx += ATT_THREADS) {
+    for (int idx = tid; idx < 16 * HD_MAX; idx += NT) {
         const int r = idx / HD_MAX, c = idx - r * HD_MAX;
         float m = -INFINITY;
 #pragma unroll
@@ -504,7 +506,7 @@ attention_merge_kernel(const AttnArgs a) {
 }
 
 __host__ __device__ constexpr size_t attn_smem_bytes(int hd_max, bool short_rows, bool tma) {
-    return (size_t)(short_rows ? 16 : 64) * (hd_max + 8) * 2 + 1024 /* tile alignment */ +
+    return (size_t)(short_rows ? 16 : 128) * (hd_max + 8) * 2 + 1024 /* tile alignment */ +
            (size_t)2 * attn_stages(hd_max, short_rows) * KT * (tma ? hd_max : hd_max + 8) * 2 + 64 /* barriers */;
 }
 
@@ -519,7 +521,7 @@ int launch_one(const AttnArgs& a, dim3 grid, const char* what, cudaStream_t stre
                                              cudaGetErrorString(e));
         configured = true;
     }
-    fb_launch((kern), grid, ATT_THREADS, smem, stream, a);
+    fb_launch((kern), grid, SHORT ? ATT_THREADS : LONG_THREADS, smem, stream, a);
     return fb_check_launch(what);
 }
 
@@ -528,7 +530,7 @@ int launch_attention_mma(const AttnArgs& a, bool tma, int n_seqs, int max_q_len,
                          cudaStream_t stream) {
     const int G = a.nh / a.nkv;
     if (any_long) {
-        const int TQ = 64 / G;
+        const int TQ = 128 / G;
         const dim3 grid((max_q_len + TQ - 1) / TQ, a.nkv, n_seqs);
         int rc;
         if constexpr (HD_MAX >= 64) {

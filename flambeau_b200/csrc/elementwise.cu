@@ -316,6 +316,78 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stri
     for (int d = threadIdx.x; d < hd; d += blockDim.x) vdst[d] = fb_from_float<T>(slab_sum(vsrc, d, n_partials, partial_stride));
 }
 
+// The same work four elements at a time (all strides, the head size and the rotary half multiples of 4,
+// 16-byte aligned rows): one item = four consecutive pairs of one head, or four untouched dimensions, or four
+// values.  Items of a token: (nh + nkv) * (hd - half) / 4 rotary items, then nkv * hd / 4 value items.
+template <typename TI>
+__device__ __forceinline__ float4 slab_sum4(const TI* __restrict__ p, int n_partials, long partial_stride) {
+    float4 acc = Vec4<TI>::load(p);
+#pragma unroll 4
+    for (int s = 1; s < n_partials; ++s) {
+        const float4 a = Vec4<TI>::load(p + (size_t)s * partial_stride);
+        acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+    }
+    return acc;
+}
+
+template <typename TI, typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_write_vec_kernel(const TI* __restrict__ q_in, long q_in_stride, int n_partials, long partial_stride,
+                         T* __restrict__ q_out, long q_out_stride, const TI* __restrict__ k, long k_stride,
+                         const TI* __restrict__ v, long v_stride, const float* __restrict__ cos_t,
+                         const float* __restrict__ sin_t, int half, const int* __restrict__ positions,
+                         const int* __restrict__ row_seq, const int* __restrict__ block_table, int table_stride,
+                         T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size, int n_pages, int nh, int nkv,
+                         int hd, int write_kv, int* status) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const int t = blockIdx.x;
+    const int per_head = (hd - half) >> 2;                  // items per head
+    const int rot_items = half >> 2;
+    const int q_items = nh * per_head, k_items = write_kv ? nkv * per_head : 0;
+    const int v_items = write_kv ? nkv * (hd >> 2) : 0;
+    const int item = blockIdx.y * blockDim.x + threadIdx.x;
+    if (item >= q_items + k_items + v_items) return;
+
+    size_t cache_row = 0;
+    if (item >= q_items) {
+        const int pos = positions[t];
+        const int page = block_table[(size_t)row_seq[t] * table_stride + pos / page_size];
+        if (page < 0 || page >= n_pages) {
+            atomicOr(status, FB_STATUS_BAD_PAGE);
+            return;
+        }
+        cache_row = ((size_t)page * nkv) * page_size + (pos % page_size);     // + head * page_size below
+    }
+    if (item >= q_items + k_items) {
+        const int idx = item - q_items - k_items;
+        const int h = idx / (hd >> 2), d = (idx - h * (hd >> 2)) << 2;
+        const float4 val = slab_sum4(v + (size_t)t * v_stride + (size_t)h * hd + d, n_partials, partial_stride);
+        Vec4<T>::store(v_pool + (cache_row + (size_t)h * page_size) * hd + d, val);
+        return;
+    }
+    const bool is_q = item < q_items;
+    const int idx = is_q ? item : item - q_items;
+    const int h = idx / per_head, j = idx - h * per_head;
+    const TI* src = is_q ? q_in + (size_t)t * q_in_stride + (size_t)h * hd : k + (size_t)t * k_stride + (size_t)h * hd;
+    T* dst = is_q ? q_out + (size_t)t * q_out_stride + (size_t)h * hd
+                  : k_pool + (cache_row + (size_t)h * page_size) * hd;
+    if (j < rot_items) {
+        const int d = j << 2;
+        const float4 a = slab_sum4(src + d, n_partials, partial_stride);
+        const float4 b = slab_sum4(src + d + half, n_partials, partial_stride);
+        const float4 c = *reinterpret_cast<const float4*>(cos_t + (size_t)t * half + d);
+        const float4 sn = *reinterpret_cast<const float4*>(sin_t + (size_t)t * half + d);
+        Vec4<T>::store(dst + d, make_float4(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y,
+                                            a.z * c.z - b.z * sn.z, a.w * c.w - b.w * sn.w));
+        Vec4<T>::store(dst + d + half, make_float4(a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y,
+                                                   a.z * sn.z + b.z * c.z, a.w * sn.w + b.w * c.w));
+    } else {
+        const int d = 2 * half + ((j - rot_items) << 2);     // untouched dimensions behind the rotary part
+        Vec4<T>::store(dst + d, slab_sum4(src + d, n_partials, partial_stride));
+    }
+}
+
 // q_in/k/v have dtype `in_dtype` (the projection's output, float32 in both engine modes so that q and k are
 // rounded once, after the rotation); q_out and the cache have dtype `out_dtype`.  The inputs may be split-K
 // shares: `n_partials` slabs `partial_stride` elements apart, which are added here.
@@ -336,6 +408,21 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, int n_parti
     if (n_partials < 1) n_partials = 1;
     if (n == 0) return 0;
     FB_REQUIRE(nh + nkv <= 65535, "rope_kv_write: too many heads");
+    const bool aligned16 = ((uintptr_t)q_in % 16 == 0) && ((uintptr_t)q_out % 16 == 0) && ((uintptr_t)k % 16 == 0) &&
+                           ((uintptr_t)v % 16 == 0) && ((uintptr_t)cos_t % 16 == 0) && ((uintptr_t)sin_t % 16 == 0) &&
+                           ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0);
+    const bool vec = aligned16 && hd % 4 == 0 && half % 4 == 0 && q_in_stride % 4 == 0 && q_out_stride % 4 == 0 &&
+                     k_stride % 4 == 0 && v_stride % 4 == 0 && partial_stride % 4 == 0 && q_in != q_out;
+    if (vec) {
+        const int items = (nh + (write_kv ? nkv : 0)) * ((hd - half) / 4) + (write_kv ? nkv * (hd / 4) : 0);
+        const dim3 grid(n, (items + 255) / 256);
+        FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
+            (fb_launch((rope_kv_write_vec_kernel<TI, T>), grid, 256, 0, stream, (const TI*)q_in, (long)q_in_stride,
+                n_partials, (long)partial_stride, (T*)q_out, (long)q_out_stride, (const TI*)k, (long)k_stride,
+                (const TI*)v, (long)v_stride, cos_t, sin_t, half, positions, row_seq, block_table, table_stride,
+                (T*)k_pool, (T*)v_pool, page_size, n_pages, nh, nkv, hd, write_kv, status))));
+        return fb_check_launch("rope_kv_write");
+    }
     FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
         (fb_launch((rope_kv_write_kernel<TI, T>), dim3(n, nh + (write_kv ? nkv : 0)), hd >= 128 ? 64 : 32, 0, stream, (const TI*)q_in, q_in_stride, n_partials, (long)partial_stride, (T*)q_out, q_out_stride,
             (const TI*)k, k_stride, (const TI*)v, v_stride, cos_t, sin_t, half, positions, row_seq, block_table,
@@ -344,9 +431,13 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, int n_parti
 }
 
 // ---------------------------------------------------------------------------
-// SiLU(gate) * up on a fused [n, 2I] buffer (gate in columns [0,I), up in [I,2I)).
+// SiLU(gate) * up on a fused [n, 2I] buffer whose columns alternate: column 2c is gate c, column 2c+1 is up c
+// (the feed-forward stacks its gate and up weights row by row in that order, so that the tensor-core product
+// can apply the activation in its epilogue with a neighbour exchange; this kernel serves the other paths).
 // crates/kernels-hip/src/kernels/swiglu_f32_to_f16.cu; activation.rs:107-118.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ float silu_times(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
 template <typename TI, typename T>
 __global__ void silu_mul_kernel(const TI* __restrict__ gu, long stride, int n_partials, long partial_stride,
                                 T* __restrict__ out, int n, int I) {
@@ -356,33 +447,25 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, long stride, int n_pa
     if (idx >= (size_t)n * I) return;
     const int r = (int)(idx / I), c = (int)(idx - (size_t)r * I);
     const TI* row = gu + (size_t)r * stride;
-    const float g = slab_sum(row, c, n_partials, partial_stride);
-    const float u = slab_sum(row, I + c, n_partials, partial_stride);
-    out[idx] = fb_from_float<T>(g / (1.0f + expf(-g)) * u);
+    const float g = slab_sum(row, 2 * c, n_partials, partial_stride);
+    const float u = slab_sum(row, 2 * c + 1, n_partials, partial_stride);
+    out[idx] = fb_from_float<T>(silu_times(g, u));
 }
 
-// Four elements per thread (I and the strides multiples of 4, 16-byte aligned rows for float / 8-byte for bf16).
+// Two outputs per thread from one 4-wide load (g0, u0, g1, u1); I even, strides multiples of 4, aligned rows.
 template <typename TI, typename T>
 __global__ void silu_mul_vec_kernel(const TI* __restrict__ gu, long stride, int n_partials, long partial_stride,
                                     T* __restrict__ out, int n, int I) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
-    const int nvec = I >> 2;
+    const int nvec = I >> 1;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n * nvec) return;
     const int r = (int)(idx / nvec), c = (int)(idx - (size_t)r * nvec);
-    const TI* row = gu + (size_t)r * stride;
-    float4 g = Vec4<TI>::load(row + 4 * c), u = Vec4<TI>::load(row + I + 4 * c);
-#pragma unroll 4
-    for (int p = 1; p < n_partials; ++p) {
-        const float4 g2 = Vec4<TI>::load(row + (size_t)p * partial_stride + 4 * c);
-        const float4 u2 = Vec4<TI>::load(row + (size_t)p * partial_stride + I + 4 * c);
-        g.x += g2.x; g.y += g2.y; g.z += g2.z; g.w += g2.w;
-        u.x += u2.x; u.y += u2.y; u.z += u2.z; u.w += u2.w;
-    }
-    Vec4<T>::store(out + (size_t)r * I + 4 * c,
-                   make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
-                               g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
+    const float4 v = slab_sum4(gu + (size_t)r * stride + 4 * c, n_partials, partial_stride);
+    T* o = out + (size_t)r * I + 2 * c;
+    o[0] = fb_from_float<T>(silu_times(v.x, v.y));
+    o[1] = fb_from_float<T>(silu_times(v.z, v.w));
 }
 
 // gate_up has dtype in_dtype and may be split-K shares (n_partials slabs partial_stride elements apart);
@@ -392,18 +475,17 @@ FB_API int fb_silu_mul(const void* gate_up, long long stride, int in_dtype, int 
     FB_REQUIRE(n >= 0 && I > 0 && stride >= 2LL * I, "silu_mul: bad sizes n=%d I=%d stride=%lld", n, I, stride);
     if (n == 0) return 0;
     if (n_partials < 1) n_partials = 1;
-    const bool vec = I % 4 == 0 && stride % 4 == 0 && partial_stride % 4 == 0 && (uintptr_t)gate_up % 16 == 0 &&
-                     (uintptr_t)out % 16 == 0;
+    const bool vec = I % 2 == 0 && stride % 4 == 0 && partial_stride % 4 == 0 && (uintptr_t)gate_up % 16 == 0;
     if (vec) {
-        const size_t total = (size_t)n * (I / 4);
+        const size_t total = (size_t)n * (I / 2);
         FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
-            (fb_launch((silu_mul_vec_kernel<TI, T>), (unsigned)((total + 255) / 256), 256, 0, stream, 
+            (fb_launch((silu_mul_vec_kernel<TI, T>), (unsigned)((total + 255) / 256), 256, 0, stream,
                 (const TI*)gate_up, stride, n_partials, (long)partial_stride, (T*)out, n, I))));
         return fb_check_launch("silu_mul");
     }
     const size_t total = (size_t)n * I;
     FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
-        (fb_launch((silu_mul_kernel<TI, T>), (unsigned)((total + 255) / 256), 256, 0, stream, 
+        (fb_launch((silu_mul_kernel<TI, T>), (unsigned)((total + 255) / 256), 256, 0, stream,
             (const TI*)gate_up, stride, n_partials, (long)partial_stride, (T*)out, n, I))));
     return fb_check_launch("silu_mul");
 }

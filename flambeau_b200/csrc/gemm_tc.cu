@@ -10,7 +10,8 @@
 // warps whose lanes are the output features, so that a warp stores 32
 // consecutive features of one token.
 //
-// Warps: 0 = TMA producer, 1 = tensor-memory owner and MMA issuer, 2..5 = epilogue.
+// Warps: 0 = TMA producer, 1 = tensor-memory owner and MMA issuer, 2..9 = epilogue (a warp may only read the
+// quarter of the tensor-memory lanes given by its index modulo 4; two warps share a quarter and split the columns).
 // Split-K: grid.z CTAs share one output tile; each writes its float32 partial
 // to scratch, and the CTA that arrives last (an atomic counter per tile, no
 // waiting) adds the partials in split order and writes the result, so the sum
@@ -34,7 +35,8 @@ namespace {
 constexpr int BM = 128;          // output features per CTA (UMMA M)
 constexpr int BK = 64;           // K elements per stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;      // warp 0: TMA, warp 1: MMA, warps 2..9: epilogue (two per lane quarter)
+constexpr int EPI_THREADS = 256;
 // Shared-memory matrix descriptor: K-major tile of rows x 64 bf16, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -106,7 +108,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                TO* __restrict__ out, long ldo, long slab_stride, float* __restrict__ partials,
                int* __restrict__ tile_counters, int M, int N, int K, int splits, int tiles_m, int tiles_n,
-               int n_units, int* status) {
+               int n_units, int gated, int* status) {
     using Cfg = TileCfg<BN>;
     constexpr int S = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -128,8 +130,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         mbar_init(smem_u32(&bars[2 * S]), 1);
         mbar_init(smem_u32(&bars[2 * S + 1]), 1);
-        mbar_init(smem_u32(&bars[2 * S + 2]), 128);
-        mbar_init(smem_u32(&bars[2 * S + 3]), 128);
+        mbar_init(smem_u32(&bars[2 * S + 2]), EPI_THREADS);
+        mbar_init(smem_u32(&bars[2 * S + 3]), EPI_THREADS);
         *bail = 0;
         mbar_fence_init();
     }
@@ -223,9 +225,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         __syncwarp();
     } else {
-        // ---------------- epilogue: warps 2..5, lane quarter = warp % 4 ----------------
+        // ---------------- epilogue: warps 2..9, lane quarter = warp % 4, column half = (warp - 2) / 4 ----------
         fb_pdl_wait();                                              // before any global write of this kernel
         const int quarter = warp & 3;
+        const int half_id = (warp - 2) >> 2;                        // which 16-column chunks this warp takes
         const int row_local = quarter * 32 + lane;                  // output feature within the tile
         int j = 0;
         for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
@@ -243,7 +246,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 TO* dst = out + (size_t)split * (size_t)slab_stride;
                 if (got) {
 #pragma unroll 1
-                    for (int c = 0; c < BN; c += 16) {
+                    for (int c = half_id * 16; c < BN; c += 32) {
                         if (m0 + c >= M) break;
                         float v[16];
                         if (n_kb > 0) {
@@ -252,7 +255,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                             for (int q = 0; q < 16; ++q) v[q] = 0.0f;
                         }
-                        if (n < N) {
+                        if (gated) {
+                            // output features alternate gate, up: even lanes hold a gate, their odd neighbour its
+                            // up; the even lane writes silu(gate) * up to column n / 2 of a half-as-wide output.
+                            // Every lane computes (straight-line code, sixteen independent chains); odd lanes'
+                            // results are dropped.
+                            float r[16];
+#pragma unroll
+                            for (int q = 0; q < 16; ++q) {
+                                const float up = __shfl_xor_sync(0xffffffffu, v[q], 1);
+                                r[q] = v[q] / (1.0f + expf(-v[q])) * up;
+                            }
+                            const bool writes = !(lane & 1) && n + 1 < N;
+#pragma unroll
+                            for (int q = 0; q < 16; ++q)
+                                if (writes && m0 + c + q < M)
+                                    dst[(size_t)(m0 + c + q) * ldo + (n >> 1)] = fb_from_float<TO>(r[q]);
+                        } else if (n < N) {
 #pragma unroll
                             for (int q = 0; q < 16; ++q)
                                 if (m0 + c + q < M) dst[(size_t)(m0 + c + q) * ldo + n] = fb_from_float<TO>(v[q]);
@@ -263,7 +282,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const int tile_id = w.tile_id;
                 float* mine = partials + ((size_t)tile_id * splits + split) * (size_t)(BN * BM);
 #pragma unroll 1
-                for (int c = 0; c < BN; c += 16) {
+                for (int c = half_id * 16; c < BN; c += 32) {
                     if (m0 + c >= M) break;
                     float v[16];
                     if (got && n_kb > 0) {
@@ -276,17 +295,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     for (int q = 0; q < 16; ++q) mine[(size_t)(c + q) * BM + row_local] = v[q];
                 }
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 if (warp == 2 && lane == 0) {
                     const int arrived = atomicAdd(&tile_counters[tile_id], 1);
                     *last_flag = (arrived == splits - 1) ? 1 : 0;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 if (*last_flag) {
                     __threadfence();
                     const float* base = partials + (size_t)tile_id * splits * (size_t)(BN * BM);
 #pragma unroll 1
-                    for (int c = 0; c < BN && m0 + c < M; c += 4) {
+                    for (int c = half_id * 4; c < BN && m0 + c < M; c += 8) {
                         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                         for (int s = 0; s < splits; ++s) {
                             float v[4];
@@ -303,7 +322,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     }
                     if (warp == 2 && lane == 0) tile_counters[tile_id] = 0;  // ready for the next launch
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");                // last_flag may be rewritten
+                asm volatile("bar.sync 1, 256;" ::: "memory");                // last_flag may be rewritten
             }
             // this accumulator may be overwritten now
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -339,7 +358,7 @@ int pick_splits(int tiles, int kb_total, int slots, int max_splits, double share
 template <int BN, typename TO>
 int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo, long slab_stride, int max_slabs,
               int* splits_used, float* partials, long partial_floats, int* counters, int n_counters, int M, int N,
-              int K, int force_splits, int* status, cudaStream_t stream) {
+              int K, int force_splits, int* status, cudaStream_t stream, int gated = 0) {
     using Cfg = TileCfg<BN>;
     const int tiles_n = (N + BM - 1) / BM, tiles_m = (M + BN - 1) / BN;
     const int tiles = tiles_n * tiles_m;
@@ -353,6 +372,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
                                        : 2.0 * BM * BN * BK / 9.0e12;
     const double share_cost_kb = ((double)M * N * 8.0 / 6.0e12) / kb_seconds;
     int splits = force_splits > 0 ? force_splits : pick_splits(tiles, kb_total, slots, 16, share_cost_kb);
+    if (gated) splits = 1;                       // the activation needs the whole sum
     if (splits > kb_total) splits = kb_total;
     if (slab_stride > 0) {
         if (splits > max_slabs) splits = max_slabs;
@@ -372,7 +392,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
     }
     const int grid = (int)(n_units < slots ? n_units : slots);
     fb_launch((kern), grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, partials,
-              counters, M, N, K, splits, tiles_m, tiles_n, (int)n_units, status);
+              counters, M, N, K, splits, tiles_m, tiles_n, (int)n_units, gated, status);
     return fb_check_launch("gemm_tc");
 }
 
@@ -423,6 +443,43 @@ FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw
     }
 #undef FB_TC_CASE
     return fb_fail(-1, "gemm_tc: unknown output dtype code %d", o_dtype);
+}
+
+// out[M, N/2] = silu(g) * u with [g_0, u_0, g_1, u_1, ...] = X[M,K] * W[N,K]^T: W stacks gate and up rows
+// alternately, and the activation is applied in the epilogue (the whole sum in one CTA, so K is not split).
+FB_API int fb_gemm_tc_gated(const void* X, long long lda, const void* W, long long ldw, void* out, int o_dtype,
+                            long long ldo, int M, int N, int K, float* partials, long long partial_floats,
+                            int* counters, int n_counters, int* status, cudaStream_t stream) {
+    FB_REQUIRE(M >= 0 && N > 0 && K > 0 && N % 2 == 0, "gemm_tc_gated: bad sizes M=%d N=%d K=%d", M, N, K);
+    FB_REQUIRE(lda >= K && ldw >= K && ldo >= N / 2, "gemm_tc_gated: a row stride is shorter than its row");
+    FB_REQUIRE(lda % 8 == 0 && ldw % 8 == 0, "gemm_tc_gated: row strides must be multiples of 8 elements");
+    FB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tc_gated: operands must be 16-byte aligned");
+    if (M == 0) return 0;
+    const int BN = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    CUtensorMap mw, mx;
+    int rc = fb_tensor_map_bf16(&mw, W, N, K, (long)ldw, BK, BM);
+    if (rc) return rc;
+    rc = fb_tensor_map_bf16(&mx, X, M, K, (long)lda, BK, BN);
+    if (rc) return rc;
+#define FB_TCG_CASE(BN_)                                                                                        \
+    case BN_:                                                                                                   \
+        if (o_dtype == FB_F32)                                                                                  \
+            return launch_tc<BN_, float>(mw, mx, out, (long)ldo, 0, 1, nullptr, partials, (long)partial_floats, \
+                                         counters, n_counters, M, N, K, 1, status, stream, 1);                  \
+        else if (o_dtype == FB_BF16)                                                                            \
+            return launch_tc<BN_, __nv_bfloat16>(mw, mx, out, (long)ldo, 0, 1, nullptr, partials,               \
+                                                 (long)partial_floats, counters, n_counters, M, N, K, 1, status, \
+                                                 stream, 1);                                                    \
+        break;
+    switch (BN) {
+        FB_TCG_CASE(16)
+        FB_TCG_CASE(32)
+        FB_TCG_CASE(64)
+        FB_TCG_CASE(128)
+        FB_TCG_CASE(256)
+    }
+#undef FB_TCG_CASE
+    return fb_fail(-1, "gemm_tc_gated: unknown output dtype code %d", o_dtype);
 }
 
 // ---------------------------------------------------------------------------

@@ -31,6 +31,7 @@ _SIGNATURES = {
     "fb_gemm_simt": (I, [P, I, L, P, I, L, P, I, L, I, I, I, STREAM]),
     # gemm_tc.cu
     "fb_gemm_tc": (I, [P, L, P, L, P, I, L, L, I, P, I, I, I, P, L, P, I, I, P, STREAM]),
+    "fb_gemm_tc_gated": (I, [P, L, P, L, P, I, L, I, I, I, P, L, P, I, P, STREAM]),
     # attention_simt.cu
     "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, I, I, I, I, I, F, P, STREAM]),
     # attention_mma.cu

@@ -127,8 +127,9 @@ def rope_kv_write(q_in, q_out, k, v, cos, sin, half: int, positions, row_seq, bl
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, n_partials: int = 1, partial_stride: int = 0) -> None:
-    """out = silu(gate) * up for gate_up = [gate | up] rows; with n_partials > 1, gate_up is the first of that
-    many split-K shares `partial_stride` elements apart, which are added first."""
+    """out[:, c] = silu(gate_up[:, 2c]) * gate_up[:, 2c+1] (gate and up alternate along a row); with
+    n_partials > 1, gate_up is the first of that many split-K shares `partial_stride` elements apart, which are
+    added first."""
     _cuda(gate_up, out)
     n, two_i = gate_up.shape
     I = two_i // 2
@@ -249,6 +250,20 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.T
                            partials.data_ptr(), partials.numel(), counters.data_ptr(), counters.numel(),
                            int(splits), status.data_ptr(), _stream()), "gemm_tc")
     return _SPLITS_USED.value if slabs is not None else 1
+
+
+def gemm_tc_gated(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[M, N/2] = silu(g) * u where (g_0, u_0, g_1, u_1, ...) = a @ w^T: w stacks gate and up rows alternately
+    and the activation runs in the product's epilogue."""
+    _cuda(a, w, out, status)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] * 2 != N:
+        raise KernelError(f"gated gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
+    partials, counters = _SplitScratch.get(a.device)
+    check(lib().fb_gemm_tc_gated(a.data_ptr(), _rows(a), w.data_ptr(), _rows(w), out.data_ptr(), dtype_code(out),
+                                 _rows(out), M, N, K, partials.data_ptr(), partials.numel(), counters.data_ptr(),
+                                 counters.numel(), status.data_ptr(), _stream()), "gemm_tc_gated")
 
 
 def linear_slabs(a: torch.Tensor, w: torch.Tensor, slabs: torch.Tensor, ctx) -> int:

@@ -5,14 +5,15 @@ import torch
 
 from ..kernels import ops
 from .base import FeedForward, TensorSpec
-from .linear import Linear, concat_rows
+from .linear import Linear, interleave_rows
 from .spec import register_part
 
 
 class GatedMLP(FeedForward):
     """d = (silu(h Wg^T) * (h Wu^T)) Wd^T, no bias, no routing
     (crates/forward/src/core/composites/dense_ffn.rs:116-186).  Gate and up
-    weights are stacked at load so one product yields both."""
+    weights are stacked at load, row by row alternately, so one product yields
+    both and its epilogue can apply the activation to neighbouring outputs."""
     graph_safe = True
 
     def __init__(self, runtime=None, prefix="", *, width: int, inner: int, activation: str = "silu",
@@ -33,7 +34,7 @@ class GatedMLP(FeedForward):
 
     def own_bind(self, tensors):
         p = self.prefix
-        self.gate_up = Linear(concat_rows([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]]))
+        self.gate_up = Linear(interleave_rows(tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]))
         self.down = Linear(tensors[p + "down_proj.weight"])
 
     def own_weights(self):
@@ -47,6 +48,8 @@ class GatedMLP(FeedForward):
                 gu = ctx.ws.alloc((ctx.max_slabs, n, 2 * self.inner), torch.float32)
                 parts = self.gate_up.slabs(ctx, h, gu)
                 ops.silu_mul(gu[0], a, n_partials=parts, partial_stride=gu.stride(0))
+            elif ops.tc_supported(h, self.gate_up.weight, a):
+                ops.gemm_tc_gated(h, self.gate_up.weight, a, self.runtime.status)   # activation in the epilogue
             else:
                 gu = ctx.ws.alloc((n, 2 * self.inner), self.runtime.dtype)
                 self.gate_up(ctx, h, gu)

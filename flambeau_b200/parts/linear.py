@@ -23,6 +23,13 @@ class Linear:
         return ops.linear_slabs(a, self.weight, slabs, ctx)
 
 
+def interleave_rows(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Rows a_0, b_0, a_1, b_1, ...: two maps of one input whose outputs are wanted side by side."""
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise ValueError("interleaved weights must share shape and dtype")
+    return torch.stack([a, b], dim=1).reshape(2 * a.shape[0], a.shape[1]).contiguous()
+
+
 def concat_rows(tensors) -> torch.Tensor:
     """Stack weights that share their input so one product serves them all."""
     dts = {t.dtype for t in tensors}

@@ -86,3 +86,21 @@ def test_shapes_the_tma_path_cannot_take_are_refused():
         ops.gemm_tc(a, w, out, status)
     with pytest.raises(KernelError):
         ops.gemm_tc(a.float(), w, out, status)
+
+
+@pytest.mark.parametrize("M,I,K", [(3, 64, 64), (17, 100, 136), (70, 1001, 72), (300, 160, 96), (2048, 512, 256)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gated_epilogue(M, I, K, out_dtype):
+    """Gate and up rows alternate in the weight; the epilogue writes silu(gate) * up, half as wide."""
+    from flambeau_b200.kernels import ops
+    g = torch.Generator(device="cuda").manual_seed(M + I)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, device="cuda", generator=g) / 8).to(torch.bfloat16)
+    out = torch.full((M, I), float("nan"), device="cuda", dtype=out_dtype)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.gemm_tc_gated(a, w, out, status)
+    y = a.double() @ w.double().T
+    gate, up = y[:, 0::2], y[:, 1::2]
+    want = gate / (1 + torch.exp(-gate)) * up
+    assert int(status.item()) == 0 and torch.isfinite(out).all()
+    assert rel_err(out, want) < (3e-5 if out_dtype == torch.float32 else 8e-3)
