@@ -4,8 +4,9 @@
 //
 //   LONG  (prompt portions): a CTA owns one key/value head and a tile of up to 128
 //         query rows = (128 / G) tokens x the G query heads that share the head, so
-//         every K/V tile is read once for the whole group.  Its eight warps split
-//         the rows; each walks all visible key tiles with an online softmax.
+//         every K/V tile is read once for the whole group.  Its four warps take 32
+//         rows each, so that every K/V fragment fetched from shared memory feeds two
+//         row blocks; each walks all visible key tiles with an online softmax.
 //   SHORT (decoded tokens and portions of a few tokens, rows = tokens x G <= 16):
 //         a CTA owns one (sequence, key/value head, chunk of keys).  Its four warps
 //         share the 16 rows and split every 64-key tile; their partial (m, l, o)
@@ -28,11 +29,16 @@ namespace {
 
 constexpr int KT = 64;             // keys per tile
 constexpr int ATT_THREADS = 128;   // SHORT arrangement and the merge kernel
-constexpr int LONG_THREADS = 256;  // LONG arrangement: eight warps of 16 query rows
+constexpr int LONG_THREADS = 128;  // LONG arrangement: four warps of 32 query rows
 
-// Three K/V tiles in shared memory (two in flight) where the head size leaves room for them.
+// 16-row blocks per warp of the LONG arrangement: two while the accumulators fit in registers.
+__host__ __device__ constexpr int long_row_blocks(int hd_max, bool short_rows) {
+    return (short_rows || hd_max > 128) ? 1 : 2;
+}
 __host__ __device__ constexpr int attn_stages(int hd_max, bool short_rows) {
-    return hd_max <= 128 ? 3 : 2;
+    // SHORT streams the cache once: three tiles (two in flight).  LONG reuses a tile for 128 rows and wants two
+    // CTAs on an SM more than it wants a third tile.
+    return (short_rows && hd_max <= 128) ? 3 : 2;
 }
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return smem_u32(p); }
@@ -102,10 +108,11 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     constexpr int TILE_ELEMS = TMA ? KT * HD_MAX : KT * LDS;
     constexpr int NKS = HD_MAX / 16;                // k-steps of Q K^T
     constexpr int NDB = HD_MAX / 8;                 // n-blocks of P V
-    constexpr int ROWS = SHORT ? 16 : 128;          // query rows per CTA
+    constexpr int ROWS = SHORT ? 16 : 64 * long_row_blocks(HD_MAX, SHORT);   // query rows per CTA
     constexpr int WARP_KEYS = SHORT ? 16 : KT;      // keys of a tile that one warp scores
     constexpr int NSB = WARP_KEYS / 8;              // n-blocks of S per warp
-    constexpr bool Q_IN_REGS = HD_MAX <= 128;
+    constexpr int R = long_row_blocks(HD_MAX, SHORT);   // 16-row blocks per warp: K/V fragments are reused R times
+    constexpr bool Q_IN_REGS = SHORT && HD_MAX <= 128;
     constexpr int NST = attn_stages(HD_MAX, SHORT);    // K/V tiles in shared memory (NST - 1 in flight)
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -185,28 +192,45 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     // One row of 64 keys (threads 0..63) or 64 values (threads 64..127) per thread and tile: a single bulk copy
     // of the row's hd*2 bytes, counted on the tile's barrier.  A row that no query of this CTA may see (before
     // the window, past the last position, or in another chunk) is not read: its slot is filled with zeros.
-    auto load_tile = [&](int buf, int tile_start) {
+    // The page id this thread will need for the tile that starts at `tile_start`, read ahead of time so that the
+    // copy can be issued without waiting for the table: -2 = nothing to fetch there (no query of this CTA sees
+    // it), -1 = the table has no page although one is needed (flagged when the tile is issued).
+    auto lookup = [&](int tile_start) -> int {
+        int t_first, span;
+        if constexpr (TMA) {
+            if (tid >= tma_ops) return -2;
+            t_first = tile_start + ((tid >> 1) / col_blocks) * a.page_size;
+            span = a.page_size;
+        } else {
+            if (tid >= 2 * KT) return -2;
+            t_first = tile_start + (tid & (KT - 1));
+            span = 1;
+        }
+        if (!(t_first + span > kr.t_lo && t_first < k_end)) return -2;
+        const int page = table[t_first / a.page_size];
+        return (page < 0 || page >= a.n_pages) ? -1 : page;
+    };
+
+    // TMA mode: thread number = copy number: (K or V, page of the tile, 64-column block), one tensor-map copy each.
+    // Otherwise: one row of 64 keys (threads 0..63) or 64 values (threads 64..127) per thread: a bulk copy of the
+    // row's hd*2 bytes.  Copies are counted on the tile's barrier.  What no query of this CTA may see (before the
+    // window, past the last position, or in another chunk) is not read.
+    auto load_tile = [&](int buf, int tile_start, int page) {
+        const uint32_t bar = smem_u32(&full[buf]);
         if constexpr (TMA) {
             if (tid >= tma_ops) return;
             const bool is_v = tid & 1;
             const int rest = tid >> 1;
             const int cb = rest % col_blocks, pj = rest / col_blocks;
-            const int t_first = tile_start + pj * a.page_size;
-            const uint32_t bar = smem_u32(&full[buf]);
-            bool valid = t_first + a.page_size > kr.t_lo && t_first < k_end;
-            if (valid) {
-                const int page = table[t_first / a.page_size];
-                if (page < 0 || page >= a.n_pages) {
-                    atomicOr(a.status, FB_STATUS_BAD_PAGE);
-                    valid = false;
-                } else {
-                    __nv_bfloat16* dst = (is_v ? Vs : Ks) + buf * TILE_ELEMS + cb * (KT * 64) + pj * a.page_size * 64;
-                    mbar_expect_tx(bar, (uint32_t)(a.page_size * 128));
-                    tma_load_2d(smem_u32(dst), is_v ? &a.map_v : &a.map_k, bar, cb * 64,
-                                (page * a.nkv + kvh) * a.page_size);
-                }
+            if (page >= 0) {
+                __nv_bfloat16* dst = (is_v ? Vs : Ks) + buf * TILE_ELEMS + cb * (KT * 64) + pj * a.page_size * 64;
+                mbar_expect_tx(bar, (uint32_t)(a.page_size * 128));
+                tma_load_2d(smem_u32(dst), is_v ? &a.map_v : &a.map_k, bar, cb * 64,
+                            (page * a.nkv + kvh) * a.page_size);
+            } else {
+                if (page == -1) atomicOr(a.status, FB_STATUS_BAD_PAGE);
+                mbar_arrive(bar);                     // stale (finite) data stays in the slot; it is masked
             }
-            if (!valid) mbar_arrive(bar);
             return;
         }
         if (tid >= 2 * KT) return;
@@ -214,20 +238,12 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
         const bool is_v = tid >= KT;
         const int t = tile_start + r;
         __nv_bfloat16* dst = (is_v ? Vs : Ks) + buf * TILE_ELEMS + r * LDS;
-        const uint32_t bar = smem_u32(&full[buf]);
-        bool valid = t >= kr.t_lo && t < k_end;
-        if (valid) {
-            const int page = table[t / a.page_size];
-            if (page < 0 || page >= a.n_pages) {
-                atomicOr(a.status, FB_STATUS_BAD_PAGE);
-                valid = false;
-            } else {
-                const size_t off = (((size_t)page * a.nkv + kvh) * a.page_size + (t % a.page_size)) * hd;
-                mbar_expect_tx(bar, (uint32_t)(hd * 2));
-                bulk_copy_g2s(smem_u32(dst), (is_v ? a.v_pool : a.k_pool) + off, (uint32_t)(hd * 2), bar);
-            }
-        }
-        if (!valid) {
+        if (page >= 0) {
+            const size_t off = (((size_t)page * a.nkv + kvh) * a.page_size + (t % a.page_size)) * hd;
+            mbar_expect_tx(bar, (uint32_t)(hd * 2));
+            bulk_copy_g2s(smem_u32(dst), (is_v ? a.v_pool : a.k_pool) + off, (uint32_t)(hd * 2), bar);
+        } else {
+            if (page == -1) atomicOr(a.status, FB_STATUS_BAD_PAGE);
             for (int c = 0; c < hd_chunks; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
             // order these generic stores before a later bulk copy into the same row
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -235,38 +251,49 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
         }
     };
 
-    // prologue: NST - 1 tiles in flight
+    // prologue: NST - 1 tiles in flight; the page id for the tile after them is already on its way
+    int next_page = lookup(k_begin);
 #pragma unroll
     for (int st = 0; st < NST - 1; ++st)
-        if (st < n_tiles) load_tile(st, k_begin + st * KT);
+        if (st < n_tiles) {
+            load_tile(st, k_begin + st * KT, next_page);
+            next_page = lookup(k_begin + (st + 1) * KT);
+        }
 
-    const int row_base = SHORT ? 0 : warp * 16;       // first row of this warp within the CTA
-    const int key0 = SHORT ? warp * 16 : 0;           // first key of this warp within a tile
+    const int row_base = SHORT ? 0 : warp * (16 * R);   // first row of this warp within the CTA
+    const int key0 = SHORT ? warp * 16 : 0;             // first key of this warp within a tile
     uint32_t qf[Q_IN_REGS ? NKS : 1][4];
     if (Q_IN_REGS) {
 #pragma unroll
         for (int ks = 0; ks < NKS; ++ks)
             ldmatrix_x4(qf[ks], Qs + (row_base + (lane & 15)) * LDS + ks * 16 + 8 * (lane >> 4));
     }
-    // per-thread rows: r0 = row_base + lane/4 and r0 + 8
-    int p_row[2], t0_row[2];
+    // per-thread rows of row block rb: row_base + 16*rb + lane/4 and that + 8
+    int p_row[R][2], t0_row[R][2];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int r = row_base + (lane >> 2) + 8 * h;
-        if (r < rows_valid) {
-            p_row[h] = pos0 + tok0 + r / G;
-            t0_row[h] = (a.window > 0 && p_row[h] - a.window + 1 > 0) ? p_row[h] - a.window + 1 : 0;
-        } else {
-            p_row[h] = -1;                            // sees nothing
-            t0_row[h] = 0;
+    for (int rb = 0; rb < R; ++rb)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = row_base + 16 * rb + (lane >> 2) + 8 * h;
+            if (r < rows_valid) {
+                p_row[rb][h] = pos0 + tok0 + r / G;
+                t0_row[rb][h] = (a.window > 0 && p_row[rb][h] - a.window + 1 > 0) ? p_row[rb][h] - a.window + 1 : 0;
+            } else {
+                p_row[rb][h] = -1;                    // sees nothing
+                t0_row[rb][h] = 0;
+            }
         }
+    float m_run[R][2], l_run[R][2];
+    float o[R][NDB][4];
+#pragma unroll
+    for (int rb = 0; rb < R; ++rb) {
+        m_run[rb][0] = m_run[rb][1] = -INFINITY;
+        l_run[rb][0] = l_run[rb][1] = 0.0f;
+#pragma unroll
+        for (int d = 0; d < NDB; ++d)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[rb][d][e] = 0.0f;
     }
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-    float o[NDB][4];
-#pragma unroll
-    for (int d = 0; d < NDB; ++d)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) o[d][e] = 0.0f;
 
     for (int it = 0; it < n_tiles; ++it) {
         const int buf = it % NST;
@@ -274,7 +301,10 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
         if (!mbar_wait(smem_u32(&full[buf]), (uint32_t)(it / NST) & 1u, a.status)) *bail = 1;
         __syncthreads();                              // every thread is past tile it-1: its buffer is free
         if (*bail) break;
-        if (it + NST - 1 < n_tiles) load_tile((it + NST - 1) % NST, tile_start + (NST - 1) * KT);
+        if (it + NST - 1 < n_tiles) {
+            load_tile((it + NST - 1) % NST, tile_start + (NST - 1) * KT, next_page);
+            next_page = lookup(tile_start + NST * KT);    // consumed one iteration from now
+        }
         if constexpr (TMA) {
             // Whole pages arrive, the slots behind the last position included, and what a page holds there was
             // never written by this request.  Scores of such keys are masked by assignment, but their values
@@ -294,109 +324,131 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
         const __nv_bfloat16* kt = Ks + buf * TILE_ELEMS;
         const __nv_bfloat16* vt = Vs + buf * TILE_ELEMS;
 
-        // ---- S = Q K^T for this warp's rows and keys ----
-        float s[NSB][4];
+        // ---- S = Q K^T for this warp's rows and keys: every K fragment serves all R row blocks ----
+        float s[R][NSB][4];
 #pragma unroll
-        for (int nb = 0; nb < NSB; ++nb)
+        for (int rb = 0; rb < R; ++rb)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) s[nb][e] = 0.0f;
+            for (int nb = 0; nb < NSB; ++nb)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[rb][nb][e] = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < NKS; ks += 2) {
-            uint32_t qa[4], qb[4];
-            if (Q_IN_REGS) {
+            uint32_t qa[R][4], qb[R][4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) { qa[e] = qf[ks][e]; qb[e] = qf[ks + 1][e]; }
-            } else {
-                ldmatrix_x4(qa, Qs + (row_base + (lane & 15)) * LDS + ks * 16 + 8 * (lane >> 4));
-                ldmatrix_x4(qb, Qs + (row_base + (lane & 15)) * LDS + (ks + 1) * 16 + 8 * (lane >> 4));
+            for (int rb = 0; rb < R; ++rb) {
+                if (Q_IN_REGS) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { qa[rb][e] = qf[ks][e]; qb[rb][e] = qf[ks + 1][e]; }
+                } else {
+                    const __nv_bfloat16* qrow = Qs + (row_base + 16 * rb + (lane & 15)) * LDS + 8 * (lane >> 4);
+                    ldmatrix_x4(qa[rb], qrow + ks * 16);
+                    ldmatrix_x4(qb[rb], qrow + (ks + 1) * 16);
+                }
             }
 #pragma unroll
             for (int nb = 0; nb < NSB; ++nb) {
                 uint32_t b[4];     // (b0,b1): dims ks*16..+15, (b2,b3): dims (ks+1)*16..+15, keys nb*8..+7
                 ldmatrix_x4(b, tile_at<HD_MAX, TMA>(kt, key0 + nb * 8 + (lane & 7), ks * 16 + 8 * (lane >> 3)));
-                mma_bf16(s[nb], qa, b[0], b[1]);
-                mma_bf16(s[nb], qb, b[2], b[3]);
+#pragma unroll
+                for (int rb = 0; rb < R; ++rb) {
+                    mma_bf16(s[rb][nb], qa[rb], b[0], b[1]);
+                    mma_bf16(s[rb][nb], qb[rb], b[2], b[3]);
+                }
             }
         }
         // ---- scale, mask, online softmax ----
-        float tile_max[2] = {-INFINITY, -INFINITY};
+        uint32_t pa[R][WARP_KEYS / 16][4];            // the probabilities as A fragments of P V
 #pragma unroll
-        for (int nb = 0; nb < NSB; ++nb)
+        for (int rb = 0; rb < R; ++rb) {
+            float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int h = e >> 1;
-                const int t = tile_start + key0 + nb * 8 + 2 * (lane & 3) + (e & 1);
-                const bool ok = t >= t0_row[h] && t <= p_row[h] && t < k_end;
-                const float v = ok ? s[nb][e] * a.scale_log2e : -INFINITY;
-                s[nb][e] = v;
-                tile_max[h] = fmaxf(tile_max[h], v);
+            for (int nb = 0; nb < NSB; ++nb)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int h = e >> 1;
+                    const int t = tile_start + key0 + nb * 8 + 2 * (lane & 3) + (e & 1);
+                    const bool ok = t >= t0_row[rb][h] && t <= p_row[rb][h] && t < k_end;
+                    const float v = ok ? s[rb][nb][e] * a.scale_log2e : -INFINITY;
+                    s[rb][nb][e] = v;
+                    tile_max[h] = fmaxf(tile_max[h], v);
+                }
+            float corr[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float tm = tile_max[h];
+                tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
+                tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
+                const float m_new = fmaxf(m_run[rb][h], tm);
+                const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;     // a row that has seen nothing yet
+                corr[h] = exp2f(m_run[rb][h] - m_use);
+                m_run[rb][h] = m_new;
+                float sum = 0.0f;
+#pragma unroll
+                for (int nb = 0; nb < NSB; ++nb) {
+                    const float p0 = exp2f(s[rb][nb][2 * h] - m_use), p1 = exp2f(s[rb][nb][2 * h + 1] - m_use);
+                    s[rb][nb][2 * h] = p0;
+                    s[rb][nb][2 * h + 1] = p1;
+                    sum += p0 + p1;
+                }
+                l_run[rb][h] = l_run[rb][h] * corr[h] + sum;
             }
-        float corr[2];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            float tm = tile_max[h];
-            tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
-            tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
-            const float m_new = fmaxf(m_run[h], tm);
-            const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;     // a row that has seen nothing yet
-            corr[h] = exp2f(m_run[h] - m_use);
-            m_run[h] = m_new;
-            float sum = 0.0f;
-#pragma unroll
-            for (int nb = 0; nb < NSB; ++nb) {
-                const float p0 = exp2f(s[nb][2 * h] - m_use), p1 = exp2f(s[nb][2 * h + 1] - m_use);
-                s[nb][2 * h] = p0;
-                s[nb][2 * h + 1] = p1;
-                sum += p0 + p1;
+            for (int d = 0; d < NDB; ++d) {
+                o[rb][d][0] *= corr[0]; o[rb][d][1] *= corr[0];
+                o[rb][d][2] *= corr[1]; o[rb][d][3] *= corr[1];
             }
-            l_run[h] = l_run[h] * corr[h] + sum;
-        }
 #pragma unroll
-        for (int d = 0; d < NDB; ++d) {
-            o[d][0] *= corr[0]; o[d][1] *= corr[0];
-            o[d][2] *= corr[1]; o[d][3] *= corr[1];
+            for (int kk = 0; kk < WARP_KEYS / 16; ++kk) {
+                pa[rb][kk][0] = pack_bf16(s[rb][2 * kk][0], s[rb][2 * kk][1]);
+                pa[rb][kk][1] = pack_bf16(s[rb][2 * kk][2], s[rb][2 * kk][3]);
+                pa[rb][kk][2] = pack_bf16(s[rb][2 * kk + 1][0], s[rb][2 * kk + 1][1]);
+                pa[rb][kk][3] = pack_bf16(s[rb][2 * kk + 1][2], s[rb][2 * kk + 1][3]);
+            }
         }
-        // ---- O += P V ----
+        // ---- O += P V: every V fragment serves all R row blocks ----
 #pragma unroll
         for (int kk = 0; kk < WARP_KEYS / 16; ++kk) {
-            uint32_t pa[4];
-            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
             for (int d = 0; d < NDB; d += 2) {
                 uint32_t b[4];     // (b0,b1): dims d*8..+7, (b2,b3): dims (d+1)*8..+7, keys kk*16..+15
                 ldmatrix_x4_trans(b, tile_at<HD_MAX, TMA>(vt, key0 + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1),
                                                           d * 8 + 8 * (lane >> 4)));
-                mma_bf16(o[d], pa, b[0], b[1]);
-                mma_bf16(o[d + 1], pa, b[2], b[3]);
+#pragma unroll
+                for (int rb = 0; rb < R; ++rb) {
+                    mma_bf16(o[rb][d], pa[rb][kk], b[0], b[1]);
+                    mma_bf16(o[rb][d + 1], pa[rb][kk], b[2], b[3]);
+                }
             }
         }
     }
     __syncthreads();                                  // every warp is done with the tiles
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
-    }
+    for (int rb = 0; rb < R; ++rb)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            l_run[rb][h] += __shfl_xor_sync(0xffffffffu, l_run[rb][h], 1);
+            l_run[rb][h] += __shfl_xor_sync(0xffffffffu, l_run[rb][h], 2);
+        }
 
     if (!SHORT) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int r = row_base + (lane >> 2) + 8 * h;
-            if (r >= rows_valid) continue;
-            const float inv = l_run[h] > 0.0f ? 1.0f / l_run[h] : 0.0f;
-            const int token = q_start + tok0 + r / G, head = kvh * G + r % G;
-            __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd;
+        for (int rb = 0; rb < R; ++rb)
 #pragma unroll
-            for (int d = 0; d < NDB; ++d) {
-                const int col = d * 8 + 2 * (lane & 3);
-                if (col < hd)
-                    *reinterpret_cast<__nv_bfloat162*>(dst + col) =
-                        __floats2bfloat162_rn(o[d][2 * h] * inv, o[d][2 * h + 1] * inv);
+            for (int h = 0; h < 2; ++h) {
+                const int r = row_base + 16 * rb + (lane >> 2) + 8 * h;
+                if (r >= rows_valid) continue;
+                const float inv = l_run[rb][h] > 0.0f ? 1.0f / l_run[rb][h] : 0.0f;
+                const int token = q_start + tok0 + r / G, head = kvh * G + r % G;
+                __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd;
+#pragma unroll
+                for (int d = 0; d < NDB; ++d) {
+                    const int col = d * 8 + 2 * (lane & 3);
+                    if (col < hd)
+                        *reinterpret_cast<__nv_bfloat162*>(dst + col) =
+                            __floats2bfloat162_rn(o[rb][d][2 * h] * inv, o[rb][d][2 * h + 1] * inv);
+                }
             }
-        }
         return;
     }
 
@@ -410,12 +462,12 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
 #pragma unroll
         for (int d = 0; d < NDB; ++d) {
             const int col = d * 8 + 2 * (lane & 3);
-            so[(warp * 16 + r) * HD_MAX + col] = o[d][2 * h];
-            so[(warp * 16 + r) * HD_MAX + col + 1] = o[d][2 * h + 1];
+            so[(warp * 16 + r) * HD_MAX + col] = o[0][d][2 * h];
+            so[(warp * 16 + r) * HD_MAX + col + 1] = o[0][d][2 * h + 1];
         }
         if ((lane & 3) == 0) {
-            sml[(warp * 16 + r) * 2] = m_run[h];
-            sml[(warp * 16 + r) * 2 + 1] = l_run[h];
+            sml[(warp * 16 + r) * 2] = m_run[0][h];
+            sml[(warp * 16 + r) * 2 + 1] = l_run[0][h];
         }
     }
     __syncthreads();
@@ -506,7 +558,7 @@ attention_merge_kernel(const AttnArgs a) {
 }
 
 __host__ __device__ constexpr size_t attn_smem_bytes(int hd_max, bool short_rows, bool tma) {
-    return (size_t)(short_rows ? 16 : 128) * (hd_max + 8) * 2 + 1024 /* tile alignment */ +
+    return (size_t)(short_rows ? 16 : 64 * long_row_blocks(hd_max, false)) * (hd_max + 8) * 2 + 1024 /* alignment */ +
            (size_t)2 * attn_stages(hd_max, short_rows) * KT * (tma ? hd_max : hd_max + 8) * 2 + 64 /* barriers */;
 }
 
@@ -530,7 +582,7 @@ int launch_attention_mma(const AttnArgs& a, bool tma, int n_seqs, int max_q_len,
                          cudaStream_t stream) {
     const int G = a.nh / a.nkv;
     if (any_long) {
-        const int TQ = 128 / G;
+        const int TQ = 64 * long_row_blocks(HD_MAX, false) / G;
         const dim3 grid((max_q_len + TQ - 1) / TQ, a.nkv, n_seqs);
         int rc;
         if constexpr (HD_MAX >= 64) {
