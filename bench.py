@@ -75,7 +75,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -109,7 +109,7 @@ class ClockSampler:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
@@ -243,16 +243,17 @@ def main(argv=None) -> int:
         return statistics.median(times)
 
     # ---- measurements ----------------------------------------------------------
-    with ClockSampler(dev.index or 0) as clocks:
+    with ClockSampler(dev.index or 0) as clocks:        # clocks and throttle reasons while the timed regions run
+        time.sleep(0.3)                                 # let nvidia-smi start reporting before the first region
         ms_step, launches = decode_device(args.batch, args.steps, args.warmup)
+        e2e_value, h2d, d2h = decode_e2e(args.batch, args.steps, args.warmup)
+        points = {}
+        if not args.skip_points:
+            for b in (1, 64):
+                ms_b, _ = decode_device(b, max(8, args.steps // 2), 3)
+                points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
+        pre_ms = prefill(args.prefill_tokens)
     clock_summary = clocks.summary()
-    e2e_value, h2d, d2h = decode_e2e(args.batch, args.steps, args.warmup)
-    points = {}
-    if not args.skip_points:
-        for b in (1, 64):
-            ms_b, _ = decode_device(b, max(8, args.steps // 2), 3)
-            points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
-    pre_ms = prefill(args.prefill_tokens)
 
     # ---- accounting --------------------------------------------------------------
     weight_bytes = engine.model.step_weight_bytes()
