@@ -29,6 +29,7 @@
 #include "tensor_map.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 
 namespace {
 
@@ -76,7 +77,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 }
 
 template <int BN> struct TileCfg {
-    static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
+    // A stage holds KA swizzle atoms of K (64 elements each) of both operands.  (Two atoms a stage, which make
+    // every visit to a weight row 256 contiguous bytes, were measured for the 16-token tile: no gain over one.)
+    static constexpr int KA = 1;
+    static constexpr int KSTEP = KA * BK;                   // elements of K per stage
+    static constexpr int ATOM_BYTES = BM * BK * 2 + BN * BK * 2;
+    static constexpr int STAGE_BYTES = KA * ATOM_BYTES;
     static constexpr int STAGES = BN == 16 ? 6 : BN == 32 ? 5 : BN == 64 ? 4 : BN == 128 ? 3 : 4;
     static constexpr int ACC_COLS = BN < 32 ? 32 : BN;      // tensor-memory columns of one accumulator
     static constexpr int TMEM_COLS = 2 * ACC_COLS;          // two accumulators: the epilogue of one unit of work
@@ -121,7 +127,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     fb_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kb_total = (K + BK - 1) / BK;
+    const int kb_total = (K + Cfg::KSTEP - 1) / Cfg::KSTEP;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
@@ -162,13 +168,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     for (int j = 0; j < pre; ++j) {
                         const uint32_t full = smem_u32(&bars[j]);
                         mbar_expect_tx(full, (uint32_t)Cfg::STAGE_BYTES);
-                        tma_load_2d(smem_u32(smem + (size_t)j * Cfg::STAGE_BYTES), &map_w, full,
-                                    (w.kb_begin + j) * BK, w.n0);
+#pragma unroll
+                        for (int a = 0; a < Cfg::KA; ++a)
+                            tma_load_2d(smem_u32(smem + (size_t)j * Cfg::STAGE_BYTES + a * Cfg::ATOM_BYTES), &map_w, full,
+                                        (w.kb_begin + j) * Cfg::KSTEP + a * BK, w.n0);
                     }
                     fb_pdl_wait();
                     for (int j = 0; j < pre; ++j)
-                        tma_load_2d(smem_u32(smem + (size_t)j * Cfg::STAGE_BYTES + BM * BK * 2), &map_x,
-                                    smem_u32(&bars[j]), (w.kb_begin + j) * BK, m0);
+#pragma unroll
+                        for (int a = 0; a < Cfg::KA; ++a)
+                            tma_load_2d(smem_u32(smem + (size_t)j * Cfg::STAGE_BYTES + a * Cfg::ATOM_BYTES + BM * BK * 2),
+                                        &map_x, smem_u32(&bars[j]), (w.kb_begin + j) * Cfg::KSTEP + a * BK, m0);
                     i = pre;
                     it = (uint32_t)pre;
                 }
@@ -179,9 +189,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     const uint32_t full = smem_u32(&bars[s]);
                     mbar_expect_tx(full, (uint32_t)Cfg::STAGE_BYTES);
                     uint8_t* stage = smem + (size_t)s * Cfg::STAGE_BYTES;
-                    const int k0 = (w.kb_begin + i) * BK;
-                    tma_load_2d(smem_u32(stage), &map_w, full, k0, w.n0);
-                    tma_load_2d(smem_u32(stage + BM * BK * 2), &map_x, full, k0, m0);
+                    const int k0 = (w.kb_begin + i) * Cfg::KSTEP;
+#pragma unroll
+                    for (int a = 0; a < Cfg::KA; ++a) {
+                        tma_load_2d(smem_u32(stage + a * Cfg::ATOM_BYTES), &map_w, full, k0 + a * BK, w.n0);
+                        tma_load_2d(smem_u32(stage + a * Cfg::ATOM_BYTES + BM * BK * 2), &map_x, full, k0 + a * BK, m0);
+                    }
                 }
             }
             if (first) fb_pdl_wait();
@@ -209,13 +222,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     uint8_t* stage = smem + (size_t)s * Cfg::STAGE_BYTES;
-                    const uint64_t da = umma_desc(smem_u32(stage));
-                    const uint64_t db = umma_desc(smem_u32(stage + BM * BK * 2));
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // 16 elements of K = 32 bytes further along the swizzled row
-                        umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
-                                  (i > 0 || k > 0) ? 1u : 0u);
+                    for (int a = 0; a < Cfg::KA; ++a) {
+                        const uint64_t da = umma_desc(smem_u32(stage + a * Cfg::ATOM_BYTES));
+                        const uint64_t db = umma_desc(smem_u32(stage + a * Cfg::ATOM_BYTES + BM * BK * 2));
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            // 16 elements of K = 32 bytes further along the swizzled row
+                            umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
+                                      (i > 0 || a > 0 || k > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit(smem_u32(&bars[S + s]));            // frees the stage when the MMAs have read it
                 }
@@ -362,8 +378,9 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
     using Cfg = TileCfg<BN>;
     const int tiles_n = (N + BM - 1) / BM, tiles_m = (M + BN - 1) / BN;
     const int tiles = tiles_n * tiles_m;
-    const int kb_total = (K + BK - 1) / BK;
-    const int per_sm = Cfg::SMEM_BYTES <= 113 * 1024 ? 2 : 1;
+    const int kb_total = (K + Cfg::KSTEP - 1) / Cfg::KSTEP;
+    int per_sm = Cfg::SMEM_BYTES <= 113 * 1024 ? 2 : 1;
+    if (const char* env = getenv("FLAMBEAU_GEMM_CTAS_PER_SM")) per_sm = atoi(env) >= 2 ? per_sm : 1;   // experiment knob
     const int slots = 148 * per_sm;
     // One more share = one more float32 copy of the output, written and read once at about HBM speed.  A k-block
     // of one CTA takes its stage bytes at the CTA's part of that speed when the weights stream from DRAM (few
