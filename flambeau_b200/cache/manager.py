@@ -27,7 +27,7 @@ from typing import Optional
 import torch
 
 from ..parts.base import KVRequirement, StateRequirement
-from .pages import OutOfPages, PageError, PagePool
+from .pages import OutOfPages, PageError, PageList, PagePool
 
 
 @dataclass
@@ -141,7 +141,7 @@ class CacheManager:
         slot = self._free_slots.pop()
         for t in self.state.values():
             t[slot].zero_()                      # a fresh request starts from zero state
-        rec = RequestRecord(request_id, slot, pages=[[] for _ in self.groups])
+        rec = RequestRecord(request_id, slot, pages=[PageList() for _ in self.groups])
         self.requests[request_id] = rec
         return rec
 
@@ -177,6 +177,30 @@ class CacheManager:
             rec.pages[gi].extend(g.pool.take(needs[gi]))
         rec.reserved_to = max(rec.reserved_to, end)
 
+    def reserve_all(self, needs: list) -> None:
+        """reserve() for several (request_id, n_new) at once: every request gets its pages, or none does."""
+        page, limit = self.page_size, self.max_pages_per_request * self.page_size
+        want = []
+        total = [0] * len(self.groups)
+        for rid, n_new in needs:
+            rec = self.requests[rid]
+            end = rec.length + n_new
+            if end > limit:
+                raise PageError(f"request {rid!r} would reach {end} tokens; the cache holds at most {limit} per request")
+            pages_to = -(-end // page)
+            row = [max(0, pages_to - len(rec.pages[gi])) for gi in range(len(self.groups))]
+            for gi, k in enumerate(row):
+                total[gi] += k
+            want.append((rec, end, row))
+        for gi, g in enumerate(self.groups):
+            if total[gi] > g.pool.n_free:
+                raise OutOfPages(total[gi], g.pool.n_free, g.pool.n_pages)
+        for rec, end, row in want:
+            for gi, k in enumerate(row):
+                if k:
+                    rec.pages[gi].extend(self.groups[gi].pool.take(k))
+            rec.reserved_to = max(rec.reserved_to, end)
+
     def commit(self, request_id, n_new: int) -> None:
         """The step that wrote `n_new` tokens is launched: advance the length and give back the pages that
         no later query can see.  (Kernels of later steps run after this step's on the same stream, so a page
@@ -191,18 +215,15 @@ class CacheManager:
                 continue
             first_live = rec.length - w + 1           # lowest position a future query can see
             dead_pages = max(0, first_live) // self.page_size
-            pages = rec.pages[gi]
-            back = [p for p in pages[:dead_pages] if p >= 0]
+            back = rec.pages[gi].give_back_prefix(dead_pages)
             if back:
                 g.pool.give_back(back)
-                for j in range(min(dead_pages, len(pages))):
-                    pages[j] = -1
 
     def release(self, request_id) -> None:
         rec = self.requests.pop(request_id)
         for gi, g in enumerate(self.groups):
-            g.pool.give_back([p for p in rec.pages[gi] if p >= 0])
-            rec.pages[gi] = []
+            g.pool.give_back(rec.pages[gi].live())
+            rec.pages[gi] = PageList()
         self._free_slots.append(rec.slot)
 
     def release_all(self) -> None:

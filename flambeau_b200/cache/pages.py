@@ -8,6 +8,8 @@ from __future__ import annotations
 
 from collections import deque
 
+import numpy as np
+
 
 class PageError(RuntimeError):
     pass
@@ -57,3 +59,50 @@ class PagePool:
 
     def is_held(self, page: int) -> bool:
         return self._held[page]
+
+
+class PageList:
+    """The physical pages of one request in one group, by logical page index (-1 = given back), kept in a
+    numpy array so that a block-table row is one memory copy."""
+    __slots__ = ("arr", "n", "first_live")
+
+    def __init__(self, capacity: int = 16):
+        self.arr = np.full(max(capacity, 1), -1, dtype=np.int32)
+        self.n = 0
+        self.first_live = 0              # logical pages below this index have been given back
+
+    def __len__(self) -> int:
+        return self.n
+
+    def __iter__(self):
+        return iter(self.arr[:self.n].tolist())
+
+    def __getitem__(self, i):
+        return self.arr[:self.n][i]
+
+    def extend(self, pages) -> None:
+        k = len(pages)
+        if self.n + k > self.arr.size:
+            grown = np.full(max(2 * self.arr.size, self.n + k), -1, dtype=np.int32)
+            grown[:self.n] = self.arr[:self.n]
+            self.arr = grown
+        self.arr[self.n:self.n + k] = pages
+        self.n += k
+
+    def give_back_prefix(self, upto: int) -> list:
+        """Mark logical pages [first_live, upto) as given back and return their ids."""
+        upto = min(upto, self.n)
+        if upto <= self.first_live:
+            return []
+        back = self.arr[self.first_live:upto]
+        out = back[back >= 0].tolist()
+        self.arr[self.first_live:upto] = -1
+        self.first_live = upto
+        return out
+
+    def live(self) -> list:
+        a = self.arr[self.first_live:self.n]
+        return a[a >= 0].tolist()
+
+    def view(self) -> np.ndarray:
+        return self.arr[:self.n]

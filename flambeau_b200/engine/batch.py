@@ -67,60 +67,75 @@ class BatchBuffers:
         self.np_rows = self.h_rows.numpy()
         self.np_seqs = self.h_seqs.numpy()
         self.np_tables = self.h_tables.numpy()
+        self._fill = [[0] * max_seqs for _ in range(max(n_groups, 1))]     # valid entries last written per table row
 
     def build(self, entries: list, cache, vocab_size: int) -> StepBatch:
         """Validate the entries against the cache manager's records and pack them.
         Pages for the new tokens must have been reserved already."""
         b = StepBatch()
         b.entries = entries
-        if not entries:
+        S = len(entries)
+        if not S:
             raise BatchError("a step needs at least one entry")
-        if len(entries) > self.max_seqs:
-            raise BatchError(f"{len(entries)} entries in one step; the engine was built for {self.max_seqs}")
-        seen = set()
-        row = 0
-        out_rows = []
+        if S > self.max_seqs:
+            raise BatchError(f"{S} entries in one step; the engine was built for {self.max_seqs}")
+        ids = [e.request_id for e in entries]
+        if len(set(ids)) != S:
+            raise BatchError("a request appears twice in one step")
+        recs = [cache.requests[rid] for rid in ids]
+        q_len = [len(e.tokens) for e in entries]
+        if min(q_len) == 0:
+            raise BatchError("a request brings no tokens")
+        pos0 = [r.length for r in recs]
+        n = sum(q_len)
+        if n > self.max_tokens:
+            raise BatchError(f"the step has {n} tokens; the engine was built for {self.max_tokens} a step")
         rows, seqs, tables = self.np_rows, self.np_seqs, self.np_tables
+        decode_only = n == S
+        if decode_only:
+            starts = list(range(S))
+            rows[0, :S] = [e.tokens[0] for e in entries]
+            rows[1, :S] = pos0
+            rows[2, :S] = starts
+        else:
+            starts, acc = [], 0
+            for k in q_len:
+                starts.append(acc)
+                acc += k
+            rows[0, :n] = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+            rows[1, :n] = np.concatenate([np.arange(p, p + k) for p, k in zip(pos0, q_len)])
+            rows[2, :n] = np.repeat(np.arange(S), q_len)
+        toks = rows[0, :n]
+        if int(toks.min()) < 0 or int(toks.max()) >= vocab_size:
+            raise BatchError(f"token id outside [0, {vocab_size})")
+        out_rows = []
         for s, e in enumerate(entries):
-            if e.request_id in seen:
-                raise BatchError(f"request {e.request_id!r} appears twice in one step")
-            seen.add(e.request_id)
-            q_len = len(e.tokens)
-            if q_len == 0:
-                raise BatchError(f"request {e.request_id!r} brings no tokens")
-            if row + q_len > self.max_tokens:
-                raise BatchError(f"the step has more than {self.max_tokens} tokens")
-            rec = cache.requests[e.request_id]
-            toks = np.asarray(e.tokens, dtype=np.int64)
-            if toks.min() < 0 or toks.max() >= vocab_size:
-                raise BatchError(f"request {e.request_id!r}: token id outside [0, {vocab_size})")
-            pos0 = rec.length
-            if pos0 + q_len > rec.reserved_to:
-                raise BatchError(f"request {e.request_id!r}: pages for positions up to {pos0 + q_len} are not reserved")
-            rows[0, row:row + q_len] = toks
-            rows[1, row:row + q_len] = np.arange(pos0, pos0 + q_len)
-            rows[2, row:row + q_len] = s
+            if pos0[s] + q_len[s] > recs[s].reserved_to:
+                raise BatchError(f"request {e.request_id!r}: pages for positions up to {pos0[s] + q_len[s]} are not reserved")
             for w in e.want:
-                if not 0 <= w < q_len:
-                    raise BatchError(f"request {e.request_id!r}: wanted place {w} is outside its {q_len} tokens")
-                out_rows.append(row + w)
-            seqs[0, s], seqs[1, s], seqs[2, s], seqs[3, s] = row, q_len, pos0, rec.slot
-            for gi in range(cache.n_groups):
-                pages = rec.pages[gi]
-                if len(pages) > self.max_pages:
-                    raise BatchError(f"request {e.request_id!r} holds {len(pages)} pages; tables have {self.max_pages}")
-                tables[gi, s, :len(pages)] = pages
-                tables[gi, s, len(pages):] = -1
-            b.seq_q_start.append(row)
-            b.seq_q_len.append(q_len)
-            b.seq_pos_start.append(pos0)
-            b.seq_slot.append(rec.slot)
-            b.max_q_len = max(b.max_q_len, q_len)
-            b.max_kv_len = max(b.max_kv_len, pos0 + q_len)
-            row += q_len
-        n, S, n_out = row, len(entries), len(out_rows)
+                if not 0 <= w < q_len[s]:
+                    raise BatchError(f"request {e.request_id!r}: wanted place {w} is outside its {q_len[s]} tokens")
+                out_rows.append(starts[s] + w)
+        n_out = len(out_rows)
         if n_out:
             rows[3, :n_out] = out_rows
+        seqs[0, :S], seqs[1, :S], seqs[2, :S] = starts, q_len, pos0
+        seqs[3, :S] = [r.slot for r in recs]
+        fill = self._fill
+        for gi in range(cache.n_groups):
+            for s, rec in enumerate(recs):
+                pages = rec.pages[gi]
+                k = pages.n
+                if k > self.max_pages:
+                    raise BatchError(f"request {ids[s]!r} holds {k} pages; tables have {self.max_pages}")
+                tables[gi, s, :k] = pages.arr[:k]
+                if fill[gi][s] > k:
+                    tables[gi, s, k:fill[gi][s]] = -1          # what an earlier step's request left in this row
+                fill[gi][s] = k
+        b.seq_q_start, b.seq_q_len, b.seq_pos_start = starts, q_len, pos0
+        b.seq_slot = [r.slot for r in recs]
+        b.max_q_len = max(q_len)
+        b.max_kv_len = max(p + k for p, k in zip(pos0, q_len))
         b.n_tokens, b.n_seqs, b.n_out = n, S, n_out
         # ---- three copies to the device ----
         width = max(n, n_out)

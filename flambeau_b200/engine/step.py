@@ -221,23 +221,19 @@ class Engine:
                         cache.admit(e.request_id)
                         admitted.append(e.request_id)
                 needs = [(e.request_id, len(e.tokens)) for e in entries]
-                if not cache.can_reserve(needs):
-                    from ..cache.pages import OutOfPages
-                    short = [sum(cache.pages_needed(r, k)[gi] for r, k in needs) for gi in range(cache.n_groups)]
-                    raise OutOfPages(max(short), min(cache.free_pages()), cache.groups[0].pool.n_pages)
                 for rid, k in needs:
                     if cache.length(rid) + k > self.max_seq_len:
                         raise BatchError(f"request {rid!r} would reach {cache.length(rid) + k} tokens; "
                                          f"the engine was built for {self.max_seq_len} per request")
-                for rid, k in needs:
-                    cache.reserve(rid, k)
+                cache.reserve_all(needs)
+                if self._copy_pending:
+                    self._copied.synchronize()      # the staging buffers are free to be rewritten
+                batch = self.buffers.build(entries, cache, self.model.vocab_size)
             except Exception:
-                for rid in admitted:
-                    cache.release(rid)
+                for rid in admitted:                # nothing ran: requests this step brought in leave again
+                    if rid in cache.requests:
+                        cache.release(rid)
                 raise
-            if self._copy_pending:
-                self._copied.synchronize()          # the staging buffers are free to be rewritten
-            batch = self.buffers.build(entries, cache, self.model.vocab_size)
             self._copied.record()
             self._copy_pending = True
             logits = self._run(batch)
