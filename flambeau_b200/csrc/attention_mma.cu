@@ -8,10 +8,12 @@
 //         rows each, so that every K/V fragment fetched from shared memory feeds two
 //         row blocks; each walks all visible key tiles with an online softmax.
 //   SHORT (decoded tokens and portions of a few tokens, rows = tokens x G <= 16):
-//         a CTA owns one (sequence, key/value head, chunk of keys).  Its four warps
-//         share the 16 rows and split every 64-key tile; their partial (m, l, o)
-//         are merged in shared memory and written to scratch, and a second kernel
-//         merges the chunks ("split-K").
+//         the key tiles of all (sequence, key/value head) pairs of the step form one
+//         line that a fixed grid of CTAs cuts into equal stretches, so that every SM
+//         streams the same amount of cache whatever the batch looks like.  A CTA's
+//         four warps share the 16 rows and split every 64-key tile; their partial
+//         (m, l, o) are merged in shared memory.  Where a pair was cut, each of its
+//         segments goes to scratch and the CTA that arrives last adds them up.
 //
 // Keys and values come through the block table in tiles of 64 keys with
 // bulk copies through a 2-3 stage pipeline; a key outside [t0, p] of every row of the CTA is
@@ -28,7 +30,7 @@
 namespace {
 
 constexpr int KT = 64;             // keys per tile
-constexpr int ATT_THREADS = 128;   // SHORT arrangement and the merge kernel
+constexpr int ATT_THREADS = 128;   // SHORT arrangement: four warps that split each tile's keys
 constexpr int LONG_THREADS = 128;  // LONG arrangement: four warps of 32 query rows
 
 // 16-row blocks per warp of the LONG arrangement: two while the accumulators fit in registers.
@@ -72,8 +74,10 @@ struct AttnArgs {
     const int* seq_q_start; const int* seq_q_len; const int* seq_pos_start;
     int nh, nkv, hd, window;
     float scale_log2e;
-    float* part_o; float* part_ml;     // SHORT: [seq][kv head][chunk][16 rows][HD_MAX] and [..][16][2]
-    int chunk_keys, max_chunks;        // SHORT: keys per chunk, chunk slots per (seq, kv head)
+    float* part_o; float* part_ml;     // SHORT: partial results, [slot][16 rows][HD_MAX] and [slot][16][2]
+    int* part_cnt;                     // SHORT: per (sequence, key/value head), segments that have arrived; 0 at rest
+    int n_seqs;                        // sequences of the step
+    int short_ctas;                    // SHORT: CTAs of the split-key launch
     int short_rows;                    // sequences with q_len * G <= short_rows belong to the SHORT arrangement
     int* status;
 };
@@ -88,6 +92,58 @@ __device__ __forceinline__ KeyRange key_range(int p_first, int p_last, int windo
     return r;
 }
 
+// SHORT arrangement.  All key tiles of all (sequence, key/value head) pairs form one line, pair after pair (pairs
+// of one sequence side by side), and the CTAs of the launch cut that line into equal stretches: CTA c owns tiles
+// [c * per, (c + 1) * per).  A stretch may end inside a pair and go on into the next ones, so every CTA has the
+// same amount of cache to stream whatever the number and the lengths of the sequences.  Each (CTA, pair) segment
+// of a pair that is cut leaves a partial result in slot (CTA index + pair index), which is unique and needs no
+// table, and counts itself on the pair; the CTA that arrives last adds the pair's segments, in their order.
+__device__ __forceinline__ int short_tiles_of(const AttnArgs& a, int q_len, int pos0, int G) {
+    if (q_len * G > a.short_rows) return 0;                 // belongs to the LONG arrangement
+    const KeyRange kr = key_range(pos0, pos0 + q_len - 1, a.window);
+    return (kr.t_hi - kr.tile_lo) / KT + 1;
+}
+
+// Per-sequence facts of the SHORT arrangement in shared memory: five arrays of n_seqs (+1) ints.
+struct ShortSeqs {
+    int *tiles, *prefix, *q_len, *pos0, *q_start;
+    __device__ __forceinline__ explicit ShortSeqs(int* base, int n)
+        : tiles(base), prefix(base + n), q_len(base + 2 * n + 1), pos0(base + 3 * n + 1), q_start(base + 4 * n + 1) {}
+};
+__host__ __device__ constexpr size_t short_seqs_bytes(size_t n) { return 4 * (5 * n + 1); }
+
+// prefix[s] = tiles of one key/value head over sequences [0, s).  Every CTA computes it for itself from the step's
+// descriptor (one round of loads, a warp scan), so that the host has nothing to prepare and a captured graph stays
+// valid as the sequences grow.
+__device__ __forceinline__ void short_prefix(const AttnArgs& a, int G, const ShortSeqs& ss, int tid, int nt) {
+    const int n = a.n_seqs;
+    for (int s = tid; s < n; s += nt) {
+        const int q_len = a.seq_q_len[s], pos0 = a.seq_pos_start[s];
+        ss.q_len[s] = q_len;
+        ss.pos0[s] = pos0;
+        ss.q_start[s] = a.seq_q_start[s];
+        ss.tiles[s] = short_tiles_of(a, q_len, pos0, G);
+    }
+    __syncthreads();
+    if (tid < 32) {
+        int carry = 0;
+        for (int base = 0; base < n; base += 32) {
+            const int s = base + tid;
+            const int v = s < n ? ss.tiles[s] : 0;
+            int inc = v;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, inc, off);
+                if (tid >= off) inc += t;
+            }
+            if (s < n) ss.prefix[s] = carry + inc - v;
+            carry += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (tid == 0) ss.prefix[n] = carry;
+    }
+    __syncthreads();
+}
+
 // Where element (row, dim) of a K/V tile lives in shared memory (dim a multiple of 8).
 //   padded:  rows of HD_MAX + 8 elements (the per-row bulk copies land here);
 //   swizzled (TMA mode): HD_MAX / 64 column blocks of [64 rows][128 bytes], the 16-byte chunks of a row
@@ -98,12 +154,66 @@ __device__ __forceinline__ const __nv_bfloat16* tile_at(const __nv_bfloat16* til
     return tile + row * (HD_MAX + 8) + dim;
 }
 
+// Adds the segments of one row of a pair: out = sum_c 2^(m_c - m) o_c / sum_c 2^(m_c - m) l_c, segments in slots
+// slot0 .. slot0 + n_chunks - 1.  One warp: a lane first takes a segment (its maximum, sum and weight), then a share
+// of the head's columns.  The partials were written by other SMs: they are read past the L1.
+template <int HD_MAX>
+__device__ __forceinline__ void merge_row(const AttnArgs& a, size_t slot0, int n_chunks, int r, int lane,
+                                          __nv_bfloat16* dst) {
+    constexpr int U = 8;                               // segments whose loads are in flight together
+    float acc[HD_MAX / 32];
+#pragma unroll
+    for (int i = 0; i < HD_MAX / 32; ++i) acc[i] = 0.0f;
+    float m = -INFINITY;
+    for (int ch = lane + 32; ch < n_chunks; ch += 32) m = fmaxf(m, __ldcg(a.part_ml + ((slot0 + ch) * 16 + r) * 2));
+    float2 mine = make_float2(-INFINITY, 0.0f);       // segment `lane` of the first 32
+    if (lane < n_chunks) mine = __ldcg(reinterpret_cast<const float2*>(a.part_ml + ((slot0 + lane) * 16 + r) * 2));
+    m = fb_warp_max(fmaxf(m, mine.x));
+    float l = 0.0f;
+    if (m > -INFINITY) {
+        for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+            if (c0 > 0) {
+                mine = make_float2(-INFINITY, 0.0f);
+                if (c0 + lane < n_chunks)
+                    mine = __ldcg(reinterpret_cast<const float2*>(a.part_ml + ((slot0 + c0 + lane) * 16 + r) * 2));
+            }
+            const float wgt = exp2f(mine.x - m);          // 0 for a segment that saw nothing or does not exist
+            l += wgt * mine.y;
+            const int cnt = min(32, n_chunks - c0);
+            for (int j0 = 0; j0 < cnt; j0 += U) {
+                float v[U][HD_MAX / 32];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int j = j0 + u < cnt ? j0 + u : cnt - 1;
+                    const float* po = a.part_o + ((slot0 + c0 + j) * 16 + r) * HD_MAX;
+#pragma unroll
+                    for (int i = 0; i < HD_MAX / 32; ++i) v[u][i] = __ldcg(po + lane + 32 * i);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const float wj = j0 + u < cnt ? __shfl_sync(0xffffffffu, wgt, (j0 + u) & 31) : 0.0f;
+#pragma unroll
+                    for (int i = 0; i < HD_MAX / 32; ++i) acc[i] = fmaf(wj, v[u][i], acc[i]);
+                }
+            }
+        }
+    }
+    l = fb_warp_sum(l);
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+    for (int i = 0; i < HD_MAX / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < a.hd) dst[d] = __float2bfloat16_rn(acc[i] * inv);
+    }
+}
+
 template <int HD_MAX, bool SHORT, bool TMA>
 __global__ void __launch_bounds__(SHORT ? ATT_THREADS : LONG_THREADS)
 attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     constexpr int NT = SHORT ? ATT_THREADS : LONG_THREADS;
     fb_pdl_launch_dependents();
-    fb_pdl_wait();
+    // The step's descriptor was on the device before the step's first kernel: everything up to the first read of
+    // Q or of the cache (the CTA's share of the work, barriers, clearing) runs ahead of the kernel before this one.
     constexpr int LDS = HD_MAX + 8;                 // row stride of Q (and of K/V when padded): 16 bytes of padding
     constexpr int TILE_ELEMS = TMA ? KT * HD_MAX : KT * LDS;
     constexpr int NKS = HD_MAX / 16;                // k-steps of Q K^T
@@ -117,85 +227,108 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [ROWS][LDS]
-    // Q first; the K/V tiles start on a 1024-byte boundary (the swizzle pattern of TMA mode needs it)
+    // Q first; the K/V tiles start on a 1024-byte boundary (the swizzle pattern of TMA mode needs it).
+    // Stage by stage: K tile, V tile.
     const uint32_t smem_base = smem_u32(smem_raw);
-    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(
+    __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(
         smem_raw + (((smem_base + ROWS * LDS * 2 + 1023u) & ~1023u) - smem_base));
-    __nv_bfloat16* Vs = Ks + NST * TILE_ELEMS;                                  // [NST] tiles each
-    uint64_t* full = reinterpret_cast<uint64_t*>(Vs + NST * TILE_ELEMS);        // [NST] tile-complete barriers
-    int* bail = reinterpret_cast<int*>(full + NST);                             // a bounded wait ran out
+    auto k_tile = [&](int buf) { return tiles + buf * (2 * TILE_ELEMS); };
+    auto v_tile = [&](int buf) { return tiles + buf * (2 * TILE_ELEMS) + TILE_ELEMS; };
+    uint8_t* tail = reinterpret_cast<uint8_t*>(tiles + NST * 2 * TILE_ELEMS);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tail);                         // [NST] tile-complete barriers
+    int* bail = reinterpret_cast<int*>(tail + 32);                              // a bounded wait ran out
+    float* sml = reinterpret_cast<float*>(tail + 64);                           // SHORT: [4 warps][16][2]
+    const ShortSeqs ss(reinterpret_cast<int*>(tail + 64 + 512), a.n_seqs);      // SHORT: per-sequence facts
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int seq = blockIdx.z, kvh = blockIdx.y;
     const int G = a.nh / a.nkv;
-    const int q_len = a.seq_q_len[seq], q_start = a.seq_q_start[seq], pos0 = a.seq_pos_start[seq];
-    const bool is_short = q_len * G <= a.short_rows;
-    int tok0, ntok;
-    if (SHORT) {
-        if (!is_short) return;
-        tok0 = 0;
-        ntok = q_len;
-    } else {
-        if (is_short) return;
-        const int TQ = ROWS / G;
-        tok0 = (gridDim.x - 1 - blockIdx.x) * TQ;       // later tiles see more keys: start them first
-        if (tok0 >= q_len) return;
-        ntok = min(TQ, q_len - tok0);
-    }
-    const int rows_valid = ntok * G;
-    const KeyRange kr = key_range(pos0 + tok0, pos0 + tok0 + ntok - 1, a.window);
-    int k_begin = kr.tile_lo, k_end = kr.t_hi + 1;
-    if (SHORT) {
-        k_begin = kr.tile_lo + blockIdx.x * a.chunk_keys;
-        if (k_begin > kr.t_hi) return;
-        k_end = min(k_end, k_begin + a.chunk_keys);
-    }
-    const int n_tiles = (k_end - k_begin + KT - 1) / KT;
     const int hd = a.hd, hd_chunks = hd / 8;
-    const int* table = a.block_table + (size_t)seq * a.table_stride;
     // TMA mode: one copy per (K or V, page of the tile, 64-column block), issued by thread number = op number
     const int pages_per_tile = TMA ? KT / a.page_size : 1;
     const int col_blocks = TMA ? hd / 64 : 1;
     const int tma_ops = 2 * pages_per_tile * col_blocks;
+
+    // One piece of work: query tokens [tok0, tok0 + ntok) of a sequence, one key/value head, keys [k_begin, k_end).
+    // LONG: the CTA's only one.  SHORT: a segment of the CTA's stretch.
+    struct Seg {
+        int seq, kvh, q_start, pos0, tok0, ntok, t_lo, t_hi, k_begin, k_end, n_tiles;
+        int c_first, n_chunks;             // SHORT: the first CTA with a segment of this pair, and how many have one
+        const int* table;
+    };
+    auto make_seg = [&](int seq, int kvh, int q_start, int pos0, int tok0, int ntok, int tile_a, int tile_b) {
+        Seg sg;
+        sg.seq = seq; sg.kvh = kvh; sg.q_start = q_start; sg.pos0 = pos0; sg.tok0 = tok0; sg.ntok = ntok;
+        const KeyRange kr = key_range(pos0 + tok0, pos0 + tok0 + ntok - 1, a.window);
+        sg.t_lo = kr.t_lo; sg.t_hi = kr.t_hi;
+        sg.k_begin = kr.tile_lo + tile_a * KT;
+        sg.k_end = tile_b < 0 ? kr.t_hi + 1 : min(kr.t_hi + 1, kr.tile_lo + tile_b * KT);
+        sg.n_tiles = (sg.k_end - sg.k_begin + KT - 1) / KT;
+        sg.table = a.block_table + (size_t)seq * a.table_stride;
+        sg.c_first = 0; sg.n_chunks = 1;
+        return sg;
+    };
+
+    // ---- what this CTA has to do ----
+    int g = 0, seg_hi = 0, cur_seq = 0;    // SHORT: the next tile of its stretch, the stretch's end, the sequence of g
+    int per = 1;                           // SHORT: tiles per CTA
+    if (SHORT) {
+        short_prefix(a, G, ss, tid, NT);
+        const long total = (long)a.nkv * ss.prefix[a.n_seqs];
+        per = (int)((total + gridDim.x - 1) / gridDim.x);
+        g = (int)min((long)blockIdx.x * per, total);
+        seg_hi = (int)min((long)g + per, total);
+        if (g >= seg_hi) return;
+    }
+    auto next_seg = [&]() {                // SHORT: the segment that starts at tile g; moves g past it
+        while ((long)a.nkv * ss.prefix[cur_seq + 1] <= g) ++cur_seq;
+        const int seq = cur_seq, n = ss.tiles[seq];
+        const int within = g - a.nkv * ss.prefix[seq];                          // tiles into this sequence's pairs
+        const int kvh = within / n, tile_a = within - kvh * n;
+        const int tile_b = min(n, tile_a + (seg_hi - g));
+        g += tile_b - tile_a;
+        Seg sg = make_seg(seq, kvh, ss.q_start[seq], ss.pos0[seq], 0, ss.q_len[seq], tile_a, tile_b);
+        const long first_tile = (long)a.nkv * ss.prefix[seq] + (long)kvh * n;   // of the pair, in the line of tiles
+        sg.c_first = (int)(first_tile / per);
+        sg.n_chunks = (int)((first_tile + n - 1) / per) - sg.c_first + 1;
+        return sg;
+    };
+    Seg cur;
+    if (SHORT) {
+        cur = next_seg();
+    } else {
+        const int seq = blockIdx.z, q_len = a.seq_q_len[seq];
+        if (q_len * G <= a.short_rows) return;
+        const int TQ = ROWS / G;
+        const int tok0 = (gridDim.x - 1 - blockIdx.x) * TQ;       // later tiles see more keys: start them first
+        if (tok0 >= q_len) return;
+        cur = make_seg(seq, blockIdx.y, a.seq_q_start[seq], a.seq_pos_start[seq], tok0, min(TQ, q_len - tok0), 0, -1);
+    }
 
     if (tid == 0) {
         for (int st = 0; st < NST; ++st) mbar_init(smem_u32(&full[st]), TMA ? tma_ops : 2 * KT);
         *bail = 0;
         mbar_fence_init();
     }
-    // ---- stage Q (zero-padded) and clear the padding of the K/V buffers ----
-    for (int idx = tid; idx < ROWS * (HD_MAX / 8); idx += NT) {
-        const int r = idx / (HD_MAX / 8), c = idx - r * (HD_MAX / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < rows_valid && c < hd_chunks) {
-            const int token = q_start + tok0 + r / G, head = kvh * G + r % G;
-            v = *reinterpret_cast<const uint4*>(a.q + (size_t)token * a.q_stride + (size_t)head * hd + c * 8);
-        }
-        *reinterpret_cast<uint4*>(Qs + r * LDS + c * 8) = v;
-    }
+    // Pages that no query can see are not fetched, and a head narrower than the tile leaves padding columns:
+    // clear them so that what stays there is finite.
     if (TMA) {
-        // pages that no query can see are not fetched; clear the tiles once so that what stays there is finite
         for (int idx = tid; idx < 2 * NST * TILE_ELEMS / 8; idx += NT)
-            *reinterpret_cast<uint4*>(Ks + idx * 8) = make_uint4(0, 0, 0, 0);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            *reinterpret_cast<uint4*>(tiles + idx * 8) = make_uint4(0, 0, 0, 0);
     } else if (hd < HD_MAX) {
         const int pad_chunks = HD_MAX / 8 - hd_chunks;
-        for (int idx = tid; idx < NST * KT * pad_chunks; idx += NT) {
+        for (int idx = tid; idx < 2 * NST * KT * pad_chunks; idx += NT) {
             const int r = idx / pad_chunks, c = hd_chunks + idx - r * pad_chunks;
-            *reinterpret_cast<uint4*>(Ks + r * LDS + c * 8) = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(Vs + r * LDS + c * 8) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(tiles + r * LDS + c * 8) = make_uint4(0, 0, 0, 0);
         }
     }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();                                  // barriers initialised, tiles cleared
+    fb_pdl_wait();                                    // from here on: Q and the cache, which earlier kernels wrote
 
-    __syncthreads();                                  // barriers initialised, Q staged, padding cleared
-
-    // One row of 64 keys (threads 0..63) or 64 values (threads 64..127) per thread and tile: a single bulk copy
-    // of the row's hd*2 bytes, counted on the tile's barrier.  A row that no query of this CTA may see (before
-    // the window, past the last position, or in another chunk) is not read: its slot is filled with zeros.
     // The page id this thread will need for the tile that starts at `tile_start`, read ahead of time so that the
-    // copy can be issued without waiting for the table: -2 = nothing to fetch there (no query of this CTA sees
+    // copy can be issued without waiting for the table: -2 = nothing to fetch there (no query of this piece sees
     // it), -1 = the table has no page although one is needed (flagged when the tile is issued).
-    auto lookup = [&](int tile_start) -> int {
+    auto lookup = [&](const Seg& sg, int tile_start) -> int {
         int t_first, span;
         if constexpr (TMA) {
             if (tid >= tma_ops) return -2;
@@ -206,16 +339,16 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
             t_first = tile_start + (tid & (KT - 1));
             span = 1;
         }
-        if (!(t_first + span > kr.t_lo && t_first < k_end)) return -2;
-        const int page = table[t_first / a.page_size];
+        if (!(t_first + span > sg.t_lo && t_first < sg.k_end)) return -2;
+        const int page = sg.table[t_first / a.page_size];
         return (page < 0 || page >= a.n_pages) ? -1 : page;
     };
 
     // TMA mode: thread number = copy number: (K or V, page of the tile, 64-column block), one tensor-map copy each.
     // Otherwise: one row of 64 keys (threads 0..63) or 64 values (threads 64..127) per thread: a bulk copy of the
-    // row's hd*2 bytes.  Copies are counted on the tile's barrier.  What no query of this CTA may see (before the
-    // window, past the last position, or in another chunk) is not read.
-    auto load_tile = [&](int buf, int tile_start, int page) {
+    // row's hd*2 bytes.  Copies are counted on the tile's barrier.  What no query of this piece may see (before the
+    // window, past the last position, or in another segment) is not read.
+    auto load_tile = [&](const Seg& sg, int buf, int tile_start, int page) {
         const uint32_t bar = smem_u32(&full[buf]);
         if constexpr (TMA) {
             if (tid >= tma_ops) return;
@@ -223,10 +356,10 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
             const int rest = tid >> 1;
             const int cb = rest % col_blocks, pj = rest / col_blocks;
             if (page >= 0) {
-                __nv_bfloat16* dst = (is_v ? Vs : Ks) + buf * TILE_ELEMS + cb * (KT * 64) + pj * a.page_size * 64;
+                __nv_bfloat16* dst = (is_v ? v_tile(buf) : k_tile(buf)) + cb * (KT * 64) + pj * a.page_size * 64;
                 mbar_expect_tx(bar, (uint32_t)(a.page_size * 128));
                 tma_load_2d(smem_u32(dst), is_v ? &a.map_v : &a.map_k, bar, cb * 64,
-                            (page * a.nkv + kvh) * a.page_size);
+                            (page * a.nkv + sg.kvh) * a.page_size);
             } else {
                 if (page == -1) atomicOr(a.status, FB_STATUS_BAD_PAGE);
                 mbar_arrive(bar);                     // stale (finite) data stays in the slot; it is masked
@@ -237,9 +370,9 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
         const int r = tid & (KT - 1);
         const bool is_v = tid >= KT;
         const int t = tile_start + r;
-        __nv_bfloat16* dst = (is_v ? Vs : Ks) + buf * TILE_ELEMS + r * LDS;
+        __nv_bfloat16* dst = (is_v ? v_tile(buf) : k_tile(buf)) + r * LDS;
         if (page >= 0) {
-            const size_t off = (((size_t)page * a.nkv + kvh) * a.page_size + (t % a.page_size)) * hd;
+            const size_t off = (((size_t)page * a.nkv + sg.kvh) * a.page_size + (t % a.page_size)) * hd;
             mbar_expect_tx(bar, (uint32_t)(hd * 2));
             bulk_copy_g2s(smem_u32(dst), (is_v ? a.v_pool : a.k_pool) + off, (uint32_t)(hd * 2), bar);
         } else {
@@ -251,14 +384,38 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
         }
     };
 
-    // prologue: NST - 1 tiles in flight; the page id for the tile after them is already on its way
-    int next_page = lookup(k_begin);
+    // Puts the first NST - 1 tiles of a piece in flight (`count` tiles went through the buffers before it) and
+    // returns the page id for the tile after them, already on its way.
+    auto prologue = [&](const Seg& sg, uint32_t count) -> int {
+        int page = lookup(sg, sg.k_begin);
 #pragma unroll
-    for (int st = 0; st < NST - 1; ++st)
-        if (st < n_tiles) {
-            load_tile(st, k_begin + st * KT, next_page);
-            next_page = lookup(k_begin + (st + 1) * KT);
+        for (int st = 0; st < NST - 1; ++st)
+            if (st < sg.n_tiles) {
+                load_tile(sg, (int)((count + st) % NST), sg.k_begin + st * KT, page);
+                page = lookup(sg, sg.k_begin + (st + 1) * KT);
+            }
+        return page;
+    };
+
+    uint32_t tiles_done = 0;               // tiles this CTA has consumed: buffer and barrier phase follow from it
+    int next_page = prologue(cur, 0);
+
+  for (;;) {                               // one pass per piece; LONG: exactly one
+    const int kvh = cur.kvh, q_start = cur.q_start, pos0 = cur.pos0, tok0 = cur.tok0;
+    const int rows_valid = cur.ntok * G;
+    const int k_begin = cur.k_begin, k_end = cur.k_end, n_tiles = cur.n_tiles, t_hi = cur.t_hi;
+
+    // ---- stage Q (zero-padded) ----
+    for (int idx = tid; idx < ROWS * (HD_MAX / 8); idx += NT) {
+        const int r = idx / (HD_MAX / 8), c = idx - r * (HD_MAX / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows_valid && c < hd_chunks) {
+            const int token = q_start + tok0 + r / G, head = kvh * G + r % G;
+            v = *reinterpret_cast<const uint4*>(a.q + (size_t)token * a.q_stride + (size_t)head * hd + c * 8);
         }
+        *reinterpret_cast<uint4*>(Qs + r * LDS + c * 8) = v;
+    }
+    __syncthreads();                                  // Q staged (and, after a segment, its merge buffer cleared)
 
     const int row_base = SHORT ? 0 : warp * (16 * R);   // first row of this warp within the CTA
     const int key0 = SHORT ? warp * 16 : 0;             // first key of this warp within a tile
@@ -296,22 +453,23 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     }
 
     for (int it = 0; it < n_tiles; ++it) {
-        const int buf = it % NST;
+        const uint32_t seen = tiles_done + (uint32_t)it;
+        const int buf = (int)(seen % NST);
         const int tile_start = k_begin + it * KT;
-        if (!mbar_wait(smem_u32(&full[buf]), (uint32_t)(it / NST) & 1u, a.status)) *bail = 1;
+        if (!mbar_wait(smem_u32(&full[buf]), (seen / NST) & 1u, a.status)) *bail = 1;
         __syncthreads();                              // every thread is past tile it-1: its buffer is free
         if (*bail) break;
         if (it + NST - 1 < n_tiles) {
-            load_tile((it + NST - 1) % NST, tile_start + (NST - 1) * KT, next_page);
-            next_page = lookup(tile_start + NST * KT);    // consumed one iteration from now
+            load_tile(cur, (int)((seen + NST - 1) % NST), tile_start + (NST - 1) * KT, next_page);
+            next_page = lookup(cur, tile_start + NST * KT);    // consumed one iteration from now
         }
         if constexpr (TMA) {
             // Whole pages arrive, the slots behind the last position included, and what a page holds there was
             // never written by this request.  Scores of such keys are masked by assignment, but their values
             // would be multiplied by a probability of 0, and 0 * NaN is NaN: clear those value rows.
-            if (tile_start + KT > kr.t_hi + 1) {
-                const int first_dead = kr.t_hi + 1 - tile_start;            // >= 0 because tile_start <= t_hi
-                __nv_bfloat16* vz = Vs + buf * TILE_ELEMS;
+            if (tile_start + KT > t_hi + 1) {
+                const int first_dead = t_hi + 1 - tile_start;               // >= 0 because tile_start <= t_hi
+                __nv_bfloat16* vz = v_tile(buf);
                 const int chunks = (KT - first_dead) * 8;                    // 16-byte chunks per 64-column block
                 for (int idx = tid; idx < chunks * (HD_MAX / 64); idx += NT) {
                     const int cb = idx / chunks, rest = idx - cb * chunks;
@@ -321,8 +479,8 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
                 __syncthreads();
             }
         }
-        const __nv_bfloat16* kt = Ks + buf * TILE_ELEMS;
-        const __nv_bfloat16* vt = Vs + buf * TILE_ELEMS;
+        const __nv_bfloat16* kt = k_tile(buf);
+        const __nv_bfloat16* vt = v_tile(buf);
 
         // ---- S = Q K^T for this warp's rows and keys: every K fragment serves all R row blocks ----
         float s[R][NSB][4];
@@ -423,6 +581,8 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
         }
     }
     __syncthreads();                                  // every warp is done with the tiles
+    if (*bail) return;
+    tiles_done += (uint32_t)n_tiles;
 #pragma unroll
     for (int rb = 0; rb < R; ++rb)
 #pragma unroll
@@ -452,18 +612,24 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
         return;
     }
 
-    // ---- SHORT: merge the four warps (they saw different keys of the same rows), write one partial ----
-    float* so = reinterpret_cast<float*>(Ks);         // [4 warps][16][HD_MAX] floats; K/V buffers are free now
-    float* sml = so + 4 * 16 * HD_MAX;                // [4 warps][16][2]
-    static_assert(!SHORT || 4 * 16 * HD_MAX * 4 + 4 * 16 * 2 * 4 <= 2 * NST * KT * HD_MAX * 2, "merge buffer fits in K/V");
+    // ---- SHORT: the next segment's first tiles go on their way, then the four warps (they saw different keys of
+    // the same rows) are merged into one partial.  The merge buffer is the stage used last, which the next
+    // segment's first NST - 1 tiles do not touch.
+    const bool more = g < seg_hi;
+    Seg nxt = cur;
+    if (more) {
+        nxt = next_seg();
+        next_page = prologue(nxt, tiles_done);
+    }
+    float* so = reinterpret_cast<float*>(k_tile((int)((tiles_done + NST - 1) % NST)));      // [4 warps][16][HD_MAX]
+    static_assert(!SHORT || 4 * 16 * HD_MAX * 4 <= 2 * KT * HD_MAX * 2, "the merge buffer fits in one stage");
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = (lane >> 2) + 8 * h;
 #pragma unroll
         for (int d = 0; d < NDB; ++d) {
             const int col = d * 8 + 2 * (lane & 3);
-            so[(warp * 16 + r) * HD_MAX + col] = o[0][d][2 * h];
-            so[(warp * 16 + r) * HD_MAX + col + 1] = o[0][d][2 * h + 1];
+            *reinterpret_cast<float2*>(so + (warp * 16 + r) * HD_MAX + col) = make_float2(o[0][d][2 * h], o[0][d][2 * h + 1]);
         }
         if ((lane & 3) == 0) {
             sml[(warp * 16 + r) * 2] = m_run[0][h];
@@ -471,10 +637,11 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
         }
     }
     __syncthreads();
-    const size_t slot = ((size_t)seq * a.nkv + kvh) * a.max_chunks + blockIdx.x;
-    float* po = a.part_o + slot * 16 * HD_MAX;
-    float* pml = a.part_ml + slot * 16 * 2;
-    for (int idx = tid; idx < 16 * HD_MAX; idx += NT) {
+    const int pair = cur.seq * a.nkv + kvh;
+    const bool cut = cur.n_chunks > 1;                // other CTAs hold segments of this pair too
+    float* po = a.part_o + ((size_t)blockIdx.x + pair) * 16 * HD_MAX;        // slot = CTA index + pair index
+    float* pml = a.part_ml + ((size_t)blockIdx.x + pair) * 16 * 2;
+    for (int idx = tid; idx < rows_valid * HD_MAX; idx += NT) {
         const int r = idx / HD_MAX, c = idx - r * HD_MAX;
         float m = -INFINITY;
 #pragma unroll
@@ -488,88 +655,67 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
                 l += wgt * sml[(w * 16 + r) * 2 + 1];
             }
         }
-        po[idx] = acc;
-        if (c == 0) { pml[r * 2] = m; pml[r * 2 + 1] = l; }
+        if (cut) {
+            po[idx] = acc;
+            if (c == 0) { pml[r * 2] = m; pml[r * 2 + 1] = l; }
+        } else if (c < hd) {                          // the whole pair was this CTA's: the result itself
+            const int token = q_start + r / G, head = kvh * G + r % G;
+            a.out[(size_t)token * a.out_stride + (size_t)head * hd + c] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        }
     }
-}
-
-// Merges the chunks of the SHORT arrangement: out = sum_c 2^(m_c - m) o_c / sum_c 2^(m_c - m) l_c.
-// One warp per row: lanes first share the chunks (weights), then the head dimensions (sums).
-template <int HD_MAX>
-__global__ void __launch_bounds__(ATT_THREADS)
-attention_merge_kernel(const AttnArgs a) {
-    fb_pdl_launch_dependents();
-    fb_pdl_wait();
-    const int seq = blockIdx.y, kvh = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int G = a.nh / a.nkv;
-    const int q_len = a.seq_q_len[seq], q_start = a.seq_q_start[seq], pos0 = a.seq_pos_start[seq];
-    if (q_len * G > a.short_rows) return;
-    const KeyRange kr = key_range(pos0, pos0 + q_len - 1, a.window);
-    const int n_chunks = (kr.t_hi - kr.tile_lo) / a.chunk_keys + 1;
-    const size_t slot0 = ((size_t)seq * a.nkv + kvh) * a.max_chunks;
-    const int rows = q_len * G, hd = a.hd;
-    for (int r = warp; r < rows; r += ATT_THREADS / 32) {
-        float m = -INFINITY;
-        for (int ch = lane; ch < n_chunks; ch += 32) m = fmaxf(m, a.part_ml[((slot0 + ch) * 16 + r) * 2]);
-        m = fb_warp_max(m);
-        float l = 0.0f;
-        float acc[HD_MAX / 32];
-#pragma unroll
-        for (int i = 0; i < HD_MAX / 32; ++i) acc[i] = 0.0f;
-        if (m > -INFINITY) {
-            for (int c0 = 0; c0 < n_chunks; c0 += 32) {
-                const int mine = c0 + lane;
-                float wgt = 0.0f;
-                if (mine < n_chunks) {
-                    wgt = exp2f(a.part_ml[((slot0 + mine) * 16 + r) * 2] - m);
-                    l += wgt * a.part_ml[((slot0 + mine) * 16 + r) * 2 + 1];
-                }
-                const int cnt = min(32, n_chunks - c0);
-                for (int j0 = 0; j0 < cnt; j0 += 8) {
-                    // eight chunks' loads in flight, added in chunk order
-                    float v[8][HD_MAX / 32];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const int j = j0 + u < cnt ? j0 + u : cnt - 1;
-                        const float* po = a.part_o + ((slot0 + c0 + j) * 16 + r) * HD_MAX;
-#pragma unroll
-                        for (int i = 0; i < HD_MAX / 32; ++i) v[u][i] = po[lane + 32 * i];
-                    }
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const float wj = j0 + u < cnt ? __shfl_sync(0xffffffffu, wgt, (j0 + u) & 31) : 0.0f;
-#pragma unroll
-                        for (int i = 0; i < HD_MAX / 32; ++i) acc[i] = fmaf(wj, v[u][i], acc[i]);
-                    }
-                }
+    if (cut) __threadfence();                         // the partial is visible before this CTA counts itself
+    __syncthreads();                                  // every thread has read the merge buffer
+    if (cut) {
+        if (tid == 0) {
+            const int arrived = atomicAdd(a.part_cnt + pair, 1);
+            bail[1] = arrived == cur.n_chunks - 1;
+            if (bail[1]) atomicExch(a.part_cnt + pair, 0);                     // at rest again for the next launch
+        }
+        __syncthreads();
+        if (bail[1]) {                                // the last of the pair's segments: add them all
+            __threadfence();
+            const size_t slot0 = (size_t)cur.c_first + pair;                   // consecutive CTAs, consecutive slots
+            for (int r = warp; r < rows_valid; r += NT / 32) {
+                const int token = q_start + r / G, head = kvh * G + r % G;
+                merge_row<HD_MAX>(a, slot0, cur.n_chunks, r, lane,
+                                  a.out + (size_t)token * a.out_stride + (size_t)head * hd);
             }
         }
-        l = fb_warp_sum(l);
-        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-        const int token = q_start + r / G, head = kvh * G + r % G;
-        __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd;
-#pragma unroll
-        for (int i = 0; i < HD_MAX / 32; ++i) {
-            const int d = lane + 32 * i;
-            if (d < hd) dst[d] = __float2bfloat16_rn(acc[i] * inv);
+    }
+    if (!more) return;
+    // that stage receives the next segment's tile NST - 1: make it finite again (see the clearing above)
+    if (TMA) {
+        for (int idx = tid; idx < 2 * TILE_ELEMS / 8; idx += NT)
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(so) + idx * 8) = make_uint4(0, 0, 0, 0);
+    } else if (hd < HD_MAX) {
+        const int pad_chunks = HD_MAX / 8 - hd_chunks;
+        for (int idx = tid; idx < 2 * KT * pad_chunks; idx += NT) {
+            const int r = idx / pad_chunks, c = hd_chunks + idx - r * pad_chunks;
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(so) + r * LDS + c * 8) = make_uint4(0, 0, 0, 0);
         }
     }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    cur = nxt;
+  }
 }
 
+// (plus 16 + short_seqs_bytes(sequences) for the SHORT arrangement's per-sequence facts, added at launch)
 __host__ __device__ constexpr size_t attn_smem_bytes(int hd_max, bool short_rows, bool tma) {
     return (size_t)(short_rows ? 16 : 64 * long_row_blocks(hd_max, false)) * (hd_max + 8) * 2 + 1024 /* alignment */ +
-           (size_t)2 * attn_stages(hd_max, short_rows) * KT * (tma ? hd_max : hd_max + 8) * 2 + 64 /* barriers */;
+           (size_t)2 * attn_stages(hd_max, short_rows) * KT * (tma ? hd_max : hd_max + 8) * 2 + 64 /* barriers */ +
+           (short_rows ? 512 : 0) /* merge maxima and sums */;
 }
 
 template <int HD_MAX, bool SHORT, bool TMA>
 int launch_one(const AttnArgs& a, dim3 grid, const char* what, cudaStream_t stream) {
-    constexpr size_t smem = attn_smem_bytes(HD_MAX, SHORT, TMA);
+    constexpr size_t base = attn_smem_bytes(HD_MAX, SHORT, TMA);
+    constexpr size_t room = base + 16 + short_seqs_bytes(1024);      // up to 1024 sequences in the SHORT arrangement
+    const size_t smem = base + 16 + (SHORT ? short_seqs_bytes(a.n_seqs) : 0);
     auto kern = attention_mma_kernel<HD_MAX, SHORT, TMA>;
     static bool configured = false;
-    if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return fb_fail(-2, "%s: cannot reserve %d bytes of shared memory: %s", what, (int)smem,
+    if (!configured && room > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)room);
+        if (e != cudaSuccess) return fb_fail(-2, "%s: cannot reserve %d bytes of shared memory: %s", what, (int)room,
                                              cudaGetErrorString(e));
         configured = true;
     }
@@ -577,10 +723,37 @@ int launch_one(const AttnArgs& a, dim3 grid, const char* what, cudaStream_t stre
     return fb_check_launch(what);
 }
 
+// CTAs of the SHORT arrangement that are resident at once on this device (its grid: one equal stretch each).
+template <int HD_MAX, bool TMA>
+int short_resident_ctas(int n_seqs) {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const size_t smem = attn_smem_bytes(HD_MAX, true, TMA) + 16 + short_seqs_bytes(n_seqs);
+    int per_sm = (int)(227 * 1024 / (smem + 1024));           // shared memory is what limits them
+    per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+    return sms * per_sm;
+}
+
 template <int HD_MAX>
-int launch_attention_mma(const AttnArgs& a, bool tma, int n_seqs, int max_q_len, int any_short, int any_long,
-                         cudaStream_t stream) {
+int launch_attention_mma(const AttnArgs& args, bool tma, int n_seqs, int max_q_len, int any_short, int any_long,
+                         long long scratch_floats, cudaStream_t stream) {
+    AttnArgs a = args;
     const int G = a.nh / a.nkv;
+    if (any_short) {
+        if constexpr (HD_MAX >= 64) a.short_ctas = tma ? short_resident_ctas<HD_MAX, true>(n_seqs)
+                                                       : short_resident_ctas<HD_MAX, false>(n_seqs);
+        else a.short_ctas = short_resident_ctas<HD_MAX, false>(n_seqs);
+        const long slots = a.short_ctas + (long)n_seqs * a.nkv;          // CTA index + pair index < slots
+        FB_REQUIRE(slots * (16L * HD_MAX + 32) + (long)n_seqs * a.nkv <= scratch_floats,
+                   "attention_mma: the scratch buffer (%lld floats) is too small for %d sequences", scratch_floats,
+                   n_seqs);
+        a.part_ml = a.part_o + (size_t)slots * 16 * HD_MAX;
+        a.part_cnt = reinterpret_cast<int*>(a.part_ml + (size_t)slots * 32);
+    }
     if (any_long) {
         const int TQ = 64 * long_row_blocks(HD_MAX, false) / G;
         const dim3 grid((max_q_len + TQ - 1) / TQ, a.nkv, n_seqs);
@@ -594,7 +767,7 @@ int launch_attention_mma(const AttnArgs& a, bool tma, int n_seqs, int max_q_len,
         if (rc) return rc;
     }
     if (any_short) {
-        const dim3 grid(a.max_chunks, a.nkv, n_seqs);
+        const dim3 grid(a.short_ctas, 1, 1);
         int rc;
         if constexpr (HD_MAX >= 64) {
             rc = tma ? launch_one<HD_MAX, true, true>(a, grid, "attention_mma (short)", stream)
@@ -602,9 +775,6 @@ int launch_attention_mma(const AttnArgs& a, bool tma, int n_seqs, int max_q_len,
         } else {
             rc = launch_one<HD_MAX, true, false>(a, grid, "attention_mma (short)", stream);
         }
-        if (rc) return rc;
-        fb_launch((attention_merge_kernel<HD_MAX>), dim3(a.nkv, n_seqs), ATT_THREADS, 0, stream, a);
-        rc = fb_check_launch("attention_merge");
         if (rc) return rc;
     }
     return 0;
@@ -644,12 +814,6 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     a.status = status;
     a.short_rows = G <= 16 ? 16 : 0;               // with more than 16 heads per group even one token is "long"
     if (a.short_rows == 0) { any_long = any_long || any_short; any_short = 0; }
-    // chunking of the SHORT arrangement: enough CTAs to fill the GPU, chunks a multiple of the tile
-    int span = max_kv_len;
-    if (window > 0 && window + max_q_len < span) span = window + max_q_len;
-    span += KT;                                     // tile alignment of the first key
-    const int pairs = n_seqs * nkv;
-    const int total_tiles = (span + KT - 1) / KT;
     // whole pages fetched by tensor-map copies when a 64-key tile is a whole number of pages and the head a whole
     // number of 64-column blocks; single rows by bulk copies otherwise
     const bool tma = hd % 64 == 0 && page_size >= 8 && page_size <= KT && KT % page_size == 0;
@@ -660,34 +824,16 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
         rc = fb_tensor_map_bf16(&a.map_v, v_pool, pool_rows, hd, hd, 64, page_size);
         if (rc) return rc;
     }
-    const size_t short_smem = attn_smem_bytes(HD_MAX, true, tma);
-    const int per_sm = (int)(227 * 1024 / (short_smem + 1024)) > 4 ? 4 : (int)(227 * 1024 / (short_smem + 1024));
-    const int slots = 148 * (per_sm < 1 ? 1 : per_sm);
-    int want_chunks = 1;
-    double best_cost = 1e30;
-    for (int c = 1; c <= total_tiles && c <= 256; ++c) {
-        // time ~ waves * (tiles per chunk + the fixed cost of a CTA, counted in tiles)
-        const int tiles_per_chunk = (total_tiles + c - 1) / c;
-        const long ctas = (long)pairs * ((total_tiles + tiles_per_chunk - 1) / tiles_per_chunk);
-        const double cost = (double)((ctas + slots - 1) / slots) * (tiles_per_chunk + 6.0) + 0.05 * c;
-        if (cost < best_cost - 1e-9) { best_cost = cost; want_chunks = c; }
-    }
-    int chunk_keys = ((total_tiles + want_chunks - 1) / want_chunks) * KT;
-    int max_chunks = (span + chunk_keys - 1) / chunk_keys;
-    const long per_slot = 16L * HD_MAX + 32;
-    while ((long)pairs * max_chunks * per_slot > scratch_floats && chunk_keys < (1 << 24)) {
-        chunk_keys *= 2;
-        max_chunks = (span + chunk_keys - 1) / chunk_keys;
-    }
-    FB_REQUIRE(!any_short || (long)pairs * max_chunks * per_slot <= scratch_floats,
-               "attention_mma: the scratch buffer is too small for %d sequences", n_seqs);
-    a.chunk_keys = chunk_keys; a.max_chunks = max_chunks;
+    a.n_seqs = n_seqs;
+    a.short_ctas = 0;
     a.part_o = scratch;
-    a.part_ml = scratch + (size_t)pairs * max_chunks * 16 * HD_MAX;
+    a.part_ml = nullptr;
+    a.part_cnt = nullptr;
+    FB_REQUIRE(!any_short || n_seqs <= 1024, "attention_mma: %d sequences in one step exceed 1024", n_seqs);
     switch (HD_MAX) {
-        case 32: return launch_attention_mma<32>(a, tma, n_seqs, max_q_len, any_short, any_long, stream);
-        case 64: return launch_attention_mma<64>(a, tma, n_seqs, max_q_len, any_short, any_long, stream);
-        case 128: return launch_attention_mma<128>(a, tma, n_seqs, max_q_len, any_short, any_long, stream);
-        default: return launch_attention_mma<256>(a, tma, n_seqs, max_q_len, any_short, any_long, stream);
+        case 32: return launch_attention_mma<32>(a, tma, n_seqs, max_q_len, any_short, any_long, scratch_floats, stream);
+        case 64: return launch_attention_mma<64>(a, tma, n_seqs, max_q_len, any_short, any_long, scratch_floats, stream);
+        case 128: return launch_attention_mma<128>(a, tma, n_seqs, max_q_len, any_short, any_long, scratch_floats, stream);
+        default: return launch_attention_mma<256>(a, tma, n_seqs, max_q_len, any_short, any_long, scratch_floats, stream);
     }
 }

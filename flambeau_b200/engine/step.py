@@ -137,14 +137,14 @@ class Engine:
     def _graph_key(self, batch: StepBatch):
         """Steps of single decoded tokens repeat with the same shape; everything that differs between them
         (tokens, positions, block tables, wanted rows) lives in the descriptor buffers, whose addresses are
-        fixed.  The key holds what is baked into kernel arguments: the number of sequences and wanted rows,
-        and the bucket of the longest context (it sets the split of the attention's key range)."""
+        fixed.  The key holds what is baked into kernel arguments: the number of sequences and wanted rows.
+        Context lengths are not in it: the attention kernel splits the key range on the device, from the
+        descriptor, with a grid that does not depend on them."""
         if not self.use_graphs or batch.max_q_len != 1:
             return None
         if batch.n_out not in (0, batch.n_seqs):
             return None
-        bucket = 1 << max(8, (batch.max_kv_len - 1).bit_length())
-        return (batch.n_seqs, batch.n_out, bucket)
+        return (batch.n_seqs, batch.n_out)
 
     def _run(self, batch: StepBatch):
         key = self._graph_key(batch)
@@ -171,9 +171,9 @@ class Engine:
 
     def _capture(self, batch: StepBatch, key):
         rt = self.runtime
-        # kernels size their key-range split from max_kv_len: capture with the bucket's upper end
+        # a replay serves any context length: a part that sizes something by the longest context sees the limit
         real = batch.max_kv_len
-        batch.max_kv_len = key[2]
+        batch.max_kv_len = self.max_seq_len
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         launches_before = library.LAUNCHES[0]

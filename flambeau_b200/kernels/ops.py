@@ -286,7 +286,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ctx=None) -> Non
 
 
 class _AttentionScratch:
-    """Float32 partial outputs of the split-key attention arrangement, per device."""
+    """Float32 partial outputs of the split-key attention arrangement and its per-pair arrival counters, per
+    device.  The counters must be zero between launches: the kernel leaves them so."""
     FLOATS = 8 << 20
     _by_device: dict = {}
 
@@ -294,7 +295,7 @@ class _AttentionScratch:
     def get(cls, device):
         hit = cls._by_device.get(device)
         if hit is None:
-            hit = cls._by_device[device] = torch.empty(cls.FLOATS, dtype=torch.float32, device=device)
+            hit = cls._by_device[device] = torch.zeros(cls.FLOATS, dtype=torch.float32, device=device)
         return hit
 
 
