@@ -287,15 +287,24 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ctx=None) -> Non
 
 class _AttentionScratch:
     """Float32 partial outputs of the split-key attention arrangement and its per-pair arrival counters, per
-    device.  The counters must be zero between launches: the kernel leaves them so."""
-    FLOATS = 8 << 20
+    device.  The counters must be zero between launches: the kernel leaves them so.  The buffer grows with the
+    largest step seen; outgrown buffers stay alive because captured graphs may hold their addresses."""
     _by_device: dict = {}
+    _outgrown: list = []
 
     @classmethod
-    def get(cls, device):
+    def get(cls, device, n_seqs: int, nkv: int, hd: int):
+        hd_max = 32 if hd <= 32 else 64 if hd <= 64 else 128 if hd <= 128 else 256
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        pairs = n_seqs * nkv
+        # 65536 counters, then one partial per slot: at most 4 resident CTAs per SM plus one slot per pair
+        need = (1 << 16) + (4 * sms + pairs) * (16 * hd_max + 32)
         hit = cls._by_device.get(device)
-        if hit is None:
-            hit = cls._by_device[device] = torch.zeros(cls.FLOATS, dtype=torch.float32, device=device)
+        if hit is None or hit.numel() < need:
+            if hit is not None:
+                cls._outgrown.append(hit)
+            floats = max(1 << 22, 1 << (need - 1).bit_length())
+            hit = cls._by_device[device] = torch.zeros(floats, dtype=torch.float32, device=device)
         return hit
 
 
@@ -318,7 +327,7 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
         raise KernelError("attention_mma: q, out and the cache must be bfloat16")
     if not k_pool.is_contiguous() or not v_pool.is_contiguous():
         raise KernelError("attention: cache pools must be contiguous")
-    scratch = _AttentionScratch.get(q.device)
+    scratch = _AttentionScratch.get(q.device, n_seqs, nkv, hd)
     check(lib().fb_paged_attention_mma(
         q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), k_pool.data_ptr(), v_pool.data_ptr(), page_size, n_pages,
         block_table.data_ptr(), block_table.stride(0), seq_q_start.data_ptr(), seq_q_len.data_ptr(),

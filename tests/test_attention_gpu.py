@@ -162,3 +162,26 @@ def test_one_key_stands_out(kernel, dtype, where):
     elif where != "self" or True:
         # heads whose query the key was built from see (almost) only that key
         assert closeness < 0.05, "the key that dominates was lost"
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page_size", [(8, 2, 64, 16), (6, 3, 40, 8), (4, 1, 128, 32)])
+@pytest.mark.parametrize("window", [0, 300])
+def test_many_decoded_sequences_of_unequal_length(nh, nkv, hd, page_size, window):
+    """Forty decoded tokens with contexts from one key to a few thousand: the split-key kernel cuts the line of all
+    their key tiles into equal stretches, so a CTA's stretch ends inside one sequence, runs over several short ones
+    and starts inside another; every result must still be the plain softmax over that sequence's own keys."""
+    rnd = random.Random(hd + window)
+    seqs = [(rnd.choice([0, 1, 15, 63, 64, 65, 127, 128, 500, 1000, 2100]) + rnd.randrange(3), rnd.choice([1, 1, 1, 2]))
+            for _ in range(40)]
+    check(Scene(seqs, nh, nkv, hd, window, torch.bfloat16, page_size=page_size, seed=hd + window), "mma")
+
+
+def test_steps_of_different_shapes_alternate():
+    """The split-key kernel keeps counters and partial results in one scratch buffer between launches; steps of
+    other head sizes and batch sizes in between must leave it usable (each scene is checked twice)."""
+    scenes = [Scene([(900, 1), (70, 1), (2500, 2)], 8, 2, 128, 0, torch.bfloat16, seed=1),
+              Scene([(300, 1)] * 9, 4, 4, 32, 0, torch.bfloat16, seed=2),
+              Scene([(1200, 1), (5, 1)], 16, 2, 64, 500, torch.bfloat16, page_size=8, seed=3)]
+    for _ in range(2):
+        for sc in scenes:
+            check(sc, "mma")
