@@ -75,3 +75,7 @@ __device__ __forceinline__ const __nv_bfloat16* tile_at(const __nv_bfloat16* til
 // on its grid, launches, returns 0 or an error code with the message set.
 int fb_launch_attention_split(fb_attn::AttnArgs& a, int hd_max, bool tma, int n_seqs, float* scratch,
                               long long scratch_floats, cudaStream_t stream);
+
+// The tcgen05 arrangement for portions of prompts (attention_tc.cu): whether it takes this geometry, and its launch.
+bool fb_attention_tc_takes(const fb_attn::AttnArgs& a, bool tma);
+int fb_launch_attention_tc(const fb_attn::AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream);

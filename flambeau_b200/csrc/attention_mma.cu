@@ -15,6 +15,8 @@
 // size that is a multiple of 8 runs.
 //
 // Formulas: crates/kernels-hip/src/kernels/attention_prefill_flash_tile_f16.cu:73-213 (tile + online softmax).
+#include <stdlib.h>
+
 #include "attention_common.cuh"
 
 namespace {
@@ -394,7 +396,21 @@ int launch_long(const AttnArgs& a, int hd_max, bool tma, int n_seqs, int max_q_l
     }
 }
 
+int g_attention_tc = -1;           // -1: not decided yet (the environment decides), 0: off, 1: on
+
+bool attention_tc_enabled() {
+    if (g_attention_tc < 0) {
+        const char* env = getenv("FLAMBEAU_ATTN_TC");
+        g_attention_tc = (env && env[0] == '0') ? 0 : 1;
+    }
+    return g_attention_tc == 1;
+}
+
 }  // namespace
+
+// Portions of prompts run on the tcgen05 kernel where it takes the geometry (1, the default) or always on the
+// mma.sync kernel (0).
+FB_API void fb_set_attention_tc(int on) { g_attention_tc = on ? 1 : 0; }
 
 // q, out: bfloat16 [rows, heads*hd]; pools bfloat16 [pages][kv heads][page size][hd].
 // seq_*: per sequence of the step (device int32).  max_q_len / max_kv_len / any_short / any_long come from the
@@ -442,7 +458,9 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     a.short_ctas = 0; a.min_tiles = 1;
     a.part_o = nullptr; a.part_ml = nullptr; a.part_cnt = nullptr;
     if (any_long) {
-        const int rc = launch_long(a, HD_MAX, tma, n_seqs, max_q_len, stream);
+        const int rc = (attention_tc_enabled() && fb_attention_tc_takes(a, tma))
+                           ? fb_launch_attention_tc(a, n_seqs, max_q_len, stream)
+                           : launch_long(a, HD_MAX, tma, n_seqs, max_q_len, stream);
         if (rc) return rc;
     }
     if (any_short) return fb_launch_attention_split(a, HD_MAX, tma, n_seqs, scratch, scratch_floats, stream);

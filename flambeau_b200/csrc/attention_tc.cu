@@ -1,0 +1,394 @@
+// Paged causal (sliding-window) attention for portions of prompts on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory), for heads of 64 or 128 bfloat16 and pages that tile 128 keys.
+//
+// A CTA owns one key/value head and 128 query rows = (128 / G) tokens x the G query heads that share the head,
+// and walks the visible keys in tiles of 128:
+//
+//   S = Q K^T      tcgen05.mma, Q and K K-major in shared memory (128-byte swizzle), S in tensor memory
+//                  (two buffers, so the product of the next tile runs under the softmax of this one);
+//   softmax        128 threads, one per row (thread = tensor-memory lane): tcgen05.ld of the row, base-2 online
+//                  softmax in float32, P rounded to bfloat16 into shared memory (K-major, swizzled);
+//   O += P V       tcgen05.mma, V as it lies in the cache ([key][dim], the MN-major operand), O in tensor memory.
+//
+// O is rescaled only when a row's maximum has grown by more than 2^8 since the exponentials' reference point was
+// last moved (the sum l is kept against the same reference, so O / l is exact either way); the first tile sets
+// the reference.  Warps: 0 fetches K/V pages with tensor-map copies through a two-stage pipeline, 1 owns tensor
+// memory and issues the MMAs, 2..5 are the softmax (a warp reads the quarter of the lanes given by its index
+// modulo 4).  Every wait is bounded in time; when one runs out the kernel flags it, leaves its loops, frees its
+// tensor memory and returns.
+//
+// Formulas: crates/kernels-hip/src/kernels/attention_prefill_flash_tile_f16.cu:73-213 (tile + online softmax).
+#include "attention_common.cuh"
+#include "umma.cuh"
+
+namespace {
+
+using namespace fb_attn;
+
+constexpr int BM = 128;            // query rows per CTA
+constexpr int BN = 128;            // keys per tile
+constexpr int TC_THREADS = 192;
+constexpr int NKV = 2;             // K/V stages
+constexpr int TMEM_COLS = 512;     // S0 [0,128), S1 [128,256), O [256, 256 + HD)
+constexpr float RESCALE_STEP = 8.0f;
+
+template <int HD> struct TcSmem {
+    static constexpr int Q_BYTES = BM * HD * 2;                 // [HD/64 column blocks][128 rows][128 bytes]
+    static constexpr int KV_BYTES = BN * HD * 2;                // one K or V tile: [HD/64][128 keys][128 bytes]
+    static constexpr int P_BYTES = BM * BN * 2;                 // [2 key blocks][128 rows][128 bytes]
+    static constexpr int TAIL_BYTES = 256;                      // barriers, tensor-memory address, flag
+    static constexpr int USED = Q_BYTES + NKV * 2 * KV_BYTES + P_BYTES + TAIL_BYTES + 1024 /* alignment */;
+    // one CTA per SM: two would both want all of tensor memory
+    static constexpr int BYTES = USED > 120 * 1024 ? USED : 120 * 1024;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+attention_tc_kernel(const __grid_constant__ AttnArgs a) {
+    fb_pdl_launch_dependents();
+    using SM = TcSmem<HD>;
+    constexpr int CB = HD / 64;                                 // 64-column blocks of a head
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+    uint8_t* Qs = smem;
+    uint8_t* Ks = Qs + SM::Q_BYTES;                             // [NKV] tiles
+    uint8_t* Vs = Ks + NKV * SM::KV_BYTES;                      // [NKV] tiles
+    uint8_t* Ps = Vs + NKV * SM::KV_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + SM::P_BYTES);
+    uint64_t* kv_full = bars;                                   // [NKV] a K/V tile has landed
+    uint64_t* kv_empty = bars + NKV;                            // [NKV] the MMAs have read it
+    uint64_t* s_full = bars + 2 * NKV;                          // [2]   S of a tile is in tensor memory
+    uint64_t* s_empty = bars + 2 * NKV + 2;                     // [2]   the softmax has read it out
+    uint64_t* q_full = bars + 2 * NKV + 4;                      //       Q is staged
+    uint64_t* p_full = bars + 2 * NKV + 5;                      //       P of a tile is in shared memory
+    uint64_t* pv_done = bars + 2 * NKV + 6;                     //       O holds the tile's product
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NKV + 7);
+    int* bail = reinterpret_cast<int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = a.nh / a.nkv, hd = a.hd;
+
+    // ---- what this CTA has to do: query tokens [tok0, tok0 + ntok) of a sequence, one key/value head ----
+    const int seq = blockIdx.z, kvh = blockIdx.y;
+    const int q_len = a.seq_q_len[seq];
+    if (q_len * G <= a.short_rows) return;                      // the split-key arrangement's
+    const int TQ = BM / G;
+    const int tok0 = (gridDim.x - 1 - blockIdx.x) * TQ;         // later tiles see more keys: start them first
+    if (tok0 >= q_len) return;
+    const int ntok = min(TQ, q_len - tok0);
+    const int q_start = a.seq_q_start[seq], pos0 = a.seq_pos_start[seq];
+    const int rows_valid = ntok * G;
+    const int p_first = pos0 + tok0, p_last = pos0 + tok0 + ntok - 1;
+    const int t_lo = (a.window > 0 && p_first - a.window + 1 > 0) ? p_first - a.window + 1 : 0;
+    const int t_hi = p_last;
+    const int k_begin = (t_lo / BN) * BN, k_end = t_hi + 1;
+    const int n_tiles = (k_end - k_begin + BN - 1) / BN;
+    const int* table = a.block_table + (size_t)seq * a.table_stride;
+    const int pages_per_tile = BN / a.page_size;
+    const int n_ops = 2 * pages_per_tile * CB;                  // copies per tile: (K or V, page, column block)
+
+    if (tid == 0) {
+        for (int s = 0; s < NKV; ++s) {
+            mbar_init(smem_u32(&kv_full[s]), n_ops);
+            mbar_init(smem_u32(&kv_empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&s_full[b]), 1);
+            mbar_init(smem_u32(&s_empty[b]), BM);
+        }
+        mbar_init(smem_u32(q_full), BM);
+        mbar_init(smem_u32(p_full), BM);
+        mbar_init(smem_u32(pv_done), 1);
+        *bail = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    // pages that no query can see are not fetched: clear the tiles once so that what stays there is finite
+    for (int idx = tid; idx < NKV * 2 * SM::KV_BYTES / 16; idx += TC_THREADS)
+        reinterpret_cast<uint4*>(Ks)[idx] = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tmem_fence_before();
+    __syncthreads();
+    tmem_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    fb_pdl_wait();                                              // from here on: Q and the cache
+
+    // a wait that ran out anywhere ends every loop of the CTA
+    auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+        if (*(volatile int*)bail) return false;
+        if (mbar_wait(smem_u32(bar), parity, a.status)) return true;
+        *(volatile int*)bail = 1;
+        return false;
+    };
+
+    if (warp == 0) {
+        // ================= fetch: lane l issues copies l, l + 32, ... of every tile =================
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j % NKV;
+            if (j >= NKV && !wait(&kv_empty[s], (uint32_t)(j / NKV - 1) & 1u)) break;
+            const int tile_start = k_begin + j * BN;
+            const uint32_t bar = smem_u32(&kv_full[s]);
+            for (int op = lane; op < n_ops; op += 32) {
+                const bool is_v = op & 1;
+                const int rest = op >> 1;
+                const int cb = rest % CB, pj = rest / CB;
+                const int t_first = tile_start + pj * a.page_size;
+                bool fetch = t_first + a.page_size > t_lo && t_first < k_end;
+                int page = -1;
+                if (fetch) {
+                    page = table[t_first / a.page_size];
+                    if (page < 0 || page >= a.n_pages) {
+                        atomicOr(a.status, FB_STATUS_BAD_PAGE);
+                        fetch = false;
+                    }
+                }
+                if (fetch) {
+                    uint8_t* dst = (is_v ? Vs : Ks) + s * SM::KV_BYTES + cb * (BN * 128) + pj * a.page_size * 128;
+                    mbar_expect_tx(bar, (uint32_t)(a.page_size * 128));
+                    tma_load_2d(smem_u32(dst), is_v ? &a.map_v : &a.map_k, bar, cb * 64,
+                                (page * a.nkv + kvh) * a.page_size);
+                } else {
+                    mbar_arrive(bar);                           // stale (finite) data stays in the slot; it is masked
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issue =================
+        if (elect_one()) {
+            constexpr uint32_t idesc_s = umma_idesc(BN);
+            constexpr uint32_t idesc_o = umma_idesc(HD, true);
+            const uint32_t q_addr = smem_u32(Qs), p_addr = smem_u32(Ps);
+            auto issue_s = [&](int j) {                         // S[j & 1] = Q K_j^T
+                const uint32_t k_addr = smem_u32(Ks + (j % NKV) * SM::KV_BYTES);
+                const uint32_t d = tmem_base + (uint32_t)((j & 1) * BN);
+#pragma unroll
+                for (int kk = 0; kk < HD / UMMA_K; ++kk) {
+                    const uint32_t off = (uint32_t)((kk / 4) * (128 * 128) + (kk % 4) * 32);
+                    umma_bf16(d, umma_desc(q_addr + off), umma_desc(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&s_full[j & 1]));
+            };
+            bool ok = wait(q_full, 0) && wait(&kv_full[0], 0);
+            if (ok) {
+                tmem_fence_after();
+                issue_s(0);
+            }
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                if (j + 1 < n_tiles) {
+                    // the next tile's scores, under this tile's softmax
+                    ok = wait(&kv_full[(j + 1) % NKV], (uint32_t)((j + 1) / NKV) & 1u);
+                    if (ok && j + 1 >= 2) ok = wait(&s_empty[(j + 1) & 1], (uint32_t)((j + 1) / 2 - 1) & 1u);
+                    if (!ok) break;
+                    tmem_fence_after();
+                    issue_s(j + 1);
+                }
+                ok = wait(p_full, (uint32_t)j & 1u);
+                if (!ok) break;
+                tmem_fence_after();
+                const uint32_t v_addr = smem_u32(Vs + (j % NKV) * SM::KV_BYTES);
+                const uint32_t d = tmem_base + (uint32_t)(2 * BN);
+#pragma unroll
+                for (int kk = 0; kk < BN / UMMA_K; ++kk) {      // 16 keys each
+                    const uint64_t da = umma_desc(p_addr + (uint32_t)((kk / 4) * (128 * 128) + (kk % 4) * 32));
+                    const uint64_t db = umma_desc_mn(v_addr + (uint32_t)(kk * 16 * 128), BN * 128, 1024);
+                    umma_bf16(d, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&kv_empty[j % NKV]));
+                umma_commit(smem_u32(pv_done));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ================= softmax: thread = query row = tensor-memory lane =================
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const bool valid = r < rows_valid;
+        const int token = q_start + tok0 + r / G, head = kvh * G + r % G;
+        // ---- stage Q (zero rows beyond the CTA's share) ----
+        {
+            const __nv_bfloat16* src = a.q + (size_t)token * a.q_stride + (size_t)head * hd;
+#pragma unroll
+            for (int c = 0; c < HD / 8; ++c) {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
+                *reinterpret_cast<uint4*>(Qs + (c / 8) * (BM * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(smem_u32(q_full));
+        }
+        const int p_row = valid ? pos0 + tok0 + r / G : -1;     // a row beyond the share sees nothing
+        const int t0_row = (a.window > 0 && p_row - a.window + 1 > 0) ? p_row - a.window + 1 : 0;
+        const int t0_max = (a.window > 0 && p_last - a.window + 1 > 0) ? p_last - a.window + 1 : 0;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float m_ref = -INFINITY;                                // reference point of the exponentials (scaled, base 2)
+        float l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int b = j & 1;
+            const int tile_start = k_begin + j * BN;
+            ok = __all_sync(0xffffffffu, wait(&s_full[b], (uint32_t)(j / 2) & 1u));
+            if (!ok) break;
+            tmem_fence_after();
+            const uint32_t s_addr = lane_addr + (uint32_t)(b * BN);
+            // every row of the CTA sees every key of the tile, or the comparison per key is needed
+            const bool need_mask = tile_start + BN - 1 > p_first || tile_start < t0_max || rows_valid < BM;
+            // ---- first pass: the row's maximum ----
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c4 = 0; c4 < BN / 32; ++c4) {
+                uint32_t v[32];
+                tmem_ld32_nowait(s_addr + (uint32_t)(c4 * 32), v);
+                tmem_wait_ld();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int t = tile_start + c4 * 32 + i;
+                        mx = fmaxf(mx, (t >= t0_row && t <= p_row) ? __uint_as_float(v[i]) : -INFINITY);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                }
+            }
+            const float m_new = fmaxf(m_ref, mx * a.scale_log2e);
+            bool o_waited = false;
+            if (j == 0) {
+                m_ref = m_new;                                  // O is overwritten by the first product
+            } else if (__any_sync(0xffffffffu, m_new > m_ref + RESCALE_STEP || (m_ref == -INFINITY && m_new > m_ref))) {
+                // move the reference point: O *= 2^(old - new), for the whole warp at once
+                ok = __all_sync(0xffffffffu, wait(pv_done, (uint32_t)(j - 1) & 1u));
+                if (!ok) break;
+                o_waited = true;
+                tmem_fence_after();
+                const float f = m_new == -INFINITY ? 1.0f : exp2f(m_ref - m_new);
+#pragma unroll
+                for (int c4 = 0; c4 < HD / 32; ++c4) {
+                    uint32_t v[32];
+                    tmem_ld32_nowait(lane_addr + (uint32_t)(2 * BN + c4 * 32), v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+                    tmem_st32(lane_addr + (uint32_t)(2 * BN + c4 * 32), v);
+                }
+                tmem_wait_st();
+                l *= f;
+                m_ref = m_new;
+            }
+            if (j > 0 && !o_waited) {                           // P of the tile before must have been read
+                ok = __all_sync(0xffffffffu, wait(pv_done, (uint32_t)(j - 1) & 1u));
+                if (!ok) break;
+            }
+            // ---- second pass: P = 2^(s - reference), rounded to bfloat16 into shared memory ----
+            const float m_eff = m_ref == -INFINITY ? 0.0f : m_ref;
+            float sum = 0.0f;
+#pragma unroll
+            for (int c4 = 0; c4 < BN / 32; ++c4) {
+                uint32_t v[32];
+                tmem_ld32_nowait(s_addr + (uint32_t)(c4 * 32), v);
+                tmem_wait_ld();
+                if (c4 == BN / 32 - 1) {                        // S has been read out: the MMA warp may reuse it
+                    tmem_fence_before();
+                    mbar_arrive(smem_u32(&s_empty[b]));
+                }
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = exp2f(__uint_as_float(v[i]) * a.scale_log2e - m_eff);
+                    float p1 = exp2f(__uint_as_float(v[i + 1]) * a.scale_log2e - m_eff);
+                    if (need_mask) {
+                        const int t = tile_start + c4 * 32 + i;
+                        if (!(t >= t0_row && t <= p_row)) p0 = 0.0f;
+                        if (!(t + 1 >= t0_row && t + 1 <= p_row)) p1 = 0.0f;
+                    }
+                    sum += p0 + p1;
+                    packed[i / 2] = pack_bf16(p0, p1);
+                }
+                // keys c4*32 .. +31 of row r: key block c4 / 2, 16-byte chunks (c4 % 2) * 4 .. + 3 of the row
+                uint8_t* row = Ps + (c4 / 2) * (BM * 128) + r * 128;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int chunk = (c4 & 1) * 4 + q4;
+                    *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) =
+                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                }
+            }
+            l += sum;
+            if (tile_start + BN > t_hi + 1) {
+                // Whole pages arrive, the slots behind the last position included, and what a page holds there was
+                // never written by this request.  Their probabilities are 0, but 0 * NaN is NaN: clear those value
+                // rows (128 bytes per key and column block) before the product reads them.
+                ok = __all_sync(0xffffffffu, wait(&kv_full[j % NKV], (uint32_t)(j / NKV) & 1u));
+                if (!ok) break;
+                uint8_t* vt = Vs + (j % NKV) * SM::KV_BYTES;
+                const int first_dead = t_hi + 1 - tile_start;   // >= 1
+                const int chunks = (BN - first_dead) * 8;
+                for (int idx = tid - 64; idx < chunks * CB; idx += BM) {
+                    const int cb = idx / chunks, rest = idx - cb * chunks;
+                    *reinterpret_cast<uint4*>(vt + cb * (BN * 128) + (first_dead + rest / 8) * 128 + (rest & 7) * 16) =
+                        make_uint4(0, 0, 0, 0);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(smem_u32(p_full));
+        }
+        // ---- O / l, written as bfloat16 ----
+        if (ok) ok = __all_sync(0xffffffffu, wait(pv_done, (uint32_t)(n_tiles - 1) & 1u));
+        if (ok) {
+            tmem_fence_after();
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd;
+#pragma unroll
+            for (int c4 = 0; c4 < HD / 32; ++c4) {
+                uint32_t v[32];
+                tmem_ld32_nowait(lane_addr + (uint32_t)(2 * BN + c4 * 32), v);
+                tmem_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            w[e] = pack_bf16(__uint_as_float(v[8 * q4 + 2 * e]) * inv,
+                                             __uint_as_float(v[8 * q4 + 2 * e + 1]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c4 * 32 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    tmem_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tmem_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int HD>
+int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream) {
+    auto kern = attention_tc_kernel<HD>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<HD>::BYTES);
+        if (e != cudaSuccess) return fb_fail(-2, "attention_tc: cannot reserve %d bytes of shared memory: %s",
+                                             TcSmem<HD>::BYTES, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int TQ = BM / (a.nh / a.nkv);
+    const dim3 grid((max_q_len + TQ - 1) / TQ, a.nkv, n_seqs);
+    fb_launch((kern), grid, TC_THREADS, (size_t)TcSmem<HD>::BYTES, stream, a);
+    return fb_check_launch("attention_tc");
+}
+
+}  // namespace
+
+bool fb_attention_tc_takes(const AttnArgs& a, bool tma) {
+    const int G = a.nh / a.nkv;
+    return tma && (a.hd == 64 || a.hd == 128) && G <= BM && BN % a.page_size == 0 && a.out_stride % 8 == 0 &&
+           (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
+}
+
+int fb_launch_attention_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream) {
+    return a.hd == 64 ? launch_tc<64>(a, n_seqs, max_q_len, stream) : launch_tc<128>(a, n_seqs, max_q_len, stream);
+}

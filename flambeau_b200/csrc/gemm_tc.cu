@@ -24,9 +24,8 @@
 // The reference multiplies with scalar-FMA tiles of 64 outputs x 8 rows
 // (crates/kernels-hip/src/kernels/mmq_f16_tile.cu:32-107); the weight layout
 // (rows = outputs) is the same.
-#include "async_copy.cuh"
-
 #include "tensor_map.cuh"
+#include "umma.cuh"
 
 #include <mutex>
 #include <stdlib.h>
@@ -35,46 +34,8 @@ namespace {
 
 constexpr int BM = 128;          // output features per CTA (UMMA M)
 constexpr int BK = 64;           // K elements per stage: 128 bytes, one swizzle row
-constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 320;      // warp 0: TMA, warp 1: MMA, warps 2..9: epilogue (two per lane quarter)
 constexpr int EPI_THREADS = 256;
-// Shared-memory matrix descriptor: K-major tile of rows x 64 bf16, 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address, bits [0,14)
-    d |= (uint64_t)1 << 16;                                // leading byte offset (unused with this swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset, bits [32,46)
-    d |= (uint64_t)1 << 46;                                // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;                                // layout: 128-byte swizzle
-    return d;
-}
-
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t umma_idesc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 template <int BN> struct TileCfg {
     // A stage holds KA swizzle atoms of K (64 elements each) of both operands.  (Two atoms a stage, which make

@@ -21,6 +21,7 @@ _SIGNATURES = {
     "fb_last_error": (c_char_p, []),
     "fb_abi_version": (I, []),
     "fb_set_pdl": (None, [I]),
+    "fb_set_attention_tc": (None, [I]),
     # elementwise.cu
     "fb_embedding": (I, [P, I, P, P, I, I, I, P, STREAM]),
     "fb_add_rmsnorm": (I, [P, P, I, I, L, P, I, P, I, P, I, I, F, STREAM]),

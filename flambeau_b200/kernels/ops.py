@@ -308,6 +308,12 @@ class _AttentionScratch:
         return hit
 
 
+def set_attention_tc(on: bool) -> None:
+    """Portions of prompts on the tcgen05 attention kernel where it takes the geometry (the default), or always on
+    the mma.sync kernel."""
+    lib().fb_set_attention_tc(1 if on else 0)
+
+
 def mma_attention_supported(q: torch.Tensor, nh: int, nkv: int, hd: int) -> bool:
     return (q.dtype == torch.bfloat16 and hd % 8 == 0 and hd <= 256 and nh % nkv == 0 and nh // nkv <= 64
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
