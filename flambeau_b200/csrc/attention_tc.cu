@@ -6,16 +6,17 @@
 //
 //   S = Q K^T      tcgen05.mma, Q and K K-major in shared memory (128-byte swizzle), S in tensor memory
 //                  (two buffers, so the product of the next tile runs under the softmax of this one);
-//   softmax        128 threads, one per row (thread = tensor-memory lane): tcgen05.ld of the row, base-2 online
-//                  softmax in float32, P rounded to bfloat16 into shared memory (K-major, swizzled);
+//   softmax        256 threads, two per row (the row = their tensor-memory lane, 64 of the tile's keys each):
+//                  tcgen05.ld of the scores, base-2 online softmax in float32, P rounded to bfloat16 into shared
+//                  memory (K-major, swizzled);
 //   O += P V       tcgen05.mma, V as it lies in the cache ([key][dim], the MN-major operand), O in tensor memory.
 //
 // O is rescaled only when a row's maximum has grown by more than 2^8 since the exponentials' reference point was
 // last moved (the sum l is kept against the same reference, so O / l is exact either way); the first tile sets
-// the reference.  Warps: 0 fetches K/V pages with tensor-map copies through a two-stage pipeline, 1 owns tensor
-// memory and issues the MMAs, 2..5 are the softmax (a warp reads the quarter of the lanes given by its index
-// modulo 4).  Every wait is bounded in time; when one runs out the kernel flags it, leaves its loops, frees its
-// tensor memory and returns.
+// the reference.  Warps: 0 fetches K and V pages with tensor-map copies through two-slot rings, 1 owns tensor
+// memory and issues the MMAs, 2..9 are the softmax (a warp reads the quarter of the lanes given by its index
+// modulo 4; two warps share a quarter).  Every wait is bounded in time; when one runs out the kernel flags it,
+// leaves its loops, frees its tensor memory and returns.
 //
 // Formulas: crates/kernels-hip/src/kernels/attention_prefill_flash_tile_f16.cu:73-213 (tile + online softmax).
 #include "attention_common.cuh"
@@ -27,16 +28,24 @@ using namespace fb_attn;
 
 constexpr int BM = 128;            // query rows per CTA
 constexpr int BN = 128;            // keys per tile
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;       // warp 0 fetches, warp 1 issues the MMAs, warps 2..9 are the softmax
+constexpr int SOFTMAX_THREADS = 256;
 constexpr int NKV = 2;             // K/V stages
 constexpr int TMEM_COLS = 512;     // S0 [0,128), S1 [128,256), O [256, 256 + HD)
 constexpr float RESCALE_STEP = 8.0f;
+
+__device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 template <int HD> struct TcSmem {
     static constexpr int Q_BYTES = BM * HD * 2;                 // [HD/64 column blocks][128 rows][128 bytes]
     static constexpr int KV_BYTES = BN * HD * 2;                // one K or V tile: [HD/64][128 keys][128 bytes]
     static constexpr int P_BYTES = BM * BN * 2;                 // [2 key blocks][128 rows][128 bytes]
-    static constexpr int TAIL_BYTES = 256;                      // barriers, tensor-memory address, flag
+    static constexpr int TAIL_BYTES = 256 + 4 * BM * 4;         // barriers, tensor-memory address, flag; row maxima
     static constexpr int USED = Q_BYTES + NKV * 2 * KV_BYTES + P_BYTES + TAIL_BYTES + 1024 /* alignment */;
     // one CTA per SM: two would both want all of tensor memory
     static constexpr int BYTES = USED > 120 * 1024 ? USED : 120 * 1024;
@@ -56,15 +65,18 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     uint8_t* Vs = Ks + NKV * SM::KV_BYTES;                      // [NKV] tiles
     uint8_t* Ps = Vs + NKV * SM::KV_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + SM::P_BYTES);
-    uint64_t* kv_full = bars;                                   // [NKV] a K/V tile has landed
-    uint64_t* kv_empty = bars + NKV;                            // [NKV] the MMAs have read it
-    uint64_t* s_full = bars + 2 * NKV;                          // [2]   S of a tile is in tensor memory
-    uint64_t* s_empty = bars + 2 * NKV + 2;                     // [2]   the softmax has read it out
-    uint64_t* q_full = bars + 2 * NKV + 4;                      //       Q is staged
-    uint64_t* p_full = bars + 2 * NKV + 5;                      //       P of a tile is in shared memory
-    uint64_t* pv_done = bars + 2 * NKV + 6;                     //       O holds the tile's product
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NKV + 7);
+    uint64_t* k_full = bars;                                    // [NKV] a K tile has landed
+    uint64_t* k_empty = bars + NKV;                             // [NKV] its scores are computed
+    uint64_t* v_full = bars + 2 * NKV;                          // [NKV] a V tile has landed
+    uint64_t* v_empty = bars + 3 * NKV;                         // [NKV] its product is computed
+    uint64_t* s_full = bars + 4 * NKV;                          // [2]   S of a tile is in tensor memory
+    uint64_t* s_empty = bars + 4 * NKV + 2;                     // [2]   the softmax has read it out
+    uint64_t* q_full = bars + 4 * NKV + 4;                      //       Q is staged
+    uint64_t* p_full = bars + 4 * NKV + 5;                      //       P of a tile is in shared memory
+    uint64_t* pv_done = bars + 4 * NKV + 6;                     //       O holds the tile's product
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * NKV + 7);
     int* bail = reinterpret_cast<int*>(tmem_slot + 1);
+    float* xchg = reinterpret_cast<float*>(Ps + SM::P_BYTES + 256);   // [2 tiles][2 halves][128 rows]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = a.nh / a.nkv, hd = a.hd;
@@ -90,15 +102,17 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
 
     if (tid == 0) {
         for (int s = 0; s < NKV; ++s) {
-            mbar_init(smem_u32(&kv_full[s]), n_ops);
-            mbar_init(smem_u32(&kv_empty[s]), 1);
+            mbar_init(smem_u32(&k_full[s]), n_ops / 2);
+            mbar_init(smem_u32(&k_empty[s]), 1);
+            mbar_init(smem_u32(&v_full[s]), n_ops / 2);
+            mbar_init(smem_u32(&v_empty[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&s_full[b]), 1);
-            mbar_init(smem_u32(&s_empty[b]), BM);
+            mbar_init(smem_u32(&s_empty[b]), SOFTMAX_THREADS);
         }
-        mbar_init(smem_u32(q_full), BM);
-        mbar_init(smem_u32(p_full), BM);
+        mbar_init(smem_u32(q_full), SOFTMAX_THREADS);
+        mbar_init(smem_u32(p_full), SOFTMAX_THREADS);
         mbar_init(smem_u32(pv_done), 1);
         *bail = 0;
         mbar_fence_init();
@@ -123,35 +137,39 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     };
 
     if (warp == 0) {
-        // ================= fetch: lane l issues copies l, l + 32, ... of every tile =================
+        // ================= fetch: lane l copies (page l / CB, column block l % CB) of every K and V tile ==========
+        // K tiles and V tiles run through rings of their own: a K slot is free as soon as its scores are computed
+        // (a tile ahead of the softmax), a V slot after the tile's product, so a copy has two tiles' time to land.
+        // -2 = nothing to fetch (no query of the CTA sees the page), -1 = the table has no page although needed.
+        auto lookup = [&](int j) -> int {
+            if (lane >= n_ops / 2 || j >= n_tiles) return -2;
+            const int t_first = k_begin + j * BN + (lane / CB) * a.page_size;
+            if (!(t_first + a.page_size > t_lo && t_first < k_end)) return -2;
+            const int page = table[t_first / a.page_size];
+            return (page < 0 || page >= a.n_pages) ? -1 : page;
+        };
+        auto issue = [&](uint8_t* tile, const CUtensorMap* map, uint64_t* full, int page) {
+            if (lane >= n_ops / 2) return;
+            const uint32_t bar = smem_u32(full);
+            if (page >= 0) {
+                const int cb = lane % CB, pj = lane / CB;
+                mbar_expect_tx(bar, (uint32_t)(a.page_size * 128));
+                tma_load_2d(smem_u32(tile + cb * (BN * 128) + pj * a.page_size * 128), map, bar, cb * 64,
+                            (page * a.nkv + kvh) * a.page_size);
+            } else {
+                if (page == -1) atomicOr(a.status, FB_STATUS_BAD_PAGE);
+                mbar_arrive(bar);                               // stale (finite) data stays in the slot; it is masked
+            }
+        };
+        int page = lookup(0);
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j % NKV;
-            if (j >= NKV && !wait(&kv_empty[s], (uint32_t)(j / NKV - 1) & 1u)) break;
-            const int tile_start = k_begin + j * BN;
-            const uint32_t bar = smem_u32(&kv_full[s]);
-            for (int op = lane; op < n_ops; op += 32) {
-                const bool is_v = op & 1;
-                const int rest = op >> 1;
-                const int cb = rest % CB, pj = rest / CB;
-                const int t_first = tile_start + pj * a.page_size;
-                bool fetch = t_first + a.page_size > t_lo && t_first < k_end;
-                int page = -1;
-                if (fetch) {
-                    page = table[t_first / a.page_size];
-                    if (page < 0 || page >= a.n_pages) {
-                        atomicOr(a.status, FB_STATUS_BAD_PAGE);
-                        fetch = false;
-                    }
-                }
-                if (fetch) {
-                    uint8_t* dst = (is_v ? Vs : Ks) + s * SM::KV_BYTES + cb * (BN * 128) + pj * a.page_size * 128;
-                    mbar_expect_tx(bar, (uint32_t)(a.page_size * 128));
-                    tma_load_2d(smem_u32(dst), is_v ? &a.map_v : &a.map_k, bar, cb * 64,
-                                (page * a.nkv + kvh) * a.page_size);
-                } else {
-                    mbar_arrive(bar);                           // stale (finite) data stays in the slot; it is masked
-                }
-            }
+            const uint32_t reuse = (uint32_t)(j / NKV - 1) & 1u;
+            if (j >= NKV && !wait(&k_empty[s], reuse)) break;
+            issue(Ks + s * SM::KV_BYTES, &a.map_k, &k_full[s], page);
+            if (j >= NKV && !wait(&v_empty[s], reuse)) break;
+            issue(Vs + s * SM::KV_BYTES, &a.map_v, &v_full[s], page);
+            page = lookup(j + 1);                               // in flight while this warp waits for the next slot
         }
     } else if (warp == 1) {
         // ================= MMA issue =================
@@ -168,8 +186,9 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
                     umma_bf16(d, umma_desc(q_addr + off), umma_desc(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&s_full[j & 1]));
+                umma_commit(smem_u32(&k_empty[j % NKV]));
             };
-            bool ok = wait(q_full, 0) && wait(&kv_full[0], 0);
+            bool ok = wait(q_full, 0) && wait(&k_full[0], 0);
             if (ok) {
                 tmem_fence_after();
                 issue_s(0);
@@ -177,13 +196,13 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
             for (int j = 0; ok && j < n_tiles; ++j) {
                 if (j + 1 < n_tiles) {
                     // the next tile's scores, under this tile's softmax
-                    ok = wait(&kv_full[(j + 1) % NKV], (uint32_t)((j + 1) / NKV) & 1u);
+                    ok = wait(&k_full[(j + 1) % NKV], (uint32_t)((j + 1) / NKV) & 1u);
                     if (ok && j + 1 >= 2) ok = wait(&s_empty[(j + 1) & 1], (uint32_t)((j + 1) / 2 - 1) & 1u);
                     if (!ok) break;
                     tmem_fence_after();
                     issue_s(j + 1);
                 }
-                ok = wait(p_full, (uint32_t)j & 1u);
+                ok = wait(p_full, (uint32_t)j & 1u) && wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u);
                 if (!ok) break;
                 tmem_fence_after();
                 const uint32_t v_addr = smem_u32(Vs + (j % NKV) * SM::KV_BYTES);
@@ -194,22 +213,24 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
                     const uint64_t db = umma_desc_mn(v_addr + (uint32_t)(kk * 16 * 128), BN * 128, 1024);
                     umma_bf16(d, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(smem_u32(&kv_empty[j % NKV]));
+                umma_commit(smem_u32(&v_empty[j % NKV]));
                 umma_commit(smem_u32(pv_done));
             }
         }
         __syncwarp();
     } else {
-        // ================= softmax: thread = query row = tensor-memory lane =================
-        const int quarter = warp & 3;
+        // ================= softmax: two threads per query row (= tensor-memory lane), 64 keys of a tile each ==========
+        const int quarter = warp & 3;                           // the lanes this warp may read
+        const int half = (warp - 2) >> 2;                       // which 64 keys of a tile, which half of O's columns
         const int r = quarter * 32 + lane;
         const bool valid = r < rows_valid;
         const int token = q_start + tok0 + r / G, head = kvh * G + r % G;
-        // ---- stage Q (zero rows beyond the CTA's share) ----
+        // ---- stage Q (zero rows beyond the CTA's share); each thread of a pair takes half of the row ----
         {
             const __nv_bfloat16* src = a.q + (size_t)token * a.q_stride + (size_t)head * hd;
 #pragma unroll
-            for (int c = 0; c < HD / 8; ++c) {
+            for (int i = 0; i < HD / 16; ++i) {
+                const int c = half * (HD / 16) + i;
                 uint4 v = make_uint4(0, 0, 0, 0);
                 if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
                 *reinterpret_cast<uint4*>(Qs + (c / 8) * (BM * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
@@ -219,57 +240,75 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
         }
         const int p_row = valid ? pos0 + tok0 + r / G : -1;     // a row beyond the share sees nothing
         const int t0_row = (a.window > 0 && p_row - a.window + 1 > 0) ? p_row - a.window + 1 : 0;
-        const int t0_max = (a.window > 0 && p_last - a.window + 1 > 0) ? p_last - a.window + 1 : 0;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t o_addr = lane_addr + (uint32_t)(2 * BN + half * (HD / 2));   // this thread's columns of O
         float m_ref = -INFINITY;                                // reference point of the exponentials (scaled, base 2)
-        float l = 0.0f;
+        float l = 0.0f;                                         // sum over this thread's keys
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int b = j & 1;
-            const int tile_start = k_begin + j * BN;
-            ok = __all_sync(0xffffffffu, wait(&s_full[b], (uint32_t)(j / 2) & 1u));
-            if (!ok) break;
+            const int key0 = k_begin + j * BN + half * 64;      // this thread's first key of the tile
+            // (after a wait has run out every warp still goes through each tile's barrier, so that none is left at it)
+            ok = ok && __all_sync(0xffffffffu, wait(&s_full[b], (uint32_t)(j / 2) & 1u));
+            if (!ok) {
+                softmax_barrier();
+                continue;
+            }
             tmem_fence_after();
-            const uint32_t s_addr = lane_addr + (uint32_t)(b * BN);
-            // every row of the CTA sees every key of the tile, or the comparison per key is needed
-            const bool need_mask = tile_start + BN - 1 > p_first || tile_start < t0_max || rows_valid < BM;
-            // ---- first pass: the row's maximum ----
-            float mx = -INFINITY;
+            // ---- this thread's 64 scores into registers; then S may be overwritten ----
+            uint32_t v0[32], v1[32];
+            tmem_ld32_nowait(lane_addr + (uint32_t)(b * BN + half * 64), v0);
+            tmem_ld32_nowait(lane_addr + (uint32_t)(b * BN + half * 64 + 32), v1);
+            tmem_wait_ld();
+            tmem_fence_before();
+            mbar_arrive(smem_u32(&s_empty[b]));
+            // every key of this thread's 64 is visible to its row, for the whole warp, or each is compared
+            const bool plain = __all_sync(0xffffffffu, key0 + 63 <= p_row && key0 >= t0_row);
+            float s[64];
+            if (plain) {
 #pragma unroll
-            for (int c4 = 0; c4 < BN / 32; ++c4) {
-                uint32_t v[32];
-                tmem_ld32_nowait(s_addr + (uint32_t)(c4 * 32), v);
-                tmem_wait_ld();
-                if (need_mask) {
+                for (int i = 0; i < 32; ++i) {
+                    s[i] = __uint_as_float(v0[i]) * a.scale_log2e;
+                    s[32 + i] = __uint_as_float(v1[i]) * a.scale_log2e;
+                }
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int t = tile_start + c4 * 32 + i;
-                        mx = fmaxf(mx, (t >= t0_row && t <= p_row) ? __uint_as_float(v[i]) : -INFINITY);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                for (int i = 0; i < 32; ++i) {
+                    const int t = key0 + i;
+                    s[i] = (t >= t0_row && t <= p_row) ? __uint_as_float(v0[i]) * a.scale_log2e : -INFINITY;
+                    s[32 + i] = (t + 32 >= t0_row && t + 32 <= p_row) ? __uint_as_float(v1[i]) * a.scale_log2e : -INFINITY;
                 }
             }
-            const float m_new = fmaxf(m_ref, mx * a.scale_log2e);
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < 64; i += 4) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], s[i + e]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // the row's maximum over both halves
+            xchg[(b * 2 + half) * BM + r] = mx;
+            softmax_barrier();
+            const float m_new = fmaxf(m_ref, fmaxf(mx, xchg[(b * 2 + (half ^ 1)) * BM + r]));
             bool o_waited = false;
             if (j == 0) {
                 m_ref = m_new;                                  // O is overwritten by the first product
             } else if (__any_sync(0xffffffffu, m_new > m_ref + RESCALE_STEP || (m_ref == -INFINITY && m_new > m_ref))) {
-                // move the reference point: O *= 2^(old - new), for the whole warp at once
+                // move the reference point: O *= 2^(old - new), for the whole warp at once (both warps of a pair
+                // see the same maxima and decide alike; each scales its half of O's columns)
                 ok = __all_sync(0xffffffffu, wait(pv_done, (uint32_t)(j - 1) & 1u));
-                if (!ok) break;
+                if (!ok) continue;
                 o_waited = true;
                 tmem_fence_after();
                 const float f = m_new == -INFINITY ? 1.0f : exp2f(m_ref - m_new);
 #pragma unroll
-                for (int c4 = 0; c4 < HD / 32; ++c4) {
+                for (int c4 = 0; c4 < HD / 64; ++c4) {
                     uint32_t v[32];
-                    tmem_ld32_nowait(lane_addr + (uint32_t)(2 * BN + c4 * 32), v);
+                    tmem_ld32_nowait(o_addr + (uint32_t)(c4 * 32), v);
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-                    tmem_st32(lane_addr + (uint32_t)(2 * BN + c4 * 32), v);
+                    tmem_st32(o_addr + (uint32_t)(c4 * 32), v);
                 }
                 tmem_wait_st();
                 l *= f;
@@ -277,53 +316,35 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
             }
             if (j > 0 && !o_waited) {                           // P of the tile before must have been read
                 ok = __all_sync(0xffffffffu, wait(pv_done, (uint32_t)(j - 1) & 1u));
-                if (!ok) break;
+                if (!ok) continue;
             }
-            // ---- second pass: P = 2^(s - reference), rounded to bfloat16 into shared memory ----
+            // ---- P = 2^(s - reference), rounded to bfloat16 into this thread's key block of the row ----
             const float m_eff = m_ref == -INFINITY ? 0.0f : m_ref;
-            float sum = 0.0f;
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint8_t* row = Ps + half * (BM * 128) + r * 128;
 #pragma unroll
-            for (int c4 = 0; c4 < BN / 32; ++c4) {
-                uint32_t v[32];
-                tmem_ld32_nowait(s_addr + (uint32_t)(c4 * 32), v);
-                tmem_wait_ld();
-                if (c4 == BN / 32 - 1) {                        // S has been read out: the MMA warp may reuse it
-                    tmem_fence_before();
-                    mbar_arrive(smem_u32(&s_empty[b]));
-                }
-                uint32_t packed[16];
+            for (int c = 0; c < 8; ++c) {                       // 16-byte chunks of 8 keys
+                uint32_t w[4];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = exp2f(__uint_as_float(v[i]) * a.scale_log2e - m_eff);
-                    float p1 = exp2f(__uint_as_float(v[i + 1]) * a.scale_log2e - m_eff);
-                    if (need_mask) {
-                        const int t = tile_start + c4 * 32 + i;
-                        if (!(t >= t0_row && t <= p_row)) p0 = 0.0f;
-                        if (!(t + 1 >= t0_row && t + 1 <= p_row)) p1 = 0.0f;
-                    }
-                    sum += p0 + p1;
-                    packed[i / 2] = pack_bf16(p0, p1);
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = fast_exp2(s[c * 8 + 2 * e] - m_eff), p1 = fast_exp2(s[c * 8 + 2 * e + 1] - m_eff);
+                    sum4[e] += p0 + p1;
+                    w[e] = pack_bf16(p0, p1);
                 }
-                // keys c4*32 .. +31 of row r: key block c4 / 2, 16-byte chunks (c4 % 2) * 4 .. + 3 of the row
-                uint8_t* row = Ps + (c4 / 2) * (BM * 128) + r * 128;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = (c4 & 1) * 4 + q4;
-                    *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) =
-                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-                }
+                *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            l += sum;
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            const int tile_start = k_begin + j * BN;
             if (tile_start + BN > t_hi + 1) {
                 // Whole pages arrive, the slots behind the last position included, and what a page holds there was
                 // never written by this request.  Their probabilities are 0, but 0 * NaN is NaN: clear those value
                 // rows (128 bytes per key and column block) before the product reads them.
-                ok = __all_sync(0xffffffffu, wait(&kv_full[j % NKV], (uint32_t)(j / NKV) & 1u));
-                if (!ok) break;
+                ok = __all_sync(0xffffffffu, wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u));
+                if (!ok) continue;
                 uint8_t* vt = Vs + (j % NKV) * SM::KV_BYTES;
                 const int first_dead = t_hi + 1 - tile_start;   // >= 1
                 const int chunks = (BN - first_dead) * 8;
-                for (int idx = tid - 64; idx < chunks * CB; idx += BM) {
+                for (int idx = tid - 64; idx < chunks * CB; idx += SOFTMAX_THREADS) {
                     const int cb = idx / chunks, rest = idx - cb * chunks;
                     *reinterpret_cast<uint4*>(vt + cb * (BN * 128) + (first_dead + rest / 8) * 128 + (rest & 7) * 16) =
                         make_uint4(0, 0, 0, 0);
@@ -332,16 +353,19 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(smem_u32(p_full));
         }
-        // ---- O / l, written as bfloat16 ----
+        // ---- O / l, written as bfloat16: each thread of a pair its half of the columns ----
         if (ok) ok = __all_sync(0xffffffffu, wait(pv_done, (uint32_t)(n_tiles - 1) & 1u));
+        xchg[half * BM + r] = l;
+        softmax_barrier();
         if (ok) {
             tmem_fence_after();
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd;
+            const float l_row = l + xchg[(half ^ 1) * BM + r];
+            const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
+            __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd + half * (HD / 2);
 #pragma unroll
-            for (int c4 = 0; c4 < HD / 32; ++c4) {
+            for (int c4 = 0; c4 < HD / 64; ++c4) {
                 uint32_t v[32];
-                tmem_ld32_nowait(lane_addr + (uint32_t)(2 * BN + c4 * 32), v);
+                tmem_ld32_nowait(o_addr + (uint32_t)(c4 * 32), v);
                 tmem_wait_ld();
                 if (valid) {
 #pragma unroll
