@@ -5,11 +5,12 @@
 // and walks the visible keys in tiles of 128:
 //
 //   S = Q K^T      tcgen05.mma, Q and K K-major in shared memory (128-byte swizzle), S in tensor memory
-//                  (two buffers, so the product of the next tile runs under the softmax of this one);
+//                  (two buffers, so the products of other tiles run under the softmax of this one);
 //   softmax        256 threads, two per row (the row = their tensor-memory lane, 64 of the tile's keys each):
-//                  tcgen05.ld of the scores, base-2 online softmax in float32, P rounded to bfloat16 into shared
-//                  memory (K-major, swizzled);
-//   O += P V       tcgen05.mma, V as it lies in the cache ([key][dim], the MN-major operand), O in tensor memory.
+//                  tcgen05.ld of the scores, base-2 online softmax in float32, P rounded to bfloat16 and stored
+//                  with tcgen05.st over the scores it came from;
+//   O += P V       tcgen05.mma with P read from tensor memory and V as it lies in the cache ([key][dim], the
+//                  MN-major operand); O in tensor memory.
 //
 // O is rescaled only when a row's maximum has grown by more than 2^8 since the exponentials' reference point was
 // last moved (the sum l is kept against the same reference, so O / l is exact either way); the first tile sets
@@ -31,7 +32,7 @@ constexpr int BN = 128;            // keys per tile
 constexpr int TC_THREADS = 320;       // warp 0 fetches, warp 1 issues the MMAs, warps 2..9 are the softmax
 constexpr int SOFTMAX_THREADS = 256;
 constexpr int NKV = 2;             // K/V stages
-constexpr int TMEM_COLS = 512;     // S0 [0,128), S1 [128,256), O [256, 256 + HD)
+constexpr int TMEM_COLS = 512;     // S0 / P0 [0,128), S1 / P1 [128,256), O [256, 256 + HD)
 constexpr float RESCALE_STEP = 8.0f;
 
 __device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory"); }
@@ -44,9 +45,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 template <int HD> struct TcSmem {
     static constexpr int Q_BYTES = BM * HD * 2;                 // [HD/64 column blocks][128 rows][128 bytes]
     static constexpr int KV_BYTES = BN * HD * 2;                // one K or V tile: [HD/64][128 keys][128 bytes]
-    static constexpr int P_BYTES = BM * BN * 2;                 // [2 key blocks][128 rows][128 bytes]
     static constexpr int TAIL_BYTES = 256 + 4 * BM * 4;         // barriers, tensor-memory address, flag; row maxima
-    static constexpr int USED = Q_BYTES + NKV * 2 * KV_BYTES + P_BYTES + TAIL_BYTES + 1024 /* alignment */;
+    static constexpr int USED = Q_BYTES + NKV * 2 * KV_BYTES + TAIL_BYTES + 1024 /* alignment */;
     // one CTA per SM: two would both want all of tensor memory
     static constexpr int BYTES = USED > 120 * 1024 ? USED : 120 * 1024;
 };
@@ -63,20 +63,19 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     uint8_t* Qs = smem;
     uint8_t* Ks = Qs + SM::Q_BYTES;                             // [NKV] tiles
     uint8_t* Vs = Ks + NKV * SM::KV_BYTES;                      // [NKV] tiles
-    uint8_t* Ps = Vs + NKV * SM::KV_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + SM::P_BYTES);
+    uint8_t* tail = Vs + NKV * SM::KV_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
     uint64_t* k_full = bars;                                    // [NKV] a K tile has landed
     uint64_t* k_empty = bars + NKV;                             // [NKV] its scores are computed
     uint64_t* v_full = bars + 2 * NKV;                          // [NKV] a V tile has landed
     uint64_t* v_empty = bars + 3 * NKV;                         // [NKV] its product is computed
     uint64_t* s_full = bars + 4 * NKV;                          // [2]   S of a tile is in tensor memory
-    uint64_t* s_empty = bars + 4 * NKV + 2;                     // [2]   the softmax has read it out
     uint64_t* q_full = bars + 4 * NKV + 4;                      //       Q is staged
-    uint64_t* p_full = bars + 4 * NKV + 5;                      //       P of a tile is in shared memory
+    uint64_t* p_full = bars + 4 * NKV + 5;                      //       P of a tile is in tensor memory
     uint64_t* pv_done = bars + 4 * NKV + 6;                     //       O holds the tile's product
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * NKV + 7);
     int* bail = reinterpret_cast<int*>(tmem_slot + 1);
-    float* xchg = reinterpret_cast<float*>(Ps + SM::P_BYTES + 256);   // [2 tiles][2 halves][128 rows]
+    float* xchg = reinterpret_cast<float*>(tail + 256);         // [2 tiles][2 halves][128 rows]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = a.nh / a.nkv, hd = a.hd;
@@ -109,7 +108,6 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&s_full[b]), 1);
-            mbar_init(smem_u32(&s_empty[b]), SOFTMAX_THREADS);
         }
         mbar_init(smem_u32(q_full), SOFTMAX_THREADS);
         mbar_init(smem_u32(p_full), SOFTMAX_THREADS);
@@ -118,10 +116,6 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
-    // pages that no query can see are not fetched: clear the tiles once so that what stays there is finite
-    for (int idx = tid; idx < NKV * 2 * SM::KV_BYTES / 16; idx += TC_THREADS)
-        reinterpret_cast<uint4*>(Ks)[idx] = make_uint4(0, 0, 0, 0);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tmem_fence_before();
     __syncthreads();
     tmem_fence_after();
@@ -176,7 +170,7 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
         if (elect_one()) {
             constexpr uint32_t idesc_s = umma_idesc(BN);
             constexpr uint32_t idesc_o = umma_idesc(HD, true);
-            const uint32_t q_addr = smem_u32(Qs), p_addr = smem_u32(Ps);
+            const uint32_t q_addr = smem_u32(Qs);
             auto issue_s = [&](int j) {                         // S[j & 1] = Q K_j^T
                 const uint32_t k_addr = smem_u32(Ks + (j % NKV) * SM::KV_BYTES);
                 const uint32_t d = tmem_base + (uint32_t)((j & 1) * BN);
@@ -188,33 +182,36 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
                 umma_commit(smem_u32(&s_full[j & 1]));
                 umma_commit(smem_u32(&k_empty[j % NKV]));
             };
-            bool ok = wait(q_full, 0) && wait(&k_full[0], 0);
-            if (ok) {
+            // the scores of the first two tiles: both buffers are free
+            bool ok = wait(q_full, 0);
+            for (int j = 0; ok && j < 2 && j < n_tiles; ++j) {
+                ok = wait(&k_full[j % NKV], (uint32_t)(j / NKV) & 1u);
+                if (!ok) break;
                 tmem_fence_after();
-                issue_s(0);
+                issue_s(j);
             }
             for (int j = 0; ok && j < n_tiles; ++j) {
-                if (j + 1 < n_tiles) {
-                    // the next tile's scores, under this tile's softmax
-                    ok = wait(&k_full[(j + 1) % NKV], (uint32_t)((j + 1) / NKV) & 1u);
-                    if (ok && j + 1 >= 2) ok = wait(&s_empty[(j + 1) & 1], (uint32_t)((j + 1) / 2 - 1) & 1u);
-                    if (!ok) break;
-                    tmem_fence_after();
-                    issue_s(j + 1);
-                }
                 ok = wait(p_full, (uint32_t)j & 1u) && wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u);
                 if (!ok) break;
                 tmem_fence_after();
                 const uint32_t v_addr = smem_u32(Vs + (j % NKV) * SM::KV_BYTES);
+                const uint32_t p_addr = tmem_base + (uint32_t)((j & 1) * BN);   // bf16 pairs over the tile's scores
                 const uint32_t d = tmem_base + (uint32_t)(2 * BN);
 #pragma unroll
-                for (int kk = 0; kk < BN / UMMA_K; ++kk) {      // 16 keys each
-                    const uint64_t da = umma_desc(p_addr + (uint32_t)((kk / 4) * (128 * 128) + (kk % 4) * 32));
+                for (int kk = 0; kk < BN / UMMA_K; ++kk) {      // 16 keys = 8 columns of P each
                     const uint64_t db = umma_desc_mn(v_addr + (uint32_t)(kk * 16 * 128), BN * 128, 1024);
-                    umma_bf16(d, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                    umma_bf16_ts(d, p_addr + (uint32_t)(kk * 8), db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&v_empty[j % NKV]));
                 umma_commit(smem_u32(pv_done));
+                if (j + 2 < n_tiles) {
+                    // the scores of the tile after next go where this tile's P lay; the MMAs run in the order of
+                    // their issue, so the product above has read P by then
+                    ok = wait(&k_full[(j + 2) % NKV], (uint32_t)((j + 2) / NKV) & 1u);
+                    if (!ok) break;
+                    tmem_fence_after();
+                    issue_s(j + 2);
+                }
             }
         }
         __syncwarp();
@@ -255,13 +252,11 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
                 continue;
             }
             tmem_fence_after();
-            // ---- this thread's 64 scores into registers; then S may be overwritten ----
+            // ---- this thread's 64 scores into registers ----
             uint32_t v0[32], v1[32];
             tmem_ld32_nowait(lane_addr + (uint32_t)(b * BN + half * 64), v0);
             tmem_ld32_nowait(lane_addr + (uint32_t)(b * BN + half * 64 + 32), v1);
             tmem_wait_ld();
-            tmem_fence_before();
-            mbar_arrive(smem_u32(&s_empty[b]));
             // every key of this thread's 64 is visible to its row, for the whole warp, or each is compared
             const bool plain = __all_sync(0xffffffffu, key0 + 63 <= p_row && key0 >= t0_row);
             float s[64];
@@ -290,7 +285,6 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
             xchg[(b * 2 + half) * BM + r] = mx;
             softmax_barrier();
             const float m_new = fmaxf(m_ref, fmaxf(mx, xchg[(b * 2 + (half ^ 1)) * BM + r]));
-            bool o_waited = false;
             if (j == 0) {
                 m_ref = m_new;                                  // O is overwritten by the first product
             } else if (__any_sync(0xffffffffu, m_new > m_ref + RESCALE_STEP || (m_ref == -INFINITY && m_new > m_ref))) {
@@ -298,7 +292,6 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
                 // see the same maxima and decide alike; each scales its half of O's columns)
                 ok = __all_sync(0xffffffffu, wait(pv_done, (uint32_t)(j - 1) & 1u));
                 if (!ok) continue;
-                o_waited = true;
                 tmem_fence_after();
                 const float f = m_new == -INFINITY ? 1.0f : exp2f(m_ref - m_new);
 #pragma unroll
@@ -314,43 +307,40 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
                 l *= f;
                 m_ref = m_new;
             }
-            if (j > 0 && !o_waited) {                           // P of the tile before must have been read
-                ok = __all_sync(0xffffffffu, wait(pv_done, (uint32_t)(j - 1) & 1u));
-                if (!ok) continue;
-            }
-            // ---- P = 2^(s - reference), rounded to bfloat16 into this thread's key block of the row ----
+            // ---- P = 2^(s - reference), rounded to bfloat16, over this thread's scores (the partner has read its
+            // own before the barrier above): 64 keys = 32 columns ----
             const float m_eff = m_ref == -INFINITY ? 0.0f : m_ref;
             float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint8_t* row = Ps + half * (BM * 128) + r * 128;
+            uint32_t pk[32];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {                       // 16-byte chunks of 8 keys
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = fast_exp2(s[c * 8 + 2 * e] - m_eff), p1 = fast_exp2(s[c * 8 + 2 * e + 1] - m_eff);
-                    sum4[e] += p0 + p1;
-                    w[e] = pack_bf16(p0, p1);
-                }
-                *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int i = 0; i < 32; ++i) {
+                const float p0 = fast_exp2(s[2 * i] - m_eff), p1 = fast_exp2(s[2 * i + 1] - m_eff);
+                sum4[i & 3] += p0 + p1;
+                pk[i] = pack_bf16(p0, p1);
             }
+            tmem_st32(lane_addr + (uint32_t)(b * BN + half * 32), pk);
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            // Whole pages arrive, the slots behind the last position included, and what a page holds there was never
+            // written by this request; pages wholly before the window or behind the last position do not arrive at
+            // all, and their slots hold whatever was there.  The probabilities of such keys are 0, but 0 * NaN is
+            // NaN: clear those value rows (128 bytes per key and column block) before the product reads them.
             const int tile_start = k_begin + j * BN;
-            if (tile_start + BN > t_hi + 1) {
-                // Whole pages arrive, the slots behind the last position included, and what a page holds there was
-                // never written by this request.  Their probabilities are 0, but 0 * NaN is NaN: clear those value
-                // rows (128 bytes per key and column block) before the product reads them.
+            const int dead_lo = tile_start < t_lo ? ((t_lo - tile_start) / a.page_size) * a.page_size : 0;   // rows [0, dead_lo)
+            const int dead_hi = min(max(t_hi + 1 - tile_start, 0), BN);                                       // rows [dead_hi, BN)
+            if (dead_lo > 0 || dead_hi < BN) {
                 ok = __all_sync(0xffffffffu, wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u));
                 if (!ok) continue;
                 uint8_t* vt = Vs + (j % NKV) * SM::KV_BYTES;
-                const int first_dead = t_hi + 1 - tile_start;   // >= 1
-                const int chunks = (BN - first_dead) * 8;
-                for (int idx = tid - 64; idx < chunks * CB; idx += SOFTMAX_THREADS) {
-                    const int cb = idx / chunks, rest = idx - cb * chunks;
-                    *reinterpret_cast<uint4*>(vt + cb * (BN * 128) + (first_dead + rest / 8) * 128 + (rest & 7) * 16) =
-                        make_uint4(0, 0, 0, 0);
+                const int n_dead = dead_lo + (BN - dead_hi);
+                for (int idx = tid - 64; idx < n_dead * 8 * CB; idx += SOFTMAX_THREADS) {
+                    const int cb = idx / (n_dead * 8), rest = idx - cb * (n_dead * 8);
+                    const int k = rest / 8, row = k < dead_lo ? k : dead_hi + (k - dead_lo);
+                    *reinterpret_cast<uint4*>(vt + cb * (BN * 128) + row * 128 + (rest & 7) * 16) = make_uint4(0, 0, 0, 0);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tmem_wait_st();
+            tmem_fence_before();
             mbar_arrive(smem_u32(p_full));
         }
         // ---- O / l, written as bfloat16: each thread of a pair its half of the columns ----
