@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 class Scene:
     """A set of sequences with keys/values scattered over a paged pool, plus this step's queries."""
 
-    def __init__(self, seqs, nh, nkv, hd, window, dtype, page_size=16, seed=0, spread=1.0, extra_pages=7):
+    def __init__(self, seqs, nh, nkv, hd, window, dtype, page_size=16, seed=0, spread=1.0, extra_pages=7, ramp=0.0):
         # seqs: list of (cached tokens before the step, new tokens in the step)
         g = torch.Generator().manual_seed(seed)
         rnd = random.Random(seed)
@@ -32,6 +32,8 @@ class Scene:
         for s, (cached, new) in enumerate(seqs):
             T = cached + new
             k = torch.randn(T, nkv, hd, generator=g) * spread
+            if ramp:                                                    # later keys score higher and higher
+                k = k * (1.0 + ramp * torch.arange(T, dtype=torch.float32)).view(T, 1, 1)
             v = torch.randn(T, nkv, hd, generator=g)
             q = torch.randn(new, nh, hd, generator=g) * spread
             k, v, q = (t.to(dtype).float() for t in (k, v, q))          # values exactly representable in dtype
@@ -185,3 +187,48 @@ def test_steps_of_different_shapes_alternate():
     for _ in range(2):
         for sc in scenes:
             check(sc, "mma")
+
+
+@pytest.fixture(params=[True, False], ids=["tcgen05", "mma_sync"])
+def prompt_kernel(request):
+    """Portions of prompts on the tcgen05 kernel (where it takes the geometry) and on the mma.sync kernel."""
+    from flambeau_b200.kernels import ops
+    ops.set_attention_tc(request.param)
+    yield request.param
+    ops.set_attention_tc(True)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page_size", [(8, 2, 128, 16), (8, 2, 64, 8), (4, 4, 128, 64), (6, 3, 64, 32),
+                                                  (16, 1, 128, 16)])
+@pytest.mark.parametrize("window", [0, 300])
+def test_whole_prompts_and_late_portions(prompt_kernel, nh, nkv, hd, page_size, window):
+    """Prompts over several 128-key tiles, from position 0 and after a cached prefix, beside a decoded token;
+    token counts that fill no tile of rows; grouped heads 1, 2, 4 and 16."""
+    seqs = [(0, 700), (900, 131), (415, 1), (250, 7)]
+    check(Scene(seqs, nh, nkv, hd, window, torch.bfloat16, page_size=page_size, seed=hd + window + nh), "mma")
+
+
+def test_scores_that_grow_along_the_keys(prompt_kernel):
+    """Keys whose scores rise with the position: the running maximum of a row grows from tile to tile by more than
+    the step at which the tcgen05 kernel moves its reference point, so the accumulated output is rescaled there."""
+    sc = Scene([(0, 900), (100, 400)], 8, 2, 128, 0, torch.bfloat16, seed=11, spread=1.0, ramp=0.03)
+    check(sc, "mma")
+
+
+def test_one_far_key_among_a_long_prompt(prompt_kernel):
+    """One key of a 1,000-token prompt is scaled so that the last tokens' queries of its group see (almost) only
+    it: a tile that is dropped, fetched from the wrong page or multiplied with the wrong value rows shows."""
+    nh, nkv, hd = 8, 2, 128
+    for target in (0, 127, 128, 517, 895):
+        sc = Scene([(0, 1000)], nh, nkv, hd, 0, torch.bfloat16, seed=target, spread=0.3)
+        for h in range(nkv):
+            qh = sc.q[0][-1, h * (nh // nkv)]
+            sc.k[0][target, h] = (qh / qh.norm() * 100.0).to(torch.bfloat16).float()
+        pid = int(sc.table[0, target // 16])
+        sc.k_pool[pid, :, target % 16] = sc.k[0][target]
+        scale = 1.0 / math.sqrt(hd)
+        got = sc.run("mma", scale).reshape(-1, nh, hd)
+        want = sc.reference(scale).reshape(-1, nh, hd)
+        assert float((got.double() - want).abs().max() / want.abs().max()) < 1.2e-2
+        assert float((want[-1, 0] - sc.v[0][target][0]).abs().max()) < 0.01, "the planted key does not dominate"
+        assert float((got[-1, 0] - sc.v[0][target][0]).abs().max()) < 0.05, "the key that dominates was lost"
