@@ -1,22 +1,22 @@
 // Paged causal (sliding-window) attention for portions of prompts on the 5th-generation tensor cores
 // (tcgen05.mma, accumulators in tensor memory), for heads of 64 or 128 bfloat16 and pages that tile 128 keys.
 //
-// A CTA owns one key/value head and 128 query rows = (128 / G) tokens x the G query heads that share the head,
-// and walks the visible keys in tiles of 128:
+// A CTA owns one key/value head and 256 query rows = (256 / G) tokens x the G query heads that share the head, as
+// two row tiles of 128 that use every K/V tile fetched, and walks the visible keys in tiles of 128:
 //
-//   S = Q K^T      tcgen05.mma, Q and K K-major in shared memory (128-byte swizzle), S in tensor memory
-//                  (two buffers, so the products of other tiles run under the softmax of this one);
-//   softmax        256 threads, two per row (the row = their tensor-memory lane, 64 of the tile's keys each):
-//                  tcgen05.ld of the scores, base-2 online softmax in float32, P rounded to bfloat16 and stored
-//                  with tcgen05.st over the scores it came from;
+//   S = Q K^T      tcgen05.mma, Q and K K-major in shared memory (128-byte swizzle), S in tensor memory, one
+//                  buffer per row tile (the tensor pipe works for one row tile under the softmax of the other);
+//   softmax        256 threads, one per row (the row = its tensor-memory lane): tcgen05.ld of the scores in two
+//                  passes (maximum; exponentials), base-2 online softmax in float32, P rounded to bfloat16 and
+//                  stored with tcgen05.st over the scores it came from;
 //   O += P V       tcgen05.mma with P read from tensor memory and V as it lies in the cache ([key][dim], the
 //                  MN-major operand); O in tensor memory.
 //
 // O is rescaled only when a row's maximum has grown by more than 2^8 since the exponentials' reference point was
 // last moved (the sum l is kept against the same reference, so O / l is exact either way); the first tile sets
 // the reference.  Warps: 0 fetches K and V pages with tensor-map copies through two-slot rings, 1 owns tensor
-// memory and issues the MMAs, 2..9 are the softmax (a warp reads the quarter of the lanes given by its index
-// modulo 4; two warps share a quarter).  Every wait is bounded in time; when one runs out the kernel flags it,
+// memory and issues the MMAs, 2..5 and 6..9 are the softmax of the two row tiles (a warp reads the quarter of the
+// lanes given by its index modulo 4).  Every wait is bounded in time; when one runs out the kernel flags it,
 // leaves its loops, frees its tensor memory and returns.
 //
 // Formulas: crates/kernels-hip/src/kernels/attention_prefill_flash_tile_f16.cu:73-213 (tile + online softmax).
@@ -27,15 +27,14 @@ namespace {
 
 using namespace fb_attn;
 
-constexpr int BM = 128;            // query rows per CTA
+constexpr int BM = 128;            // query rows per row tile (the M of the MMAs)
+constexpr int RT = 2;              // row tiles per CTA: both use every K/V tile that is fetched
 constexpr int BN = 128;            // keys per tile
-constexpr int TC_THREADS = 320;       // warp 0 fetches, warp 1 issues the MMAs, warps 2..9 are the softmax
-constexpr int SOFTMAX_THREADS = 256;
-constexpr int NKV = 2;             // K/V stages
-constexpr int TMEM_COLS = 512;     // S0 / P0 [0,128), S1 / P1 [128,256), O [256, 256 + HD)
+constexpr int TC_THREADS = 320;    // warp 0 fetches, warp 1 issues the MMAs, warps 2..5 / 6..9 are the softmax of row tile 0 / 1
+constexpr int NKV = 2;             // K slots and V slots
+constexpr int TMEM_COLS = 512;     // S/P of row tile 0 [0,128), of row tile 1 [128,256); O of tile 0 [256,384), of tile 1 [384,512)
 constexpr float RESCALE_STEP = 8.0f;
 
-__device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -43,10 +42,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 template <int HD> struct TcSmem {
-    static constexpr int Q_BYTES = BM * HD * 2;                 // [HD/64 column blocks][128 rows][128 bytes]
+    static constexpr int Q_BYTES = BM * HD * 2;                 // one row tile: [HD/64 column blocks][128 rows][128 bytes]
     static constexpr int KV_BYTES = BN * HD * 2;                // one K or V tile: [HD/64][128 keys][128 bytes]
-    static constexpr int TAIL_BYTES = 256 + 4 * BM * 4;         // barriers, tensor-memory address, flag; row maxima
-    static constexpr int USED = Q_BYTES + NKV * 2 * KV_BYTES + TAIL_BYTES + 1024 /* alignment */;
+    static constexpr int TAIL_BYTES = 256;                      // barriers, tensor-memory address, flag
+    static constexpr int USED = RT * Q_BYTES + NKV * 2 * KV_BYTES + TAIL_BYTES + 1024 /* alignment */;
     // one CTA per SM: two would both want all of tensor memory
     static constexpr int BYTES = USED > 120 * 1024 ? USED : 120 * 1024;
 };
@@ -60,22 +59,21 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
-    uint8_t* Qs = smem;
-    uint8_t* Ks = Qs + SM::Q_BYTES;                             // [NKV] tiles
+    uint8_t* Qs = smem;                                         // [RT] row tiles
+    uint8_t* Ks = Qs + RT * SM::Q_BYTES;                        // [NKV] tiles
     uint8_t* Vs = Ks + NKV * SM::KV_BYTES;                      // [NKV] tiles
     uint8_t* tail = Vs + NKV * SM::KV_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
     uint64_t* k_full = bars;                                    // [NKV] a K tile has landed
-    uint64_t* k_empty = bars + NKV;                             // [NKV] its scores are computed
+    uint64_t* k_empty = bars + NKV;                             // [NKV] both row tiles' scores are computed
     uint64_t* v_full = bars + 2 * NKV;                          // [NKV] a V tile has landed
-    uint64_t* v_empty = bars + 3 * NKV;                         // [NKV] its product is computed
-    uint64_t* s_full = bars + 4 * NKV;                          // [2]   S of a tile is in tensor memory
-    uint64_t* q_full = bars + 4 * NKV + 4;                      //       Q is staged
-    uint64_t* p_full = bars + 4 * NKV + 5;                      //       P of a tile is in tensor memory
-    uint64_t* pv_done = bars + 4 * NKV + 6;                     //       O holds the tile's product
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * NKV + 7);
+    uint64_t* v_empty = bars + 3 * NKV;                         // [NKV] both row tiles' products are computed
+    uint64_t* s_full = bars + 4 * NKV;                          // [RT]  S of a row tile is in tensor memory
+    uint64_t* p_full = bars + 4 * NKV + RT;                     // [RT]  P of a row tile is in tensor memory
+    uint64_t* pv_done = bars + 4 * NKV + 2 * RT;                // [RT]  O of a row tile holds the key tile's product
+    uint64_t* q_full = bars + 4 * NKV + 3 * RT;                 //       Q is staged
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * NKV + 3 * RT + 1);
     int* bail = reinterpret_cast<int*>(tmem_slot + 1);
-    float* xchg = reinterpret_cast<float*>(tail + 256);         // [2 tiles][2 halves][128 rows]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = a.nh / a.nkv, hd = a.hd;
@@ -84,34 +82,34 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     const int seq = blockIdx.z, kvh = blockIdx.y;
     const int q_len = a.seq_q_len[seq];
     if (q_len * G <= a.short_rows) return;                      // the split-key arrangement's
-    const int TQ = BM / G;
-    const int tok0 = (gridDim.x - 1 - blockIdx.x) * TQ;         // later tiles see more keys: start them first
+    const int TQ = RT * BM / G;
+    const int tok0 = (gridDim.x - 1 - blockIdx.x) * TQ;         // later tokens see more keys: start them first
     if (tok0 >= q_len) return;
     const int ntok = min(TQ, q_len - tok0);
     const int q_start = a.seq_q_start[seq], pos0 = a.seq_pos_start[seq];
-    const int rows_valid = ntok * G;
+    const int rows_valid = ntok * G;                            // of the CTA's RT * 128 rows
     const int p_first = pos0 + tok0, p_last = pos0 + tok0 + ntok - 1;
     const int t_lo = (a.window > 0 && p_first - a.window + 1 > 0) ? p_first - a.window + 1 : 0;
     const int t_hi = p_last;
     const int k_begin = (t_lo / BN) * BN, k_end = t_hi + 1;
-    const int n_tiles = (k_end - k_begin + BN - 1) / BN;
+    const int n_tiles = (k_end - k_begin + BN - 1) / BN;        // both row tiles walk all of them
     const int* table = a.block_table + (size_t)seq * a.table_stride;
     const int pages_per_tile = BN / a.page_size;
-    const int n_ops = 2 * pages_per_tile * CB;                  // copies per tile: (K or V, page, column block)
+    const int n_ops = pages_per_tile * CB;                      // copies per K or V tile: (page, column block)
 
     if (tid == 0) {
         for (int s = 0; s < NKV; ++s) {
-            mbar_init(smem_u32(&k_full[s]), n_ops / 2);
+            mbar_init(smem_u32(&k_full[s]), n_ops);
             mbar_init(smem_u32(&k_empty[s]), 1);
-            mbar_init(smem_u32(&v_full[s]), n_ops / 2);
+            mbar_init(smem_u32(&v_full[s]), n_ops);
             mbar_init(smem_u32(&v_empty[s]), 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&s_full[b]), 1);
+        for (int t = 0; t < RT; ++t) {
+            mbar_init(smem_u32(&s_full[t]), 1);
+            mbar_init(smem_u32(&p_full[t]), BM);
+            mbar_init(smem_u32(&pv_done[t]), 1);
         }
-        mbar_init(smem_u32(q_full), SOFTMAX_THREADS);
-        mbar_init(smem_u32(p_full), SOFTMAX_THREADS);
-        mbar_init(smem_u32(pv_done), 1);
+        mbar_init(smem_u32(q_full), RT * BM);
         *bail = 0;
         mbar_fence_init();
     }
@@ -133,17 +131,17 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     if (warp == 0) {
         // ================= fetch: lane l copies (page l / CB, column block l % CB) of every K and V tile ==========
         // K tiles and V tiles run through rings of their own: a K slot is free as soon as its scores are computed
-        // (a tile ahead of the softmax), a V slot after the tile's product, so a copy has two tiles' time to land.
+        // (a tile ahead of the softmax), a V slot after the tile's products, so a copy has two tiles' time to land.
         // -2 = nothing to fetch (no query of the CTA sees the page), -1 = the table has no page although needed.
         auto lookup = [&](int j) -> int {
-            if (lane >= n_ops / 2 || j >= n_tiles) return -2;
+            if (lane >= n_ops || j >= n_tiles) return -2;
             const int t_first = k_begin + j * BN + (lane / CB) * a.page_size;
             if (!(t_first + a.page_size > t_lo && t_first < k_end)) return -2;
             const int page = table[t_first / a.page_size];
             return (page < 0 || page >= a.n_pages) ? -1 : page;
         };
         auto issue = [&](uint8_t* tile, const CUtensorMap* map, uint64_t* full, int page) {
-            if (lane >= n_ops / 2) return;
+            if (lane >= n_ops) return;
             const uint32_t bar = smem_u32(full);
             if (page >= 0) {
                 const int cb = lane % CB, pj = lane / CB;
@@ -152,7 +150,7 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
                             (page * a.nkv + kvh) * a.page_size);
             } else {
                 if (page == -1) atomicOr(a.status, FB_STATUS_BAD_PAGE);
-                mbar_arrive(bar);                               // stale (finite) data stays in the slot; it is masked
+                mbar_arrive(bar);                               // whatever lies in the slot stays; it is masked
             }
         };
         int page = lookup(0);
@@ -167,70 +165,71 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
         }
     } else if (warp == 1) {
         // ================= MMA issue =================
+        // Per key tile and row tile: O += P V, then the scores of the next key tile into the columns P lay in (the
+        // MMAs run in the order of their issue, so the product has read P by then).  The two row tiles alternate,
+        // so the tensor pipe works for one while the softmax of the other runs.
         if (elect_one()) {
             constexpr uint32_t idesc_s = umma_idesc(BN);
             constexpr uint32_t idesc_o = umma_idesc(HD, true);
-            const uint32_t q_addr = smem_u32(Qs);
-            auto issue_s = [&](int j) {                         // S[j & 1] = Q K_j^T
+            auto issue_s = [&](int j, int t) {                  // S of row tile t = Q_t K_j^T
+                const uint32_t q_addr = smem_u32(Qs + t * SM::Q_BYTES);
                 const uint32_t k_addr = smem_u32(Ks + (j % NKV) * SM::KV_BYTES);
-                const uint32_t d = tmem_base + (uint32_t)((j & 1) * BN);
+                const uint32_t d = tmem_base + (uint32_t)(t * BN);
 #pragma unroll
                 for (int kk = 0; kk < HD / UMMA_K; ++kk) {
                     const uint32_t off = (uint32_t)((kk / 4) * (128 * 128) + (kk % 4) * 32);
                     umma_bf16(d, umma_desc(q_addr + off), umma_desc(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(smem_u32(&s_full[j & 1]));
-                umma_commit(smem_u32(&k_empty[j % NKV]));
+                umma_commit(smem_u32(&s_full[t]));
+                if (t == RT - 1) umma_commit(smem_u32(&k_empty[j % NKV]));
             };
-            // the scores of the first two tiles: both buffers are free
-            bool ok = wait(q_full, 0);
-            for (int j = 0; ok && j < 2 && j < n_tiles; ++j) {
-                ok = wait(&k_full[j % NKV], (uint32_t)(j / NKV) & 1u);
-                if (!ok) break;
+            bool ok = wait(q_full, 0) && wait(&k_full[0], 0);
+            if (ok) {
                 tmem_fence_after();
-                issue_s(j);
+                for (int t = 0; t < RT; ++t) issue_s(0, t);
             }
             for (int j = 0; ok && j < n_tiles; ++j) {
-                ok = wait(p_full, (uint32_t)j & 1u) && wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u);
-                if (!ok) break;
-                tmem_fence_after();
-                const uint32_t v_addr = smem_u32(Vs + (j % NKV) * SM::KV_BYTES);
-                const uint32_t p_addr = tmem_base + (uint32_t)((j & 1) * BN);   // bf16 pairs over the tile's scores
-                const uint32_t d = tmem_base + (uint32_t)(2 * BN);
-#pragma unroll
-                for (int kk = 0; kk < BN / UMMA_K; ++kk) {      // 16 keys = 8 columns of P each
-                    const uint64_t db = umma_desc_mn(v_addr + (uint32_t)(kk * 16 * 128), BN * 128, 1024);
-                    umma_bf16_ts(d, p_addr + (uint32_t)(kk * 8), db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-                }
-                umma_commit(smem_u32(&v_empty[j % NKV]));
-                umma_commit(smem_u32(pv_done));
-                if (j + 2 < n_tiles) {
-                    // the scores of the tile after next go where this tile's P lay; the MMAs run in the order of
-                    // their issue, so the product above has read P by then
-                    ok = wait(&k_full[(j + 2) % NKV], (uint32_t)((j + 2) / NKV) & 1u);
+                for (int t = 0; ok && t < RT; ++t) {
+                    ok = wait(&p_full[t], (uint32_t)j & 1u);
+                    if (ok && t == 0) ok = wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u);
                     if (!ok) break;
                     tmem_fence_after();
-                    issue_s(j + 2);
+                    const uint32_t v_addr = smem_u32(Vs + (j % NKV) * SM::KV_BYTES);
+                    const uint32_t p_addr = tmem_base + (uint32_t)(t * BN);        // bf16 pairs over the scores
+                    const uint32_t d = tmem_base + (uint32_t)(RT * BN + t * BM);
+#pragma unroll
+                    for (int kk = 0; kk < BN / UMMA_K; ++kk) {  // 16 keys = 8 columns of P each
+                        const uint64_t db = umma_desc_mn(v_addr + (uint32_t)(kk * 16 * 128), BN * 128, 1024);
+                        umma_bf16_ts(d, p_addr + (uint32_t)(kk * 8), db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&pv_done[t]));
+                    if (t == RT - 1) umma_commit(smem_u32(&v_empty[j % NKV]));
+                    if (j + 1 < n_tiles) {
+                        if (t == 0) ok = wait(&k_full[(j + 1) % NKV], (uint32_t)((j + 1) / NKV) & 1u);
+                        if (!ok) break;
+                        tmem_fence_after();
+                        issue_s(j + 1, t);
+                    }
                 }
             }
         }
         __syncwarp();
     } else {
-        // ================= softmax: two threads per query row (= tensor-memory lane), 64 keys of a tile each ==========
+        // ================= softmax: thread = query row = tensor-memory lane; warps 2..5 row tile 0, 6..9 row tile 1 =====
         const int quarter = warp & 3;                           // the lanes this warp may read
-        const int half = (warp - 2) >> 2;                       // which 64 keys of a tile, which half of O's columns
-        const int r = quarter * 32 + lane;
+        const int t = (warp - 2) >> 2;                          // its row tile
+        const int r = t * BM + quarter * 32 + lane;             // row of the CTA
         const bool valid = r < rows_valid;
         const int token = q_start + tok0 + r / G, head = kvh * G + r % G;
-        // ---- stage Q (zero rows beyond the CTA's share); each thread of a pair takes half of the row ----
+        // ---- stage Q (zero rows beyond the CTA's share) ----
         {
             const __nv_bfloat16* src = a.q + (size_t)token * a.q_stride + (size_t)head * hd;
+            uint8_t* qrow = Qs + t * SM::Q_BYTES + (r - t * BM) * 128;
 #pragma unroll
-            for (int i = 0; i < HD / 16; ++i) {
-                const int c = half * (HD / 16) + i;
+            for (int c = 0; c < HD / 8; ++c) {
                 uint4 v = make_uint4(0, 0, 0, 0);
                 if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
-                *reinterpret_cast<uint4*>(Qs + (c / 8) * (BM * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+                *reinterpret_cast<uint4*>(qrow + (c / 8) * (BM * 128) + (((c & 7) ^ (r & 7)) << 4)) = v;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(smem_u32(q_full));
@@ -238,124 +237,114 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
         const int p_row = valid ? pos0 + tok0 + r / G : -1;     // a row beyond the share sees nothing
         const int t0_row = (a.window > 0 && p_row - a.window + 1 > 0) ? p_row - a.window + 1 : 0;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t o_addr = lane_addr + (uint32_t)(2 * BN + half * (HD / 2));   // this thread's columns of O
+        const uint32_t s_addr = lane_addr + (uint32_t)(t * BN);             // S, and P over it, of this row
+        const uint32_t o_addr = lane_addr + (uint32_t)(RT * BN + t * BM);   // O of this row
         float m_ref = -INFINITY;                                // reference point of the exponentials (scaled, base 2)
-        float l = 0.0f;                                         // sum over this thread's keys
+        float l = 0.0f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1;
-            const int key0 = k_begin + j * BN + half * 64;      // this thread's first key of the tile
-            // (after a wait has run out every warp still goes through each tile's barrier, so that none is left at it)
-            ok = ok && __all_sync(0xffffffffu, wait(&s_full[b], (uint32_t)(j / 2) & 1u));
-            if (!ok) {
-                softmax_barrier();
-                continue;
-            }
+            const int tile_start = k_begin + j * BN;
+            ok = ok && __all_sync(0xffffffffu, wait(&s_full[t], (uint32_t)j & 1u));
+            if (!ok) continue;
             tmem_fence_after();
-            // ---- this thread's 64 scores into registers ----
-            uint32_t v0[32], v1[32];
-            tmem_ld32_nowait(lane_addr + (uint32_t)(b * BN + half * 64), v0);
-            tmem_ld32_nowait(lane_addr + (uint32_t)(b * BN + half * 64 + 32), v1);
+            // every key of the tile is visible to every row of the warp, or each is compared
+            const bool plain = __all_sync(0xffffffffu, tile_start + BN - 1 <= p_row && tile_start >= t0_row);
+            // ---- the row's 128 scores into registers (one round trip), masked where needed; their maximum ----
+            uint32_t v[BN / 32][32];
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) tmem_ld32_nowait(s_addr + (uint32_t)(c * 32), v[c]);
             tmem_wait_ld();
-            // every key of this thread's 64 is visible to its row, for the whole warp, or each is compared
-            const bool plain = __all_sync(0xffffffffu, key0 + 63 <= p_row && key0 >= t0_row);
-            float s[64];
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (plain) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    s[i] = __uint_as_float(v0[i]) * a.scale_log2e;
-                    s[32 + i] = __uint_as_float(v1[i]) * a.scale_log2e;
-                }
+                for (int c = 0; c < BN / 32; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[c][i]));
             } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int t = key0 + i;
-                    s[i] = (t >= t0_row && t <= p_row) ? __uint_as_float(v0[i]) * a.scale_log2e : -INFINITY;
-                    s[32 + i] = (t + 32 >= t0_row && t + 32 <= p_row) ? __uint_as_float(v1[i]) * a.scale_log2e : -INFINITY;
-                }
-            }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                for (int c = 0; c < BN / 32; ++c)
 #pragma unroll
-            for (int i = 0; i < 64; i += 4) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], s[i + e]);
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = tile_start + c * 32 + i;
+                        if (!(key >= t0_row && key <= p_row)) v[c][i] = 0xff800000u;      // -inf
+                        mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[c][i]));
+                    }
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            // the row's maximum over both halves
-            xchg[(b * 2 + half) * BM + r] = mx;
-            softmax_barrier();
-            const float m_new = fmaxf(m_ref, fmaxf(mx, xchg[(b * 2 + (half ^ 1)) * BM + r]));
+            const float m_new = fmaxf(m_ref, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2e);
             if (j == 0) {
                 m_ref = m_new;                                  // O is overwritten by the first product
             } else if (__any_sync(0xffffffffu, m_new > m_ref + RESCALE_STEP || (m_ref == -INFINITY && m_new > m_ref))) {
-                // move the reference point: O *= 2^(old - new), for the whole warp at once (both warps of a pair
-                // see the same maxima and decide alike; each scales its half of O's columns)
-                ok = __all_sync(0xffffffffu, wait(pv_done, (uint32_t)(j - 1) & 1u));
+                // move the reference point: O *= 2^(old - new), for the whole warp at once
+                ok = __all_sync(0xffffffffu, wait(&pv_done[t], (uint32_t)(j - 1) & 1u));
                 if (!ok) continue;
                 tmem_fence_after();
                 const float f = m_new == -INFINITY ? 1.0f : exp2f(m_ref - m_new);
-#pragma unroll
-                for (int c4 = 0; c4 < HD / 64; ++c4) {
-                    uint32_t v[32];
-                    tmem_ld32_nowait(o_addr + (uint32_t)(c4 * 32), v);
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t w[32];
+                    tmem_ld32_nowait(o_addr + (uint32_t)(c * 32), w);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-                    tmem_st32(o_addr + (uint32_t)(c4 * 32), v);
+                    for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__uint_as_float(w[i]) * f);
+                    tmem_st32(o_addr + (uint32_t)(c * 32), w);
                 }
                 tmem_wait_st();
                 l *= f;
                 m_ref = m_new;
             }
-            // ---- P = 2^(s - reference), rounded to bfloat16, over this thread's scores (the partner has read its
-            // own before the barrier above): 64 keys = 32 columns ----
-            const float m_eff = m_ref == -INFINITY ? 0.0f : m_ref;
+            // ---- P = 2^(s - reference), rounded to bfloat16, over the scores it came from: keys 32c .. 32c + 31
+            // go to columns 16c .. 16c + 15 ----
+            const float neg_ref = m_ref == -INFINITY ? 0.0f : -m_ref;
             float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t pk[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float p0 = fast_exp2(s[2 * i] - m_eff), p1 = fast_exp2(s[2 * i + 1] - m_eff);
-                sum4[i & 3] += p0 + p1;
-                pk[i] = pack_bf16(p0, p1);
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    // a masked score is -inf: 2^-inf = 0
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(v[c][2 * i]), a.scale_log2e, neg_ref));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(v[c][2 * i + 1]), a.scale_log2e, neg_ref));
+                    sum4[i & 3] += p0 + p1;
+                    pk[i] = pack_bf16(p0, p1);
+                }
+                tmem_st16(s_addr + (uint32_t)(c * 16), pk);
             }
-            tmem_st32(lane_addr + (uint32_t)(b * BN + half * 32), pk);
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             // Whole pages arrive, the slots behind the last position included, and what a page holds there was never
             // written by this request; pages wholly before the window or behind the last position do not arrive at
             // all, and their slots hold whatever was there.  The probabilities of such keys are 0, but 0 * NaN is
-            // NaN: clear those value rows (128 bytes per key and column block) before the product reads them.
-            const int tile_start = k_begin + j * BN;
-            const int dead_lo = tile_start < t_lo ? ((t_lo - tile_start) / a.page_size) * a.page_size : 0;   // rows [0, dead_lo)
-            const int dead_hi = min(max(t_hi + 1 - tile_start, 0), BN);                                       // rows [dead_hi, BN)
-            if (dead_lo > 0 || dead_hi < BN) {
-                ok = __all_sync(0xffffffffu, wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u));
-                if (!ok) continue;
-                uint8_t* vt = Vs + (j % NKV) * SM::KV_BYTES;
-                const int n_dead = dead_lo + (BN - dead_hi);
-                for (int idx = tid - 64; idx < n_dead * 8 * CB; idx += SOFTMAX_THREADS) {
-                    const int cb = idx / (n_dead * 8), rest = idx - cb * (n_dead * 8);
-                    const int k = rest / 8, row = k < dead_lo ? k : dead_hi + (k - dead_lo);
-                    *reinterpret_cast<uint4*>(vt + cb * (BN * 128) + row * 128 + (rest & 7) * 16) = make_uint4(0, 0, 0, 0);
+            // NaN: row tile 0 (whose product is issued first) clears those value rows, 128 bytes per key and
+            // column block, before the products read them.
+            if (t == 0) {
+                const int dead_lo = tile_start < t_lo ? ((t_lo - tile_start) / a.page_size) * a.page_size : 0;   // rows [0, dead_lo)
+                const int dead_hi = min(max(t_hi + 1 - tile_start, 0), BN);                                       // rows [dead_hi, BN)
+                if (dead_lo > 0 || dead_hi < BN) {
+                    ok = __all_sync(0xffffffffu, wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u));
+                    if (!ok) continue;
+                    uint8_t* vt = Vs + (j % NKV) * SM::KV_BYTES;
+                    const int n_dead = dead_lo + (BN - dead_hi);
+                    for (int idx = tid - 64; idx < n_dead * 8 * CB; idx += BM) {
+                        const int cb = idx / (n_dead * 8), rest = idx - cb * (n_dead * 8);
+                        const int k = rest / 8, row = k < dead_lo ? k : dead_hi + (k - dead_lo);
+                        *reinterpret_cast<uint4*>(vt + cb * (BN * 128) + row * 128 + (rest & 7) * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             tmem_wait_st();
             tmem_fence_before();
-            mbar_arrive(smem_u32(p_full));
+            mbar_arrive(smem_u32(&p_full[t]));
         }
-        // ---- O / l, written as bfloat16: each thread of a pair its half of the columns ----
-        if (ok) ok = __all_sync(0xffffffffu, wait(pv_done, (uint32_t)(n_tiles - 1) & 1u));
-        xchg[half * BM + r] = l;
-        softmax_barrier();
+        // ---- O / l, written as bfloat16 ----
+        if (ok) ok = __all_sync(0xffffffffu, wait(&pv_done[t], (uint32_t)(n_tiles - 1) & 1u));
         if (ok) {
             tmem_fence_after();
-            const float l_row = l + xchg[(half ^ 1) * BM + r];
-            const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
-            __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd + half * (HD / 2);
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd;
 #pragma unroll
-            for (int c4 = 0; c4 < HD / 64; ++c4) {
+            for (int c = 0; c < HD / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld32_nowait(o_addr + (uint32_t)(c4 * 32), v);
+                tmem_ld32_nowait(o_addr + (uint32_t)(c * 32), v);
                 tmem_wait_ld();
                 if (valid) {
 #pragma unroll
@@ -365,7 +354,7 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
                         for (int e = 0; e < 4; ++e)
                             w[e] = pack_bf16(__uint_as_float(v[8 * q4 + 2 * e]) * inv,
                                              __uint_as_float(v[8 * q4 + 2 * e + 1]) * inv);
-                        *reinterpret_cast<uint4*>(dst + c4 * 32 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
@@ -389,7 +378,7 @@ int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream)
                                              TcSmem<HD>::BYTES, cudaGetErrorString(e));
         configured = true;
     }
-    const int TQ = BM / (a.nh / a.nkv);
+    const int TQ = RT * BM / (a.nh / a.nkv);
     const dim3 grid((max_q_len + TQ - 1) / TQ, a.nkv, n_seqs);
     fb_launch((kern), grid, TC_THREADS, (size_t)TcSmem<HD>::BYTES, stream, a);
     return fb_check_launch("attention_tc");
