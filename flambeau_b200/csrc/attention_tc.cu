@@ -28,9 +28,10 @@ namespace {
 using namespace fb_attn;
 
 constexpr int BM = 128;            // query rows per row tile (the M of the MMAs)
-constexpr int RT = 2;              // row tiles per CTA: both use every K/V tile that is fetched
 constexpr int BN = 128;            // keys per tile
-constexpr int TC_THREADS = 320;    // warp 0 fetches, warp 1 issues the MMAs, warps 2..5 / 6..9 are the softmax of row tile 0 / 1
+// Threads of a CTA with RT row tiles: warp 0 fetches, warp 1 issues the MMAs, warps 2..5 (and 6..9) are the softmax
+// of row tile 0 (and 1).
+__host__ __device__ constexpr int tc_threads(int rt) { return 64 + BM * rt; }
 constexpr int NKV = 2;             // K slots and V slots
 constexpr int TMEM_COLS = 512;     // S/P of row tile 0 [0,128), of row tile 1 [128,256); O of tile 0 [256,384), of tile 1 [384,512)
 constexpr float RESCALE_STEP = 8.0f;
@@ -41,7 +42,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-template <int HD> struct TcSmem {
+template <int HD, int RT> struct TcSmem {
     static constexpr int Q_BYTES = BM * HD * 2;                 // one row tile: [HD/64 column blocks][128 rows][128 bytes]
     static constexpr int KV_BYTES = BN * HD * 2;                // one K or V tile: [HD/64][128 keys][128 bytes]
     static constexpr int TAIL_BYTES = 256;                      // barriers, tensor-memory address, flag
@@ -50,11 +51,13 @@ template <int HD> struct TcSmem {
     static constexpr int BYTES = USED > 120 * 1024 ? USED : 120 * 1024;
 };
 
-template <int HD>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+// RT row tiles of 128 rows per CTA: with two, both use every K/V tile that is fetched and the tensor pipe works for
+// one under the softmax of the other; with one, a short portion still spreads over enough CTAs.
+template <int HD, int RT>
+__global__ void __launch_bounds__(tc_threads(RT), 1)
 attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     fb_pdl_launch_dependents();
-    using SM = TcSmem<HD>;
+    using SM = TcSmem<HD, RT>;
     constexpr int CB = HD / 64;                                 // 64-column blocks of a head
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -368,20 +371,35 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     }
 }
 
-template <int HD>
+template <int HD, int RT>
 int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream) {
-    auto kern = attention_tc_kernel<HD>;
+    auto kern = attention_tc_kernel<HD, RT>;
+    using SM = TcSmem<HD, RT>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<HD>::BYTES);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::BYTES);
         if (e != cudaSuccess) return fb_fail(-2, "attention_tc: cannot reserve %d bytes of shared memory: %s",
-                                             TcSmem<HD>::BYTES, cudaGetErrorString(e));
+                                             SM::BYTES, cudaGetErrorString(e));
         configured = true;
     }
     const int TQ = RT * BM / (a.nh / a.nkv);
     const dim3 grid((max_q_len + TQ - 1) / TQ, a.nkv, n_seqs);
-    fb_launch((kern), grid, TC_THREADS, (size_t)TcSmem<HD>::BYTES, stream, a);
+    fb_launch((kern), grid, tc_threads(RT), (size_t)SM::BYTES, stream, a);
     return fb_check_launch("attention_tc");
+}
+
+// Two row tiles per CTA when that still gives every SM a CTA, else one.
+template <int HD>
+int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream) {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const int TQ2 = 2 * BM / (a.nh / a.nkv);
+    const long ctas2 = (long)((max_q_len + TQ2 - 1) / TQ2) * a.nkv * n_seqs;      // an upper bound: short sequences leave early
+    return ctas2 >= sms ? launch_tc<HD, 2>(a, n_seqs, max_q_len, stream) : launch_tc<HD, 1>(a, n_seqs, max_q_len, stream);
 }
 
 }  // namespace
