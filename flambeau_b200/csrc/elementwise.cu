@@ -243,15 +243,14 @@ FB_API int fb_rope_table(const int* positions, const double* inv_freq, float* co
 template <typename TI>
 __device__ __forceinline__ float slab_sum(const TI* __restrict__ row, int j, int n_partials, long partial_stride) {
     float acc = fb_to_float(row[j]);
-    int p = 1;
-    for (; p + 3 < n_partials; p += 4) {              // four independent loads in flight, added in slab order
-        const float a0 = fb_to_float(row[(size_t)p * partial_stride + j]);
-        const float a1 = fb_to_float(row[(size_t)(p + 1) * partial_stride + j]);
-        const float a2 = fb_to_float(row[(size_t)(p + 2) * partial_stride + j]);
-        const float a3 = fb_to_float(row[(size_t)(p + 3) * partial_stride + j]);
-        acc = (((acc + a0) + a1) + a2) + a3;
+    for (int p = 1; p < n_partials; p += 8) {         // eight independent loads in flight, added in slab order
+        float a[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            a[u] = p + u < n_partials ? fb_to_float(row[(size_t)(p + u) * partial_stride + j]) : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc += a[u];
     }
-    for (; p < n_partials; ++p) acc += fb_to_float(row[(size_t)p * partial_stride + j]);
     return acc;
 }
 
@@ -322,10 +321,13 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stri
 template <typename TI>
 __device__ __forceinline__ float4 slab_sum4(const TI* __restrict__ p, int n_partials, long partial_stride) {
     float4 acc = Vec4<TI>::load(p);
-#pragma unroll 4
-    for (int s = 1; s < n_partials; ++s) {
-        const float4 a = Vec4<TI>::load(p + (size_t)s * partial_stride);
-        acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+    for (int s = 1; s < n_partials; s += 8) {         // eight independent loads in flight, added in slab order
+        float4 a[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            a[u] = s + u < n_partials ? Vec4<TI>::load(p + (size_t)(s + u) * partial_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { acc.x += a[u].x; acc.y += a[u].y; acc.z += a[u].z; acc.w += a[u].w; }
     }
     return acc;
 }
