@@ -76,6 +76,30 @@ def test_add_rms_norm_rows_and_slabs():
     close(x, x0.double() + slabs.double().sum(0), 2e-6)
 
 
+@pytest.mark.parametrize("n,H,P", [(1, 1024, 1), (8, 4096, 16), (3, 2048, 5), (64, 4096, 8), (8, 5120, 20)])
+@pytest.mark.parametrize("od", ["f", "b"])
+def test_add_rms_norm_few_wide_rows(n, H, P, od):
+    """The widths of real models with the row counts of decoding, and as many split-K slabs as the products leave."""
+    from flambeau_b200.kernels import ops
+    eps = 1e-5
+    g = torch.Generator(device=DEV).manual_seed(n * H + P)
+    x = torch.randn(n, H, device=DEV, generator=g)
+    slabs = torch.randn(P, n, H, device=DEV, generator=g) * 0.3
+    w = (1 + 0.1 * torch.randn(H, device=DEV, generator=g)).to(DT[od])
+    out = torch.empty(n, H, device=DEV, dtype=DT[od])
+    x0 = x.clone()
+    ops.add_rms_norm(x, slabs[0], w, eps, out, n_partials=P, partial_stride=slabs.stride(0))
+    v = x0.double() + slabs.double().sum(0)
+    close(x, v, 2e-6)
+    close(out, pm.rms_norm(v, w.double(), eps), 3e-6 if od == "f" else 6e-3)
+    rows = torch.tensor([n - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, H, device=DEV, dtype=DT[od])
+    x1 = x.clone()
+    ops.add_rms_norm(x, None, w, eps, out2, rows=rows)
+    assert torch.equal(x, x1)
+    close(out2, pm.rms_norm(x1.double()[rows.long()], w.double(), eps), 3e-6 if od == "f" else 6e-3)
+
+
 @pytest.mark.parametrize("half,theta", [(8, 1e4), (12, 1e6), (64, 1e4)])
 def test_rope_table_is_right_at_far_positions(half, theta):
     from flambeau_b200.kernels import ops
