@@ -183,16 +183,16 @@ def main(argv=None) -> int:
         ids = seat(batch, args.context)
         tok = torch.randint(0, vocab, (batch,), generator=gen).tolist()
         entries = [Entry(r, [t], [0]) for r, t in zip(ids, tok)]
-        ex = EngineExecutor(engine)
         from flambeau_b200.kernels import ops
+        chosen = torch.zeros(batch, dtype=torch.int32, device=dev)
         for _ in range(warmup):
-            ops.sample(engine.step(entries), ex.sampler.out, n=batch)
+            ops.sample(engine.step(entries), chosen, n=batch)
         torch.cuda.synchronize()
         l0 = library.LAUNCHES[0]
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
         for _ in range(steps):
-            ops.sample(engine.step(entries), ex.sampler.out, n=batch)
+            ops.sample(engine.step(entries), chosen, n=batch)
         t1.record()
         torch.cuda.synchronize()
         engine.runtime.check_status("bench decode")
@@ -208,16 +208,22 @@ def main(argv=None) -> int:
                         generated=[int(torch.randint(0, vocab, (1,), generator=gen))], arrival=i)
             r.fed = args.context - 1
             sched.running.append(r)
-        for _ in range(warmup):
-            sched.step()
+        ahead = sched.run_ahead
+
+        def run_steps(n: int) -> None:
+            # the scheduler queues each step before it reads the tokens of the one before; the last step of a
+            # region queues nothing, so the region holds exactly the device work of the tokens it delivers
+            for i in range(n):
+                sched.run_ahead = ahead and i < n - 1
+                assert len(sched.step()) == batch
+
+        run_steps(warmup)
         torch.cuda.synchronize()
         h0, d0 = ex.h2d_bytes, ex.d2h_bytes
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         w0 = time.perf_counter()
         t0.record()
-        for _ in range(steps):
-            out = sched.step()
-            assert len(out) == batch
+        run_steps(steps)
         t1.record()
         torch.cuda.synchronize()
         wall = time.perf_counter() - w0

@@ -28,15 +28,30 @@ class EngineExecutor:
         self.d2h_bytes = 0
 
     def run(self, entries, sampled) -> list:
-        logits = self.engine.step(entries)
+        handle = self.launch(entries, sampled)
+        return self.collect(handle) if handle is not None else []
+
+    def launch(self, entries, sampled, feed=None, pending: int = 0):
+        """Queue a step and the sampling of its wanted rows without waiting for anything.  `feed`: the handle of
+        the step before, whose sampled tokens (in the order of `entries`) are this step's token ids; `pending`:
+        how many tokens of each sampled request the host has not seen yet (they count for the draw index)."""
+        logits = self.engine.step(entries, token_feed=feed.tokens if feed is not None else None)
         self.h2d_bytes += self.engine.last_batch.h2d_bytes
         if not sampled:
-            return []
-        rows = [(r.params, r.generated, len(r.generated)) for r in sampled]
-        toks = self.sampler.sample(logits, rows)
+            return None
+        rows = [(r.params, r.generated, len(r.generated) + pending) for r in sampled]
+        handle = self.sampler.launch(logits, rows)
         self.h2d_bytes += 8 * 4 * len(rows)
         self.d2h_bytes += 4 * len(rows)
-        return toks
+        return handle
+
+    def collect(self, handle) -> list:
+        return self.sampler.collect(handle)
+
+    def can_run_ahead(self, sampled) -> bool:
+        """A step may be queued before the tokens of the step before it are known if sampling does not need them
+        on the host (penalties count the generated tokens there)."""
+        return all(not r.params.has_penalties for r in sampled)
 
     def finish(self, request_id) -> None:
         self.engine.finish(request_id)
@@ -44,8 +59,9 @@ class EngineExecutor:
 
 class Generator:
     def __init__(self, engine: Engine, *, prefill_chunk_tokens: int = 512, prefill_ubatch: int | None = None,
-                 inflight_slots: int | None = None):
+                 inflight_slots: int | None = None, run_ahead: bool = True):
         self.engine = engine
+        self.run_ahead = run_ahead             # queue decode steps before the tokens of the step before are read
         self.executor = EngineExecutor(engine)
         self.prefill_chunk_tokens = prefill_chunk_tokens
         self.token_budget = min(prefill_ubatch or engine.options.max_step_tokens, engine.options.max_step_tokens)
@@ -61,7 +77,7 @@ class Generator:
         if len(plist) != len(prompts):
             raise ValueError("one SamplingParams per prompt, or one for all")
         sched = Scheduler(self.executor, token_budget=self.token_budget, prefill_chunk=self.prefill_chunk_tokens,
-                          max_running=self.inflight_slots)
+                          max_running=self.inflight_slots, run_ahead=self.run_ahead)
         reqs = [sched.add(i, p, sp) for i, (p, sp) in enumerate(zip(prompts, plist))]
         sched.run()
         self.engine.runtime.check_status("generate")

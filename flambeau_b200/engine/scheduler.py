@@ -20,6 +20,13 @@ fails for lack of pages:
     returns to the front of the queue with prompt := prompt + generated so far,
     to be fed again later (its draws continue where they stopped);
   * a request that cannot fit even alone is finished with reason 'capacity'.
+
+Running ahead.  While every running request is decoding and none is about to reach its token limit, the next
+step is known but for the token ids, and those are on the device: the scheduler queues it (token ids fed from the
+sampler's output buffer) before it reads the tokens of the step that is running, so the device never waits for
+the host.  A request that turns out to have stopped in the meantime has one row too many in the step already
+queued; that row's token is dropped.  What is generated does not change: a request's logits do not depend on the
+other rows of its step, and its draws are numbered.
 """
 from __future__ import annotations
 
@@ -73,9 +80,11 @@ class PlannedStep:
 
 
 class Scheduler:
-    def __init__(self, executor, *, token_budget: int = 512, prefill_chunk: int = 512, max_running: int = 4):
+    def __init__(self, executor, *, token_budget: int = 512, prefill_chunk: int = 512, max_running: int = 4,
+                 run_ahead: bool = True):
         """`executor` has .cache (a CacheManager), .run(entries, sampled_requests) -> list of token ids, and
-        .finish(request_id)."""
+        .finish(request_id); for running ahead also .launch(entries, sampled, feed, pending) -> handle,
+        .collect(handle) -> list of token ids and .can_run_ahead(sampled)."""
         if token_budget < 1 or prefill_chunk < 1 or max_running < 1:
             raise ValueError("token_budget, prefill_chunk and max_running must be positive")
         self.executor = executor
@@ -86,6 +95,10 @@ class Scheduler:
         self.finished: list = []
         self._arrivals = 0
         self.steps = 0
+        self._two_phase = all(hasattr(executor, m) for m in ("launch", "collect", "can_run_ahead"))
+        self.run_ahead = run_ahead and self._two_phase      # may be switched while running
+        self._ahead = None                 # (PlannedStep, handle) of a step that is queued but not collected
+        self.steps_ahead = 0               # steps that were queued ahead
 
     # ---- requests ----------------------------------------------------------------
     def add(self, request_id, prompt, params: SamplingParams | None = None) -> Request:
@@ -102,7 +115,7 @@ class Scheduler:
 
     @property
     def idle(self) -> bool:
-        return not self.waiting and not self.running
+        return not self.waiting and not self.running and self._ahead is None
 
     # ---- planning ----------------------------------------------------------------
     def _pages_free(self) -> list:
@@ -208,23 +221,40 @@ class Scheduler:
 
     # ---- running -----------------------------------------------------------------
     def step(self) -> list:
-        """Plan and run one step; returns [(request, token)] for the tokens sampled in it."""
-        plan = self.plan()
-        if not plan.entries:
-            if self.running or self.waiting:
-                # nothing could be scheduled although work is left: the head of the queue can never fit
-                if self.waiting and not self.running:
-                    self._finish(self.waiting.popleft(), "capacity")
-                    return []
-                raise RuntimeError("scheduler: running requests but nothing to run")
-            return []
-        tokens = self.executor.run(plan.entries, plan.sampled)
+        """Plan and run one step (or collect the one that was queued ahead); returns [(request, token)] for the
+        tokens sampled in it."""
+        tokens = None
+        if self._ahead is not None:
+            plan, handle = self._ahead
+            self._ahead = None
+        else:
+            plan = self.plan()
+            if not plan.entries:
+                if self.running or self.waiting:
+                    # nothing could be scheduled although work is left: the head of the queue can never fit
+                    if self.waiting and not self.running:
+                        self._finish(self.waiting.popleft(), "capacity")
+                        return []
+                    raise RuntimeError("scheduler: running requests but nothing to run")
+                return []
+            if self._two_phase:
+                handle = self.executor.launch(plan.entries, plan.sampled)
+            else:
+                handle = None
+                tokens = self.executor.run(plan.entries, plan.sampled)
         self.steps += 1
+        if tokens is None:
+            if self.run_ahead:
+                self._queue_ahead(plan, handle)
+            tokens = self.executor.collect(handle) if handle is not None else []
         by_id = {r.request_id: r for r in self.running}
         for e in plan.entries:
-            by_id[e.request_id].fed += len(e.tokens)
+            if e.request_id in by_id:                      # (a request that stopped has left meanwhile)
+                by_id[e.request_id].fed += len(e.tokens)
         out = []
         for r, tok in zip(plan.sampled, tokens):
+            if r.finish_reason is not None:
+                continue                                   # it stopped in the step before: a row too many
             r.generated.append(int(tok))
             out.append((r, int(tok)))
             if not r.params.ignore_eos and int(tok) in r.params.stop_token_ids:
@@ -232,6 +262,36 @@ class Scheduler:
             elif len(r.generated) >= r.params.max_tokens:
                 self._finish(r, "length")
         return out
+
+    def _queue_ahead(self, plan: PlannedStep, handle) -> None:
+        """Queue the step after `plan` (whose tokens are not known yet) if it is sure to be one decoded token for
+        every running request."""
+        if handle is None or self.waiting or not self.running:
+            return
+        sampled = plan.sampled
+        if len(sampled) != len(self.running) or len(sampled) > self.token_budget:
+            return
+        live = set(id(r) for r in self.running)
+        for r in sampled:
+            # running, its whole prompt fed by `plan`, and not at its limit with the token that is on its way
+            if id(r) not in live or r.finish_reason is not None or len(r.generated) + 2 > r.params.max_tokens:
+                return
+        fed_by_plan = {e.request_id: len(e.tokens) for e in plan.entries}
+        for r in sampled:
+            if r.remaining - fed_by_plan.get(r.request_id, 0) != 0:
+                return
+        if not self.executor.can_run_ahead(sampled):
+            return
+        need = [0] * self.cache.n_groups
+        for r in sampled:
+            for gi, k in enumerate(self.cache.pages_needed(r.request_id, 1)):
+                need[gi] += k
+        if not self._fits(self._pages_free(), need):
+            return                                         # the planner will make room, knowing the tokens
+        entries = [Entry(r.request_id, [0], [0]) for r in sampled]          # the ids come from the device
+        nxt = PlannedStep(entries, list(sampled), [], [])
+        self._ahead = (nxt, self.executor.launch(entries, sampled, feed=handle, pending=1))
+        self.steps_ahead += 1
 
     def run(self) -> list:
         """Run until every request has finished; returns them in arrival order."""

@@ -203,8 +203,12 @@ class Engine:
         return request_id in self.cache.requests
 
     # ---- the step ------------------------------------------------------------------
-    def step(self, entries: list, end=()) -> Optional[torch.Tensor]:
+    def step(self, entries: list, end=(), token_feed: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run `entries` (Entry or (request_id, tokens, want) tuples) as one batch.
+
+        `token_feed` (device int32, one id per entry, every entry a single token): the token ids are taken from
+        it on the device, in stream order, instead of from the entries; this is how a decode step is queued
+        before the host has seen the tokens the step before it sampled.
 
         Unknown request ids are admitted.  Returns float32 logits [wanted, vocab] on the device, in the
         order of the entries and of each entry's `want` (None if nothing is wanted); the tensor is
@@ -234,6 +238,10 @@ class Engine:
                     if rid in cache.requests:
                         cache.release(rid)
                 raise
+            if token_feed is not None:
+                if batch.n_tokens != batch.n_seqs or token_feed.numel() < batch.n_seqs:
+                    raise BatchError("a token feed needs single-token entries and one id per entry")
+                self.buffers.d_rows[0, :batch.n_seqs].copy_(token_feed[:batch.n_seqs])
             self._copied.record()
             self._copy_pending = True
             logits = self._run(batch)

@@ -75,6 +75,41 @@ def test_generation_under_page_pressure_gives_the_same_tokens(model):
     assert not tight.cache.requests
 
 
+def test_running_ahead_changes_no_token(model):
+    """Decode steps queued before the host has read the tokens of the step before (their ids fed on the device),
+    against the loop that waits every step: stop tokens in mid-flight, unequal limits, draws and greedy rows."""
+    from flambeau_b200.engine.generate import Generator
+    from flambeau_b200.engine.step import Engine, EngineOptions
+    from flambeau_b200.sampling.params import SamplingParams
+    prompts = list(tiny.random_requests(model["cfg"], [9, 30, 4, 17], seed=21).values())
+    engine = Engine.from_folder(model["folder"], EngineOptions(dtype=model["dtype"], cache_tokens=512, max_requests=4,
+                                                               max_step_tokens=64, max_seq_len=128))
+    free = Generator(engine, prefill_chunk_tokens=16, run_ahead=False).generate(
+        prompts, [SamplingParams(max_tokens=24, temperature=0.9, seed=3 + i) for i in range(4)])
+    # stop tokens taken from what the requests really generate, so that they stop in the middle of the run
+    params = [SamplingParams(max_tokens=24, temperature=0.9, seed=3, stop_token_ids=(free[0][7],)),
+              SamplingParams(max_tokens=13, temperature=0.9, seed=4),
+              SamplingParams(max_tokens=24, temperature=0.0, stop_token_ids=(free[2][3], free[2][15])),
+              SamplingParams(max_tokens=24, temperature=0.9, seed=6, repetition_penalty=1.0)]
+    waiting = Generator(engine, prefill_chunk_tokens=16, run_ahead=False)
+    want = waiting.generate(prompts, params)
+    ahead = Generator(engine, prefill_chunk_tokens=16, run_ahead=True)
+    got = ahead.generate(prompts, params)
+    assert got == want
+    assert ahead.last_scheduler.steps_ahead > 5, "steps were meant to be queued ahead"
+    assert waiting.last_scheduler.steps_ahead == 0
+    assert [r.finish_reason for r in ahead.last_scheduler.finished] == \
+           [r.finish_reason for r in waiting.last_scheduler.finished]
+    assert len(got[0]) < 24 and len(got[1]) == 13
+    engine.cache.check_invariants()
+    assert not engine.cache.requests
+    # a request with penalties needs its tokens on the host: nothing is queued ahead, the tokens agree all the same
+    pen = [SamplingParams(max_tokens=10, temperature=0.7, seed=9, repetition_penalty=1.3)] * 4
+    a = Generator(engine, prefill_chunk_tokens=16, run_ahead=True)
+    assert a.generate(prompts, pen) == waiting.generate(prompts, pen)
+    assert a.last_scheduler.steps_ahead == 0
+
+
 def test_temperature_sampling_is_seeded_and_independent_of_the_batch(model):
     from flambeau_b200 import generate
     prompts = list(tiny.random_requests(model["cfg"], [6, 19, 11], seed=10).values())

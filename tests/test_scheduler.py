@@ -151,3 +151,98 @@ def test_random_load_never_breaks_the_books():
         assert sum(n for _, n, _ in ex.log[-1]) <= 24 if ex.log else True
     assert all(r.finish_reason == "length" and len(r.generated) == r.params.max_tokens for r in reqs)
     assert ex.cache.free_pages() == [10] and not ex.cache.requests
+
+
+class TwoPhaseExecutor(BookkeepingExecutor):
+    """The same books with the launch / collect interface: a step is queued with `launch`, its tokens are read
+    later with `collect`; `pending` tokens of a request are on their way when its row is queued."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.in_flight = 0
+        self.most_in_flight = 0
+        self.fed_from_device = 0
+
+    def launch(self, entries, sampled, feed=None, pending=0):
+        if feed is not None:
+            assert all(len(e.tokens) == 1 for e in entries) and len(feed) == len(entries)
+            self.fed_from_device += 1
+        if True:
+            for e in entries:
+                if e.request_id not in self.cache.requests:
+                    self.cache.admit(e.request_id)
+            assert self.cache.can_reserve([(e.request_id, len(e.tokens)) for e in entries])
+            for e in entries:
+                self.cache.reserve(e.request_id, len(e.tokens))
+                self.cache.commit(e.request_id, len(e.tokens))
+            self.log.append([(e.request_id, len(e.tokens), list(e.want)) for e in entries])
+        if not sampled:
+            return None
+        self.in_flight += 1
+        self.most_in_flight = max(self.most_in_flight, self.in_flight)
+        return [100 + len(r.generated) + pending for r in sampled]
+
+    def collect(self, handle):
+        self.in_flight -= 1
+        return handle
+
+    def can_run_ahead(self, sampled):
+        return all(not r.params.has_penalties for r in sampled)
+
+
+def run_both(add_requests, **kw):
+    results = []
+    for ahead in (False, True):
+        ex = TwoPhaseExecutor()
+        s = Scheduler(ex, run_ahead=ahead, **kw)
+        reqs = add_requests(s)
+        s.run()
+        ex.cache.check_invariants()
+        assert not ex.cache.requests and ex.in_flight == 0
+        results.append((ex, s, [(r.generated, r.finish_reason) for r in reqs]))
+    return results
+
+
+def test_running_ahead_gives_the_same_tokens_and_reasons():
+    def add(s):
+        return [s.add("a", list(range(20)), SamplingParams(max_tokens=12, stop_token_ids=(105,))),
+                s.add("b", list(range(7)), SamplingParams(max_tokens=9)),
+                s.add("c", list(range(33)), SamplingParams(max_tokens=20, stop_token_ids=(111, 103), ignore_eos=True))]
+    (ex0, s0, want), (ex1, s1, got) = run_both(add, token_budget=16, prefill_chunk=8, max_running=3)
+    assert got == want
+    assert want[0] == ([100, 101, 102, 103, 104, 105], "stop") and want[1][1] == "length" and len(want[2][0]) == 20
+    assert s0.steps_ahead == 0 and ex0.most_in_flight == 1
+    assert s1.steps_ahead > 0 and ex1.most_in_flight == 2 and ex1.fed_from_device == s1.steps_ahead
+
+
+def test_nothing_is_queued_ahead_while_a_prompt_waits_or_a_limit_is_near():
+    ex = TwoPhaseExecutor()
+    s = Scheduler(ex, token_budget=8, prefill_chunk=8, max_running=1)
+    a = s.add("a", [1, 2, 3], SamplingParams(max_tokens=4))
+    s.add("b", [1, 2, 3], SamplingParams(max_tokens=2))
+    s.step()                                                     # a's prompt; b waits for the slot
+    assert s._ahead is None and a.generated == [100]
+    s.step(); s.step()
+    assert s._ahead is None and s.steps_ahead == 0               # b still waits: every step is planned afresh
+    s.run()
+    assert s.steps_ahead == 1                                    # b, alone at last, had its second token queued
+    # alone, a request is run ahead until its last token is queued
+    ex = TwoPhaseExecutor()
+    s = Scheduler(ex, token_budget=8, prefill_chunk=8)
+    a = s.add("a", [1, 2, 3], SamplingParams(max_tokens=4))
+    s.step()
+    assert s._ahead is not None and a.generated == [100]         # token 2 of 4 is queued
+    s.step()
+    assert s._ahead is not None and a.generated == [100, 101]    # token 3 of 4 is queued
+    s.step()
+    assert s._ahead is not None and a.generated == [100, 101, 102]   # token 4, the last, is queued
+    s.step()
+    assert s._ahead is None and a.generated == [100, 101, 102, 103] and a.finish_reason == "length"
+    assert s.idle and ex.log[-1] == [("a", 1, [0])] and len(ex.log) == 4
+
+
+def test_penalties_keep_the_loop_waiting():
+    def add(s):
+        return [s.add("a", [1, 2, 3], SamplingParams(max_tokens=6, repetition_penalty=1.2))]
+    (_, s0, want), (_, s1, got) = run_both(add)
+    assert got == want and s1.steps_ahead == 0
