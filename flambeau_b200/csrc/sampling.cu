@@ -126,11 +126,23 @@ sample_kernel(const float* __restrict__ logits, long stride, int V, const float*
     const int c0 = min(V, tid * chunk), c1 = min(V, c0 + chunk);
 
     // ---- argmax, lowest index on ties ----
+    // (consecutive threads read consecutive entries; a thread meets its entries in rising order, so `>` keeps the
+    // lowest index among equals, and the reduction below compares indices)
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = c0; i < c1; ++i) {
-        const float v = l[i];
-        if (v > best) { best = v; best_i = i; }
+    {
+        int i = tid;
+        for (; i + 3 * SAMPLE_THREADS < V; i += 4 * SAMPLE_THREADS) {
+            const float v0 = l[i], v1 = l[i + SAMPLE_THREADS], v2 = l[i + 2 * SAMPLE_THREADS], v3 = l[i + 3 * SAMPLE_THREADS];
+            if (v0 > best) { best = v0; best_i = i; }
+            if (v1 > best) { best = v1; best_i = i + SAMPLE_THREADS; }
+            if (v2 > best) { best = v2; best_i = i + 2 * SAMPLE_THREADS; }
+            if (v3 > best) { best = v3; best_i = i + 3 * SAMPLE_THREADS; }
+        }
+        for (; i < V; i += SAMPLE_THREADS) {
+            const float v = l[i];
+            if (v > best) { best = v; best_i = i; }
+        }
     }
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
