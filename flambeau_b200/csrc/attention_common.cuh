@@ -46,6 +46,7 @@ struct AttnArgs {
     int short_ctas;                    // split-key: CTAs of the split-key launch
     int min_tiles;                     // split-key: a CTA's stretch is at least this long
     int short_rows;                    // sequences with q_len * G <= short_rows belong to the split-key arrangement
+    FbPrefetch prefetch;               // split-key: rows to fetch into L2 when a CTA has issued its last tile
     int* status;
 };
 

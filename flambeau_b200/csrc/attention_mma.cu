@@ -456,6 +456,7 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     }
     a.n_seqs = n_seqs;
     a.short_ctas = 0; a.min_tiles = 1;
+    a.prefetch = fb_take_prefetch_hint();
     a.part_o = nullptr; a.part_ml = nullptr; a.part_cnt = nullptr;
     if (any_long) {
         const int rc = (attention_tc_enabled() && fb_attention_tc_takes(a, tma))

@@ -318,7 +318,11 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
             if (count >= NST && !wait(&empty[buf], ((count / NST) - 1) & 1u)) return;
             issue(sg, buf, sg.k_begin + it * KT);
             if (++it == sg.n_tiles) {
-                if (g >= seg_hi) return;
+                if (g >= seg_hi) {
+                    // the stream of cache ends here: the memory system is free for the product that follows
+                    fb_prefetch_issue(a.prefetch, (long)blockIdx.x * 32 + lane, (long)gridDim.x * 32);
+                    return;
+                }
                 sg = next_seg();
                 it = 0;
             }

@@ -63,6 +63,24 @@ inline void fb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);     // an error shows in fb_check_launch()
 }
 
+// ---- a running start for the product that follows ---------------------------
+// The first `bytes` of every row of a weight matrix, fetched into L2 by a kernel that has the memory system to
+// spare (the split-key attention kernel when its stream of cache ends), so that the product after it finds its
+// first k-blocks there.  Set for the next launch with fb_set_prefetch_hint(); a hint, nothing depends on it.
+struct FbPrefetch {
+    const char* base;      // nullptr: nothing to do
+    int rows;
+    long row_stride;       // bytes
+    int bytes;             // per row, a multiple of 16
+};
+FbPrefetch fb_take_prefetch_hint();     // the pending hint (cleared by the call)
+
+__device__ __forceinline__ void fb_prefetch_issue(const FbPrefetch& pf, long worker, long n_workers) {
+    if (!pf.base) return;
+    for (long r = worker; r < pf.rows; r += n_workers)
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf.base + r * pf.row_stride), "r"(pf.bytes) : "memory");
+}
+
 // ---- typed access -----------------------------------------------------------
 __device__ __forceinline__ float fb_to_float(float v) { return v; }
 __device__ __forceinline__ float fb_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

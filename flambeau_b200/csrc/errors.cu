@@ -2,6 +2,7 @@
 #include "common.cuh"
 
 #include <stdarg.h>
+#include <stdint.h>
 #include <stdio.h>
 
 static thread_local char g_last_error[1024] = "";
@@ -10,6 +11,25 @@ int g_fb_pdl = 1;
 
 // Switches programmatic dependent launch on (1, the default) or off (0) for all later launches.
 FB_API void fb_set_pdl(int on) { g_fb_pdl = on ? 1 : 0; }
+
+static thread_local FbPrefetch g_prefetch = {nullptr, 0, 0, 0};
+
+// The next launch of the bfloat16 attention (its split-key kernel) also fetches the first
+// `bytes_per_row` bytes of each of `rows` rows (`row_stride_bytes` apart, from `base`) into L2.
+FB_API void fb_set_prefetch_hint(const void* base, long long rows, long long row_stride_bytes, int bytes_per_row) {
+    const bool ok = base && rows > 0 && rows < (1LL << 31) && bytes_per_row >= 16 && row_stride_bytes >= bytes_per_row &&
+                    ((uintptr_t)base & 15) == 0 && row_stride_bytes % 16 == 0;
+    g_prefetch.base = ok ? (const char*)base : nullptr;
+    g_prefetch.rows = (int)rows;
+    g_prefetch.row_stride = (long)row_stride_bytes;
+    g_prefetch.bytes = bytes_per_row & ~15;
+}
+
+FbPrefetch fb_take_prefetch_hint() {
+    const FbPrefetch pf = g_prefetch;
+    g_prefetch.base = nullptr;
+    return pf;
+}
 
 int fb_fail(int code, const char* fmt, ...) {
     va_list ap;

@@ -10,13 +10,14 @@ is just a portion of length one and any number of portions may share a step.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
 import torch
 
 from ..cache.manager import CacheManager
-from ..kernels import library
+from ..kernels import library, ops
 from .batch import BatchBuffers, BatchError, Entry, StepBatch
 from .runtime import Runtime, Workspace
 
@@ -46,6 +47,7 @@ class StepContext:
         self.normed = self.delta = self.delta_slabs = None
         self.max_slabs = 1                  # how many split-K slabs a product may leave for the next kernel to add
         self.pending_slabs = 1
+        self.l2_hints = engine.l2_hints
 
     def open_stream(self, width: int):
         """Allocate what the blocks of a step share: the float32 residual stream (returned), the buffer for
@@ -61,6 +63,13 @@ class StepContext:
         self.delta = self.delta_slabs[0]
         self.pending_slabs = 1
         return x
+
+    def hint(self, weight) -> None:
+        """Tell the attention kernel that follows which matrix the product after it reads, so that it fetches the
+        start of that matrix into L2 when its own stream of cache ends (few rows only: a step of many rows is
+        bound by its products' arithmetic; bfloat16 kernels only).  It changes no result."""
+        if weight is not None and self.l2_hints and self.n_tokens <= 64:
+            ops.prefetch_hint(weight)
 
     def step_alloc(self, shape, dtype):
         """Scratch that lives until the step ends (ctx.ws allocations end with their scope)."""
@@ -96,6 +105,8 @@ class Engine:
         self.last_batch: Optional[StepBatch] = None
         self._graphs: dict = {}            # step shape -> captured graph (or the count of eager runs so far)
         self.use_graphs = bool(options.cuda_graphs) and model.graph_safe()
+        # the decode attention kernel fetches the start of the output projection's weights into L2 at its end
+        self.l2_hints = options.dtype == "bfloat16" and os.environ.get("FLAMBEAU_L2_HINTS", "1") != "0"
         self.graph_replays = 0
 
     # ---- construction ----------------------------------------------------------

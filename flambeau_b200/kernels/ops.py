@@ -308,6 +308,20 @@ class _AttentionScratch:
         return hit
 
 
+def prefetch_hint(weight: torch.Tensor, budget_bytes: int = 16 << 20) -> None:
+    """The next bfloat16 attention launch also fetches the first bytes of every row of `weight` ([rows, K], the
+    matrix of the product that follows) into L2 when its split-key kernel's stream of cache ends, `budget_bytes`
+    in all: the product starts on data that is already on the chip.  A hint: results do not depend on it.
+    (Measured for the row-wise kernels between the products as well: there it costs more than it brings.)"""
+    if weight.dim() != 2 or weight.stride(1) != 1:
+        return
+    rows = weight.shape[0]
+    row_bytes = weight.shape[1] * weight.element_size()
+    per_row = min(row_bytes, max(512, (budget_bytes // max(rows, 1)) // 512 * 512)) // 16 * 16
+    if per_row >= 16:
+        lib().fb_set_prefetch_hint(weight.data_ptr(), rows, weight.stride(0) * weight.element_size(), per_row)
+
+
 def set_attention_tc(on: bool) -> None:
     """Portions of prompts on the tcgen05 attention kernel where it takes the geometry (the default), or always on
     the mma.sync kernel."""
@@ -353,5 +367,6 @@ def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int,
                             b.seq_pos_start_d, b.n_seqs, b.max_q_len, b.max_kv_len, any(short), not all(short),
                             nh, nkv, hd, window, scale, ctx.runtime.status)
     else:
+        lib().fb_set_prefetch_hint(None, 0, 0, 0)          # this kernel takes no hint: none stays behind
         paged_attention_simt(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.positions, b.row_seq,
                              nh, nkv, hd, window, scale, ctx.runtime.status)

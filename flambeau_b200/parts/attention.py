@@ -91,6 +91,7 @@ class PagedAttention(Mixer):
                                   cache.k_pool, cache.v_pool, cache.page_size, self.nh, self.nkv, self.hd,
                                   cache.writable, rt.status)
             a = ctx.ws.alloc((n, self.qw), rt.dtype)
+            ctx.hint(self.o.weight)
             ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale)
             ctx.pending_slabs = self.o.slabs(ctx, a, ctx.delta_slabs)
 

@@ -232,3 +232,18 @@ def test_one_far_key_among_a_long_prompt(prompt_kernel):
         assert float((got.double() - want).abs().max() / want.abs().max()) < 1.2e-2
         assert float((want[-1, 0] - sc.v[0][target][0]).abs().max()) < 0.01, "the planted key does not dominate"
         assert float((got[-1, 0] - sc.v[0][target][0]).abs().max()) < 0.05, "the key that dominates was lost"
+
+
+def test_a_prefetch_hint_changes_nothing():
+    """The split-key kernel fetches the start of the next product's weights into L2 when asked to; the output is
+    the same bit for bit, and a hint the kernel cannot use (odd strides) is dropped."""
+    from flambeau_b200.kernels import ops
+    sc = Scene([(700, 1), (90, 1), (1500, 2)], 8, 2, 128, 0, torch.bfloat16, seed=3)
+    scale = 1.0 / math.sqrt(128)
+    plain = sc.run("mma", scale)
+    w = torch.randn(1024, 4096, device="cuda").bfloat16()
+    ops.prefetch_hint(w)
+    assert torch.equal(sc.run("mma", scale), plain)
+    ops.prefetch_hint(w[:, 1:])                 # rows that do not start on 16 bytes
+    ops.prefetch_hint(w.t())                    # not row-major
+    assert torch.equal(sc.run("mma", scale), plain)
