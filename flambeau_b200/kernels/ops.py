@@ -312,7 +312,8 @@ def prefetch_hint(weight: torch.Tensor, budget_bytes: int = 16 << 20) -> None:
     """The next bfloat16 attention launch also fetches the first bytes of every row of `weight` ([rows, K], the
     matrix of the product that follows) into L2 when its split-key kernel's stream of cache ends, `budget_bytes`
     in all: the product starts on data that is already on the chip.  A hint: results do not depend on it.
-    (Measured for the row-wise kernels between the products as well: there it costs more than it brings.)"""
+    (Measured for the row-wise kernels between the products and for the products' own tails as well: there it
+    costs more than it brings.)"""
     if weight.dim() != 2 or weight.stride(1) != 1:
         return
     rows = weight.shape[0]
