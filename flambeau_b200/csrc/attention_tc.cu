@@ -28,12 +28,12 @@ namespace {
 using namespace fb_attn;
 
 constexpr int BM = 128;            // query rows per row tile (the M of the MMAs)
-constexpr int BN = 128;            // keys per tile
+constexpr int BN = 64;             // keys per tile
 // Threads of a CTA with RT row tiles: warp 0 fetches, warp 1 issues the MMAs, warps 2..5 (and 6..9) are the softmax
 // of row tile 0 (and 1).
 __host__ __device__ constexpr int tc_threads(int rt) { return 64 + BM * rt; }
-constexpr int NKV = 2;             // K slots and V slots
-constexpr int TMEM_COLS = 512;     // S/P of row tile 0 [0,128), of row tile 1 [128,256); O of tile 0 [256,384), of tile 1 [384,512)
+constexpr int NKV = 4;             // K slots and V slots
+constexpr int TMEM_COLS = 512;     // S/P buffer b of row tile t at (2t + b) * 64; O of row tile t at RT * 128 + t * 128
 constexpr float RESCALE_STEP = 8.0f;
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -44,7 +44,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 template <int HD, int RT> struct TcSmem {
     static constexpr int Q_BYTES = BM * HD * 2;                 // one row tile: [HD/64 column blocks][128 rows][128 bytes]
-    static constexpr int KV_BYTES = BN * HD * 2;                // one K or V tile: [HD/64][128 keys][128 bytes]
+    static constexpr int KV_BYTES = BN * HD * 2;                // one K or V tile: [HD/64][64 keys][128 bytes]
     static constexpr int TAIL_BYTES = 256;                      // barriers, tensor-memory address, flag
     static constexpr int USED = RT * Q_BYTES + NKV * 2 * KV_BYTES + TAIL_BYTES + 1024 /* alignment */;
     // one CTA per SM: two would both want all of tensor memory
@@ -71,11 +71,13 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     uint64_t* k_empty = bars + NKV;                             // [NKV] both row tiles' scores are computed
     uint64_t* v_full = bars + 2 * NKV;                          // [NKV] a V tile has landed
     uint64_t* v_empty = bars + 3 * NKV;                         // [NKV] both row tiles' products are computed
-    uint64_t* s_full = bars + 4 * NKV;                          // [RT]  S of a row tile is in tensor memory
-    uint64_t* p_full = bars + 4 * NKV + RT;                     // [RT]  P of a row tile is in tensor memory
-    uint64_t* pv_done = bars + 4 * NKV + 2 * RT;                // [RT]  O of a row tile holds the key tile's product
-    uint64_t* q_full = bars + 4 * NKV + 3 * RT;                 //       Q is staged
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * NKV + 3 * RT + 1);
+    uint64_t* s_full = bars + 4 * NKV;                          // [RT][2] S of a row tile is in tensor memory (two buffers)
+    uint64_t* p_full = bars + 4 * NKV + 2 * RT;                 // [RT][2] P of a row tile is in tensor memory, per buffer:
+                                                                //       the softmax may be two tiles ahead of the products
+    uint64_t* pv_done = bars + 4 * NKV + 4 * RT;                // [RT]  O of a row tile holds the key tile's product
+    uint64_t* o_done = bars + 4 * NKV + 5 * RT;                 // [RT]  O of a row tile holds all products (used once)
+    uint64_t* q_full = bars + 4 * NKV + 6 * RT;                 //       Q is staged
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * NKV + 6 * RT + 1);
     int* bail = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -108,9 +110,12 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
             mbar_init(smem_u32(&v_empty[s]), 1);
         }
         for (int t = 0; t < RT; ++t) {
-            mbar_init(smem_u32(&s_full[t]), 1);
-            mbar_init(smem_u32(&p_full[t]), BM);
+            mbar_init(smem_u32(&s_full[2 * t]), 1);
+            mbar_init(smem_u32(&s_full[2 * t + 1]), 1);
+            mbar_init(smem_u32(&p_full[2 * t]), BM);
+            mbar_init(smem_u32(&p_full[2 * t + 1]), BM);
             mbar_init(smem_u32(&pv_done[t]), 1);
+            mbar_init(smem_u32(&o_done[t]), 1);
         }
         mbar_init(smem_u32(q_full), RT * BM);
         *bail = 0;
@@ -168,50 +173,53 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
         }
     } else if (warp == 1) {
         // ================= MMA issue =================
-        // Per key tile and row tile: O += P V, then the scores of the next key tile into the columns P lay in (the
-        // MMAs run in the order of their issue, so the product has read P by then).  The two row tiles alternate,
-        // so the tensor pipe works for one while the softmax of the other runs.
+        // Scores run two key tiles ahead of the softmax (two buffers per row tile), so a row tile's softmax never
+        // waits for the tensor pipe.  Per key tile and row tile: O += P V, then the scores of the tile after next
+        // into the columns P lay in (the MMAs run in the order of their issue, so the product has read P by then).
         if (elect_one()) {
             constexpr uint32_t idesc_s = umma_idesc(BN);
             constexpr uint32_t idesc_o = umma_idesc(HD, true);
-            auto issue_s = [&](int j, int t) {                  // S of row tile t = Q_t K_j^T
+            auto issue_s = [&](int j, int t) {                  // S buffer j & 1 of row tile t = Q_t K_j^T
                 const uint32_t q_addr = smem_u32(Qs + t * SM::Q_BYTES);
                 const uint32_t k_addr = smem_u32(Ks + (j % NKV) * SM::KV_BYTES);
-                const uint32_t d = tmem_base + (uint32_t)(t * BN);
+                const uint32_t d = tmem_base + (uint32_t)((2 * t + (j & 1)) * BN);
 #pragma unroll
-                for (int kk = 0; kk < HD / UMMA_K; ++kk) {
-                    const uint32_t off = (uint32_t)((kk / 4) * (128 * 128) + (kk % 4) * 32);
-                    umma_bf16(d, umma_desc(q_addr + off), umma_desc(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
-                }
-                umma_commit(smem_u32(&s_full[t]));
+                for (int kk = 0; kk < HD / UMMA_K; ++kk)
+                    umma_bf16(d, umma_desc(q_addr + (uint32_t)((kk / 4) * (BM * 128) + (kk % 4) * 32)),
+                              umma_desc(k_addr + (uint32_t)((kk / 4) * (BN * 128) + (kk % 4) * 32)), idesc_s,
+                              kk > 0 ? 1u : 0u);
+                umma_commit(smem_u32(&s_full[2 * t + (j & 1)]));
                 if (t == RT - 1) umma_commit(smem_u32(&k_empty[j % NKV]));
             };
-            bool ok = wait(q_full, 0) && wait(&k_full[0], 0);
-            if (ok) {
+            bool ok = wait(q_full, 0);
+            for (int j = 0; ok && j < 2 && j < n_tiles; ++j) {
+                ok = wait(&k_full[j % NKV], (uint32_t)(j / NKV) & 1u);
+                if (!ok) break;
                 tmem_fence_after();
-                for (int t = 0; t < RT; ++t) issue_s(0, t);
+                for (int t = 0; t < RT; ++t) issue_s(j, t);
             }
             for (int j = 0; ok && j < n_tiles; ++j) {
                 for (int t = 0; ok && t < RT; ++t) {
-                    ok = wait(&p_full[t], (uint32_t)j & 1u);
+                    ok = wait(&p_full[2 * t + (j & 1)], (uint32_t)(j >> 1) & 1u);
                     if (ok && t == 0) ok = wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u);
                     if (!ok) break;
                     tmem_fence_after();
                     const uint32_t v_addr = smem_u32(Vs + (j % NKV) * SM::KV_BYTES);
-                    const uint32_t p_addr = tmem_base + (uint32_t)(t * BN);        // bf16 pairs over the scores
-                    const uint32_t d = tmem_base + (uint32_t)(RT * BN + t * BM);
+                    const uint32_t p_addr = tmem_base + (uint32_t)((2 * t + (j & 1)) * BN);   // bf16 pairs over the scores
+                    const uint32_t d = tmem_base + (uint32_t)(RT * 128 + t * 128);
 #pragma unroll
                     for (int kk = 0; kk < BN / UMMA_K; ++kk) {  // 16 keys = 8 columns of P each
                         const uint64_t db = umma_desc_mn(v_addr + (uint32_t)(kk * 16 * 128), BN * 128, 1024);
                         umma_bf16_ts(d, p_addr + (uint32_t)(kk * 8), db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&pv_done[t]));
+                    if (j == n_tiles - 1) umma_commit(smem_u32(&o_done[t]));
                     if (t == RT - 1) umma_commit(smem_u32(&v_empty[j % NKV]));
-                    if (j + 1 < n_tiles) {
-                        if (t == 0) ok = wait(&k_full[(j + 1) % NKV], (uint32_t)((j + 1) / NKV) & 1u);
+                    if (j + 2 < n_tiles) {
+                        if (t == 0) ok = wait(&k_full[(j + 2) % NKV], (uint32_t)((j + 2) / NKV) & 1u);
                         if (!ok) break;
                         tmem_fence_after();
-                        issue_s(j + 1, t);
+                        issue_s(j + 2, t);
                     }
                 }
             }
@@ -240,19 +248,19 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
         const int p_row = valid ? pos0 + tok0 + r / G : -1;     // a row beyond the share sees nothing
         const int t0_row = (a.window > 0 && p_row - a.window + 1 > 0) ? p_row - a.window + 1 : 0;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t s_addr = lane_addr + (uint32_t)(t * BN);             // S, and P over it, of this row
-        const uint32_t o_addr = lane_addr + (uint32_t)(RT * BN + t * BM);   // O of this row
+        const uint32_t o_addr = lane_addr + (uint32_t)(RT * 128 + t * 128); // O of this row
         float m_ref = -INFINITY;                                // reference point of the exponentials (scaled, base 2)
         float l = 0.0f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int tile_start = k_begin + j * BN;
-            ok = ok && __all_sync(0xffffffffu, wait(&s_full[t], (uint32_t)j & 1u));
+            const uint32_t s_addr = lane_addr + (uint32_t)((2 * t + (j & 1)) * BN);   // S, and P over it, of this row
+            ok = ok && __all_sync(0xffffffffu, wait(&s_full[2 * t + (j & 1)], (uint32_t)(j >> 1) & 1u));
             if (!ok) continue;
             tmem_fence_after();
             // every key of the tile is visible to every row of the warp, or each is compared
             const bool plain = __all_sync(0xffffffffu, tile_start + BN - 1 <= p_row && tile_start >= t0_row);
-            // ---- the row's 128 scores into registers (one round trip), masked where needed; their maximum ----
+            // ---- the row's 64 scores into registers (one round trip), masked where needed; their maximum ----
             uint32_t v[BN / 32][32];
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c) tmem_ld32_nowait(s_addr + (uint32_t)(c * 32), v[c]);
@@ -277,7 +285,9 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
             if (j == 0) {
                 m_ref = m_new;                                  // O is overwritten by the first product
             } else if (__any_sync(0xffffffffu, m_new > m_ref + RESCALE_STEP || (m_ref == -INFINITY && m_new > m_ref))) {
-                // move the reference point: O *= 2^(old - new), for the whole warp at once
+                // move the reference point: O *= 2^(old - new), for the whole warp at once.  (The product of tile
+                // j - 2 is complete, that of tile j cannot start before this thread is through: the phase asked
+                // for is the current one or the one just completed.)
                 ok = __all_sync(0xffffffffu, wait(&pv_done[t], (uint32_t)(j - 1) & 1u));
                 if (!ok) continue;
                 tmem_fence_after();
@@ -336,10 +346,11 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
             }
             tmem_wait_st();
             tmem_fence_before();
-            mbar_arrive(smem_u32(&p_full[t]));
+            mbar_arrive(smem_u32(&p_full[2 * t + (j & 1)]));
         }
         // ---- O / l, written as bfloat16 ----
-        if (ok) ok = __all_sync(0xffffffffu, wait(&pv_done[t], (uint32_t)(n_tiles - 1) & 1u));
+        // (a barrier of its own: pv_done may be one or two phases on by now, and a wait names a phase by its parity)
+        if (ok) ok = __all_sync(0xffffffffu, wait(&o_done[t], 0));
         if (ok) {
             tmem_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
