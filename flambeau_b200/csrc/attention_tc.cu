@@ -140,12 +140,27 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
         // ================= fetch: lane l copies (page l / CB, column block l % CB) of every K and V tile ==========
         // K tiles and V tiles run through rings of their own: a K slot is free as soon as its scores are computed
         // (a tile ahead of the softmax), a V slot after the tile's products, so a copy has two tiles' time to land.
-        // -2 = nothing to fetch (no query of the CTA sees the page), -1 = the table has no page although needed.
+        // Page ids come from the block table 32 at a time (one per lane, the next 32 already on their way), so a
+        // tile does not wait for the table: -2 = nothing to fetch (no query of the CTA sees the page), -1 = the
+        // table has no page although one is needed.
+        const int first_entry = k_begin / a.page_size;          // the table entry of tile 0's first page
+        auto entries = [&](int block) -> int {                  // table entries first_entry + 32 * block + lane
+            const int e = first_entry + 32 * block + lane;
+            return e < a.table_stride ? table[e] : -1;
+        };
+        int ids_block = 0, ids_cur = entries(0), ids_next = entries(1);
         auto lookup = [&](int j) -> int {
+            const int rel = j * pages_per_tile + lane / CB;     // this lane's page of tile j, counted from tile 0
+            const int block = (j * pages_per_tile) / 32;        // the same for all lanes: a tile's pages share a block
+            if (block != ids_block) {                           // tiles come in order: the next block
+                ids_cur = ids_next;
+                ids_next = entries(block + 1);
+                ids_block = block;
+            }
+            const int page = __shfl_sync(0xffffffffu, ids_cur, rel & 31);
             if (lane >= n_ops || j >= n_tiles) return -2;
-            const int t_first = k_begin + j * BN + (lane / CB) * a.page_size;
+            const int t_first = k_begin + rel * a.page_size;
             if (!(t_first + a.page_size > t_lo && t_first < k_end)) return -2;
-            const int page = table[t_first / a.page_size];
             return (page < 0 || page >= a.n_pages) ? -1 : page;
         };
         auto issue = [&](uint8_t* tile, const CUtensorMap* map, uint64_t* full, int page) {
