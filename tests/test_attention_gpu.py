@@ -247,3 +247,11 @@ def test_a_prefetch_hint_changes_nothing():
     ops.prefetch_hint(w[:, 1:])                 # rows that do not start on 16 bytes
     ops.prefetch_hint(w.t())                    # not row-major
     assert torch.equal(sc.run("mma", scale), plain)
+
+
+def test_hundreds_of_decoded_sequences_in_one_step():
+    """Three hundred sequences at once: the split-key kernel's per-sequence arrays and its scratch grow with the step."""
+    rnd = random.Random(7)
+    seqs = [(rnd.randrange(0, 150), 1) for _ in range(300)]
+    check(Scene(seqs, 8, 4, 64, 0, torch.bfloat16, page_size=16, seed=9), "mma")
+    check(Scene(seqs[:130], 4, 4, 128, 40, torch.bfloat16, page_size=8, seed=10), "mma")
