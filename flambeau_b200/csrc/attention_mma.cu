@@ -67,11 +67,16 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     const int tma_ops = 2 * pages_per_tile * col_blocks;
 
     // ---- what this CTA has to do: query tokens [tok0, tok0 + ntok) of a sequence, one key/value head ----
-    const int seq = blockIdx.z, kvh = blockIdx.y;
+    // CTAs are numbered heaviest first over the whole step: the last tokens of every sequence and head (they see
+    // the most keys) get the first SMs, whatever head or sequence they belong to
+    const int pairs = a.nkv * a.n_seqs;
+    const int rank = blockIdx.x / pairs, pair = blockIdx.x - rank * pairs;
+    const int seq = pair / a.nkv, kvh = pair - seq * a.nkv;
+    const int q_tiles = gridDim.x / pairs;
     const int q_len = a.seq_q_len[seq];
     if (q_len * G <= a.short_rows) return;                      // the split-key arrangement's
     const int TQ = ROWS / G;
-    const int tok0 = (gridDim.x - 1 - blockIdx.x) * TQ;         // later tiles see more keys: start them first
+    const int tok0 = (q_tiles - 1 - rank) * TQ;               // later tiles see more keys: start them first
     if (tok0 >= q_len) return;
     const int ntok = min(TQ, q_len - tok0);
     const int q_start = a.seq_q_start[seq], pos0 = a.seq_pos_start[seq];
@@ -379,7 +384,7 @@ int launch_long(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t strea
         configured = true;
     }
     const int TQ = 64 * long_row_blocks(HD_MAX) / (a.nh / a.nkv);
-    const dim3 grid((max_q_len + TQ - 1) / TQ, a.nkv, n_seqs);
+    const dim3 grid(((max_q_len + TQ - 1) / TQ) * a.nkv * n_seqs);
     fb_launch((kern), grid, LONG_THREADS, smem, stream, a);
     return fb_check_launch("attention_mma");
 }

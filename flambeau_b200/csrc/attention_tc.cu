@@ -84,11 +84,16 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     const int G = a.nh / a.nkv, hd = a.hd;
 
     // ---- what this CTA has to do: query tokens [tok0, tok0 + ntok) of a sequence, one key/value head ----
-    const int seq = blockIdx.z, kvh = blockIdx.y;
+    // CTAs are numbered heaviest first over the whole step: the last tokens of every sequence and head (they see
+    // the most keys) get the first SMs, whatever head or sequence they belong to
+    const int pairs = a.nkv * a.n_seqs;
+    const int rank = blockIdx.x / pairs, pair = blockIdx.x - rank * pairs;
+    const int seq = pair / a.nkv, kvh = pair - seq * a.nkv;
+    const int q_tiles = gridDim.x / pairs;
     const int q_len = a.seq_q_len[seq];
     if (q_len * G <= a.short_rows) return;                      // the split-key arrangement's
     const int TQ = RT * BM / G;
-    const int tok0 = (gridDim.x - 1 - blockIdx.x) * TQ;         // later tokens see more keys: start them first
+    const int tok0 = (q_tiles - 1 - rank) * TQ;               // later tokens see more keys: start them first
     if (tok0 >= q_len) return;
     const int ntok = min(TQ, q_len - tok0);
     const int q_start = a.seq_q_start[seq], pos0 = a.seq_pos_start[seq];
@@ -409,7 +414,7 @@ int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream)
         configured = true;
     }
     const int TQ = RT * BM / (a.nh / a.nkv);
-    const dim3 grid((max_q_len + TQ - 1) / TQ, a.nkv, n_seqs);
+    const dim3 grid(((max_q_len + TQ - 1) / TQ) * a.nkv * n_seqs);
     fb_launch((kern), grid, tc_threads(RT), (size_t)SM::BYTES, stream, a);
     return fb_check_launch("attention_tc");
 }
