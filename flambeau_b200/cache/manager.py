@@ -17,7 +17,10 @@ nothing), and given back
 The reference bounds windowed layers with ring slabs instead and rejects paged
 windowed attention (crates/forward/src/core/composites/standard_attn.rs:436-441).
 
-The manager, not the caller, owns each request's length.
+The manager, not the caller, owns each request's length.  The books themselves (pools, page lists, lengths,
+reservation, release, invariants) are kept by the C++ host code of the kernel library (`csrc/host_cache.cpp`,
+reached through `cache.pages.Books`); this module owns the device tensors, the grouping of layers and the
+request ids.
 """
 from __future__ import annotations
 
@@ -27,7 +30,7 @@ from typing import Optional
 import torch
 
 from ..parts.base import KVRequirement, StateRequirement
-from .pages import OutOfPages, PageError, PageList, PagePool
+from .pages import Books, OutOfPages, PageError
 
 
 @dataclass
@@ -50,20 +53,68 @@ class LayerCacheView:
     state: Optional[torch.Tensor] = None      # [slots, *shape] for mixers with fixed-size state
 
 
-@dataclass
+class PageView:
+    """The physical pages of one request in one group, by logical page index (-1 = given back)."""
+    __slots__ = ("_books", "_slot", "_group")
+
+    def __init__(self, books: Books, slot: int, group: int):
+        self._books, self._slot, self._group = books, slot, group
+
+    def __len__(self) -> int:
+        return self._books.n_pages_of(self._slot, self._group)
+
+    def __iter__(self):
+        return iter(self._books.pages(self._slot, self._group))
+
+    def __getitem__(self, i):
+        return self._books.pages(self._slot, self._group)[i]
+
+
 class RequestRecord:
-    request_id: object
-    slot: int
-    length: int = 0                           # tokens whose keys/state are in the cache
-    pages: list = field(default_factory=list)         # per group: list of physical page ids, -1 = given back
-    reserved_to: int = 0                      # positions [0, reserved_to) have pages (where still live)
+    """A live request as the books see it."""
+    __slots__ = ("request_id", "slot", "pages", "_books")
+
+    def __init__(self, request_id, slot: int, books: Books):
+        self.request_id, self.slot, self._books = request_id, slot, books
+        self.pages = [PageView(books, slot, g) for g in range(books.n_groups)]
+
+    @property
+    def length(self) -> int:                  # tokens whose keys/state are in the cache
+        return self._books.length(self.slot)
+
+    @property
+    def reserved_to(self) -> int:             # positions [0, reserved_to) have pages (where still live)
+        return self._books.reserved_to(self.slot)
+
+
+class PoolView:
+    """One group's page pool as the books see it."""
+
+    def __init__(self, books: Books, group: int):
+        self._books, self._group = books, group
+
+    @property
+    def n_pages(self) -> int:
+        return self._books.pool_pages(self._group)
+
+    @property
+    def n_free(self) -> int:
+        return self._books.free_pages()[self._group]
+
+    @property
+    def n_held(self) -> int:
+        return self.n_pages - self.n_free
+
+    def is_held(self, page: int) -> bool:
+        return self._books.is_held(self._group, page)
 
 
 class CacheGroup:
     def __init__(self, index: int, req: KVRequirement, owners: list, n_pages: int, page_size: int, device, dtype):
         self.index, self.req, self.owners = index, req, owners
         self.page_size = page_size
-        self.pool = PagePool(n_pages)
+        self.n_pages = n_pages
+        self.pool = None                      # a PoolView, set by the manager once the books exist
         shape = (n_pages, req.kv_heads, page_size, req.head_dim)
         # Zeroed once (the reference leaves its pools uninitialised, scratch.rs:546-573).  A key is always
         # written before any query can see it, but the tensor-core attention fetches whole pages, masked slots
@@ -112,7 +163,10 @@ class CacheManager:
             if plan.state is not None:
                 sd = dtype if plan.state.dtype == "engine" else getattr(torch, plan.state.dtype)
                 self.state[ci] = torch.zeros((self.max_requests, *plan.state.shape), dtype=sd, device=device)
-        self._free_slots = list(range(self.max_requests - 1, -1, -1))
+        self.books = Books([g.n_pages for g in self.groups], [g.req.window for g in self.groups], self.page_size,
+                           self.max_requests, self.max_pages_per_request)
+        for g in self.groups:
+            g.pool = PoolView(self.books, g.index)
         self.requests: dict[object, RequestRecord] = {}
 
     # ---- sizes -------------------------------------------------------------
@@ -127,21 +181,19 @@ class CacheManager:
         return sum(g.bytes_per_token() for g in self.groups)
 
     def free_pages(self) -> list:
-        return [g.pool.n_free for g in self.groups]
+        return self.books.free_pages()
 
     # ---- requests ----------------------------------------------------------
     def has_slot(self) -> bool:
-        return bool(self._free_slots)
+        return self.books.has_slot()
 
     def admit(self, request_id) -> RequestRecord:
         if request_id in self.requests:
             raise PageError(f"request {request_id!r} is already live")
-        if not self._free_slots:
-            raise PageError(f"all {self.max_requests} request slots are taken")
-        slot = self._free_slots.pop()
+        slot = self.books.admit()
         for t in self.state.values():
             t[slot].zero_()                      # a fresh request starts from zero state
-        rec = RequestRecord(request_id, slot, pages=[PageList() for _ in self.groups])
+        rec = RequestRecord(request_id, slot, self.books)
         self.requests[request_id] = rec
         return rec
 
@@ -150,81 +202,33 @@ class CacheManager:
 
     def pages_needed(self, request_id, n_new: int) -> list:
         """Pages each group would have to take so that `n_new` more tokens fit."""
-        rec = self.requests[request_id]
-        want = -(-(rec.length + n_new) // self.page_size)
-        return [max(0, want - len(rec.pages[g.index])) for g in self.groups]
+        return self.books.pages_needed(self.requests[request_id].slot, n_new)
 
     def can_reserve(self, needs: list) -> bool:
         """`needs` = list of (request_id, n_new) considered together."""
-        total = [0] * len(self.groups)
-        for rid, n_new in needs:
-            for gi, k in enumerate(self.pages_needed(rid, n_new)):
-                total[gi] += k
-        return all(total[gi] <= g.pool.n_free for gi, g in enumerate(self.groups))
+        return self.books.reserve_all([self.requests[rid].slot for rid, _ in needs], [k for _, k in needs],
+                                      dry_run=True)
 
     def reserve(self, request_id, n_new: int) -> None:
         """Take the pages for positions [length, length + n_new) in every group, or none at all."""
-        rec = self.requests[request_id]
-        end = rec.length + n_new
-        if end > self.max_pages_per_request * self.page_size:
-            raise PageError(f"request {request_id!r} would reach {end} tokens; the cache holds at most "
-                            f"{self.max_pages_per_request * self.page_size} per request")
-        needs = self.pages_needed(request_id, n_new)
-        for gi, g in enumerate(self.groups):
-            if needs[gi] > g.pool.n_free:
-                raise OutOfPages(needs[gi], g.pool.n_free, g.pool.n_pages)
-        for gi, g in enumerate(self.groups):
-            rec.pages[gi].extend(g.pool.take(needs[gi]))
-        rec.reserved_to = max(rec.reserved_to, end)
+        self.books.reserve_all([self.requests[request_id].slot], [n_new])
 
     def reserve_all(self, needs: list) -> None:
         """reserve() for several (request_id, n_new) at once: every request gets its pages, or none does."""
-        page, limit = self.page_size, self.max_pages_per_request * self.page_size
-        want = []
-        total = [0] * len(self.groups)
-        for rid, n_new in needs:
-            rec = self.requests[rid]
-            end = rec.length + n_new
-            if end > limit:
-                raise PageError(f"request {rid!r} would reach {end} tokens; the cache holds at most {limit} per request")
-            pages_to = -(-end // page)
-            row = [max(0, pages_to - len(rec.pages[gi])) for gi in range(len(self.groups))]
-            for gi, k in enumerate(row):
-                total[gi] += k
-            want.append((rec, end, row))
-        for gi, g in enumerate(self.groups):
-            if total[gi] > g.pool.n_free:
-                raise OutOfPages(total[gi], g.pool.n_free, g.pool.n_pages)
-        for rec, end, row in want:
-            for gi, k in enumerate(row):
-                if k:
-                    rec.pages[gi].extend(self.groups[gi].pool.take(k))
-            rec.reserved_to = max(rec.reserved_to, end)
+        self.books.reserve_all([self.requests[rid].slot for rid, _ in needs], [k for _, k in needs])
 
     def commit(self, request_id, n_new: int) -> None:
         """The step that wrote `n_new` tokens is launched: advance the length and give back the pages that
         no later query can see.  (Kernels of later steps run after this step's on the same stream, so a page
         that is reused is only overwritten after its last reader.)"""
-        rec = self.requests[request_id]
-        rec.length += n_new
-        if rec.length > rec.reserved_to:
-            raise PageError(f"request {request_id!r}: {rec.length} tokens committed, {rec.reserved_to} reserved")
-        for gi, g in enumerate(self.groups):
-            w = g.req.window
-            if w <= 0:
-                continue
-            first_live = rec.length - w + 1           # lowest position a future query can see
-            dead_pages = max(0, first_live) // self.page_size
-            back = rec.pages[gi].give_back_prefix(dead_pages)
-            if back:
-                g.pool.give_back(back)
+        self.books.commit([self.requests[request_id].slot], [n_new])
+
+    def commit_all(self, needs: list) -> None:
+        self.books.commit([self.requests[rid].slot for rid, _ in needs], [k for _, k in needs])
 
     def release(self, request_id) -> None:
         rec = self.requests.pop(request_id)
-        for gi, g in enumerate(self.groups):
-            g.pool.give_back(rec.pages[gi].live())
-            rec.pages[gi] = PageList()
-        self._free_slots.append(rec.slot)
+        self.books.release(rec.slot)
 
     def release_all(self) -> None:
         for rid in list(self.requests):
@@ -249,19 +253,8 @@ class CacheManager:
 
     # ---- invariants (used by tests) ------------------------------------------
     def check_invariants(self) -> None:
-        for gi, g in enumerate(self.groups):
-            seen = set()
-            for rec in self.requests.values():
-                for p in rec.pages[gi]:
-                    if p < 0:
-                        continue
-                    if p in seen:
-                        raise PageError(f"group {gi}: page {p} is held twice")
-                    if not g.pool.is_held(p):
-                        raise PageError(f"group {gi}: page {p} is in a table but free in the pool")
-                    seen.add(p)
-            if len(seen) != g.pool.n_held:
-                raise PageError(f"group {gi}: {g.pool.n_held} pages held in the pool, {len(seen)} in tables (lost pages)")
+        """No page lost, held twice or free while in a table; no slot held twice; the ids and the books agree."""
+        self.books.check_invariants()
         slots = [r.slot for r in self.requests.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
+        if len(set(slots)) != len(slots):
             raise PageError("a request slot is held twice")

@@ -1,9 +1,10 @@
 """The descriptor of one step: which rows, at which positions, of which
 sequences, against which pages, and which rows' logits are wanted.
 
-It is packed on the host into pinned buffers with a fixed layout and sent to
-the device in three copies (rows, sequences, block tables), once per step; no
-kernel of the step needs the host again.  The reference uploads positions and
+It is packed on the host (by the C++ host code of the kernel library) into
+pinned buffers with a fixed layout and sent to the device in three copies
+(rows, sequences, block tables), once per step; no kernel of the step needs
+the host again.  The reference uploads positions and
 slot tables inside every layer and syncs the stream there
 (crates/forward/src/core/composites/standard_attn.rs:315-329, 1133-1175).
 
@@ -14,8 +15,14 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import ctypes
+
 import numpy as np
 import torch
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(ctypes.c_void_p)
 
 
 @dataclass
@@ -67,75 +74,46 @@ class BatchBuffers:
         self.np_rows = self.h_rows.numpy()
         self.np_seqs = self.h_seqs.numpy()
         self.np_tables = self.h_tables.numpy()
-        self._fill = [[0] * max_seqs for _ in range(max(n_groups, 1))]     # valid entries last written per table row
+        self._fill = np.zeros((max(n_groups, 1), max_seqs), dtype=np.int32)   # valid entries last written per table row
+        self._info = np.zeros(4, dtype=np.int32)
+        from ..kernels.library import lib
+        self._lib = lib()
 
     def build(self, entries: list, cache, vocab_size: int) -> StepBatch:
-        """Validate the entries against the cache manager's records and pack them.
-        Pages for the new tokens must have been reserved already."""
+        """Validate the entries against the cache manager's books and pack them (in the C++ host code,
+        csrc/host_cache.cpp: fbh_build_step).  Pages for the new tokens must have been reserved already."""
         b = StepBatch()
         b.entries = entries
         S = len(entries)
         if not S:
             raise BatchError("a step needs at least one entry")
-        if S > self.max_seqs:
-            raise BatchError(f"{S} entries in one step; the engine was built for {self.max_seqs}")
         ids = [e.request_id for e in entries]
-        if len(set(ids)) != S:
-            raise BatchError("a request appears twice in one step")
         recs = [cache.requests[rid] for rid in ids]
-        q_len = [len(e.tokens) for e in entries]
-        if min(q_len) == 0:
-            raise BatchError("a request brings no tokens")
-        pos0 = [r.length for r in recs]
-        n = sum(q_len)
-        if n > self.max_tokens:
-            raise BatchError(f"the step has {n} tokens; the engine was built for {self.max_tokens} a step")
-        rows, seqs, tables = self.np_rows, self.np_seqs, self.np_tables
-        decode_only = n == S
-        if decode_only:
-            starts = list(range(S))
-            rows[0, :S] = [e.tokens[0] for e in entries]
-            rows[1, :S] = pos0
-            rows[2, :S] = starts
+        slots = np.fromiter((r.slot for r in recs), dtype=np.int32, count=S)
+        q_len = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=S)
+        n = int(q_len.sum())
+        if n == S:
+            tokens = np.fromiter((e.tokens[0] if e.tokens else 0 for e in entries), dtype=np.int64, count=S)
         else:
-            starts, acc = [], 0
-            for k in q_len:
-                starts.append(acc)
-                acc += k
-            rows[0, :n] = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
-            rows[1, :n] = np.concatenate([np.arange(p, p + k) for p, k in zip(pos0, q_len)])
-            rows[2, :n] = np.repeat(np.arange(S), q_len)
-        toks = rows[0, :n]
-        if int(toks.min()) < 0 or int(toks.max()) >= vocab_size:
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries]) if n else np.zeros(0, np.int64)
+        if tokens.size and (int(tokens.min()) < 0 or int(tokens.max()) >= vocab_size):
             raise BatchError(f"token id outside [0, {vocab_size})")
-        out_rows = []
-        for s, e in enumerate(entries):
-            if pos0[s] + q_len[s] > recs[s].reserved_to:
-                raise BatchError(f"request {e.request_id!r}: pages for positions up to {pos0[s] + q_len[s]} are not reserved")
-            for w in e.want:
-                if not 0 <= w < q_len[s]:
-                    raise BatchError(f"request {e.request_id!r}: wanted place {w} is outside its {q_len[s]} tokens")
-                out_rows.append(starts[s] + w)
-        n_out = len(out_rows)
-        if n_out:
-            rows[3, :n_out] = out_rows
-        seqs[0, :S], seqs[1, :S], seqs[2, :S] = starts, q_len, pos0
-        seqs[3, :S] = [r.slot for r in recs]
-        fill = self._fill
-        for gi in range(cache.n_groups):
-            for s, rec in enumerate(recs):
-                pages = rec.pages[gi]
-                k = pages.n
-                if k > self.max_pages:
-                    raise BatchError(f"request {ids[s]!r} holds {k} pages; tables have {self.max_pages}")
-                tables[gi, s, :k] = pages.arr[:k]
-                if fill[gi][s] > k:
-                    tables[gi, s, k:fill[gi][s]] = -1          # what an earlier step's request left in this row
-                fill[gi][s] = k
-        b.seq_q_start, b.seq_q_len, b.seq_pos_start = starts, q_len, pos0
-        b.seq_slot = [r.slot for r in recs]
-        b.max_q_len = max(q_len)
-        b.max_kv_len = max(p + k for p, k in zip(pos0, q_len))
+        tokens = tokens.astype(np.int32)
+        n_want = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=S)
+        wants = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=int(n_want.sum()))
+        info = self._info
+        code = self._lib.fbh_build_step(
+            cache.books.handle, S, _p(slots), _p(q_len), _p(tokens), _p(n_want), _p(wants), int(vocab_size),
+            self.max_tokens, self.max_seqs, self.max_pages, _p(self.np_rows), _p(self.np_seqs), _p(self.np_tables),
+            _p(self._fill), _p(info))
+        if code != 0:
+            raise BatchError(self._lib.fbh_last_error().decode(errors="replace"))
+        n, n_out = int(info[0]), int(info[1])
+        b.seq_q_start = self.np_seqs[0, :S].tolist()
+        b.seq_q_len = q_len.tolist()
+        b.seq_pos_start = self.np_seqs[2, :S].tolist()
+        b.seq_slot = slots.tolist()
+        b.max_q_len, b.max_kv_len = int(info[2]), int(info[3])
         b.n_tokens, b.n_seqs, b.n_out = n, S, n_out
         # ---- three copies to the device ----
         width = max(n, n_out)

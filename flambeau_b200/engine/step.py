@@ -256,8 +256,7 @@ class Engine:
             self._copied.record()
             self._copy_pending = True
             logits = self._run(batch)
-            for e in entries:
-                cache.commit(e.request_id, len(e.tokens))
+            cache.commit_all(needs)
             self.last_batch = batch
             self.steps_run += 1
         for rid in end:

@@ -46,12 +46,13 @@ def find_nvcc() -> str:
 
 
 def sources() -> list[Path]:
-    return sorted(CSRC.glob("*.cu"))
+    """The CUDA kernels (.cu) and the host-side C++ of the cache manager (.cpp, compiled by nvcc's host compiler)."""
+    return sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cpp")))
 
 
 def source_key() -> str:
     h = hashlib.sha256()
-    for p in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
+    for p in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cpp")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     h.update(" ".join(NVCC_FLAGS).encode())

@@ -42,6 +42,24 @@ _SIGNATURES = {
     "fb_apply_penalties": (I, [P, L, I, P, P, P, P, P, P, I, STREAM]),
     "fb_apply_logit_bias": (I, [P, L, I, P, P, P, I, STREAM]),
     "fb_sample": (I, [P, L, I, I, P, P, P, P, P, P, STREAM]),
+    # host side of the cache manager and of a step's descriptor (csrc/host_cache.cpp)
+    "fbh_last_error": (c_char_p, []),
+    "fbh_cache_new": (P, [I, P, P, I, I, I]),
+    "fbh_cache_free": (None, [P]),
+    "fbh_has_slot": (I, [P]),
+    "fbh_admit": (I, [P]),
+    "fbh_release": (I, [P, I]),
+    "fbh_length": (I, [P, I]),
+    "fbh_reserved_to": (I, [P, I]),
+    "fbh_free_pages": (I, [P, P]),
+    "fbh_pool_pages": (I, [P, I]),
+    "fbh_is_held": (I, [P, I, I]),
+    "fbh_pages_needed": (I, [P, I, I, P]),
+    "fbh_reserve_all": (I, [P, I, P, P, I]),
+    "fbh_commit": (I, [P, I, P, P]),
+    "fbh_pages": (I, [P, I, I, P, I]),
+    "fbh_check_invariants": (I, [P]),
+    "fbh_build_step": (I, [P, I, P, P, P, P, P, I, I, I, I, P, P, P, P, P]),
 }
 
 _LIB = None
