@@ -1,8 +1,10 @@
 """One layer with the layer sizes of the 7B shape (width 4096, 32 heads / 8 key-value heads of 128, inner 14336,
-vocabulary 32000) against the plain implementation: the shapes the serving kernels are tuned for (128-wide heads
-fetched page by page, 128 x 256 product tiles, split-K slabs), which the tiny configurations do not reach.  The
-window is shortened to 48 so that a 150-token request crosses it and gives pages back.  Weights are stored in
-bfloat16 except the norm weights, which are stored in float32 and must stay so in the bfloat16 engine."""
+vocabulary 32000) and one with those of the 12B shape (width 5120 with 32 heads of 128, so heads x head size is not
+the width; no window; rope base 1e6; a vocabulary that is no multiple of the product's tiles) against the plain
+implementation: the shapes the serving kernels are tuned for (128-wide heads fetched page by page, 128 x 256 product
+tiles, split-K slabs), which the tiny configurations do not reach.  The 7B layer's window is shortened to 48 so
+that a 150-token request crosses it and gives pages back.  Weights are stored in bfloat16 except the norm weights,
+which are stored in float32 and must stay so in the bfloat16 engine."""
 import pytest
 import torch
 
@@ -11,13 +13,19 @@ import tiny
 
 pytestmark = pytest.mark.gpu
 
-CONFIG = dict(architectures=["MistralForCausalLM"], hidden_size=4096, num_hidden_layers=1, num_attention_heads=32,
-              num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=32000, rope_theta=10000.0,
-              sliding_window=48, rms_norm_eps=1e-5, tie_word_embeddings=False, hidden_act="silu")
+CONFIGS = {
+    "7b": dict(architectures=["MistralForCausalLM"], hidden_size=4096, num_hidden_layers=1, num_attention_heads=32,
+               num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=32000, rope_theta=10000.0,
+               sliding_window=48, rms_norm_eps=1e-5, tie_word_embeddings=False, hidden_act="silu"),
+    "12b": dict(architectures=["MistralForCausalLM"], hidden_size=5120, num_hidden_layers=1, num_attention_heads=32,
+                num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=40010, rope_theta=1e6,
+                sliding_window=None, rms_norm_eps=1e-5, tie_word_embeddings=False, hidden_act="silu"),
+}
 
 
-@pytest.fixture(scope="module")
-def big(tmp_path_factory):
+@pytest.fixture(scope="module", params=list(CONFIGS))
+def big(request, tmp_path_factory):
+    CONFIG = CONFIGS[request.param]
     from flambeau_b200.config.mistral import MistralConfig
     from flambeau_b200.weights.random_init import write_random_model
     folder = tmp_path_factory.mktemp("layer7b")
@@ -26,7 +34,7 @@ def big(tmp_path_factory):
     pcfg, W = pm.read_model_folder(folder)
     requests = tiny.random_requests(CONFIG, [150, 70], seed=2)
     want = {rid: pm.forward_logits(pcfg, W, toks) for rid, toks in requests.items()}
-    return dict(folder=folder, requests=requests, want=want)
+    return dict(folder=folder, requests=requests, want=want, config=CONFIG, name=request.param)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -54,5 +62,5 @@ def test_layer_of_the_7b_shape(big, dtype, tmp_path):
     replay(engine, sched.lines(), tmp_path)
     engine.cache.check_invariants()
     assert not engine.cache.requests
-    got = tiny.read_rows(tmp_path, sched, CONFIG["vocab_size"])
-    tiny.compare_rows(got, big["want"], tiny.TOL[dtype], f"7B layer sizes {dtype}")
+    got = tiny.read_rows(tmp_path, sched, big["config"]["vocab_size"])
+    tiny.compare_rows(got, big["want"], tiny.TOL[dtype], f"{big['name']} layer sizes {dtype}")
