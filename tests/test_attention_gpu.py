@@ -255,3 +255,27 @@ def test_hundreds_of_decoded_sequences_in_one_step():
     seqs = [(rnd.randrange(0, 150), 1) for _ in range(300)]
     check(Scene(seqs, 8, 4, 64, 0, torch.bfloat16, page_size=16, seed=9), "mma")
     check(Scene(seqs[:130], 4, 4, 128, 40, torch.bfloat16, page_size=8, seed=10), "mma")
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_geometries_and_mixes(seed):
+    """Seeded random scenes: head sizes in steps of 8 and 16, any grouping, page sizes that do and do not tile a
+    key tile, windows, and mixes of long portions, short portions and decoded tokens, on the bfloat16 kernels."""
+    rnd = random.Random(1000 + seed)
+    hd = rnd.choice([16, 24, 32, 40, 48, 64, 64, 80, 96, 128, 128, 128, 160, 256])
+    nkv = rnd.choice([1, 2, 3, 4, 8])
+    G = rnd.choice([1, 2, 3, 4, 7, 8, 16])
+    page_size = rnd.choice([8, 16, 16, 32, 64, 24, 48])
+    window = rnd.choice([0, 0, 17, 64, 300])
+    seqs = []
+    for _ in range(rnd.randrange(1, 7)):
+        kind = rnd.random()
+        if kind < 0.4:
+            seqs.append((rnd.randrange(0, 1200), 1))                          # a decoded token
+        elif kind < 0.6:
+            seqs.append((rnd.randrange(0, 600), rnd.randrange(2, 6)))         # a portion of a few tokens
+        else:
+            seqs.append((rnd.choice([0, 0, rnd.randrange(1, 700)]), rnd.randrange(6, 400)))   # a long portion
+    if hd * nkv * G > 8192:
+        nkv = 1
+    check(Scene(seqs, nkv * G, nkv, hd, window, torch.bfloat16, page_size=page_size, seed=seed), "mma")
