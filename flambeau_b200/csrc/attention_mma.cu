@@ -4,8 +4,10 @@
 // A CTA owns one key/value head and a tile of up to 128 query rows = (128 / G) tokens x the G query heads that
 // share the head, so every K/V tile is read once for the whole group.  Its four warps take 32 rows each (16 for
 // heads wider than 128), so that every K/V fragment fetched from shared memory feeds two row blocks; each walks
-// all visible key tiles with an online softmax.  Sequences of a step with at most 16 rows (decoded tokens, portions
-// of a few tokens) go to the split-key arrangement instead (attention_split.cu).
+// all visible key tiles with an online softmax.  CTAs are numbered heaviest first over all heads and sequences.
+// Sequences of a step with at most 16 rows (decoded tokens, portions of a few tokens) go to the split-key
+// arrangement instead (attention_split.cu); heads of 64 and 128 with pages that tile 64 keys go to the tcgen05
+// kernel (attention_tc.cu) unless that is switched off.
 //
 // Keys and values come through the block table in tiles of 64 keys through a two-stage pipeline: whole pages by
 // tensor-map copies (128-byte swizzle) when a tile is a whole number of pages and the head a whole number of

@@ -2,17 +2,20 @@
 // tensor cores (mma.sync m16n8k16, float32 accumulation and softmax): the split-key arrangement.
 //
 // All key tiles of all (sequence, key/value head) pairs form one line, pair after pair (pairs of one sequence side
-// by side), and the CTAs of the launch cut that line into equal stretches: CTA c owns tiles [c * per, (c + 1) * per).  A stretch may end inside a pair and go on into the next ones, so every CTA has the
-// same amount of cache to stream whatever the number and the lengths of the sequences.  Each (CTA, pair) segment
-// of a pair that is cut leaves a partial result in slot (CTA index + pair index), which is unique and needs no
-// table, and counts itself on the pair; the CTA that arrives last adds the pair's segments, in their order.
+// by side), and the CTAs of the launch cut that line into equal stretches: CTA c owns tiles [c * per, (c + 1) * per).
+// A stretch may end inside a pair and go on into the next ones, so every CTA has the same amount of cache to stream
+// whatever the number and the lengths of the sequences.  Each (CTA, pair) segment of a pair that is cut leaves a
+// partial result in slot (CTA index + pair index), which is unique and needs no table, and counts itself on the
+// pair; the CTA that arrives last adds the pair's segments, in their order.
 //
 // One warp fetches, four warps score.  The fetching warp walks the CTA's stretch of key tiles, segment after
 // segment, and keeps NST tiles in flight (page ids looked up one tile ahead, a tile's slot refilled as soon as its
-// four readers have left it), so the stream of cache never stops at a tile's or a segment's end.  Each scoring warp takes 16 of a tile's 64 keys and
-// keeps its own running maximum, sum and output for the segment's rows; nothing synchronises the four between
-// tiles.  At a segment's end the four are added up in shared memory; where a pair was cut, the sum goes to scratch
-// and the CTA that arrives last at the pair adds the partials of all its segments, in their order.
+// four readers have left it), so the stream of cache never stops at a tile's or a segment's end; when the stretch
+// is through, it fetches its share of the start of the next product's weights into L2, if the caller said which.
+// Each scoring warp takes 16 of a tile's 64 keys and keeps its own running maximum, sum and output for the
+// segment's rows; nothing synchronises the four between tiles.  At a segment's end the four are added up in shared
+// memory; where a pair was cut, the sum goes to scratch and the CTA that arrives last at the pair adds the partials
+// of all its segments, in their order.
 //
 // Keys and values come through the block table in tiles of 64 keys: whole pages by tensor-map copies (128-byte
 // swizzle) when a tile is a whole number of pages and the head a whole number of 64-column blocks, single rows by

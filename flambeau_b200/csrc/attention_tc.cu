@@ -1,23 +1,26 @@
 // Paged causal (sliding-window) attention for portions of prompts on the 5th-generation tensor cores
-// (tcgen05.mma, accumulators in tensor memory), for heads of 64 or 128 bfloat16 and pages that tile 128 keys.
+// (tcgen05.mma, accumulators in tensor memory), for heads of 64 or 128 bfloat16 and pages that tile 64 keys.
 //
 // A CTA owns one key/value head and 256 query rows = (256 / G) tokens x the G query heads that share the head, as
-// two row tiles of 128 that use every K/V tile fetched, and walks the visible keys in tiles of 128:
+// two row tiles of 128 that use every K/V tile fetched (one row tile when two would leave SMs without work), and
+// walks the visible keys in tiles of 64.  CTAs are numbered heaviest first over all heads and sequences.
 //
-//   S = Q K^T      tcgen05.mma, Q and K K-major in shared memory (128-byte swizzle), S in tensor memory, one
-//                  buffer per row tile (the tensor pipe works for one row tile under the softmax of the other);
-//   softmax        256 threads, one per row (the row = its tensor-memory lane): tcgen05.ld of the scores in two
-//                  passes (maximum; exponentials), base-2 online softmax in float32, P rounded to bfloat16 and
-//                  stored with tcgen05.st over the scores it came from;
+//   S = Q K^T      tcgen05.mma, Q and K K-major in shared memory (128-byte swizzle), S in tensor memory, two
+//                  buffers per row tile: the scores run two key tiles ahead of the softmax;
+//   softmax        one thread per row (the row = its tensor-memory lane): the row's 64 scores in one tcgen05.ld
+//                  round trip, base-2 online softmax in float32, P rounded to bfloat16 and stored with tcgen05.st
+//                  over the scores it came from;
 //   O += P V       tcgen05.mma with P read from tensor memory and V as it lies in the cache ([key][dim], the
 //                  MN-major operand); O in tensor memory.
 //
 // O is rescaled only when a row's maximum has grown by more than 2^8 since the exponentials' reference point was
 // last moved (the sum l is kept against the same reference, so O / l is exact either way); the first tile sets
-// the reference.  Warps: 0 fetches K and V pages with tensor-map copies through two-slot rings, 1 owns tensor
-// memory and issues the MMAs, 2..5 and 6..9 are the softmax of the two row tiles (a warp reads the quarter of the
-// lanes given by its index modulo 4).  Every wait is bounded in time; when one runs out the kernel flags it,
-// leaves its loops, frees its tensor memory and returns.
+// the reference.  Warps: 0 fetches K and V pages with tensor-map copies through four-slot rings of their own (page
+// ids read from the block table 32 at a time), 1 owns tensor memory and issues the MMAs, 2..5 and 6..9 are the
+// softmax of the two row tiles (a warp reads the quarter of the lanes given by its index modulo 4).  A wait names a
+// phase of an mbarrier only by its parity, so every barrier here is waited on for the phase that is current or
+// just completed: one barrier per buffer, and one of its own for the last product.  Every wait is bounded in
+// time; when one runs out the kernel flags it, leaves its loops, frees its tensor memory and returns.
 //
 // Formulas: crates/kernels-hip/src/kernels/attention_prefill_flash_tile_f16.cu:73-213 (tile + online softmax).
 #include "attention_common.cuh"
