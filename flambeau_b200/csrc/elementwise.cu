@@ -95,7 +95,8 @@ template <> struct Vec4<__nv_bfloat16> {
 };
 
 template <typename TD, typename TW, typename TO, int VPT>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_partials,
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_partials,
                                        size_t partial_stride, const TW* __restrict__ w, TO* __restrict__ out,
                                        const int* __restrict__ rows, int H, float eps) {
     fb_pdl_launch_dependents();
@@ -161,12 +162,80 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restri
     }
 }
 
+// Many rows with one delta each (a prompt's portion): R rows per CTA and V vectors per thread and row, every
+// load of the CTA's rows issued before the first use.  One row per CTA leaves too few loads in flight to fill
+// the memory pipe when each thread has only one vector of the row.
+template <typename TD, typename TW, typename TO, int R, int V>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta, const TW* __restrict__ w,
+                        TO* __restrict__ out, int n, int H, float eps) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    __shared__ float red[R][32];
+    const int r0 = R * blockIdx.x;
+    float4 a[R][V], d[R][V], wv[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) wv[v] = Vec4<TW>::load(w + 4 * (threadIdx.x + v * blockDim.x));
+#pragma unroll
+    for (int r = 0; r < R; ++r)                     // a row past the end reads the last row again and stores nothing
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            const size_t at = (size_t)min(r0 + r, n - 1) * H + 4 * (threadIdx.x + v * blockDim.x);
+            a[r][v] = Vec4<float>::load(x + at);
+            d[r][v] = Vec4<TD>::load(delta + at);
+        }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            a[r][v].x += d[r][v].x; a[r][v].y += d[r][v].y; a[r][v].z += d[r][v].z; a[r][v].w += d[r][v].w;
+            if (r0 + r < n) Vec4<float>::store(x + (size_t)(r0 + r) * H + 4 * (threadIdx.x + v * blockDim.x), a[r][v]);
+        }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float ss[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        float s = 0.0f;
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+            s += a[r][v].x * a[r][v].x + a[r][v].y * a[r][v].y + a[r][v].z * a[r][v].z + a[r][v].w * a[r][v].w;
+        s = fb_warp_sum(s);
+        if (lane == 0) red[r][warp] = s;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        float s = lane < nw ? red[r][lane] : 0.0f;
+        ss[r] = fb_warp_sum(s);
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        if (r0 + r >= n) break;
+        const float inv = 1.0f / sqrtf(ss[r] / (float)H + eps);
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+            Vec4<TO>::store(out + (size_t)(r0 + r) * H + 4 * (threadIdx.x + v * blockDim.x),
+                            make_float4(a[r][v].x * wv[v].x * inv, a[r][v].y * wv[v].y * inv,
+                                        a[r][v].z * wv[v].z * inv, a[r][v].w * wv[v].w * inv));
+    }
+}
+
 template <typename TD, typename TW, typename TO>
 static int launch_add_rmsnorm(float* x, const void* delta, int n_partials, size_t partial_stride,
                               const void* w, void* out, const int* rows, int n_out, int H, float eps,
                               cudaStream_t stream) {
     const bool aligned = H % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
                          ((uintptr_t)out % 16 == 0) && (!delta || ((uintptr_t)delta % 16 == 0 && partial_stride % 4 == 0));
+    const int nvec4 = H / 4, per_thread = (nvec4 + 1023) / 1024;
+    if (aligned && delta && !rows && n_partials == 1 && n_out > 256 && per_thread <= 2 && nvec4 % (32 * per_thread) == 0) {
+        const int threads = nvec4 / per_thread;
+#define FB_NORM_ROWS(R_, V_)                                                                                  \
+        fb_launch((add_rmsnorm_rows_kernel<TD, TW, TO, R_, V_>), (n_out + R_ - 1) / R_, threads, 0, stream, x, \
+                  (const TD*)delta, (const TW*)w, (TO*)out, n_out, H, eps)
+        if (per_thread == 2) FB_NORM_ROWS(1, 2); else if (nvec4 <= 256) FB_NORM_ROWS(4, 1); else FB_NORM_ROWS(2, 1);
+#undef FB_NORM_ROWS
+        return fb_check_launch("add_rmsnorm");
+    }
     if (aligned && H <= 16384) {
         const int nvec = H / 4;
         int threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;

@@ -100,6 +100,27 @@ def test_add_rms_norm_few_wide_rows(n, H, P, od):
     close(out2, pm.rms_norm(x1.double()[rows.long()], w.double(), eps), 3e-6 if od == "f" else 6e-3)
 
 
+@pytest.mark.parametrize("n,H", [(257, 128), (300, 1024), (513, 4096), (258, 5120), (259, 8192), (260, 4100), (261, 9216)])
+@pytest.mark.parametrize("dd,od", [("f", "f"), ("f", "b"), ("b", "b")])
+def test_add_rms_norm_many_rows(n, H, dd, od):
+    """A prompt's portion: hundreds of rows with one delta each, at widths that take each of the kernel's forms
+    (several rows per block, two vectors per thread, and the widths that neither takes), with an odd row count."""
+    from flambeau_b200.kernels import ops
+    eps = 1e-5
+    g = torch.Generator(device=DEV).manual_seed(n + H)
+    x = torch.randn(n, H, device=DEV, generator=g)
+    x[n - 1] *= 7.0                                              # the last row stands out: a block that took its
+    x[n - 2] *= 0.01                                             # neighbour's sum of squares would show
+    delta = (torch.randn(n, H, device=DEV, generator=g) * 0.5).to(DT[dd])
+    w = (1 + 0.1 * torch.randn(H, device=DEV, generator=g)).to(DT[od])
+    out = torch.empty(n, H, device=DEV, dtype=DT[od])
+    x0 = x.clone()
+    ops.add_rms_norm(x, delta, w, eps, out)
+    v = x0.double() + delta.double()
+    close(x, v, 1e-6)
+    close(out, pm.rms_norm(v, w.double(), eps), 3e-6 if od == "f" else 6e-3)
+
+
 @pytest.mark.parametrize("half,theta", [(8, 1e4), (12, 1e6), (64, 1e4)])
 def test_rope_table_is_right_at_far_positions(half, theta):
     from flambeau_b200.kernels import ops
