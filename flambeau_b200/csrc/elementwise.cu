@@ -401,18 +401,21 @@ __device__ __forceinline__ float4 slab_sum4(const TI* __restrict__ p, int n_part
     return acc;
 }
 
-template <typename TI, typename T>
+// TOK tokens per thread (the same item of each): every load of the thread's tokens is issued before the first
+// use, which is what fills the memory pipe when a prompt's portion brings thousands of tokens.  A token past the
+// end reads the last token again and stores nothing.
+template <typename TI, typename T, int TOK>
 __global__ void __launch_bounds__(256)
 rope_kv_write_vec_kernel(const TI* __restrict__ q_in, long q_in_stride, int n_partials, long partial_stride,
                          T* __restrict__ q_out, long q_out_stride, const TI* __restrict__ k, long k_stride,
                          const TI* __restrict__ v, long v_stride, const float* __restrict__ cos_t,
                          const float* __restrict__ sin_t, int half, const int* __restrict__ positions,
                          const int* __restrict__ row_seq, const int* __restrict__ block_table, int table_stride,
-                         T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size, int n_pages, int nh, int nkv,
-                         int hd, int write_kv, int* status) {
+                         T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size, int n_pages, int n, int nh,
+                         int nkv, int hd, int write_kv, int* status) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
-    const int t = blockIdx.x;
+    const int t0 = blockIdx.x * TOK;
     const int per_head = (hd - half) >> 2;                  // items per head
     const int rot_items = half >> 2;
     const int q_items = nh * per_head, k_items = write_kv ? nkv * per_head : 0;
@@ -420,42 +423,82 @@ rope_kv_write_vec_kernel(const TI* __restrict__ q_in, long q_in_stride, int n_pa
     const int item = blockIdx.y * blockDim.x + threadIdx.x;
     if (item >= q_items + k_items + v_items) return;
 
-    size_t cache_row = 0;
+    int tok[TOK];
+    bool live[TOK];
+    size_t cache_row[TOK];
+#pragma unroll
+    for (int i = 0; i < TOK; ++i) {
+        live[i] = t0 + i < n;
+        tok[i] = min(t0 + i, n - 1);
+        cache_row[i] = 0;
+    }
     if (item >= q_items) {
-        const int pos = positions[t];
-        const int page = block_table[(size_t)row_seq[t] * table_stride + pos / page_size];
-        if (page < 0 || page >= n_pages) {
-            atomicOr(status, FB_STATUS_BAD_PAGE);
-            return;
+        int pos[TOK], page[TOK];
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) pos[i] = positions[tok[i]];
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) page[i] = block_table[(size_t)row_seq[tok[i]] * table_stride + pos[i] / page_size];
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) {
+            if (page[i] < 0 || page[i] >= n_pages) {
+                if (live[i]) atomicOr(status, FB_STATUS_BAD_PAGE);
+                live[i] = false;
+                page[i] = 0;
+            }
+            cache_row[i] = ((size_t)page[i] * nkv) * page_size + (pos[i] % page_size);   // + head * page_size below
         }
-        cache_row = ((size_t)page * nkv) * page_size + (pos % page_size);     // + head * page_size below
     }
     if (item >= q_items + k_items) {
         const int idx = item - q_items - k_items;
         const int h = idx / (hd >> 2), d = (idx - h * (hd >> 2)) << 2;
-        const float4 val = slab_sum4(v + (size_t)t * v_stride + (size_t)h * hd + d, n_partials, partial_stride);
-        Vec4<T>::store(v_pool + (cache_row + (size_t)h * page_size) * hd + d, val);
+        float4 val[TOK];
+#pragma unroll
+        for (int i = 0; i < TOK; ++i)
+            val[i] = slab_sum4(v + (size_t)tok[i] * v_stride + (size_t)h * hd + d, n_partials, partial_stride);
+#pragma unroll
+        for (int i = 0; i < TOK; ++i)
+            if (live[i]) Vec4<T>::store(v_pool + (cache_row[i] + (size_t)h * page_size) * hd + d, val[i]);
         return;
     }
     const bool is_q = item < q_items;
     const int idx = is_q ? item : item - q_items;
     const int h = idx / per_head, j = idx - h * per_head;
-    const TI* src = is_q ? q_in + (size_t)t * q_in_stride + (size_t)h * hd : k + (size_t)t * k_stride + (size_t)h * hd;
-    T* dst = is_q ? q_out + (size_t)t * q_out_stride + (size_t)h * hd
-                  : k_pool + (cache_row + (size_t)h * page_size) * hd;
+    const TI* src = is_q ? q_in + (size_t)h * hd : k + (size_t)h * hd;
+    const long src_stride = is_q ? q_in_stride : k_stride;
     if (j < rot_items) {
         const int d = j << 2;
-        const float4 a = slab_sum4(src + d, n_partials, partial_stride);
-        const float4 b = slab_sum4(src + d + half, n_partials, partial_stride);
-        const float4 c = *reinterpret_cast<const float4*>(cos_t + (size_t)t * half + d);
-        const float4 sn = *reinterpret_cast<const float4*>(sin_t + (size_t)t * half + d);
-        Vec4<T>::store(dst + d, make_float4(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y,
-                                            a.z * c.z - b.z * sn.z, a.w * c.w - b.w * sn.w));
-        Vec4<T>::store(dst + d + half, make_float4(a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y,
-                                                   a.z * sn.z + b.z * c.z, a.w * sn.w + b.w * c.w));
+        float4 a[TOK], b[TOK], c[TOK], sn[TOK];
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) {
+            const TI* row = src + (size_t)tok[i] * src_stride;
+            a[i] = slab_sum4(row + d, n_partials, partial_stride);
+            b[i] = slab_sum4(row + d + half, n_partials, partial_stride);
+            c[i] = *reinterpret_cast<const float4*>(cos_t + (size_t)tok[i] * half + d);
+            sn[i] = *reinterpret_cast<const float4*>(sin_t + (size_t)tok[i] * half + d);
+        }
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) {
+            if (!live[i]) continue;
+            T* dst = is_q ? q_out + (size_t)tok[i] * q_out_stride + (size_t)h * hd
+                          : k_pool + (cache_row[i] + (size_t)h * page_size) * hd;
+            Vec4<T>::store(dst + d, make_float4(a[i].x * c[i].x - b[i].x * sn[i].x, a[i].y * c[i].y - b[i].y * sn[i].y,
+                                                a[i].z * c[i].z - b[i].z * sn[i].z, a[i].w * c[i].w - b[i].w * sn[i].w));
+            Vec4<T>::store(dst + d + half,
+                           make_float4(a[i].x * sn[i].x + b[i].x * c[i].x, a[i].y * sn[i].y + b[i].y * c[i].y,
+                                       a[i].z * sn[i].z + b[i].z * c[i].z, a[i].w * sn[i].w + b[i].w * c[i].w));
+        }
     } else {
         const int d = 2 * half + ((j - rot_items) << 2);     // untouched dimensions behind the rotary part
-        Vec4<T>::store(dst + d, slab_sum4(src + d, n_partials, partial_stride));
+        float4 val[TOK];
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) val[i] = slab_sum4(src + (size_t)tok[i] * src_stride + d, n_partials, partial_stride);
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) {
+            if (!live[i]) continue;
+            T* dst = is_q ? q_out + (size_t)tok[i] * q_out_stride + (size_t)h * hd
+                          : k_pool + (cache_row[i] + (size_t)h * page_size) * hd;
+            Vec4<T>::store(dst + d, val[i]);
+        }
     }
 }
 
@@ -486,12 +529,16 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, int n_parti
                      k_stride % 4 == 0 && v_stride % 4 == 0 && partial_stride % 4 == 0 && q_in != q_out;
     if (vec) {
         const int items = (nh + (write_kv ? nkv : 0)) * ((hd - half) / 4) + (write_kv ? nkv * (hd / 4) : 0);
-        const dim3 grid(n, (items + 255) / 256);
-        FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
-            (fb_launch((rope_kv_write_vec_kernel<TI, T>), grid, 256, 0, stream, (const TI*)q_in, (long)q_in_stride,
-                n_partials, (long)partial_stride, (T*)q_out, (long)q_out_stride, (const TI*)k, (long)k_stride,
-                (const TI*)v, (long)v_stride, cos_t, sin_t, half, positions, row_seq, block_table, table_stride,
-                (T*)k_pool, (T*)v_pool, page_size, n_pages, nh, nkv, hd, write_kv, status))));
+        const int per = n >= 1024 ? 2 : 1;             // tokens per thread
+#define FB_ROPE_VEC(TOK_)                                                                                     \
+        FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,                                       \
+            (fb_launch((rope_kv_write_vec_kernel<TI, T, TOK_>), dim3((n + TOK_ - 1) / TOK_, (items + 255) / 256), 256, \
+                0, stream, (const TI*)q_in, (long)q_in_stride, n_partials, (long)partial_stride, (T*)q_out,   \
+                (long)q_out_stride, (const TI*)k, (long)k_stride, (const TI*)v, (long)v_stride, cos_t, sin_t, \
+                half, positions, row_seq, block_table, table_stride, (T*)k_pool, (T*)v_pool, page_size,       \
+                n_pages, n, nh, nkv, hd, write_kv, status))))
+        if (per == 2) FB_ROPE_VEC(2); else FB_ROPE_VEC(1);
+#undef FB_ROPE_VEC
         return fb_check_launch("rope_kv_write");
     }
     FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,

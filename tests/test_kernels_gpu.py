@@ -178,6 +178,48 @@ def test_rope_and_cache_write(nh, nkv, hd, rot, dt_in, dt_out, slabs):
     assert int((kp.float().abs().sum(dim=(1, 3)) > 0).sum()) == written, "only the rows of the step are written"
 
 
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(3, 3, 40, 16), (32, 8, 128, 128)])
+@pytest.mark.parametrize("dt_out", ["f", "b"])
+def test_rope_and_cache_write_of_a_long_portion(nh, nkv, hd, rot, dt_out):
+    """Over a thousand tokens in one call (an odd count, three sequences, pages in a shuffled order): the form of
+    the kernel that takes several tokens per thread."""
+    from flambeau_b200.kernels import ops
+    ps, theta = 8, 1e4
+    lens = [700, 3, 326]
+    starts = [5, 0, 1000]
+    n = sum(lens)
+    half = rot // 2
+    g = torch.Generator(device=DEV).manual_seed(nh * hd)
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(n, width, device=DEV, generator=g)
+    positions = torch.cat([torch.arange(s, s + l) for s, l in zip(starts, lens)]).int().to(DEV)
+    row_seq = torch.cat([torch.full((l,), i) for i, l in enumerate(lens)]).int().to(DEV)
+    per_seq = max(-(-(s + l) // ps) for s, l in zip(starts, lens))
+    n_pages = 3 * per_seq
+    table = torch.randperm(n_pages, device=DEV, generator=g).int().view(3, per_seq)
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / rot)
+    cos = torch.empty(n, half, device=DEV)
+    sin = torch.empty(n, half, device=DEV)
+    ops.rope_table(positions, inv.to(DEV), cos, sin)
+    kp = torch.zeros(n_pages, nkv, ps, hd, device=DEV, dtype=DT[dt_out])
+    vp = torch.zeros_like(kp)
+    q_out = torch.empty(n, nh * hd, device=DEV, dtype=DT[dt_out])
+    st = status()
+    ops.rope_kv_write(qkv[:, :nh * hd], q_out, qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:], cos, sin,
+                      half, positions, row_seq, table, kp, vp, ps, nh, nkv, hd, True, st)
+    assert int(st.item()) == 0
+    q = qkv[:, :nh * hd].reshape(n, nh, hd).double().cpu()
+    k = qkv[:, nh * hd:(nh + nkv) * hd].reshape(n, nkv, hd).double().cpu()
+    v = qkv[:, (nh + nkv) * hd:].reshape(n, nkv, hd).double().cpu()
+    tol = 2e-6 if dt_out == "f" else 5e-3
+    close(q_out.reshape(n, nh, hd), pm.rope_split_half(q, positions.cpu(), theta, rot), tol)
+    page = table.cpu().long()[row_seq.cpu().long(), (positions.cpu() // ps).long()]
+    slot = (positions.cpu() % ps).long()
+    close(kp.cpu()[page, :, slot], pm.rope_split_half(k, positions.cpu(), theta, rot), tol)
+    close(vp.cpu()[page, :, slot], v, tol)
+    assert int((kp.float().abs().sum(dim=(1, 3)) > 0).sum()) == n, "only the rows of the step are written"
+
+
 def test_cache_write_flags_a_missing_page():
     from flambeau_b200.kernels import ops
     qkv = torch.randn(2, 4 * 16, device=DEV)
