@@ -37,7 +37,7 @@ def test_embedding(V, H, dt):
     assert int(st.item()) == 1, "an id outside the table must be flagged"
 
 
-@pytest.mark.parametrize("H", [8, 100, 96, 4096, 5120, 6000, 20000])
+@pytest.mark.parametrize("H", [8, 100, 96, 4096, 5120, 6000, 9216, 12288, 16384, 20000])
 @pytest.mark.parametrize("dd,wd,od", ["fff", "fbb", "ffb", "bbb"])
 def test_add_rms_norm(H, dd, wd, od):
     from flambeau_b200.kernels import ops
