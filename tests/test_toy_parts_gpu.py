@@ -1,6 +1,6 @@
 """Generality of the parts framework, shown with toy parts that are defined here and never become a model:
-a mixer with state of its own (no keys or values), a position encoding with a rotate() of its own, a run order
-that names a layer twice and lets a call read another call's cache.  They are registered, built, loaded from a
+a mixer with state of its own (no keys or values), a feed-forward that routes each token to two of four experts,
+a position encoding with a rotate() of its own, a run order that names a layer twice and lets a call read another call's cache.  They are registered, built, loaded from a
 random model folder and stepped through the engine (whole, in portions, mixed with page reuse, decoded one by
 one) without a change to the framework's files, and compared with a plain computation written here."""
 import json
@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 # ---- toy parts ---------------------------------------------------------------------------------------------------
 
 def toy_parts():
-    from flambeau_b200.parts.base import Mixer, PositionEncoding, StateRequirement, TensorSpec
+    from flambeau_b200.parts.base import FeedForward, Mixer, PositionEncoding, StateRequirement, TensorSpec
 
     class DecayMixer(Mixer):
         """s_t = a * s_{t-1} + (1 - a) * h_t, out_t = s_t * w: a running average per request, kept in the
@@ -73,7 +73,45 @@ def toy_parts():
                 x[..., 1::2] = even * s + odd * c
                 t.copy_(x.reshape(n, -1).to(t.dtype))
 
-    return DecayMixer, ShiftedRotary
+    class RoutedFeedForward(FeedForward):
+        """Each token goes to the two experts with the largest router logits; an expert's weight is its logit's
+        lead over the third-largest over (1 + the sum of both leads), so it falls to zero as the expert leaves the top two and the
+        output is continuous in the input.  Experts are relu(h Up^T) Down^T.  Router logits in float32."""
+
+        def __init__(self, runtime=None, prefix="", *, width: int, inner: int, experts: int):
+            super().__init__(runtime, prefix)
+            self.width, self.inner, self.experts = width, inner, experts
+            self.router = self.up = self.down = None
+
+        def own_tensor_specs(self):
+            p, E = self.prefix, self.experts
+            return {p + "router": TensorSpec((E, self.width), init=("normal", 0.3)),
+                    p + "up": TensorSpec((E, self.inner, self.width), init=("normal", 0.2)),
+                    p + "down": TensorSpec((E, self.width, self.inner), init=("normal", 0.2))}
+
+        def own_bind(self, tensors):
+            p = self.prefix
+            self.router, self.up, self.down = tensors[p + "router"], tensors[p + "up"], tensors[p + "down"]
+
+        def forward(self, ctx, h, out):
+            n = ctx.n_tokens
+            x = h[:n].float()
+            weights = routing_weights(x @ self.router.float().T)
+            out[:n].zero_()
+            for e in range(self.experts):
+                rows = (weights[:, e] > 0).nonzero().flatten()             # only the tokens routed here
+                if rows.numel():
+                    a = torch.relu(x[rows] @ self.up[e].float().T)
+                    out[rows] += weights[rows, e:e + 1] * (a @ self.down[e].float().T)
+
+    return DecayMixer, ShiftedRotary, RoutedFeedForward
+
+
+def routing_weights(logits):
+    """[n, E] router logits -> [n, E] weights, zero outside each row's top two."""
+    third = logits.topk(3, dim=-1).values[:, 2:3]
+    lead = (logits - third).clamp_min(0)
+    return lead / (lead.sum(-1, keepdim=True) + 1.0)          # + 1: small leads give small weights, not a 0/0
 
 
 @dataclass(frozen=True)
@@ -88,6 +126,8 @@ class ToyConfig:
     theta: float = 100.0
     window: int = 12
     decay: float = 0.8
+    experts: int = 4
+    expert_inner: int = 20
     attn_std: float = 0.3            # spread of the query/key projections (see SHARP in test_replay_gpu.py)
     architecture = "ToyForCausalLM"
 
@@ -115,9 +155,12 @@ def toy_spec(cfg: ToyConfig):
     def ffn(prefix):
         return PartSpec("feed_forward", "gated_mlp", dict(width=H, inner=cfg.inner), prefix)
 
+    def routed(prefix):
+        return PartSpec("feed_forward", "toy_routed", dict(width=H, inner=cfg.expert_inner, experts=cfg.experts), prefix)
+
     def block(i, mixer):
         p = f"layers.{i}."
-        return PartSpec("block", "pre_norm", dict(mixer=mixer, feed_forward=ffn(p + "ffn."),
+        return PartSpec("block", "pre_norm", dict(mixer=mixer, feed_forward=(routed if i == 1 else ffn)(p + "ffn."),
                                                   mixer_norm=norm(p + "norm1."), feed_forward_norm=norm(p + "norm2.")), p)
 
     attn0 = PartSpec("mixer", "attention", dict(
@@ -182,7 +225,13 @@ def plain_toy_logits(cfg: ToyConfig, W, tokens):
             att = pm.attention_causal_window(q, k, v, pos, window, 1.0 / math.sqrt(cfg.head_dim))
             x = x + att.reshape(T, nh * cfg.head_dim) @ W[a + "o_proj.weight"].T
         h = pm.rms_norm(x, W[p + "norm2.weight"], cfg.eps)
-        x = x + pm.gated_mlp(h, W[p + "ffn.gate_proj.weight"], W[p + "ffn.up_proj.weight"], W[p + "ffn.down_proj.weight"])
+        if layer == 1:
+            weights = routing_weights(h @ W[p + "ffn.router"].T)
+            for e in range(cfg.experts):
+                x = x + weights[:, e:e + 1] * (torch.relu(h @ W[p + "ffn.up"][e].T) @ W[p + "ffn.down"][e].T)
+        else:
+            x = x + pm.gated_mlp(h, W[p + "ffn.gate_proj.weight"], W[p + "ffn.up_proj.weight"],
+                                 W[p + "ffn.down_proj.weight"])
     return pm.rms_norm(x, W["final_norm.weight"], cfg.eps) @ W["head.weight"].T
 
 
@@ -190,13 +239,15 @@ def plain_toy_logits(cfg: ToyConfig, W, tokens):
 def registered():
     from flambeau_b200.config.registry import register_architecture, unregister_architecture
     from flambeau_b200.parts.spec import register_part, unregister_part
-    DecayMixer, ShiftedRotary = toy_parts()
+    DecayMixer, ShiftedRotary, RoutedFeedForward = toy_parts()
     register_part("mixer", "toy_decay", DecayMixer)
+    register_part("feed_forward", "toy_routed", RoutedFeedForward)
     register_part("position", "toy_shifted_rotary", ShiftedRotary)
     register_architecture("ToyForCausalLM", ToyConfig, toy_spec)
     yield
     unregister_architecture("ToyForCausalLM")
     unregister_part("mixer", "toy_decay")
+    unregister_part("feed_forward", "toy_routed")
     unregister_part("position", "toy_shifted_rotary")
 
 
@@ -221,6 +272,8 @@ def test_the_cache_manager_sees_the_toy_model(toy):
     assert cm.group_of_call[4] == cm.group_of_call[0] and not cm.view(4, [None, None]).writable
     assert cm.state_bytes_per_request() == 2 * 48 * 4
     assert e.model.layers[1].mixer.__class__.__name__ == "DecayMixer"
+    assert e.model.layers[1].feed_forward.__class__.__name__ == "RoutedFeedForward"
+    assert e.model.layers[0].feed_forward.__class__.__name__ == "GatedMLP"
 
 
 @pytest.mark.parametrize("schedule", ["whole", "tail", "portions", "mixed1", "mixed2"])
