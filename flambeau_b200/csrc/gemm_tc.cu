@@ -24,6 +24,7 @@
 // The reference multiplies with scalar-FMA tiles of 64 outputs x 8 rows
 // (crates/kernels-hip/src/kernels/mmq_f16_tile.cu:32-107); the weight layout
 // (rows = outputs) is the same.
+#include "gemm_tc_pair.cuh"
 #include "tensor_map.cuh"
 #include "umma.cuh"
 
@@ -396,6 +397,8 @@ FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw
     if (splits_used) *splits_used = 1;
     if (M == 0) return 0;
     const int BN = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    if (BN == 256 && force_splits <= 1 && (o_dtype == FB_F32 || o_dtype == FB_BF16) && fb_gemm_pair_takes(M, N, K))
+        return fb_launch_gemm_pair(X, (long)lda, W, (long)ldw, out, o_dtype, (long)ldo, M, N, K, 0, status, stream);
     CUtensorMap mw, mx;
     int rc = fb_tensor_map_bf16(&mw, W, N, K, (long)ldw, BK, BM);
     if (rc) return rc;
@@ -434,6 +437,8 @@ FB_API int fb_gemm_tc_gated(const void* X, long long lda, const void* W, long lo
     FB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tc_gated: operands must be 16-byte aligned");
     if (M == 0) return 0;
     const int BN = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    if (BN == 256 && (o_dtype == FB_F32 || o_dtype == FB_BF16) && fb_gemm_pair_takes(M, N, K))
+        return fb_launch_gemm_pair(X, (long)lda, W, (long)ldw, out, o_dtype, (long)ldo, M, N, K, 1, status, stream);
     CUtensorMap mw, mx;
     int rc = fb_tensor_map_bf16(&mw, W, N, K, (long)ldw, BK, BM);
     if (rc) return rc;

@@ -1,0 +1,297 @@
+// out[M,N] = X[M,K] * W[N,K]^T in bfloat16 with two SMs on one tile (tcgen05.mma cta_group::2), for products with
+// hundreds of rows (portions of prompts).
+//
+// A cluster of two CTAs owns 256 output features x 256 tokens.  Each CTA stages its own 128 weight rows and its
+// own 128 of the 256 tokens, so a CTA fetches and holds half of what the one-CTA kernel (gemm_tc.cu) does for
+// the token operand; the even CTA of the pair issues one MMA of M = 256, N = 256 that reads both CTAs' shared
+// memory and writes both CTAs' tensor memory (128 features x 256 tokens in each).  Otherwise it is the
+// arrangement of gemm_tc.cu: swap-AB, K-major operands with the 128-byte swizzle, 64 elements of K a stage,
+// two accumulators so that the epilogue of one tile overlaps the products of the next, persistent pairs.
+//
+// Barriers.  full[s] lives in the even CTA and counts the bytes of both CTAs' copies (the copies carry
+// cta_group::2, which lets them signal the peer's barrier).  empty[s] and acc_full[b] exist in both CTAs and are
+// signalled in both by one tcgen05.commit with a CTA mask.  acc_empty[b] lives in the even CTA and takes one
+// arrival from each CTA's epilogue.  No copy is multicast.  Every wait on an mbarrier is bounded in time as in
+// gemm_tc.cu; the two cluster barriers (after set-up, before the tensor memory is freed) are reached by every
+// thread on every path.
+#include "gemm_tc_pair.cuh"
+#include "umma.cuh"
+
+#include <stdlib.h>
+
+namespace {
+
+constexpr int PBM = 128;               // output features per CTA
+constexpr int PBN = 256;               // tokens per pair (UMMA N)
+constexpr int PBNH = PBN / 2;          // tokens staged by one CTA
+constexpr int PBK = 64;
+constexpr int P_THREADS = 320;         // warp 0: copies, warp 1: tensor memory and MMA, warps 2..9: epilogue
+constexpr int P_STAGES = 6;
+constexpr int P_A_BYTES = PBM * PBK * 2;
+constexpr int P_STAGE_BYTES = P_A_BYTES + PBNH * PBK * 2;
+constexpr int P_TMEM_COLS = 2 * PBN;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address of this CTA's shared-memory location `addr` in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t in_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// A box of a tensor map into this CTA's shared memory; its bytes are counted on `bar`, which may lie in the peer.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+// One arrival on the barrier at this offset in both CTAs when the MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+template <typename TO>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    TO* __restrict__ out, long ldo, int M, int N, int K, int tiles_m, int n_units, int gated,
+                    int* status) {
+    constexpr int S = P_STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + S * P_STAGE_BYTES);
+    // bars[0..S): stage full (even CTA's are used), [S..2S): stage empty, [2S..2S+2): accumulator full,
+    // [2S+2..2S+4): accumulator empty (even CTA's are used)
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 4);
+    int* bail = (int*)(tmem_slot + 1);
+
+    fb_pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int kb_total = (K + PBK - 1) / PBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[S + s]), 1);
+        }
+        mbar_init(smem_u32(&bars[2 * S]), 1);
+        mbar_init(smem_u32(&bars[2 * S + 1]), 1);
+        mbar_init(smem_u32(&bars[2 * S + 2]), 2);
+        mbar_init(smem_u32(&bars[2 * S + 3]), 2);
+        *bail = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)P_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                          // both CTAs' barriers exist before either signals the other's
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- copies: this CTA's weight rows and its half of the tokens ----------------
+        if (elect_one()) {
+            uint32_t it = 0;
+            bool first = true;
+            for (int u = pair; u < n_units && !*(volatile int*)bail; u += n_pairs) {
+                const int mt = u % tiles_m, nt = u / tiles_m;
+                const int n0 = nt * (2 * PBM) + (int)rank * PBM;
+                const int m0 = mt * PBN + (int)rank * PBNH;
+                int i = 0;
+                if (first) {
+                    // weights do not depend on the kernel before this one; the activations do
+                    first = false;
+                    const int pre = kb_total < S ? kb_total : S;
+                    for (int j = 0; j < pre; ++j) {
+                        if (rank == 0) mbar_expect_tx(smem_u32(&bars[j]), 2u * P_STAGE_BYTES);
+                        tma_load_2d_pair(smem_u32(smem + (size_t)j * P_STAGE_BYTES), &map_w,
+                                         in_cta(smem_u32(&bars[j]), 0), j * PBK, n0);
+                    }
+                    fb_pdl_wait();
+                    for (int j = 0; j < pre; ++j)
+                        tma_load_2d_pair(smem_u32(smem + (size_t)j * P_STAGE_BYTES + P_A_BYTES), &map_x,
+                                         in_cta(smem_u32(&bars[j]), 0), j * PBK, m0);
+                    i = pre;
+                    it = (uint32_t)pre;
+                }
+                for (; i < kb_total; ++i, ++it) {
+                    const int s = (int)(it % S);
+                    const uint32_t round = it / S;
+                    if (!mbar_wait(smem_u32(&bars[S + s]), (round & 1u) ^ 1u, status)) { *bail = 1; break; }
+                    if (rank == 0) mbar_expect_tx(smem_u32(&bars[s]), 2u * P_STAGE_BYTES);
+                    const uint32_t full = in_cta(smem_u32(&bars[s]), 0);
+                    uint8_t* stage = smem + (size_t)s * P_STAGE_BYTES;
+                    tma_load_2d_pair(smem_u32(stage), &map_w, full, i * PBK, n0);
+                    tma_load_2d_pair(smem_u32(stage + P_A_BYTES), &map_x, full, i * PBK, m0);
+                }
+            }
+            if (first) fb_pdl_wait();
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA: the even CTA issues for the pair ----------------
+        if (rank == 0 && elect_one()) {
+            constexpr uint32_t idesc = umma_idesc(PBN, false, 2 * PBM);
+            uint32_t it = 0;
+            int j = 0;
+            for (int u = pair; u < n_units && !*(volatile int*)bail; u += n_pairs, ++j) {
+                const int b = j & 1;
+                const uint32_t use = (uint32_t)(j >> 1);
+                // both CTAs' epilogues must have drained this accumulator (two units ago)
+                if (!mbar_wait(smem_u32(&bars[2 * S + 2 + b]), (use & 1u) ^ 1u, status)) { *bail = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + (uint32_t)(b * PBN);
+                bool ok = true;
+                for (int i = 0; i < kb_total; ++i, ++it) {
+                    const int s = (int)(it % S);
+                    const uint32_t round = it / S;
+                    ok = mbar_wait(smem_u32(&bars[s]), round & 1u, status);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    uint8_t* stage = smem + (size_t)s * P_STAGE_BYTES;
+                    const uint64_t da = umma_desc(smem_u32(stage));
+                    const uint64_t db = umma_desc(smem_u32(stage + P_A_BYTES));
+#pragma unroll
+                    for (int k = 0; k < PBK / UMMA_K; ++k)
+                        umma_bf16_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
+                                       (i > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(smem_u32(&bars[S + s]));       // the stage is free in both CTAs
+                }
+                if (!ok) { *bail = 1; break; }
+                umma_commit_pair(smem_u32(&bars[2 * S + b]));       // the accumulator is complete in both CTAs
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: this CTA's 128 features x 256 tokens ----------------
+        fb_pdl_wait();
+        const int quarter = warp & 3;
+        const int half_id = (warp - 2) >> 2;
+        const int row_local = quarter * 32 + lane;
+        int j = 0;
+        for (int u = pair; u < n_units; u += n_pairs, ++j) {
+            const int mt = u % tiles_m, nt = u / tiles_m;
+            const int m0 = mt * PBN;
+            const int n = nt * (2 * PBM) + (int)rank * PBM + row_local;
+            const int b = j & 1;
+            const uint32_t use = (uint32_t)(j >> 1);
+            const bool got = !*(volatile int*)bail && mbar_wait(smem_u32(&bars[2 * S + b]), use & 1u, status);
+            if (!got) *bail = 1;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * PBN);
+            if (got) {
+#pragma unroll 1
+                for (int c = half_id * 16; c < PBN; c += 32) {
+                    if (m0 + c >= M) break;
+                    float v[16];
+                    if (kb_total > 0) {
+                        tmem_ld16(taddr + (uint32_t)c, v);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 16; ++q) v[q] = 0.0f;
+                    }
+                    if (gated) {
+                        // features alternate gate, up: the even lane writes silu(gate) * up to column n / 2
+                        float r[16];
+#pragma unroll
+                        for (int q = 0; q < 16; ++q) {
+                            const float up = __shfl_xor_sync(0xffffffffu, v[q], 1);
+                            r[q] = v[q] / (1.0f + expf(-v[q])) * up;
+                        }
+                        const bool writes = !(lane & 1) && n + 1 < N;
+#pragma unroll
+                        for (int q = 0; q < 16; ++q)
+                            if (writes && m0 + c + q < M)
+                                out[(size_t)(m0 + c + q) * ldo + (n >> 1)] = fb_from_float<TO>(r[q]);
+                    } else if (n < N) {
+#pragma unroll
+                        for (int q = 0; q < 16; ++q)
+                            if (m0 + c + q < M) out[(size_t)(m0 + c + q) * ldo + n] = fb_from_float<TO>(v[q]);
+                    }
+                }
+            }
+            // this CTA's half of the accumulator may be overwritten: one arrival per CTA at the even CTA
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (warp == 2 && lane == 0) mbar_arrive_remote(in_cta(smem_u32(&bars[2 * S + 2 + b]), 0));
+            if (*(volatile int*)bail) break;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                          // neither CTA leaves while the other may still reach into it
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)P_TMEM_COLS) : "memory");
+    }
+}
+
+template <typename TO>
+int launch_pair(const void* X, long lda, const void* W, long ldw, void* out, long ldo, int M, int N, int K, int gated,
+                int* status, cudaStream_t stream) {
+    CUtensorMap mw, mx;
+    int rc = fb_tensor_map_bf16(&mw, W, N, K, ldw, PBK, PBM);
+    if (rc) return rc;
+    rc = fb_tensor_map_bf16(&mx, X, M, K, lda, PBK, PBNH);
+    if (rc) return rc;
+    auto kern = gemm_tc_pair_kernel<TO>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+        if (e != cudaSuccess) return fb_fail(-2, "gemm_tc_pair: cannot reserve %d bytes of shared memory: %s",
+                                             P_SMEM_BYTES, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int tiles_m = (M + PBN - 1) / PBN, tiles_n = (N + 2 * PBM - 1) / (2 * PBM);
+    const long n_units = (long)tiles_m * tiles_n;
+    const int pairs = (int)(n_units < fb_gemm_pair_slots() ? n_units : fb_gemm_pair_slots());
+    fb_launch((kern), 2 * pairs, P_THREADS, P_SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, M, N, K, tiles_m,
+              (int)n_units, gated, status);
+    return fb_check_launch("gemm_tc_pair");
+}
+
+}  // namespace
+
+int fb_gemm_pair_slots() { return 74; }          // one pair per two SMs
+
+static int g_pair_on = -1;                       // -1: not yet read from the environment
+FB_API void fb_set_gemm_pair(int on) { g_pair_on = on ? 1 : 0; }
+
+bool fb_gemm_pair_takes(int M, int N, int K) {
+    if (g_pair_on < 0) g_pair_on = (getenv("FLAMBEAU_GEMM_PAIR") && atoi(getenv("FLAMBEAU_GEMM_PAIR")) == 0) ? 0 : 1;
+    if (!g_pair_on || K <= 0) return false;
+    const long units = (long)((M + PBN - 1) / PBN) * ((N + 2 * PBM - 1) / (2 * PBM));
+    return M > 128 && units >= fb_gemm_pair_slots();      // enough tiles to give every pair of SMs one
+}
+
+int fb_launch_gemm_pair(const void* X, long lda, const void* W, long ldw, void* out, int o_dtype, long ldo, int M,
+                        int N, int K, int gated, int* status, cudaStream_t stream) {
+    if (o_dtype == FB_F32) return launch_pair<float>(X, lda, W, ldw, out, ldo, M, N, K, gated, status, stream);
+    if (o_dtype == FB_BF16) return launch_pair<__nv_bfloat16>(X, lda, W, ldw, out, ldo, M, N, K, gated, status, stream);
+    return fb_fail(-1, "gemm_tc_pair: unknown output dtype code %d", o_dtype);
+}

@@ -32,10 +32,11 @@ __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t mn
     return d;
 }
 
-// Instruction descriptor: bf16 x bf16 -> f32, M = 128, N = n; operand B K-major, or MN-major with b_mn_major.
-__host__ __device__ constexpr uint32_t umma_idesc(int n, bool b_mn_major = false) {
+// Instruction descriptor: bf16 x bf16 -> f32, M = m (128; 256 for a pair of CTAs), N = n; operand B K-major, or
+// MN-major with b_mn_major.
+__host__ __device__ constexpr uint32_t umma_idesc(int n, bool b_mn_major = false, int m = 128) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) |
-           ((uint32_t)(128 >> 4) << 24);
+           ((uint32_t)(m >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by one thread for the CTA.

@@ -22,6 +22,7 @@ _SIGNATURES = {
     "fb_abi_version": (I, []),
     "fb_set_pdl": (None, [I]),
     "fb_set_attention_tc": (None, [I]),
+    "fb_set_gemm_pair": (None, [I]),
     "fb_set_prefetch_hint": (None, [P, L, L, I]),
     # elementwise.cu
     "fb_embedding": (I, [P, I, P, P, I, I, I, P, STREAM]),

@@ -323,6 +323,12 @@ def prefetch_hint(weight: torch.Tensor, budget_bytes: int = 16 << 20) -> None:
         lib().fb_set_prefetch_hint(weight.data_ptr(), rows, weight.stride(0) * weight.element_size(), per_row)
 
 
+def set_gemm_pair(on: bool) -> None:
+    """Products with hundreds of rows on the two-SM kernel (tcgen05 cta_group::2) where there are enough tiles
+    (the default), or always on the one-SM kernel."""
+    lib().fb_set_gemm_pair(1 if on else 0)
+
+
 def set_attention_tc(on: bool) -> None:
     """Portions of prompts on the tcgen05 attention kernel where it takes the geometry (the default), or always on
     the mma.sync kernel."""

@@ -30,6 +30,8 @@ SHAPES_TC = [
     (1, 128, 64), (8, 256, 512), (8, 6144, 4096), (16, 384, 1024), (17, 130, 72), (33, 4096, 4096),
     (64, 1000, 264), (65, 257, 8), (128, 512, 2048), (200, 320, 96), (256, 1024, 1024), (300, 200, 136),
     (515, 4096, 1024), (2048, 1024, 4096),
+    # enough tiles of 256 x 256 for every pair of SMs: the two-SM kernel
+    (300, 10000, 200), (700, 6500, 1000), (2048, 4096, 4096), (515, 20000, 64), (129, 19000, 72),
 ]
 
 
@@ -57,6 +59,28 @@ def test_tensor_core_product(M, N, K, out_dtype, splits):
     out2 = torch.empty_like(out)
     ops.gemm_tc(a, w, out2, status, splits=splits)
     assert torch.equal(out, out2), "the product is not reproducible"
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 10000, 200), (2048, 6144, 1024), (1000, 9999, 136)])
+def test_two_sm_product_equals_the_one_sm_product(M, N, K):
+    """Both kernels add the same products in the same order, so they agree to the bit."""
+    from flambeau_b200.kernels import ops
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", generator=g).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    outs = []
+    try:
+        for pair in (True, False):
+            ops.set_gemm_pair(pair)
+            out = torch.full((M, N), float("nan"), device="cuda")
+            ops.gemm_tc(a, w, out, status)
+            outs.append(out)
+    finally:
+        ops.set_gemm_pair(True)
+    assert int(status.item()) == 0
+    assert torch.equal(outs[0], outs[1])
+    assert rel_err(outs[0], a.double() @ w.double().T) < 2e-5
 
 
 def test_tensor_core_product_on_strided_views():
@@ -88,7 +112,8 @@ def test_shapes_the_tma_path_cannot_take_are_refused():
         ops.gemm_tc(a.float(), w, out, status)
 
 
-@pytest.mark.parametrize("M,I,K", [(3, 64, 64), (17, 100, 136), (70, 1001, 72), (300, 160, 96), (2048, 512, 256)])
+@pytest.mark.parametrize("M,I,K", [(3, 64, 64), (17, 100, 136), (70, 1001, 72), (300, 160, 96), (2048, 512, 256),
+                                   (600, 4001, 136), (2048, 2560, 256)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gated_epilogue(M, I, K, out_dtype):
     """Gate and up rows alternate in the weight; the epilogue writes silu(gate) * up, half as wide."""
