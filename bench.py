@@ -236,14 +236,14 @@ def main(argv=None) -> int:
         engine.cache.release_all()
         toks = torch.randint(0, vocab, (tokens,), generator=gen).tolist()
         times = []
-        for i in range(4):
+        for i in range(8):                              # 3 warm-up steps, then the median of 5
             torch.cuda.synchronize()
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0.record()
             engine.step([Entry("prompt", toks, [tokens - 1])], end=["prompt"])
             t1.record()
             torch.cuda.synchronize()
-            if i:
+            if i >= 3:
                 times.append(t0.elapsed_time(t1))
         engine.runtime.check_status("bench prefill")
         return statistics.median(times)

@@ -397,8 +397,14 @@ FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw
     if (splits_used) *splits_used = 1;
     if (M == 0) return 0;
     const int BN = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-    if (BN == 256 && force_splits <= 1 && (o_dtype == FB_F32 || o_dtype == FB_BF16) && fb_gemm_pair_takes(M, N, K))
-        return fb_launch_gemm_pair(X, (long)lda, W, (long)ldw, out, o_dtype, (long)ldo, M, N, K, 0, status, stream);
+    if (BN == 256 && force_splits <= 1 && (o_dtype == FB_F32 || o_dtype == FB_BF16)) {
+        const int slabs = (slab_stride > 0 && o_dtype == FB_F32 && force_splits == 0) ? max_slabs : 1;
+        if (const int shares = fb_gemm_pair_plan(M, N, K, slabs)) {
+            if (splits_used) *splits_used = shares;
+            return fb_launch_gemm_pair(X, (long)lda, W, (long)ldw, out, o_dtype, (long)ldo, (long)slab_stride, shares,
+                                       M, N, K, 0, status, stream);
+        }
+    }
     CUtensorMap mw, mx;
     int rc = fb_tensor_map_bf16(&mw, W, N, K, (long)ldw, BK, BM);
     if (rc) return rc;
@@ -437,8 +443,9 @@ FB_API int fb_gemm_tc_gated(const void* X, long long lda, const void* W, long lo
     FB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tc_gated: operands must be 16-byte aligned");
     if (M == 0) return 0;
     const int BN = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-    if (BN == 256 && (o_dtype == FB_F32 || o_dtype == FB_BF16) && fb_gemm_pair_takes(M, N, K))
-        return fb_launch_gemm_pair(X, (long)lda, W, (long)ldw, out, o_dtype, (long)ldo, M, N, K, 1, status, stream);
+    if (BN == 256 && (o_dtype == FB_F32 || o_dtype == FB_BF16) && fb_gemm_pair_plan(M, N, K, 1))
+        return fb_launch_gemm_pair(X, (long)lda, W, (long)ldw, out, o_dtype, (long)ldo, 0, 1, M, N, K, 1, status,
+                                   stream);
     CUtensorMap mw, mx;
     int rc = fb_tensor_map_bf16(&mw, W, N, K, (long)ldw, BK, BM);
     if (rc) return rc;

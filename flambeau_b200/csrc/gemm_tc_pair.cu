@@ -31,6 +31,7 @@ constexpr int P_A_BYTES = PBM * PBK * 2;
 constexpr int P_STAGE_BYTES = P_A_BYTES + PBNH * PBK * 2;
 constexpr int P_TMEM_COLS = 2 * PBN;
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_SLOTS = 74;             // pairs that run at a time: one per two SMs
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -69,11 +70,25 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// One unit of work: output tile (nt, mt) and share `split` of its K range.  Token tiles vary fastest, so pairs
+// that run together share weight tiles through L2; shares of K vary slowest.
+struct PairUnit { int mt, nt, split, kb_begin, n_kb; };
+__device__ __forceinline__ PairUnit pair_unit(int u, int tiles_m, int tiles, int splits, int kb_total) {
+    PairUnit w;
+    const int t = u % tiles;
+    w.split = u / tiles;
+    w.mt = t % tiles_m;
+    w.nt = t / tiles_m;
+    w.kb_begin = (int)((long)w.split * kb_total / splits);
+    w.n_kb = (int)((long)(w.split + 1) * kb_total / splits) - w.kb_begin;
+    return w;
+}
+
 template <typename TO>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                    TO* __restrict__ out, long ldo, int M, int N, int K, int tiles_m, int n_units, int gated,
-                    int* status) {
+                    TO* __restrict__ out, long ldo, long slab_stride, int M, int N, int K, int tiles_m, int tiles,
+                    int splits, int n_units, int gated, int* status) {
     constexpr int S = P_STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -118,35 +133,35 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             uint32_t it = 0;
             bool first = true;
             for (int u = pair; u < n_units && !*(volatile int*)bail; u += n_pairs) {
-                const int mt = u % tiles_m, nt = u / tiles_m;
-                const int n0 = nt * (2 * PBM) + (int)rank * PBM;
-                const int m0 = mt * PBN + (int)rank * PBNH;
+                const PairUnit w = pair_unit(u, tiles_m, tiles, splits, kb_total);
+                const int n0 = w.nt * (2 * PBM) + (int)rank * PBM;
+                const int m0 = w.mt * PBN + (int)rank * PBNH;
                 int i = 0;
                 if (first) {
                     // weights do not depend on the kernel before this one; the activations do
                     first = false;
-                    const int pre = kb_total < S ? kb_total : S;
+                    const int pre = w.n_kb < S ? w.n_kb : S;
                     for (int j = 0; j < pre; ++j) {
                         if (rank == 0) mbar_expect_tx(smem_u32(&bars[j]), 2u * P_STAGE_BYTES);
                         tma_load_2d_pair(smem_u32(smem + (size_t)j * P_STAGE_BYTES), &map_w,
-                                         in_cta(smem_u32(&bars[j]), 0), j * PBK, n0);
+                                         in_cta(smem_u32(&bars[j]), 0), (w.kb_begin + j) * PBK, n0);
                     }
                     fb_pdl_wait();
                     for (int j = 0; j < pre; ++j)
                         tma_load_2d_pair(smem_u32(smem + (size_t)j * P_STAGE_BYTES + P_A_BYTES), &map_x,
-                                         in_cta(smem_u32(&bars[j]), 0), j * PBK, m0);
+                                         in_cta(smem_u32(&bars[j]), 0), (w.kb_begin + j) * PBK, m0);
                     i = pre;
                     it = (uint32_t)pre;
                 }
-                for (; i < kb_total; ++i, ++it) {
+                for (; i < w.n_kb; ++i, ++it) {
                     const int s = (int)(it % S);
                     const uint32_t round = it / S;
                     if (!mbar_wait(smem_u32(&bars[S + s]), (round & 1u) ^ 1u, status)) { *bail = 1; break; }
                     if (rank == 0) mbar_expect_tx(smem_u32(&bars[s]), 2u * P_STAGE_BYTES);
                     const uint32_t full = in_cta(smem_u32(&bars[s]), 0);
                     uint8_t* stage = smem + (size_t)s * P_STAGE_BYTES;
-                    tma_load_2d_pair(smem_u32(stage), &map_w, full, i * PBK, n0);
-                    tma_load_2d_pair(smem_u32(stage + P_A_BYTES), &map_x, full, i * PBK, m0);
+                    tma_load_2d_pair(smem_u32(stage), &map_w, full, (w.kb_begin + i) * PBK, n0);
+                    tma_load_2d_pair(smem_u32(stage + P_A_BYTES), &map_x, full, (w.kb_begin + i) * PBK, m0);
                 }
             }
             if (first) fb_pdl_wait();
@@ -159,6 +174,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             uint32_t it = 0;
             int j = 0;
             for (int u = pair; u < n_units && !*(volatile int*)bail; u += n_pairs, ++j) {
+                const int n_kb = pair_unit(u, tiles_m, tiles, splits, kb_total).n_kb;
                 const int b = j & 1;
                 const uint32_t use = (uint32_t)(j >> 1);
                 // both CTAs' epilogues must have drained this accumulator (two units ago)
@@ -166,7 +182,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * PBN);
                 bool ok = true;
-                for (int i = 0; i < kb_total; ++i, ++it) {
+                for (int i = 0; i < n_kb; ++i, ++it) {
                     const int s = (int)(it % S);
                     const uint32_t round = it / S;
                     ok = mbar_wait(smem_u32(&bars[s]), round & 1u, status);
@@ -194,9 +210,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int row_local = quarter * 32 + lane;
         int j = 0;
         for (int u = pair; u < n_units; u += n_pairs, ++j) {
-            const int mt = u % tiles_m, nt = u / tiles_m;
-            const int m0 = mt * PBN;
-            const int n = nt * (2 * PBM) + (int)rank * PBM + row_local;
+            const PairUnit w = pair_unit(u, tiles_m, tiles, splits, kb_total);
+            const int m0 = w.mt * PBN;
+            const int n = w.nt * (2 * PBM) + (int)rank * PBM + row_local;
+            TO* dst = out + (size_t)w.split * (size_t)slab_stride;     // this share's slab (the whole sum: slab 0)
             const int b = j & 1;
             const uint32_t use = (uint32_t)(j >> 1);
             const bool got = !*(volatile int*)bail && mbar_wait(smem_u32(&bars[2 * S + b]), use & 1u, status);
@@ -208,7 +225,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 for (int c = half_id * 16; c < PBN; c += 32) {
                     if (m0 + c >= M) break;
                     float v[16];
-                    if (kb_total > 0) {
+                    if (w.n_kb > 0) {
                         tmem_ld16(taddr + (uint32_t)c, v);
                     } else {
 #pragma unroll
@@ -226,11 +243,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                         for (int q = 0; q < 16; ++q)
                             if (writes && m0 + c + q < M)
-                                out[(size_t)(m0 + c + q) * ldo + (n >> 1)] = fb_from_float<TO>(r[q]);
+                                dst[(size_t)(m0 + c + q) * ldo + (n >> 1)] = fb_from_float<TO>(r[q]);
                     } else if (n < N) {
 #pragma unroll
                         for (int q = 0; q < 16; ++q)
-                            if (m0 + c + q < M) out[(size_t)(m0 + c + q) * ldo + n] = fb_from_float<TO>(v[q]);
+                            if (m0 + c + q < M) dst[(size_t)(m0 + c + q) * ldo + n] = fb_from_float<TO>(v[q]);
                     }
                 }
             }
@@ -252,8 +269,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 }
 
 template <typename TO>
-int launch_pair(const void* X, long lda, const void* W, long ldw, void* out, long ldo, int M, int N, int K, int gated,
-                int* status, cudaStream_t stream) {
+int launch_pair(const void* X, long lda, const void* W, long ldw, void* out, long ldo, long slab_stride, int splits,
+                int M, int N, int K, int gated, int* status, cudaStream_t stream) {
     CUtensorMap mw, mx;
     int rc = fb_tensor_map_bf16(&mw, W, N, K, ldw, PBK, PBM);
     if (rc) return rc;
@@ -268,30 +285,56 @@ int launch_pair(const void* X, long lda, const void* W, long ldw, void* out, lon
         configured = true;
     }
     const int tiles_m = (M + PBN - 1) / PBN, tiles_n = (N + 2 * PBM - 1) / (2 * PBM);
-    const long n_units = (long)tiles_m * tiles_n;
-    const int pairs = (int)(n_units < fb_gemm_pair_slots() ? n_units : fb_gemm_pair_slots());
-    fb_launch((kern), 2 * pairs, P_THREADS, P_SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, M, N, K, tiles_m,
-              (int)n_units, gated, status);
+    const long tiles = (long)tiles_m * tiles_n;
+    const long n_units = tiles * splits;
+    if (n_units > 2000000000L) return fb_fail(-1, "gemm_tc_pair: too many tiles (M=%d N=%d)", M, N);
+    const int pairs = (int)(n_units < P_SLOTS ? n_units : P_SLOTS);
+    fb_launch((kern), 2 * pairs, P_THREADS, P_SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, M, N, K,
+              tiles_m, (int)tiles, splits, (int)n_units, gated, status);
     return fb_check_launch("gemm_tc_pair");
 }
 
 }  // namespace
 
-int fb_gemm_pair_slots() { return 74; }          // one pair per two SMs
-
 static int g_pair_on = -1;                       // -1: not yet read from the environment
 FB_API void fb_set_gemm_pair(int on) { g_pair_on = on ? 1 : 0; }
 
-bool fb_gemm_pair_takes(int M, int N, int K) {
-    if (g_pair_on < 0) g_pair_on = (getenv("FLAMBEAU_GEMM_PAIR") && atoi(getenv("FLAMBEAU_GEMM_PAIR")) == 0) ? 0 : 1;
-    if (!g_pair_on || K <= 0) return false;
-    const long units = (long)((M + PBN - 1) / PBN) * ((N + 2 * PBM - 1) / (2 * PBM));
-    return M > 128 && units >= fb_gemm_pair_slots();      // enough tiles to give every pair of SMs one
+// Shares of K for the pairs: as many as make the rounds of the 74 pairs shortest, each share beyond the first
+// costing one more float32 copy of the output (written here, added by the consumer), counted in k-block times.
+static int pair_splits(long tiles, int kb_total, int max_splits, int M, int N) {
+    const double kb_seconds = 2.0 * PBM * PBN * PBK / 9.0e12;
+    const double share_cost_kb = ((double)M * N * 8.0 / 6.0e12) / kb_seconds;
+    int best = 1;
+    double best_cost = 1e30;
+    for (int s = 1; s <= max_splits && s <= kb_total; ++s) {
+        const long units = tiles * s;
+        const long rounds = (units + P_SLOTS - 1) / P_SLOTS;
+        const double cost = rounds * ((double)((kb_total + s - 1) / s) + 0.5) + (s - 1) * share_cost_kb;
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
+    }
+    return best;
 }
 
-int fb_launch_gemm_pair(const void* X, long lda, const void* W, long ldw, void* out, int o_dtype, long ldo, int M,
-                        int N, int K, int gated, int* status, cudaStream_t stream) {
-    if (o_dtype == FB_F32) return launch_pair<float>(X, lda, W, ldw, out, ldo, M, N, K, gated, status, stream);
-    if (o_dtype == FB_BF16) return launch_pair<__nv_bfloat16>(X, lda, W, ldw, out, ldo, M, N, K, gated, status, stream);
+int fb_gemm_pair_plan(int M, int N, int K, int max_slabs) {
+    if (g_pair_on < 0) g_pair_on = (getenv("FLAMBEAU_GEMM_PAIR") && atoi(getenv("FLAMBEAU_GEMM_PAIR")) == 0) ? 0 : 1;
+    if (!g_pair_on || K <= 0 || M <= PBNH) return 0;
+    const long tiles = (long)((M + PBN - 1) / PBN) * ((N + 2 * PBM - 1) / (2 * PBM));
+    const int kb_total = (K + PBK - 1) / PBK;
+    const int splits = pair_splits(tiles, kb_total, max_slabs < 1 ? 1 : (max_slabs > 16 ? 16 : max_slabs), M, N);
+    // A long K on few tiles needs shares of K; where the caller has no slabs for them, the one-SM kernel, whose
+    // shares meet in scratch, is the better choice.
+    if (splits == 1 && tiles < 48 && kb_total >= 128) return 0;
+    return splits;
+}
+
+int fb_launch_gemm_pair(const void* X, long lda, const void* W, long ldw, void* out, int o_dtype, long ldo,
+                        long slab_stride, int splits, int M, int N, int K, int gated, int* status,
+                        cudaStream_t stream) {
+    if (splits < 1 || (splits > 1 && (slab_stride <= 0 || o_dtype != FB_F32 || gated)))
+        return fb_fail(-1, "gemm_tc_pair: %d shares of K need float32 slabs", splits);
+    if (o_dtype == FB_F32)
+        return launch_pair<float>(X, lda, W, ldw, out, ldo, slab_stride, splits, M, N, K, gated, status, stream);
+    if (o_dtype == FB_BF16)
+        return launch_pair<__nv_bfloat16>(X, lda, W, ldw, out, ldo, 0, 1, M, N, K, gated, status, stream);
     return fb_fail(-1, "gemm_tc_pair: unknown output dtype code %d", o_dtype);
 }

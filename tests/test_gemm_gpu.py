@@ -83,6 +83,26 @@ def test_two_sm_product_equals_the_one_sm_product(M, N, K):
     assert rel_err(outs[0], a.double() @ w.double().T) < 2e-5
 
 
+@pytest.mark.parametrize("M,N,K,P", [(8, 4096, 4096, 16), (64, 512, 8192, 8), (40, 1000, 264, 4), (512, 4096, 14336, 8),
+                                     (300, 1000, 8192, 4), (1024, 2048, 4096, 8), (2048, 4096, 1024, 4)])
+def test_shares_of_k_left_in_slabs(M, N, K, P):
+    """With slabs the kernel leaves its split-K shares for the consumer to add: k slabs hold the product,
+    the others are untouched."""
+    from flambeau_b200.kernels import ops
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", generator=g).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    slabs = torch.full((P, M, N), float("nan"), device="cuda")
+    k = ops.gemm_tc(a, w, slabs[0], status, slabs=slabs)
+    assert 1 <= k <= P and int(status.item()) == 0
+    assert torch.isfinite(slabs[:k]).all() and torch.isnan(slabs[k:]).all()
+    assert rel_err(slabs[:k].double().sum(0), a.double() @ w.double().T) < 2e-5
+    again = torch.full((P, M, N), float("nan"), device="cuda")
+    assert ops.gemm_tc(a, w, again[0], status, slabs=again) == k
+    assert torch.equal(slabs[:k], again[:k])
+
+
 def test_tensor_core_product_on_strided_views():
     from flambeau_b200.kernels import ops
     g = torch.Generator(device="cuda").manual_seed(3)
