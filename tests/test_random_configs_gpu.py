@@ -48,3 +48,42 @@ def test_random_configuration(seed, dtype, tmp_path):
     assert all(g.pool.n_free == g.pool.n_pages for g in engine.cache.groups), "pages lost"
     got = tiny.read_rows(tmp_path / "out", sched, cfg["vocab_size"])
     tiny.compare_rows(got, want, tiny.TOL[dtype], f"seed {seed} {dtype} {cfg}")
+
+
+def random_mid_config(seed: int) -> dict:
+    rng = random.Random(1000 + seed)
+    nkv = rng.choice([1, 2, 3, 5])
+    return dict(architectures=["MistralForCausalLM"], hidden_size=8 * rng.randint(60, 260), num_hidden_layers=2,
+                num_attention_heads=nkv * rng.choice([1, 2, 3, 4]), num_key_value_heads=nkv,
+                head_dim=rng.choice([64, 96, 128, 128, 160, 256]), intermediate_size=8 * rng.randint(100, 600),
+                vocab_size=rng.randint(2000, 9000), rope_theta=rng.choice([1e4, 1e6]),
+                sliding_window=rng.choice([None, 100, 256, 333]), rms_norm_eps=1e-5,
+                tie_word_embeddings=rng.random() < 0.5, hidden_act="silu")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [2, 8])
+def test_random_mid_size_configuration(seed, dtype, tmp_path):
+    """Widths of one to two thousand and prompts of several hundred tokens: the sizes at which the tensor-core
+    kernels for portions of prompts run (products with hundreds of rows, attention over a thousand keys), with
+    most of each prompt in one step, in long portions of changing size, and mixed."""
+    from flambeau_b200.engine.step import Engine, EngineOptions
+    from flambeau_b200.engine.trace import replay
+    cfg = random_mid_config(seed)
+    sharp = (0.2 if dtype == "float32" else 0.1) * (64.0 / cfg["hidden_size"]) ** 0.5 * (16.0 / cfg["head_dim"]) ** 0.25
+    folder = tiny.make_folder(tmp_path / "model", cfg, seed=seed, dtype=dtype, sharp=sharp)
+    rng = random.Random(seed)
+    requests = tiny.random_requests(cfg, [rng.randint(300, 1300), rng.randint(40, 700)], seed=seed)
+    pcfg, W = pm.read_model_folder(folder)
+    want = {rid: pm.forward_logits(pcfg, W, toks) for rid, toks in requests.items()}
+    schedules = {"tail": tiny.schedule_tail(requests, 8), "mixed": tiny.schedule_mixed(requests, seed=seed),
+                 "portions": tiny.schedule_portions(requests, sizes=(257, 64, 130, 2, 511))}
+    for name, sched in schedules.items():
+        tokens = sched.max_live_tokens(requests)
+        engine = Engine.from_folder(folder, EngineOptions(dtype=dtype, cache_tokens=tokens, max_requests=4,
+                                                           max_step_tokens=max(tokens, 128), max_seq_len=max(tokens, 128)))
+        replay(engine, sched.lines(), tmp_path / name)
+        engine.cache.check_invariants()
+        got = tiny.read_rows(tmp_path / name, sched, cfg["vocab_size"])
+        tiny.compare_rows(got, want, tiny.TOL[dtype], f"seed {seed} {dtype} {name} {cfg}")
+        del engine
