@@ -241,7 +241,9 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();                                  // barriers initialised, tiles cleared
-    fb_pdl_wait();                                    // from here on: Q and the cache, which earlier kernels wrote
+    // Q and the cache rows of this step's own tokens come from the kernel before this one: the scoring warps wait
+    // for it before they read Q, the fetching warp before the first tile that reaches a new position.  Tiles of
+    // older keys were written by earlier steps and are fetched at once, while that kernel may still be running.
 
     // A wait that ran out anywhere makes every later wait of the CTA return at once: nobody is left behind at a
     // barrier, and the status word tells the host.
@@ -315,10 +317,15 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
         };
         Seg sg = next_seg();
         int it = 0;
+        bool waited = false;
         lookup(sg, sg.k_begin);
         for (uint32_t count = 0;; ++count) {
             const int buf = (int)(count % NST);
             if (count >= NST && !wait(&empty[buf], ((count / NST) - 1) & 1u)) return;
+            if (!waited && sg.k_begin + (it + 1) * KT > sg.pos0) {
+                fb_pdl_wait();
+                waited = true;
+            }
             issue(sg, buf, sg.k_begin + it * KT);
             if (++it == sg.n_tiles) {
                 if (g >= seg_hi) {
@@ -334,6 +341,7 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
     }
 
     // ================= the scoring warps =================
+    fb_pdl_wait();
     const int key0 = warp * 16;                       // this warp's keys within a tile
     uint32_t count = 0;                               // tiles consumed: slot and barrier phase follow from it
     Seg cur = next_seg();
