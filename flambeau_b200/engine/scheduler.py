@@ -12,13 +12,19 @@ crates/server/src/routes/decode_loop.rs:365-520).
 When pages run out the reference fails the forward call
 (crates/forward/src/core/composites/standard_attn.rs:449-458).  Here no step
 fails for lack of pages:
-  * a request is admitted only if its first portion fits with a page of
-    headroom for every running request;
+  * beside running requests, a request is admitted only if its whole prompt
+    (what a window keeps of it) and its first token fit into the pages that
+    are free after the running requests' prompts have taken theirs, and its
+    first portion fits with a page of headroom for every running request;
+    with nothing running, if its first portion fits;
   * a prompt portion is shortened to the pages that are free, or waits;
   * if the decoding requests cannot all get the page their next token needs,
     the youngest running request is preempted: its pages are given back and it
     returns to the front of the queue with prompt := prompt + generated so far,
     to be fed again later (its draws continue where they stopped);
+  * if nothing can be scheduled although requests are running (all of them
+    in the middle of their prompts, no page free), the youngest is preempted
+    in the same way;
   * a request that cannot fit even alone is finished with reason 'capacity'.
 
 Running ahead.  While every running request is decoding and none is about to reach its token limit, the next
@@ -89,6 +95,8 @@ class Scheduler:
             raise ValueError("token_budget, prefill_chunk and max_running must be positive")
         self.executor = executor
         self.cache = executor.cache
+        # never more running requests than the cache has slots for per-request state
+        max_running = min(max_running, getattr(self.cache, "max_requests", max_running))
         self.token_budget, self.prefill_chunk, self.max_running = token_budget, prefill_chunk, max_running
         self.waiting: deque = deque()
         self.running: list = []
@@ -144,6 +152,27 @@ class Scheduler:
         """Decide the next step.  Takes no pages itself (the engine's step reserves them), but preempts and
         admits as needed, so that the planned entries are sure to fit."""
         plan = PlannedStep([], [], [], [])
+        while True:
+            self._plan_once(plan)
+            if plan.entries or not self.running:
+                return plan
+            # every running request is in the middle of its prompt and no page is free: the youngest gives way
+            victim = max(self.running, key=lambda r: r.arrival)
+            if len(self.running) == 1:
+                self._finish(victim, "capacity")
+            else:
+                self._preempt(victim, plan)
+
+    def _pages_for(self, tokens: int, group: int) -> int:
+        """Pages that `tokens` tokens of one request hold in a group at most (a window keeps the last W tokens,
+        plus the portion that is being written and the page the window starts in)."""
+        window = self.cache.groups[group].req.window
+        page = self.cache.page_size
+        if window:
+            tokens = min(tokens, window + self.prefill_chunk + page)
+        return -(-tokens // page)
+
+    def _plan_once(self, plan: PlannedStep) -> None:
         budget = self.token_budget
         cache = self.cache
         page = cache.page_size
@@ -203,9 +232,20 @@ class Scheduler:
             k = portion(r, 0)
             if k > 0:
                 take(r, k)
+        # pages that the running requests' prompts will still take (this step's portions among them)
+        owed = [0] * cache.n_groups
+        for r in self.running:
+            for gi in range(cache.n_groups):
+                have = len(cache.requests[r.request_id].pages[gi]) if r.request_id in cache.requests else 0
+                owed[gi] += max(0, self._pages_for(len(r.prompt) + len(r.generated) + 1, gi) - have)
+        free_now = self._pages_free()
         while self.waiting and budget > 0 and len(self.running) < self.max_running and cache.has_slot():
             r = self.waiting[0]
             k = portion(r, headroom=len(self.running))
+            whole = [self._pages_for(len(r.prompt) + len(r.generated) + 1, gi) for gi in range(cache.n_groups)]
+            if self.running and any(whole[gi] + owed[gi] > free_now[gi]
+                                    for gi in range(cache.n_groups)):
+                k = 0                                     # it would starve the prompts that are being fed
             if k <= 0:
                 if not self.running and not plan.entries:
                     # alone, with every page free, and still no room for one token
@@ -217,7 +257,8 @@ class Scheduler:
             self.running.append(r)
             plan.admitted.append(r)
             take(r, k)
-        return plan
+            for gi in range(cache.n_groups):
+                owed[gi] += whole[gi]
 
     # ---- running -----------------------------------------------------------------
     def step(self) -> list:

@@ -153,6 +153,76 @@ def test_random_load_never_breaks_the_books():
     assert ex.cache.free_pages() == [10] and not ex.cache.requests
 
 
+def test_prompts_that_do_not_fit_together_are_not_fed_side_by_side():
+    """Four prompts of 68 to 90 tokens and a pool of 256: fed side by side they would fill the pool with all four
+    in mid-prompt and nothing could run.  The fourth waits until pages are free."""
+    ex = BookkeepingExecutor(tokens=256, max_requests=8)
+    s = Scheduler(ex, token_budget=96, prefill_chunk=16, max_running=8)
+    reqs = [s.add(i, list(range(n)), SamplingParams(max_tokens=m))
+            for i, (n, m) in enumerate([(79, 18), (90, 43), (84, 26), (68, 15)])]
+    s.step()
+    assert [e[0] for e in ex.log[-1]] == [0, 1]               # 5 + 6 pages of 16 are spoken for; 2 would need 6 more
+    s.run()
+    assert all(r.finish_reason == "length" and len(r.generated) == r.params.max_tokens for r in reqs)
+    assert ex.cache.free_pages() == [16] and not ex.cache.requests
+
+
+def test_running_requests_stuck_in_mid_prompt_make_the_youngest_give_way():
+    """The state that admission now avoids, built by hand: two running requests in mid-prompt hold every page."""
+    ex = BookkeepingExecutor(tokens=64, max_requests=4)        # 4 pages of 16
+    s = Scheduler(ex, token_budget=64, prefill_chunk=32, max_running=4)
+    a = s.add("a", list(range(60)), SamplingParams(max_tokens=2))
+    b = s.add("b", list(range(60)), SamplingParams(max_tokens=2))
+    for r in (a, b):                                           # as if both had been admitted and fed 32 tokens
+        s.waiting.remove(r)
+        s.running.append(r)
+        ex.cache.admit(r.request_id)
+        ex.cache.reserve(r.request_id, 32)
+        ex.cache.commit(r.request_id, 32)
+        r.fed = 32
+    assert ex.cache.free_pages() == [0]
+    s.step()
+    assert b.preemptions == 1 and [e[0] for e in ex.log[-1]] == ["a"]
+    s.run()
+    assert a.finish_reason == b.finish_reason == "length" and len(b.generated) == 2
+    assert ex.cache.free_pages() == [4]
+
+
+@pytest.mark.parametrize("block", range(6))
+def test_random_loads_pools_and_windows_always_end(block):
+    """Random loads on random pools (down to three pages), windows, slots, budgets and portion sizes, with and
+    without running ahead: every run ends, the books balance, every request gets its tokens, and 'capacity' is
+    given only to a request that would not fit alone."""
+    import random
+    for seed in range(block * 50, block * 50 + 50):
+        rng = random.Random(seed)
+        n = rng.randint(1, 12)
+        page = rng.choice([8, 16])
+        pool = page * rng.randint(3, 24)
+        window = rng.choice([0, 0, 0, 24, 40])
+        slots = rng.choice([1, 2, 4, 8])
+        lengths = [rng.randint(1, 120) for _ in range(n)]
+        limits = [rng.randint(1, 60) for _ in range(n)]
+        ex = TwoPhaseExecutor(tokens=pool, max_requests=slots, window=window, page_size=page)
+        s = Scheduler(ex, token_budget=rng.choice([8, 24, 96]), prefill_chunk=rng.choice([4, 16, 33, 64]),
+                      max_running=rng.choice([slots, 4]), run_ahead=rng.random() < 0.5)
+        reqs = [s.add(i, list(range(l)), SamplingParams(max_tokens=m)) for i, (l, m) in enumerate(zip(lengths, limits))]
+        steps = 0
+        while not s.idle:
+            s.step()
+            steps += 1
+            assert steps < 20000, f"seed {seed}: no end"
+        ex.cache.check_invariants()
+        assert not ex.cache.requests and ex.in_flight == 0, f"seed {seed}"
+        for r in reqs:
+            if r.finish_reason == "capacity":
+                total = len(r.prompt) + r.params.max_tokens
+                assert not (total <= pool or (window and pool >= window + 3 * page)), \
+                    f"seed {seed}: request {r.request_id} fits alone but ended with 'capacity'"
+            else:
+                assert r.finish_reason == "length" and len(r.generated) == r.params.max_tokens, f"seed {seed}"
+
+
 class TwoPhaseExecutor(BookkeepingExecutor):
     """The same books with the launch / collect interface: a step is queued with `launch`, its tokens are read
     later with `collect`; `pending` tokens of a request are on their way when its row is queued."""
