@@ -23,6 +23,7 @@ class EngineExecutor:
     def __init__(self, engine: Engine):
         self.engine = engine
         self.cache = engine.cache
+        self.max_request_tokens = engine.max_seq_len       # the scheduler ends a request there with 'length'
         self.sampler = Sampler(engine.runtime.device, engine.options.max_requests)
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -95,7 +96,10 @@ def generate(model, prompts, *, max_tokens: int = 64, temperature: float = 0.0, 
     model: a folder with config.json and model.safetensors, or an Engine to reuse.
     temperature <= 0 is greedy.  Request i draws with seed `seed + i`.
     paged_kv: number of cache pages (default: enough for `inflight_slots` requests of the longest prompt
-    plus max_tokens); ctx_cap: clamp on the tokens of one request."""
+    plus max_tokens); ctx_cap: the most tokens one request may hold, prompt and generated together: a request
+    that reaches it ends there, one whose prompt is longer gets no tokens."""
+    if max_tokens < 0:
+        raise ValueError("max_tokens must not be negative")
     longest = max((len(p) for p in prompts), default=1) + max_tokens
     if ctx_cap:
         longest = min(longest, ctx_cap)
@@ -108,7 +112,7 @@ def generate(model, prompts, *, max_tokens: int = 64, temperature: float = 0.0, 
         cache_tokens = paged_kv * page_size if paged_kv else inflight_slots * per_request
         engine = Engine.from_folder(model, EngineOptions(
             dtype=dtype, page_size=page_size, cache_tokens=cache_tokens, max_requests=inflight_slots,
-            max_step_tokens=max(prefill_ubatch, inflight_slots), max_seq_len=per_request, device=devices))
+            max_step_tokens=max(prefill_ubatch, inflight_slots), max_seq_len=longest, device=devices))
     gen = Generator(engine, prefill_chunk_tokens=prefill_chunk_tokens, prefill_ubatch=prefill_ubatch,
                     inflight_slots=inflight_slots)
     params = [SamplingParams(temperature=temperature, top_p=top_p, top_k=top_k, min_p=min_p,

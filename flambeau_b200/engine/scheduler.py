@@ -25,7 +25,9 @@ fails for lack of pages:
   * if nothing can be scheduled although requests are running (all of them
     in the middle of their prompts, no page free), the youngest is preempted
     in the same way;
-  * a request that cannot fit even alone is finished with reason 'capacity'.
+  * a request that cannot fit even alone is finished with reason 'capacity';
+    one that reaches the most tokens a request may hold (the engine's
+    max_seq_len; --ctx-cap) ends with reason 'length', as at max_tokens.
 
 Running ahead.  While every running request is decoding and none is about to reach its token limit, the next
 step is known but for the token ids, and those are on the device: the scheduler queues it (token ids fed from the
@@ -103,6 +105,8 @@ class Scheduler:
         self.finished: list = []
         self._arrivals = 0
         self.steps = 0
+        # the most tokens one request may hold (prompt and generated together); None: no limit but the pool
+        self.max_request_tokens = getattr(executor, "max_request_tokens", None)
         self._two_phase = all(hasattr(executor, m) for m in ("launch", "collect", "can_run_ahead"))
         self.run_ahead = run_ahead and self._two_phase      # may be switched while running
         self._ahead = None                 # (PlannedStep, handle) of a step that is queued but not collected
@@ -116,6 +120,9 @@ class Scheduler:
         self._arrivals += 1
         if r.params.max_tokens == 0:
             r.finish_reason = "length"
+            self.finished.append(r)
+        elif self.max_request_tokens is not None and len(r.prompt) > self.max_request_tokens:
+            r.finish_reason = "capacity"                   # the prompt alone is longer than a request may be
             self.finished.append(r)
         else:
             self.waiting.append(r)
@@ -300,9 +307,14 @@ class Scheduler:
             out.append((r, int(tok)))
             if not r.params.ignore_eos and int(tok) in r.params.stop_token_ids:
                 self._finish(r, "stop")
-            elif len(r.generated) >= r.params.max_tokens:
+            elif len(r.generated) >= r.params.max_tokens or self._at_limit(r, 0):
                 self._finish(r, "length")
         return out
+
+    def _at_limit(self, r: Request, more: int) -> bool:
+        """With `more` further tokens the request would hold as many tokens as one request may."""
+        return self.max_request_tokens is not None and \
+            len(r.prompt) + len(r.generated) + more >= self.max_request_tokens
 
     def _queue_ahead(self, plan: PlannedStep, handle) -> None:
         """Queue the step after `plan` (whose tokens are not known yet) if it is sure to be one decoded token for
@@ -315,7 +327,8 @@ class Scheduler:
         live = set(id(r) for r in self.running)
         for r in sampled:
             # running, its whole prompt fed by `plan`, and not at its limit with the token that is on its way
-            if id(r) not in live or r.finish_reason is not None or len(r.generated) + 2 > r.params.max_tokens:
+            if id(r) not in live or r.finish_reason is not None or len(r.generated) + 2 > r.params.max_tokens \
+                    or self._at_limit(r, 1):
                 return
         fed_by_plan = {e.request_id: len(e.tokens) for e in plan.entries}
         for r in sampled:

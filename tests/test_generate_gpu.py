@@ -142,6 +142,17 @@ def test_long_decoding_and_first_tokens(model, tmp_path):
     tiny.compare_rows(got, want, tiny.TOL[model["dtype"]], f"long decode {model['name']} {model['dtype']}")
 
 
+def test_context_cap_ends_a_request(model):
+    """--ctx-cap: a request never holds more tokens than that, generated ones included."""
+    from flambeau_b200 import generate
+    prompts = [list(range(1, 41)), list(range(1, 11)), list(range(1, 60))]
+    outs = generate(model["folder"], prompts, max_tokens=20, dtype=model["dtype"], ctx_cap=48, inflight_slots=3)
+    assert [len(o) for o in outs] == [8, 20, 0]
+    free = generate(model["folder"], prompts[:2], max_tokens=20, dtype=model["dtype"], inflight_slots=2)
+    if model["dtype"] == "float32":
+        assert outs[0] == free[0][:8] and outs[1] == free[1]
+
+
 def test_command_line_infer(model):
     prompts = list(tiny.random_requests(model["cfg"], [9, 4], seed=13).values())
     cmd = [sys.executable, str(ROOT / "bin" / "flambeau"), "infer", "--model", str(model["folder"]), "--max-tokens", "5",

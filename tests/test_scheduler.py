@@ -153,6 +153,23 @@ def test_random_load_never_breaks_the_books():
     assert ex.cache.free_pages() == [10] and not ex.cache.requests
 
 
+def test_a_request_ends_at_the_most_tokens_a_request_may_hold():
+    for ahead in (False, True):
+        ex = TwoPhaseExecutor(tokens=256, max_requests=4)
+        ex.max_request_tokens = 20
+        s = Scheduler(ex, token_budget=32, prefill_chunk=8, max_running=4, run_ahead=ahead)
+        a = s.add("a", list(range(12)), SamplingParams(max_tokens=50))     # 12 + 8 = 20: stops there
+        b = s.add("b", list(range(5)), SamplingParams(max_tokens=6))       # its own limit comes first
+        c = s.add("c", list(range(20)), SamplingParams(max_tokens=6))      # the prompt fills it: one token
+        d = s.add("d", list(range(21)), SamplingParams(max_tokens=6))      # longer than a request may be
+        s.run()
+        assert (len(a.generated), a.finish_reason) == (8, "length")
+        assert (len(b.generated), b.finish_reason) == (6, "length")
+        assert (len(c.generated), c.finish_reason) == (1, "length")
+        assert (len(d.generated), d.finish_reason) == (0, "capacity")
+        assert not ex.cache.requests and ex.in_flight == 0
+
+
 def test_prompts_that_do_not_fit_together_are_not_fed_side_by_side():
     """Four prompts of 68 to 90 tokens and a pool of 256: fed side by side they would fill the pool with all four
     in mid-prompt and nothing could run.  The fourth waits until pages are free."""
