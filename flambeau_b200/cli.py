@@ -118,7 +118,12 @@ def main(argv=None) -> int:
     p.set_defaults(fn=cmd_inspect)
 
     a = ap.parse_args(argv)
-    return a.fn(a)
+    from .errors import USER_ERRORS
+    try:
+        return a.fn(a)
+    except USER_ERRORS as e:                       # what the input can cause: one line, no trace
+        sys.stderr.write(f"flambeau {a.cmd}: error: {type(e).__name__}: {e}\n")
+        return 1
 
 
 if __name__ == "__main__":

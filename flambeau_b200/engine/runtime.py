@@ -27,6 +27,10 @@ def parse_dtype(name) -> torch.dtype:
         raise ValueError(f"engine dtype must be one of {sorted(DTYPES)}, not {name!r}") from None
 
 
+class NoDeviceError(RuntimeError):
+    """The engine was asked to run where there is no CUDA device."""
+
+
 class Workspace:
     """A bump arena for the activations of one step.
 
@@ -89,9 +93,9 @@ class Runtime:
         if self.page_size <= 0:
             raise ValueError("page_size must be positive")
         if self.device.type != "cuda":
-            raise RuntimeError("flambeau_b200 runs on a CUDA device only; there is no CPU path")
+            raise NoDeviceError("flambeau_b200 runs on a CUDA device only; there is no CPU path")
         if not torch.cuda.is_available():
-            raise RuntimeError("no CUDA device is available; flambeau_b200 has no CPU path")
+            raise NoDeviceError("no CUDA device is available; flambeau_b200 has no CPU path")
         from ..kernels.library import lib
         lib()                                   # fail now, loudly, if the kernels cannot be built or loaded
         self.ws = Workspace(self.device, workspace_bytes)

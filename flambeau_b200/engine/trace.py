@@ -23,6 +23,10 @@ from .batch import Entry
 from .step import Engine, EngineOptions
 
 
+class TraceError(ValueError):
+    pass
+
+
 def replay(engine: Engine, lines, out_dir, report=None) -> int:
     """Run every step in `lines` (an iterable of JSON strings); returns the number of steps run."""
     out_dir = Path(out_dir)
@@ -32,9 +36,12 @@ def replay(engine: Engine, lines, out_dir, report=None) -> int:
         raw = raw.strip()
         if not raw:
             continue
-        rec = json.loads(raw)
-        step = rec["step"]
-        entries = [Entry(e["id"], list(e["tokens"]), list(e.get("want", []))) for e in rec.get("entries", [])]
+        try:
+            rec = json.loads(raw)
+            step = rec["step"]
+            entries = [Entry(e["id"], list(e["tokens"]), list(e.get("want", []))) for e in rec.get("entries", [])]
+        except (ValueError, KeyError, TypeError) as e:
+            raise TraceError(f"input line {count + 1} is not a step record: {type(e).__name__}: {e}") from None
         logits = engine.step(entries, end=rec.get("end", []))
         if logits is not None and logits.shape[0] > 0:
             host = logits.float().cpu().contiguous().numpy().astype("<f4", copy=False)
@@ -58,13 +65,18 @@ def main(argv=None) -> int:
     ap.add_argument("--max-requests", type=int, default=8)
     args = ap.parse_args(argv)
     tokens = max(64, -(-args.max_tokens // 64) * 64)
-    engine = Engine.from_folder(args.model, EngineOptions(
-        dtype=args.dtype, page_size=args.page_size, cache_tokens=tokens, max_requests=args.max_requests,
-        max_step_tokens=tokens, max_seq_len=tokens))
 
     def report(step):
         sys.stdout.write(f"done {step}\n")
         sys.stdout.flush()
 
-    replay(engine, sys.stdin, args.out, report)
+    from ..errors import USER_ERRORS
+    try:
+        engine = Engine.from_folder(args.model, EngineOptions(
+            dtype=args.dtype, page_size=args.page_size, cache_tokens=tokens, max_requests=args.max_requests,
+            max_step_tokens=tokens, max_seq_len=tokens))
+        replay(engine, sys.stdin, args.out, report)
+    except USER_ERRORS as e:                       # what the input or the model folder can cause: one line, no trace
+        sys.stderr.write(f"trace_run: error: {type(e).__name__}: {e}\n")
+        return 1
     return 0
