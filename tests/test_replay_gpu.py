@@ -71,6 +71,29 @@ def test_mixed_with_page_reuse(case, tmp_path, seed):
     run(case, sched, tmp_path)
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_a_careless_trace(case, tmp_path, seed):
+    """Ids used again after their end, requests ended early, scattered wanted places, steps that want nothing."""
+    from flambeau_b200.engine.step import Engine, EngineOptions
+    from flambeau_b200.engine.trace import replay
+    requests, sched = tiny.schedule_wild(case["cfg"], seed)
+    by_name = {}
+    tokens = 256                                   # four live requests of at most 100 tokens, each rounded up to 64
+    engine = Engine.from_folder(case["folder"], EngineOptions(
+        dtype=case["dtype"], cache_tokens=tokens, max_requests=4, max_step_tokens=256, max_seq_len=128))
+    replay(engine, sched.lines(), tmp_path)
+    engine.cache.check_invariants()
+    got = tiny.read_rows(tmp_path, sched, case["cfg"]["vocab_size"])
+    pcfg, W = pm.read_model_folder(case["folder"])
+    worst = 0.0
+    for (u, p), row in got.items():
+        if u not in by_name:
+            by_name[u] = pm.forward_logits(pcfg, W, requests[u]).numpy()
+        ref = by_name[u]
+        worst = max(worst, float(abs(row.astype("float64") - ref[p]).max()) / float(abs(ref).max()))
+    assert got and worst <= tiny.TOL[case["dtype"]], f"error {worst:.3e} of the logit scale"
+
+
 def test_trace_run_program(case, tmp_path):
     """The program itself, in a process of its own."""
     sched = tiny.schedule_mixed(case["requests"], seed=9)

@@ -154,6 +154,44 @@ def schedule_mixed(requests, seed: int, max_live: int = 4, prompt_fraction: floa
     return s
 
 
+def schedule_wild(cfg: dict, seed: int, max_live: int = 4):
+    """A trace as a careless client writes it: ids that are used again for new requests after their `end`,
+    requests ended before their last token, steps that want nothing or a few scattered places, portions of one
+    token in mid-prompt, requests that sit steps out.  Returns (requests, schedule): the requests are keyed by a
+    serial number, not by the reused id, and so are the schedule's rows."""
+    rng = random.Random(seed)
+    names = ["x", "y", "z", "w", "v"]
+    s = Schedule()
+    requests, live, serial = {}, {}, 0          # live: id -> [serial, tokens, next position, stop position]
+    for _ in range(rng.randint(20, 70)):
+        while len(live) < max_live and rng.random() < 0.5:
+            name = rng.choice([n for n in names if n not in live])
+            n_tok = rng.randint(1, 100)
+            toks = [rng.randrange(cfg["vocab_size"]) for _ in range(n_tok)]
+            stop = n_tok if rng.random() < 0.6 else rng.randint(1, n_tok)
+            live[name] = [serial, toks, 0, stop]
+            requests[serial] = toks
+            serial += 1
+        entries, rows = [], []
+        for name in list(live):
+            u, toks, p, stop = live[name]
+            if p >= stop or (len(live) > 1 and rng.random() < 0.25):
+                continue
+            k = min(rng.choice([1, 1, 2, 3, 7, 20, 64]), stop - p)
+            want = sorted(rng.sample(range(k), rng.randint(0, min(k, 4)))) if rng.random() < 0.8 else []
+            entries.append({"id": name, "tokens": toks[p:p + k], "want": want})
+            rows += [(u, p + w) for w in want]
+            live[name][2] = p + k
+        end = [name for name in list(live) if live[name][2] >= live[name][3] and rng.random() < 0.8]
+        for name in end:
+            del live[name]
+        step = len(s.steps)
+        s.steps.append({"step": step, "entries": entries, "end": end})
+        if rows:
+            s.rows[step] = rows
+    return requests, s
+
+
 def read_rows(out_dir, schedule: Schedule, vocab: int) -> dict:
     """(request id, position) -> float32 logits row, from the files a replay wrote."""
     got = {}
