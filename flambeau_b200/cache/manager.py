@@ -46,10 +46,11 @@ class LayerCacheView:
     """What a mixer sees of the cache during one call."""
     k_pool: Optional[torch.Tensor]
     v_pool: Optional[torch.Tensor]
-    block_table: Optional[torch.Tensor]       # device int32 [sequences of the step, pages per request]
-    page_size: int
-    writable: bool
-    group: int
+    block_table: Optional[torch.Tensor]       # device int32 [sequences of the step, table columns]: live pages only
+    table_base: Optional[torch.Tensor] = None # device int32 [sequences]: the logical page column 0 stands for
+    page_size: int = 16
+    writable: bool = False
+    group: int = -1
     state: Optional[torch.Tensor] = None      # [slots, *shape] for mixers with fixed-size state
 
 
@@ -129,13 +130,17 @@ class CacheGroup:
 
 class CacheManager:
     def __init__(self, plans: list, *, max_tokens: int, page_size: int, max_requests: int, device, dtype,
-                 max_seq_len: int | None = None):
+                 max_seq_len: int | None = None, max_step_tokens: int | None = None):
+        """max_seq_len: the most tokens a request may reach (default: what the pool holds); max_step_tokens:
+        the most tokens one step brings for one request, which bounds the live pages of a windowed group and with
+        them the width of its block table (default: no bound but max_seq_len)."""
         self.page_size = int(page_size)
         self.max_requests = int(max_requests)
         self.device = device
         self.plans = plans
         n_pages = max(1, -(-int(max_tokens) // self.page_size))
         self.max_pages_per_request = -(-int(max_seq_len or max_tokens) // self.page_size)
+        self.max_step_tokens = int(max_step_tokens) if max_step_tokens else None
         # ---- groups ----
         self.groups: list[CacheGroup] = []
         self.group_of_call: dict[int, int] = {}
@@ -147,6 +152,11 @@ class CacheManager:
                     raise ValueError(f"call {ci} reads the cache of call {plan.cache_from}, which owns none")
                 if plan.kv is not None and (plan.kv.kv_heads, plan.kv.head_dim) != (src.kv.kv_heads, src.kv.head_dim):
                     raise ValueError(f"call {ci} and call {plan.cache_from} disagree on the cache geometry")
+                # pages are given back by the owner's window: a reader that looks further back than the owner
+                # would ask for keys whose pages are gone
+                if plan.kv is not None and src.kv.window > 0 and (plan.kv.window == 0 or plan.kv.window > src.kv.window):
+                    raise ValueError(f"call {ci} reads the cache of call {plan.cache_from} with a window of "
+                                     f"{plan.kv.window or 'all'} keys, but that cache keeps only {src.kv.window}")
                 continue
             if plan.kv is not None:
                 by_req.setdefault(plan.kv, []).append(ci)
@@ -165,6 +175,14 @@ class CacheManager:
                 self.state[ci] = torch.zeros((self.max_requests, *plan.state.shape), dtype=sd, device=device)
         self.books = Books([g.n_pages for g in self.groups], [g.req.window for g in self.groups], self.page_size,
                            self.max_requests, self.max_pages_per_request)
+        # Columns of a block-table row: the most live pages a request holds in any group.  A group with a window W
+        # keeps, while a step of k new tokens runs, the pages from position length - W + 1 to length + k.
+        self.table_pages = 1
+        for g in self.groups:
+            live = self.max_pages_per_request
+            if g.req.window > 0 and self.max_step_tokens:
+                live = min(live, -(-(g.req.window + self.max_step_tokens) // self.page_size) + 2)
+            self.table_pages = max(self.table_pages, live)
         for g in self.groups:
             g.pool = PoolView(self.books, g.index)
         self.requests: dict[object, RequestRecord] = {}
@@ -238,18 +256,22 @@ class CacheManager:
     def table_row(self, request_id, group: int) -> list:
         return self.requests[request_id].pages[group]
 
-    def view(self, call: int, tables: list) -> LayerCacheView:
+    def view(self, call: int, tables: list, table_bases: list | None = None) -> LayerCacheView:
         """The cache as call `call` of the run order sees it; `tables[g]` is the device block table of
-        group g for the sequences of this step."""
+        group g for the sequences of this step and `table_bases[g]` the logical page its rows start at."""
         plan = self.plans[call]
         state = self.state.get(call)
         gi = self.group_of_call.get(call)
         if gi is None:
-            return LayerCacheView(None, None, None, self.page_size, False, -1, state)
+            return LayerCacheView(None, None, None, None, self.page_size, False, -1, state)
         owner = plan.cache_from if plan.cache_from is not None else call
         g = self.groups[gi]
-        return LayerCacheView(g.k[owner], g.v[owner], tables[gi], self.page_size,
-                              plan.cache_from is None, gi, state)
+        return LayerCacheView(g.k[owner], g.v[owner], tables[gi], table_bases[gi] if table_bases else None,
+                              self.page_size, plan.cache_from is None, gi, state)
+
+    def first_live_page(self, request_id, group: int) -> int:
+        """The logical page index that the request's block-table row starts at in `group`."""
+        return self.books.first_live_page(self.requests[request_id].slot, group)
 
     # ---- invariants (used by tests) ------------------------------------------
     def check_invariants(self) -> None:

@@ -120,6 +120,9 @@ class Books:
         self._ok(self._lib.fbh_pages(self._h, slot, group, _ptr(out), n))
         return out[:n].tolist()
 
+    def first_live_page(self, slot: int, group: int) -> int:
+        return self._ok(self._lib.fbh_first_live_page(self._h, slot, group))
+
     def n_pages_of(self, slot: int, group: int) -> int:
         return self._ok(self._lib.fbh_pages(self._h, slot, group, None, 0))
 
@@ -129,50 +132,3 @@ class Books:
     @property
     def handle(self):
         return self._h
-
-
-class PagePool:
-    """A pool on its own (one group, requests as page holders): what the cache manager's groups are made of."""
-
-    def __init__(self, n_pages: int):
-        if n_pages <= 0:
-            raise ValueError("a page pool needs at least one page")
-        self.n_pages = int(n_pages)
-        # one request slot per possible holder of a single page; page_size 1 makes a token a page
-        self._books = Books([self.n_pages], [0], 1, self.n_pages + 1, self.n_pages)
-        self._holder: dict = {}              # page id -> slot that holds it
-
-    @property
-    def n_free(self) -> int:
-        return self._books.free_pages()[0]
-
-    @property
-    def n_held(self) -> int:
-        return self.n_pages - self.n_free
-
-    def take(self, count: int) -> list:
-        """`count` page ids, or OutOfPages with nothing taken."""
-        if count < 0:
-            raise ValueError("negative page count")
-        if count > self.n_free:
-            raise OutOfPages(count, self.n_free, self.n_pages)
-        out = []
-        for _ in range(count):
-            slot = self._books.admit()
-            self._books.reserve_all([slot], [1])
-            page = self._books.pages(slot, 0)[0]
-            self._holder[page] = slot
-            out.append(page)
-        return out
-
-    def give_back(self, pages) -> None:
-        for p in pages:
-            if not 0 <= p < self.n_pages:
-                raise PageError(f"page id {p} is outside the pool of {self.n_pages}")
-            slot = self._holder.pop(p, None)
-            if slot is None:
-                raise PageError(f"page {p} is given back but is not held")
-            self._books.release(slot)
-
-    def is_held(self, page: int) -> bool:
-        return self._books.is_held(0, page)

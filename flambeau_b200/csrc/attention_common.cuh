@@ -37,6 +37,8 @@ struct AttnArgs {
     const __nv_bfloat16* k_pool; const __nv_bfloat16* v_pool;
     int page_size, n_pages;
     const int* block_table; int table_stride;
+    const int* table_base;             // per sequence: the logical page that column 0 of its table row stands for
+                                       // (nullptr: page 0); released leading pages are not in the table
     const int* seq_q_start; const int* seq_q_len; const int* seq_pos_start;
     int nh, nkv, hd, window;
     float scale_log2e;
@@ -49,6 +51,14 @@ struct AttnArgs {
     FbPrefetch prefetch;               // split-key: rows to fetch into L2 when a CTA has issued its last tile
     int* status;
 };
+
+// The page id of logical page `logical` of a sequence whose table row `table` starts at logical page `base_page`
+// (-1 where the row has no such column).
+__device__ __forceinline__ int table_page(const AttnArgs& a, const int* table, int base_page, int logical) {
+    const int e = logical - base_page;
+    return (e >= 0 && e < a.table_stride) ? table[e] : -1;
+}
+__device__ __forceinline__ int table_base_of(const AttnArgs& a, int seq) { return a.table_base ? a.table_base[seq] : 0; }
 
 // The keys a group of consecutive query tokens [first, last] of a sequence can see, and where tiles start.
 struct KeyRange { int t_lo, t_hi, tile_lo; };

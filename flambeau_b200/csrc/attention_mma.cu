@@ -87,6 +87,7 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     const int k_begin = kr.tile_lo, k_end = kr.t_hi + 1, t_hi = kr.t_hi;
     const int n_tiles = (k_end - k_begin + KT - 1) / KT;
     const int* table = a.block_table + (size_t)seq * a.table_stride;
+    const int base_page = table_base_of(a, seq);
 
     if (tid == 0) {
         for (int st = 0; st < NST; ++st) mbar_init(smem_u32(&full[st]), TMA ? tma_ops : 2 * KT);
@@ -124,7 +125,7 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
             span = 1;
         }
         if (!(t_first + span > kr.t_lo && t_first < k_end)) return -2;
-        const int page = table[t_first / a.page_size];
+        const int page = table_page(a, table, base_page, t_first / a.page_size);
         return (page < 0 || page >= a.n_pages) ? -1 : page;
     };
 
@@ -378,12 +379,12 @@ template <int HD_MAX, bool TMA>
 int launch_long(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream) {
     constexpr size_t smem = long_smem_bytes(HD_MAX, TMA);
     auto kern = attention_mma_kernel<HD_MAX, TMA>;
-    static bool configured = false;
-    if (!configured && smem > 48 * 1024) {
+    static bool configured[FB_MAX_DEVICES] = {};
+    if (smem > 48 * 1024 && fb_needs_setup(configured)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fb_fail(-2, "attention_mma: cannot reserve %d bytes of shared memory: %s",
                                              (int)smem, cudaGetErrorString(e));
-        configured = true;
+        fb_setup_done(configured);
     }
     const int TQ = 64 * long_row_blocks(HD_MAX) / (a.nh / a.nkv);
     const dim3 grid(((max_q_len + TQ - 1) / TQ) * a.nkv * n_seqs);
@@ -420,15 +421,20 @@ bool attention_tc_enabled() {
 FB_API void fb_set_attention_tc(int on) { g_attention_tc = on ? 1 : 0; }
 
 // q, out: bfloat16 [rows, heads*hd]; pools bfloat16 [pages][kv heads][page size][hd].
-// seq_*: per sequence of the step (device int32).  max_q_len / max_kv_len / any_short / any_long come from the
-// host's copy of the step descriptor.  `scratch` holds the arrival counters and partial results of the split-key arrangement.
+// seq_*: per sequence of the step (device int32); table_base (may be null): the logical page that column 0 of each
+// sequence's table row stands for.  max_q_len / max_kv_len / any_short / any_long come from the host's copy of the
+// step descriptor.  `scratch` holds the arrival counters and partial results of the split-key arrangement.
+// prefetch_*: the first prefetch_bytes_per_row bytes of each of prefetch_rows rows (prefetch_row_stride bytes
+// apart, from prefetch_base) are fetched into L2 when the split-key kernel's stream of cache ends: the matrix of
+// the product that follows (a hint; null base: none).
 FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, long long out_stride,
                                   const void* k_pool, const void* v_pool, int page_size, int n_pages,
-                                  const int* block_table, int table_stride, const int* seq_q_start,
-                                  const int* seq_q_len, const int* seq_pos_start, int n_seqs, int max_q_len,
-                                  int max_kv_len, int any_short, int any_long, int nh, int nkv, int hd, int window,
-                                  float scale, float* scratch, long long scratch_floats, int* status,
-                                  cudaStream_t stream) {
+                                  const int* block_table, int table_stride, const int* table_base,
+                                  const int* seq_q_start, const int* seq_q_len, const int* seq_pos_start, int n_seqs,
+                                  int max_q_len, int max_kv_len, int any_short, int any_long, int nh, int nkv, int hd,
+                                  int window, float scale, float* scratch, long long scratch_floats,
+                                  const void* prefetch_base, long long prefetch_rows, long long prefetch_row_stride,
+                                  int prefetch_bytes_per_row, int* status, cudaStream_t stream) {
     FB_REQUIRE(n_seqs >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention_mma: bad sizes");
     FB_REQUIRE(nh % nkv == 0, "attention_mma: %d query heads are not a multiple of %d key/value heads", nh, nkv);
     FB_REQUIRE(hd % 8 == 0 && hd <= 256, "attention_mma: head size %d must be a multiple of 8 and at most 256", hd);
@@ -444,7 +450,7 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     a.out = (__nv_bfloat16*)out; a.out_stride = (long)out_stride;
     a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
     a.page_size = page_size; a.n_pages = n_pages;
-    a.block_table = block_table; a.table_stride = table_stride;
+    a.block_table = block_table; a.table_stride = table_stride; a.table_base = table_base;
     a.seq_q_start = seq_q_start; a.seq_q_len = seq_q_len; a.seq_pos_start = seq_pos_start;
     a.nh = nh; a.nkv = nkv; a.hd = hd; a.window = window;
     a.scale_log2e = scale * 1.4426950408889634f;
@@ -463,7 +469,7 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     }
     a.n_seqs = n_seqs;
     a.short_ctas = 0; a.min_tiles = 1;
-    a.prefetch = fb_take_prefetch_hint();
+    a.prefetch = fb_make_prefetch(prefetch_base, prefetch_rows, prefetch_row_stride, prefetch_bytes_per_row);
     a.part_o = nullptr; a.part_ml = nullptr; a.part_cnt = nullptr;
     if (any_long) {
         const int rc = (attention_tc_enabled() && fb_attention_tc_takes(a, tma))

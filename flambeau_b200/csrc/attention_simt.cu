@@ -9,7 +9,8 @@
 // online-softmax update is the one of attention_prefill_f16_paged.cu:69-149).
 //
 // The same kernel serves prompt portions and decoded tokens in one launch: a
-// row only needs its position and the block table of its sequence.  It is the
+// row only needs its position and the block table of its sequence (whose row starts
+// at logical page table_base[sequence], or at page 0 without table_base).  It is the
 // attention of the true 32-bit path and the reference for the faster kernels.
 #include "common.cuh"
 
@@ -18,6 +19,7 @@ __global__ void __launch_bounds__(128)
 paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ out, long out_stride,
                             const T* __restrict__ k_pool, const T* __restrict__ v_pool, int page_size,
                             int n_pages, const int* __restrict__ block_table, int table_stride,
+                            const int* __restrict__ table_base,
                             const int* __restrict__ positions, const int* __restrict__ row_seq, int n, int nh,
                             int nkv, int hd, int window, float scale, int* status) {
     fb_pdl_launch_dependents();
@@ -40,6 +42,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
     const int p = positions[row];
     const int t0 = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int* table = block_table + (size_t)row_seq[row] * table_stride;
+    const int base_page = table_base ? table_base[row_seq[row]] : 0;     // the table row starts at this logical page
 
     float m = -INFINITY, l = 0.0f;
     float acc[NDR];
@@ -52,7 +55,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
         float s = -INFINITY;
         int my_page = -1;
         if (valid) {
-            my_page = table[t / page_size];
+            const int entry = t / page_size - base_page;
+            my_page = (entry >= 0 && entry < table_stride) ? table[entry] : -1;
             if (my_page < 0 || my_page >= n_pages) {
                 atomicOr(status, FB_STATUS_BAD_PAGE);
                 my_page = -1;
@@ -98,21 +102,22 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
 template <typename T, int NDR>
 static int launch_attention_simt(const void* q, long q_stride, void* out, long out_stride, const void* k_pool,
                                  const void* v_pool, int page_size, int n_pages, const int* block_table,
-                                 int table_stride, const int* positions, const int* row_seq, int n, int nh,
+                                 int table_stride, const int* table_base, const int* positions, const int* row_seq,
+                                 int n, int nh,
                                  int nkv, int hd, int window, float scale, int* status, cudaStream_t stream) {
     const long items = (long)n * nh;
     const unsigned blocks = (unsigned)((items + 3) / 4);
     fb_launch((paged_attention_simt_kernel<T, NDR>), blocks, 128, 4 * hd * sizeof(float), stream, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, page_size, n_pages,
-        block_table, table_stride, positions, row_seq, n, nh, nkv, hd, window, scale, status);
+        block_table, table_stride, table_base, positions, row_seq, n, nh, nkv, hd, window, scale, status);
     return fb_check_launch("paged_attention_simt");
 }
 
 FB_API int fb_paged_attention_simt(const void* q, long long q_stride, void* out, long long out_stride, int dtype,
                                    const void* k_pool, const void* v_pool, int page_size, int n_pages,
-                                   const int* block_table, int table_stride, const int* positions,
-                                   const int* row_seq, int n, int nh, int nkv, int hd, int window, float scale,
-                                   int* status, cudaStream_t stream) {
+                                   const int* block_table, int table_stride, const int* table_base,
+                                   const int* positions, const int* row_seq, int n, int nh, int nkv, int hd,
+                                   int window, float scale, int* status, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention: bad sizes n=%d heads=%d kv=%d hd=%d", n, nh, nkv, hd);
     FB_REQUIRE(nh % nkv == 0, "attention: %d query heads are not a multiple of %d key/value heads", nh, nkv);
     FB_REQUIRE(hd <= 512, "attention: head size %d is larger than 512", hd);
@@ -120,8 +125,8 @@ FB_API int fb_paged_attention_simt(const void* q, long long q_stride, void* out,
     if (n == 0) return 0;
 #define FB_ATTN_CASE(NDR)                                                                                      \
     FB_DISPATCH_DTYPE(dtype, T, return (launch_attention_simt<T, NDR>(q, (long)q_stride, out, (long)out_stride,     \
-        k_pool, v_pool, page_size, n_pages, block_table, table_stride, positions, row_seq, n, nh, nkv, hd,    \
-        window, scale, status, stream)))
+        k_pool, v_pool, page_size, n_pages, block_table, table_stride, table_base, positions, row_seq, n, nh, \
+        nkv, hd, window, scale, status, stream)))
     if (hd <= 32) { FB_ATTN_CASE(1); }
     else if (hd <= 64) { FB_ATTN_CASE(2); }
     else if (hd <= 128) { FB_ATTN_CASE(4); }

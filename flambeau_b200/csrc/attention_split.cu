@@ -197,6 +197,7 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
         int seq, kvh, q_len, q_start, pos0, t_lo, t_hi, k_begin, k_end, n_tiles;
         int c_first, n_chunks;             // the first CTA with a segment of this pair, and how many have one
         const int* table;
+        int base_page;                     // the logical page that column 0 of the table row stands for
     };
     auto next_seg = [&]() {                // the segment that starts at tile g; moves g past it
         while ((long)a.nkv * ss.prefix[cur_seq + 1] <= g) ++cur_seq;
@@ -213,6 +214,7 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
         sg.k_end = min(kr.t_hi + 1, kr.tile_lo + tile_b * KT);
         sg.n_tiles = tile_b - tile_a;
         sg.table = a.block_table + (size_t)seq * a.table_stride;
+        sg.base_page = table_base_of(a, seq);
         const long first_tile = (long)a.nkv * ss.prefix[seq] + (long)kvh * n;   // of the pair, in the line of tiles
         sg.c_first = (int)(first_tile / per);
         sg.n_chunks = (int)((first_tile + n - 1) / per) - sg.c_first + 1;
@@ -272,7 +274,7 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
                 if (TMA) { t_first = tile_start + ((op >> 1) / col_blocks) * a.page_size; span = a.page_size; }
                 else { t_first = tile_start + (op & (KT - 1)); span = 1; }
                 if (!(t_first + span > sg.t_lo && t_first < sg.k_end)) continue;
-                const int page = sg.table[t_first / a.page_size];
+                const int page = table_page(a, sg.table, sg.base_page, t_first / a.page_size);
                 pages[u] = (page < 0 || page >= a.n_pages) ? -1 : page;
             }
         };
@@ -594,17 +596,18 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
 template <int HD_MAX, bool TMA>
 int launch_split(AttnArgs& a, int n_seqs, long long scratch_floats, cudaStream_t stream) {
     auto kern = attention_split_kernel<HD_MAX, TMA>;
-    static int sms = 0, per_sm = 0, per_sm_for = -1;
+    static int per_sm = 0, per_sm_for = -1;
+    static bool configured[FB_MAX_DEVICES] = {};
     const size_t smem = split_smem_bytes(HD_MAX, TMA, (size_t)n_seqs);
-    if (!sms) {
+    if (fb_needs_setup(configured)) {
         const size_t room = split_smem_bytes(HD_MAX, TMA, 1024);             // up to 1024 sequences in a step
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)room);
         if (e != cudaSuccess) return fb_fail(-2, "attention_split: cannot reserve %d bytes of shared memory: %s",
                                              (int)room, cudaGetErrorString(e));
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        fb_setup_done(configured);
+        per_sm_for = -1;
     }
+    const int sms = fb_sm_count();
     if (per_sm_for != (n_seqs + 31) / 32) {           // the per-sequence arrays grow with the step
         per_sm_for = (n_seqs + 31) / 32;
         cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(

@@ -151,10 +151,10 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
         // Page ids come from the block table 32 at a time (one per lane, the next 32 already on their way), so a
         // tile does not wait for the table: -2 = nothing to fetch (no query of the CTA sees the page), -1 = the
         // table has no page although one is needed.
-        const int first_entry = k_begin / a.page_size;          // the table entry of tile 0's first page
+        const int first_entry = k_begin / a.page_size - table_base_of(a, seq);   // the table entry of tile 0's first page
         auto entries = [&](int block) -> int {                  // table entries first_entry + 32 * block + lane
-            const int e = first_entry + 32 * block + lane;
-            return e < a.table_stride ? table[e] : -1;
+            const int e = first_entry + 32 * block + lane;      // (below 0: a page before the row's first, never needed)
+            return (e >= 0 && e < a.table_stride) ? table[e] : -1;
         };
         int ids_block = 0, ids_cur = entries(0), ids_next = entries(1);
         auto lookup = [&](int j) -> int {
@@ -409,12 +409,12 @@ template <int HD, int RT>
 int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream) {
     auto kern = attention_tc_kernel<HD, RT>;
     using SM = TcSmem<HD, RT>;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[FB_MAX_DEVICES] = {};
+    if (fb_needs_setup(configured)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::BYTES);
         if (e != cudaSuccess) return fb_fail(-2, "attention_tc: cannot reserve %d bytes of shared memory: %s",
                                              SM::BYTES, cudaGetErrorString(e));
-        configured = true;
+        fb_setup_done(configured);
     }
     const int TQ = RT * BM / (a.nh / a.nkv);
     const dim3 grid(((max_q_len + TQ - 1) / TQ) * a.nkv * n_seqs);
@@ -425,12 +425,7 @@ int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream)
 // Two row tiles per CTA when that still gives every SM a CTA, else one.
 template <int HD>
 int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream) {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
+    const int sms = fb_sm_count();
     const int TQ2 = 2 * BM / (a.nh / a.nkv);
     const long ctas2 = (long)((max_q_len + TQ2 - 1) / TQ2) * a.nkv * n_seqs;      // an upper bound: short sequences leave early
     return ctas2 >= sms ? launch_tc<HD, 2>(a, n_seqs, max_q_len, stream) : launch_tc<HD, 1>(a, n_seqs, max_q_len, stream);

@@ -31,6 +31,35 @@ int fb_check_launch(const char* what);          // cudaGetLastError -> fb_fail
         if (!(cond)) return fb_fail(-1, __VA_ARGS__);           \
     } while (0)
 
+// ---- the device ---------------------------------------------------------------
+constexpr int FB_MAX_DEVICES = 64;
+int fb_device_ordinal();    // the current device, clamped into [0, FB_MAX_DEVICES)
+int fb_sm_count();          // multiprocessors of the current device (asked once per device)
+
+// Set-up that a launcher does once per device (raising a kernel's shared-memory limit): `flags` is the
+// launcher's own static array of FB_MAX_DEVICES zeros.  Two host threads may both see "not yet" and both do the
+// set-up, which is harmless because the set-up is idempotent.
+inline bool fb_needs_setup(const bool* flags) { return !flags[fb_device_ordinal()]; }
+inline void fb_setup_done(bool* flags) { flags[fb_device_ordinal()] = true; }
+
+// Weights of the launchers' cost models (how many shares of K pay off): about what one device streams from
+// memory and what one multiprocessor's tensor pipe multiplies.  They rank choices; nothing is sized by them.
+constexpr double FB_MODEL_HBM_BYTES_PER_S = 6.0e12;
+constexpr double FB_MODEL_SM_FLOPS = 9.0e12;
+
+// ---- activations of gated feed-forwards -----------------------------------------
+// out = act(gate) * up.  The code travels as a launcher argument (0 = no gating where that is an option).
+enum FbAct : int { FB_ACT_SILU = 1, FB_ACT_GELU_TANH = 2 };
+inline bool fb_act_known(int act) { return act == FB_ACT_SILU || act == FB_ACT_GELU_TANH; }
+__device__ __forceinline__ float fb_gate_times(int act, float g, float u) {
+    if (act == FB_ACT_GELU_TANH) {
+        // 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
+        const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+        return 0.5f * g * (1.0f + t) * u;
+    }
+    return g / (1.0f + expf(-g)) * u;             // SiLU (crates/model-ops/src/ops/activation.rs:107-118)
+}
+
 // ---- launches ---------------------------------------------------------------
 // Kernels of a step run back to back on one stream.  With programmatic dependent launch the next kernel of the
 // stream may be scheduled while this one is still draining: every kernel begins with fb_pdl_launch_dependents()
@@ -66,14 +95,16 @@ inline void fb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
 // ---- a running start for the product that follows ---------------------------
 // The first `bytes` of every row of a weight matrix, fetched into L2 by a kernel that has the memory system to
 // spare (the split-key attention kernel when its stream of cache ends), so that the product after it finds its
-// first k-blocks there.  Set for the next launch with fb_set_prefetch_hint(); a hint, nothing depends on it.
+// first k-blocks there.  It travels in the launcher's arguments; a hint, nothing depends on it.
 struct FbPrefetch {
     const char* base;      // nullptr: nothing to do
     int rows;
     long row_stride;       // bytes
     int bytes;             // per row, a multiple of 16
 };
-FbPrefetch fb_take_prefetch_hint();     // the pending hint (cleared by the call)
+// The hint for `rows` rows `row_stride_bytes` apart from `base`, `bytes_per_row` of each; an empty hint when the
+// arguments cannot be used (no base, unaligned rows, too few bytes).
+FbPrefetch fb_make_prefetch(const void* base, long long rows, long long row_stride_bytes, int bytes_per_row);
 
 __device__ __forceinline__ void fb_prefetch_issue(const FbPrefetch& pf, long worker, long n_workers) {
     if (!pf.base) return;

@@ -1,5 +1,5 @@
 // Row-wise kernels between the matrix products: embedding gather, fused
-// residual add + RMSNorm, rotary tables, rotary + paged cache write, SiLU*mul.
+// residual add + RMSNorm, rotary tables, rotary + paged cache write, act(gate)*up.
 // All arithmetic is float32 whatever the storage type; the residual stream
 // itself is float32 in both engine modes.
 #include "common.cuh"
@@ -38,14 +38,15 @@ FB_API int fb_embedding(const void* table, int table_dtype, const int* ids, floa
 //   r = rows ? rows[j] : j
 //   v = x[r] + sum_p delta[p][r]        (delta optional; n_partials slabs, slab stride given)
 //   if (!rows && delta) x[r] = v        (the stream is updated in place)
-//   out[j] = v * w / sqrt(mean(v^2) + eps)
+//   out[j] = v * (w + w_offset) / sqrt(mean(v^2) + eps)      (w_offset 0 for a plain weight, 1 for a "1 + w" norm)
 // crates/kernels-hip/src/kernels/rmsnorm_f16_add_residual.cu; rmsnorm_f16.cu:41-85.
 // The row lives in shared memory between the two passes.
 // ---------------------------------------------------------------------------
 template <typename TD, typename TW, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_partials,
                                    size_t partial_stride, const TW* __restrict__ w,
-                                   TO* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+                                   TO* __restrict__ out, const int* __restrict__ rows, int H, float eps,
+                                   float w_offset) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     extern __shared__ float row[];
@@ -68,7 +69,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
     TO* o = out + (size_t)j * H;
     for (int c = threadIdx.x; c < H; c += blockDim.x)
-        o[c] = fb_from_float<TO>(row[c] * fb_to_float(w[c]) * inv);
+        o[c] = fb_from_float<TO>(row[c] * (fb_to_float(w[c]) + w_offset) * inv);
 }
 
 // Fast path: width a multiple of 4 and at most 4 * VPT * blockDim: every thread keeps its part of the row in
@@ -98,7 +99,7 @@ template <typename TD, typename TW, typename TO, int VPT>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_partials,
                                        size_t partial_stride, const TW* __restrict__ w, TO* __restrict__ out,
-                                       const int* __restrict__ rows, int H, float eps) {
+                                       const int* __restrict__ rows, int H, float eps, float w_offset) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     __shared__ float red[32];
@@ -113,6 +114,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
         if (c < nvec) {
             v[i] = Vec4<float>::load(xr + 4 * c);
             wv[i] = Vec4<TW>::load(w + 4 * c);
+            wv[i].x += w_offset; wv[i].y += w_offset; wv[i].z += w_offset; wv[i].w += w_offset;
         } else {
             v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             wv[i] = v[i];
@@ -168,14 +170,17 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
 template <typename TD, typename TW, typename TO, int R, int V>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta, const TW* __restrict__ w,
-                        TO* __restrict__ out, int n, int H, float eps) {
+                        TO* __restrict__ out, int n, int H, float eps, float w_offset) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     __shared__ float red[R][32];
     const int r0 = R * blockIdx.x;
     float4 a[R][V], d[R][V], wv[V];
 #pragma unroll
-    for (int v = 0; v < V; ++v) wv[v] = Vec4<TW>::load(w + 4 * (threadIdx.x + v * blockDim.x));
+    for (int v = 0; v < V; ++v) {
+        wv[v] = Vec4<TW>::load(w + 4 * (threadIdx.x + v * blockDim.x));
+        wv[v].x += w_offset; wv[v].y += w_offset; wv[v].z += w_offset; wv[v].w += w_offset;
+    }
 #pragma unroll
     for (int r = 0; r < R; ++r)                     // a row past the end reads the last row again and stores nothing
 #pragma unroll
@@ -223,7 +228,7 @@ add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta, con
 template <typename TD, typename TW, typename TO>
 static int launch_add_rmsnorm(float* x, const void* delta, int n_partials, size_t partial_stride,
                               const void* w, void* out, const int* rows, int n_out, int H, float eps,
-                              cudaStream_t stream) {
+                              float w_offset, cudaStream_t stream) {
     const bool aligned = H % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
                          ((uintptr_t)out % 16 == 0) && (!delta || ((uintptr_t)delta % 16 == 0 && partial_stride % 4 == 0));
     const int nvec4 = H / 4, per_thread = (nvec4 + 1023) / 1024;
@@ -231,7 +236,7 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_partials, size_
         const int threads = nvec4 / per_thread;
 #define FB_NORM_ROWS(R_, V_)                                                                                  \
         fb_launch((add_rmsnorm_rows_kernel<TD, TW, TO, R_, V_>), (n_out + R_ - 1) / R_, threads, 0, stream, x, \
-                  (const TD*)delta, (const TW*)w, (TO*)out, n_out, H, eps)
+                  (const TD*)delta, (const TW*)w, (TO*)out, n_out, H, eps, w_offset)
         if (per_thread == 2) FB_NORM_ROWS(1, 2); else if (nvec4 <= 256) FB_NORM_ROWS(4, 1); else FB_NORM_ROWS(2, 1);
 #undef FB_NORM_ROWS
         return fb_check_launch("add_rmsnorm");
@@ -242,7 +247,7 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_partials, size_
         const int vpt = (nvec + threads - 1) / threads;
 #define FB_NORM_VEC(V)                                                                                        \
         fb_launch((add_rmsnorm_vec_kernel<TD, TW, TO, V>), n_out, threads, 0, stream, x, (const TD*)delta, n_partials,  \
-            partial_stride, (const TW*)w, (TO*)out, rows, H, eps)
+            partial_stride, (const TW*)w, (TO*)out, rows, H, eps, w_offset)
         if (vpt == 1) FB_NORM_VEC(1); else if (vpt == 2) FB_NORM_VEC(2); else FB_NORM_VEC(4);
 #undef FB_NORM_VEC
         return fb_check_launch("add_rmsnorm");
@@ -255,20 +260,20 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_partials, size_
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     fb_launch((kern), n_out, threads, smem, stream, x, (const TD*)delta, n_partials, partial_stride, (const TW*)w,
-                                           (TO*)out, rows, H, eps);
+                                           (TO*)out, rows, H, eps, w_offset);
     return fb_check_launch("add_rmsnorm");
 }
 
 FB_API int fb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_partials,
                           long long partial_stride, const void* w, int w_dtype, void* out, int out_dtype,
-                          const int* rows, int n_out, int H, float eps, cudaStream_t stream) {
+                          const int* rows, int n_out, int H, float eps, float w_offset, cudaStream_t stream) {
     FB_REQUIRE(n_out >= 0 && H > 0, "add_rmsnorm: bad sizes n=%d H=%d", n_out, H);
     FB_REQUIRE(eps > 0.0f, "add_rmsnorm: eps must be positive");
     if (n_out == 0) return 0;
     if (!delta) { delta_dtype = FB_F32; n_partials = 0; }
     FB_DISPATCH_DTYPE(delta_dtype, TD, FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(out_dtype, TO,
         return (launch_add_rmsnorm<TD, TW, TO>(x, delta, n_partials, (size_t)partial_stride, w, out, rows,
-                                               n_out, H, eps, stream)))));
+                                               n_out, H, eps, w_offset, stream)))));
     return 0;
 }
 
@@ -304,7 +309,8 @@ FB_API int fb_rope_table(const int* positions, const double* inv_freq, float* co
 // Rotary (split-half pairs (i, i+half)) on q in place and on k on its way into
 // the cache; v is copied into the cache.  One block per token.
 // Cache layout: [page][kv head][slot in page][head_dim]; the physical page of
-// logical position p of sequence s is block_table[s*table_stride + p/page_size].
+// logical position p of sequence s is block_table[s*table_stride + p/page_size - table_base[s]]: a table row
+// starts at the sequence's first live page (table_base == nullptr: at page 0).
 // crates/kernels-hip/src/kernels/rope_neox_partial_f16.cu:39-52 (rotation),
 // kv_append_f16_paged_prefill.cu (row placement).
 // ---------------------------------------------------------------------------
@@ -331,6 +337,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stri
                                      const float* __restrict__ sin_t, int half,
                                      const int* __restrict__ positions, const int* __restrict__ row_seq,
                                      const int* __restrict__ block_table, int table_stride,
+                                     const int* __restrict__ table_base,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size, int n_pages,
                                      int nh, int nkv, int hd, int write_kv, int* status) {
     fb_pdl_launch_dependents();
@@ -360,7 +367,9 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stri
     if (!write_kv) return;
     const int h = hy - nh;
     const int pos = positions[t];
-    const int page = block_table[(size_t)row_seq[t] * table_stride + pos / page_size];
+    const int seq = row_seq[t];
+    const int entry = pos / page_size - (table_base ? table_base[seq] : 0);
+    const int page = (entry >= 0 && entry < table_stride) ? block_table[(size_t)seq * table_stride + entry] : -1;
     if (page < 0 || page >= n_pages) {
         if (threadIdx.x == 0) atomicOr(status, FB_STATUS_BAD_PAGE);
         return;
@@ -411,8 +420,8 @@ rope_kv_write_vec_kernel(const TI* __restrict__ q_in, long q_in_stride, int n_pa
                          const TI* __restrict__ v, long v_stride, const float* __restrict__ cos_t,
                          const float* __restrict__ sin_t, int half, const int* __restrict__ positions,
                          const int* __restrict__ row_seq, const int* __restrict__ block_table, int table_stride,
-                         T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size, int n_pages, int n, int nh,
-                         int nkv, int hd, int write_kv, int* status) {
+                         const int* __restrict__ table_base, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                         int page_size, int n_pages, int n, int nh, int nkv, int hd, int write_kv, int* status) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     const int t0 = blockIdx.x * TOK;
@@ -437,7 +446,11 @@ rope_kv_write_vec_kernel(const TI* __restrict__ q_in, long q_in_stride, int n_pa
 #pragma unroll
         for (int i = 0; i < TOK; ++i) pos[i] = positions[tok[i]];
 #pragma unroll
-        for (int i = 0; i < TOK; ++i) page[i] = block_table[(size_t)row_seq[tok[i]] * table_stride + pos[i] / page_size];
+        for (int i = 0; i < TOK; ++i) {
+            const int seq = row_seq[tok[i]];
+            const int entry = pos[i] / page_size - (table_base ? table_base[seq] : 0);
+            page[i] = (entry >= 0 && entry < table_stride) ? block_table[(size_t)seq * table_stride + entry] : -1;
+        }
 #pragma unroll
         for (int i = 0; i < TOK; ++i) {
             if (page[i] < 0 || page[i] >= n_pages) {
@@ -510,7 +523,8 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, int n_parti
                             const void* k, long long k_stride, const void* v, long long v_stride, int in_dtype,
                             int out_dtype, const float* cos_t, const float* sin_t, int half,
                             const int* positions, const int* row_seq, const int* block_table,
-                            int table_stride, void* k_pool, void* v_pool, int page_size, int n_pages, int n,
+                            int table_stride, const int* table_base, void* k_pool, void* v_pool, int page_size,
+                            int n_pages, int n,
                             int nh, int nkv, int hd, int write_kv, int* status, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && nh > 0 && nkv >= 0 && hd > 0, "rope_kv_write: bad sizes");
     FB_REQUIRE(half >= 0 && 2 * half <= hd, "rope_kv_write: rotary width %d exceeds head size %d", 2 * half, hd);
@@ -535,8 +549,8 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, int n_parti
             (fb_launch((rope_kv_write_vec_kernel<TI, T, TOK_>), dim3((n + TOK_ - 1) / TOK_, (items + 255) / 256), 256, \
                 0, stream, (const TI*)q_in, (long)q_in_stride, n_partials, (long)partial_stride, (T*)q_out,   \
                 (long)q_out_stride, (const TI*)k, (long)k_stride, (const TI*)v, (long)v_stride, cos_t, sin_t, \
-                half, positions, row_seq, block_table, table_stride, (T*)k_pool, (T*)v_pool, page_size,       \
-                n_pages, n, nh, nkv, hd, write_kv, status))))
+                half, positions, row_seq, block_table, table_stride, table_base, (T*)k_pool, (T*)v_pool,      \
+                page_size, n_pages, n, nh, nkv, hd, write_kv, status))))
         if (per == 2) FB_ROPE_VEC(2); else FB_ROPE_VEC(1);
 #undef FB_ROPE_VEC
         return fb_check_launch("rope_kv_write");
@@ -544,21 +558,19 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, int n_parti
     FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
         (fb_launch((rope_kv_write_kernel<TI, T>), dim3(n, nh + (write_kv ? nkv : 0)), hd >= 128 ? 64 : 32, 0, stream, (const TI*)q_in, q_in_stride, n_partials, (long)partial_stride, (T*)q_out, q_out_stride,
             (const TI*)k, k_stride, (const TI*)v, v_stride, cos_t, sin_t, half, positions, row_seq, block_table,
-            table_stride, (T*)k_pool, (T*)v_pool, page_size, n_pages, nh, nkv, hd, write_kv, status))));
+            table_stride, table_base, (T*)k_pool, (T*)v_pool, page_size, n_pages, nh, nkv, hd, write_kv, status))));
     return fb_check_launch("rope_kv_write");
 }
 
 // ---------------------------------------------------------------------------
-// SiLU(gate) * up on a fused [n, 2I] buffer whose columns alternate: column 2c is gate c, column 2c+1 is up c
+// act(gate) * up on a fused [n, 2I] buffer whose columns alternate: column 2c is gate c, column 2c+1 is up c
 // (the feed-forward stacks its gate and up weights row by row in that order, so that the tensor-core product
 // can apply the activation in its epilogue with a neighbour exchange; this kernel serves the other paths).
 // crates/kernels-hip/src/kernels/swiglu_f32_to_f16.cu; activation.rs:107-118.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ float silu_times(float g, float u) { return g / (1.0f + expf(-g)) * u; }
-
 template <typename TI, typename T>
-__global__ void silu_mul_kernel(const TI* __restrict__ gu, long stride, int n_partials, long partial_stride,
-                                T* __restrict__ out, int n, int I) {
+__global__ void gate_mul_kernel(const TI* __restrict__ gu, long stride, int n_partials, long partial_stride,
+                                T* __restrict__ out, int n, int I, int act) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -567,13 +579,13 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, long stride, int n_pa
     const TI* row = gu + (size_t)r * stride;
     const float g = slab_sum(row, 2 * c, n_partials, partial_stride);
     const float u = slab_sum(row, 2 * c + 1, n_partials, partial_stride);
-    out[idx] = fb_from_float<T>(silu_times(g, u));
+    out[idx] = fb_from_float<T>(fb_gate_times(act, g, u));
 }
 
 // Two outputs per thread from one 4-wide load (g0, u0, g1, u1); I even, strides multiples of 4, aligned rows.
 template <typename TI, typename T>
-__global__ void silu_mul_vec_kernel(const TI* __restrict__ gu, long stride, int n_partials, long partial_stride,
-                                    T* __restrict__ out, int n, int I) {
+__global__ void gate_mul_vec_kernel(const TI* __restrict__ gu, long stride, int n_partials, long partial_stride,
+                                    T* __restrict__ out, int n, int I, int act) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     const int nvec = I >> 1;
@@ -582,28 +594,30 @@ __global__ void silu_mul_vec_kernel(const TI* __restrict__ gu, long stride, int 
     const int r = (int)(idx / nvec), c = (int)(idx - (size_t)r * nvec);
     const float4 v = slab_sum4(gu + (size_t)r * stride + 4 * c, n_partials, partial_stride);
     T* o = out + (size_t)r * I + 2 * c;
-    o[0] = fb_from_float<T>(silu_times(v.x, v.y));
-    o[1] = fb_from_float<T>(silu_times(v.z, v.w));
+    o[0] = fb_from_float<T>(fb_gate_times(act, v.x, v.y));
+    o[1] = fb_from_float<T>(fb_gate_times(act, v.z, v.w));
 }
 
 // gate_up has dtype in_dtype and may be split-K shares (n_partials slabs partial_stride elements apart);
-// out has dtype out_dtype.
-FB_API int fb_silu_mul(const void* gate_up, long long stride, int in_dtype, int n_partials,
-                       long long partial_stride, void* out, int out_dtype, int n, int I, cudaStream_t stream) {
-    FB_REQUIRE(n >= 0 && I > 0 && stride >= 2LL * I, "silu_mul: bad sizes n=%d I=%d stride=%lld", n, I, stride);
+// out has dtype out_dtype; `act` is an FbAct code.
+FB_API int fb_gate_mul(const void* gate_up, long long stride, int in_dtype, int n_partials,
+                       long long partial_stride, void* out, int out_dtype, int n, int I, int act,
+                       cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && I > 0 && stride >= 2LL * I, "gate_mul: bad sizes n=%d I=%d stride=%lld", n, I, stride);
+    FB_REQUIRE(fb_act_known(act), "gate_mul: unknown activation code %d", act);
     if (n == 0) return 0;
     if (n_partials < 1) n_partials = 1;
     const bool vec = I % 2 == 0 && stride % 4 == 0 && partial_stride % 4 == 0 && (uintptr_t)gate_up % 16 == 0;
     if (vec) {
         const size_t total = (size_t)n * (I / 2);
         FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
-            (fb_launch((silu_mul_vec_kernel<TI, T>), (unsigned)((total + 255) / 256), 256, 0, stream,
-                (const TI*)gate_up, stride, n_partials, (long)partial_stride, (T*)out, n, I))));
-        return fb_check_launch("silu_mul");
+            (fb_launch((gate_mul_vec_kernel<TI, T>), (unsigned)((total + 255) / 256), 256, 0, stream,
+                (const TI*)gate_up, stride, n_partials, (long)partial_stride, (T*)out, n, I, act))));
+        return fb_check_launch("gate_mul");
     }
     const size_t total = (size_t)n * I;
     FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
-        (fb_launch((silu_mul_kernel<TI, T>), (unsigned)((total + 255) / 256), 256, 0, stream,
-            (const TI*)gate_up, stride, n_partials, (long)partial_stride, (T*)out, n, I))));
-    return fb_check_launch("silu_mul");
+        (fb_launch((gate_mul_kernel<TI, T>), (unsigned)((total + 255) / 256), 256, 0, stream,
+            (const TI*)gate_up, stride, n_partials, (long)partial_stride, (T*)out, n, I, act))));
+    return fb_check_launch("gate_mul");
 }

@@ -12,23 +12,33 @@ int g_fb_pdl = 1;
 // Switches programmatic dependent launch on (1, the default) or off (0) for all later launches.
 FB_API void fb_set_pdl(int on) { g_fb_pdl = on ? 1 : 0; }
 
-static thread_local FbPrefetch g_prefetch = {nullptr, 0, 0, 0};
-
-// The next launch of the bfloat16 attention (its split-key kernel) also fetches the first
-// `bytes_per_row` bytes of each of `rows` rows (`row_stride_bytes` apart, from `base`) into L2.
-FB_API void fb_set_prefetch_hint(const void* base, long long rows, long long row_stride_bytes, int bytes_per_row) {
+FbPrefetch fb_make_prefetch(const void* base, long long rows, long long row_stride_bytes, int bytes_per_row) {
+    FbPrefetch pf = {nullptr, 0, 0, 0};
     const bool ok = base && rows > 0 && rows < (1LL << 31) && bytes_per_row >= 16 && row_stride_bytes >= bytes_per_row &&
                     ((uintptr_t)base & 15) == 0 && row_stride_bytes % 16 == 0;
-    g_prefetch.base = ok ? (const char*)base : nullptr;
-    g_prefetch.rows = (int)rows;
-    g_prefetch.row_stride = (long)row_stride_bytes;
-    g_prefetch.bytes = bytes_per_row & ~15;
+    if (!ok) return pf;
+    pf.base = (const char*)base;
+    pf.rows = (int)rows;
+    pf.row_stride = (long)row_stride_bytes;
+    pf.bytes = bytes_per_row & ~15;
+    return pf;
 }
 
-FbPrefetch fb_take_prefetch_hint() {
-    const FbPrefetch pf = g_prefetch;
-    g_prefetch.base = nullptr;
-    return pf;
+int fb_device_ordinal() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
+    return dev < FB_MAX_DEVICES ? dev : FB_MAX_DEVICES - 1;
+}
+
+int fb_sm_count() {
+    static int sms[FB_MAX_DEVICES] = {};
+    const int dev = fb_device_ordinal();
+    if (!sms[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sms[dev] = n;
+    }
+    return sms[dev];
 }
 
 int fb_fail(int code, const char* fmt, ...) {

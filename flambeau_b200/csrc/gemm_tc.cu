@@ -235,14 +235,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         }
                         if (gated) {
                             // output features alternate gate, up: even lanes hold a gate, their odd neighbour its
-                            // up; the even lane writes silu(gate) * up to column n / 2 of a half-as-wide output.
+                            // up; the even lane writes act(gate) * up to column n / 2 of a half-as-wide output
+                            // (`gated` is the activation's code).
                             // Every lane computes (straight-line code, sixteen independent chains); odd lanes'
                             // results are dropped.
                             float r[16];
 #pragma unroll
                             for (int q = 0; q < 16; ++q) {
                                 const float up = __shfl_xor_sync(0xffffffffu, v[q], 1);
-                                r[q] = v[q] / (1.0f + expf(-v[q])) * up;
+                                r[q] = fb_gate_times(gated, v[q], up);
                             }
                             const bool writes = !(lane & 1) && n + 1 < N;
 #pragma unroll
@@ -341,15 +342,14 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
     const int tiles_n = (N + BM - 1) / BM, tiles_m = (M + BN - 1) / BN;
     const int tiles = tiles_n * tiles_m;
     const int kb_total = (K + Cfg::KSTEP - 1) / Cfg::KSTEP;
-    int per_sm = Cfg::SMEM_BYTES <= 113 * 1024 ? 2 : 1;
-    if (const char* env = getenv("FLAMBEAU_GEMM_CTAS_PER_SM")) per_sm = atoi(env) >= 2 ? per_sm : 1;   // experiment knob
-    const int slots = 148 * per_sm;
+    const int per_sm = Cfg::SMEM_BYTES <= 113 * 1024 ? 2 : 1;
+    const int slots = fb_sm_count() * per_sm;
     // One more share = one more float32 copy of the output, written and read once at about HBM speed.  A k-block
     // of one CTA takes its stage bytes at the CTA's part of that speed when the weights stream from DRAM (few
     // rows), or its flops at an SM's tensor rate when the tile is large enough to be bound by them.
-    const double kb_seconds = BN <= 64 ? (double)Cfg::STAGE_BYTES / (6.0e12 / slots)
-                                       : 2.0 * BM * BN * BK / 9.0e12;
-    const double share_cost_kb = ((double)M * N * 8.0 / 6.0e12) / kb_seconds;
+    const double kb_seconds = BN <= 64 ? (double)Cfg::STAGE_BYTES / (FB_MODEL_HBM_BYTES_PER_S / slots)
+                                       : 2.0 * BM * BN * BK / FB_MODEL_SM_FLOPS;
+    const double share_cost_kb = ((double)M * N * 8.0 / FB_MODEL_HBM_BYTES_PER_S) / kb_seconds;
     int splits = force_splits > 0 ? force_splits : pick_splits(tiles, kb_total, slots, 16, share_cost_kb);
     if (gated) splits = 1;                       // the activation needs the whole sum
     if (splits > kb_total) splits = kb_total;
@@ -362,12 +362,12 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
     const long n_units = (long)tiles * splits;
     if (n_units > 2000000000L) return fb_fail(-1, "gemm_tc: too many tiles (M=%d N=%d)", M, N);
     auto kern = gemm_tc_kernel<BN, TO>;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[FB_MAX_DEVICES] = {};
+    if (fb_needs_setup(configured)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return fb_fail(-2, "gemm_tc: cannot reserve %d bytes of shared memory: %s",
                                              Cfg::SMEM_BYTES, cudaGetErrorString(e));
-        configured = true;
+        fb_setup_done(configured);
     }
     const int grid = (int)(n_units < slots ? n_units : slots);
     fb_launch((kern), grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, partials,
@@ -432,19 +432,21 @@ FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw
     return fb_fail(-1, "gemm_tc: unknown output dtype code %d", o_dtype);
 }
 
-// out[M, N/2] = silu(g) * u with [g_0, u_0, g_1, u_1, ...] = X[M,K] * W[N,K]^T: W stacks gate and up rows
-// alternately, and the activation is applied in the epilogue (the whole sum in one CTA, so K is not split).
+// out[M, N/2] = act(g) * u with [g_0, u_0, g_1, u_1, ...] = X[M,K] * W[N,K]^T: W stacks gate and up rows
+// alternately, and the activation `act` (an FbAct code) is applied in the epilogue (the whole sum in one CTA, so
+// K is not split).
 FB_API int fb_gemm_tc_gated(const void* X, long long lda, const void* W, long long ldw, void* out, int o_dtype,
-                            long long ldo, int M, int N, int K, float* partials, long long partial_floats,
+                            long long ldo, int M, int N, int K, int act, float* partials, long long partial_floats,
                             int* counters, int n_counters, int* status, cudaStream_t stream) {
     FB_REQUIRE(M >= 0 && N > 0 && K > 0 && N % 2 == 0, "gemm_tc_gated: bad sizes M=%d N=%d K=%d", M, N, K);
+    FB_REQUIRE(fb_act_known(act), "gemm_tc_gated: unknown activation code %d", act);
     FB_REQUIRE(lda >= K && ldw >= K && ldo >= N / 2, "gemm_tc_gated: a row stride is shorter than its row");
     FB_REQUIRE(lda % 8 == 0 && ldw % 8 == 0, "gemm_tc_gated: row strides must be multiples of 8 elements");
     FB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tc_gated: operands must be 16-byte aligned");
     if (M == 0) return 0;
     const int BN = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     if (BN == 256 && (o_dtype == FB_F32 || o_dtype == FB_BF16) && fb_gemm_pair_plan(M, N, K, 1))
-        return fb_launch_gemm_pair(X, (long)lda, W, (long)ldw, out, o_dtype, (long)ldo, 0, 1, M, N, K, 1, status,
+        return fb_launch_gemm_pair(X, (long)lda, W, (long)ldw, out, o_dtype, (long)ldo, 0, 1, M, N, K, act, status,
                                    stream);
     CUtensorMap mw, mx;
     int rc = fb_tensor_map_bf16(&mw, W, N, K, (long)ldw, BK, BM);
@@ -455,11 +457,11 @@ FB_API int fb_gemm_tc_gated(const void* X, long long lda, const void* W, long lo
     case BN_:                                                                                                   \
         if (o_dtype == FB_F32)                                                                                  \
             return launch_tc<BN_, float>(mw, mx, out, (long)ldo, 0, 1, nullptr, partials, (long)partial_floats, \
-                                         counters, n_counters, M, N, K, 1, status, stream, 1);                  \
+                                         counters, n_counters, M, N, K, 1, status, stream, act);                \
         else if (o_dtype == FB_BF16)                                                                            \
             return launch_tc<BN_, __nv_bfloat16>(mw, mx, out, (long)ldo, 0, 1, nullptr, partials,               \
                                                  (long)partial_floats, counters, n_counters, M, N, K, 1, status, \
-                                                 stream, 1);                                                    \
+                                                 stream, act);                                                  \
         break;
     switch (BN) {
         FB_TCG_CASE(16)

@@ -31,7 +31,8 @@ constexpr int P_A_BYTES = PBM * PBK * 2;
 constexpr int P_STAGE_BYTES = P_A_BYTES + PBNH * PBK * 2;
 constexpr int P_TMEM_COLS = 2 * PBN;
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
-constexpr int P_SLOTS = 74;             // pairs that run at a time: one per two SMs
+// Pairs that run at a time: one per two SMs of the current device.
+inline int pair_slots() { return fb_sm_count() / 2 > 0 ? fb_sm_count() / 2 : 1; }
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -232,12 +233,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         for (int q = 0; q < 16; ++q) v[q] = 0.0f;
                     }
                     if (gated) {
-                        // features alternate gate, up: the even lane writes silu(gate) * up to column n / 2
+                        // features alternate gate, up: the even lane writes act(gate) * up to column n / 2
                         float r[16];
 #pragma unroll
                         for (int q = 0; q < 16; ++q) {
                             const float up = __shfl_xor_sync(0xffffffffu, v[q], 1);
-                            r[q] = v[q] / (1.0f + expf(-v[q])) * up;
+                            r[q] = fb_gate_times(gated, v[q], up);
                         }
                         const bool writes = !(lane & 1) && n + 1 < N;
 #pragma unroll
@@ -277,18 +278,18 @@ int launch_pair(const void* X, long lda, const void* W, long ldw, void* out, lon
     rc = fb_tensor_map_bf16(&mx, X, M, K, lda, PBK, PBNH);
     if (rc) return rc;
     auto kern = gemm_tc_pair_kernel<TO>;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[FB_MAX_DEVICES] = {};
+    if (fb_needs_setup(configured)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
         if (e != cudaSuccess) return fb_fail(-2, "gemm_tc_pair: cannot reserve %d bytes of shared memory: %s",
                                              P_SMEM_BYTES, cudaGetErrorString(e));
-        configured = true;
+        fb_setup_done(configured);
     }
     const int tiles_m = (M + PBN - 1) / PBN, tiles_n = (N + 2 * PBM - 1) / (2 * PBM);
     const long tiles = (long)tiles_m * tiles_n;
     const long n_units = tiles * splits;
     if (n_units > 2000000000L) return fb_fail(-1, "gemm_tc_pair: too many tiles (M=%d N=%d)", M, N);
-    const int pairs = (int)(n_units < P_SLOTS ? n_units : P_SLOTS);
+    const int pairs = (int)(n_units < pair_slots() ? n_units : pair_slots());
     fb_launch((kern), 2 * pairs, P_THREADS, P_SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, M, N, K,
               tiles_m, (int)tiles, splits, (int)n_units, gated, status);
     return fb_check_launch("gemm_tc_pair");
@@ -299,16 +300,17 @@ int launch_pair(const void* X, long lda, const void* W, long ldw, void* out, lon
 static int g_pair_on = -1;                       // -1: not yet read from the environment
 FB_API void fb_set_gemm_pair(int on) { g_pair_on = on ? 1 : 0; }
 
-// Shares of K for the pairs: as many as make the rounds of the 74 pairs shortest, each share beyond the first
+// Shares of K for the pairs: as many as make the rounds of the resident pairs shortest, each share beyond the first
 // costing one more float32 copy of the output (written here, added by the consumer), counted in k-block times.
 static int pair_splits(long tiles, int kb_total, int max_splits, int M, int N) {
-    const double kb_seconds = 2.0 * PBM * PBN * PBK / 9.0e12;
-    const double share_cost_kb = ((double)M * N * 8.0 / 6.0e12) / kb_seconds;
+    const double kb_seconds = 2.0 * PBM * PBN * PBK / FB_MODEL_SM_FLOPS;
+    const double share_cost_kb = ((double)M * N * 8.0 / FB_MODEL_HBM_BYTES_PER_S) / kb_seconds;
+    const int slots = pair_slots();
     int best = 1;
     double best_cost = 1e30;
     for (int s = 1; s <= max_splits && s <= kb_total; ++s) {
         const long units = tiles * s;
-        const long rounds = (units + P_SLOTS - 1) / P_SLOTS;
+        const long rounds = (units + slots - 1) / slots;
         const double cost = rounds * ((double)((kb_total + s - 1) / s) + 0.5) + (s - 1) * share_cost_kb;
         if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
     }

@@ -64,8 +64,9 @@ struct Pool {
 };
 
 struct PageList {
-    std::vector<int> ids;           // by logical page index; -1 = given back
-    int first_live = 0;             // logical pages below this index have been given back
+    int base = 0;                   // logical pages below this index have been given back
+    std::vector<int> ids;           // the live pages: ids[i] is logical page base + i
+    int end() const { return base + (int)ids.size(); }    // logical pages [0, end()) have been taken so far
 };
 
 struct Record {
@@ -144,9 +145,8 @@ FBH_API int fbh_release(void* h, int slot) {
     Record& r = c.records[(size_t)slot];
     for (int g = 0; g < c.n_groups(); ++g) {
         PageList& pl = r.pages[(size_t)g];
-        for (size_t i = (size_t)pl.first_live; i < pl.ids.size(); ++i)
-            if (pl.ids[i] >= 0)
-                if (int rc = c.pools[(size_t)g].give_back(pl.ids[i])) return rc;
+        for (int id : pl.ids)
+            if (int rc = c.pools[(size_t)g].give_back(id)) return rc;
         pl = PageList();
     }
     r.live = false;
@@ -187,7 +187,7 @@ FBH_API int fbh_pages_needed(void* h, int slot, int n_new, int* out) {
     const Record& r = c.records[(size_t)slot];
     const int want = (r.length + n_new + c.page_size - 1) / c.page_size;
     for (int g = 0; g < c.n_groups(); ++g) {
-        const int have = (int)r.pages[(size_t)g].ids.size();
+        const int have = r.pages[(size_t)g].end();
         out[g] = want > have ? want - have : 0;
     }
     return 0;
@@ -208,7 +208,7 @@ FBH_API int fbh_reserve_all(void* h, int n, const int* slots, const int* n_new, 
             return fail(ERR_LIMIT, "a request would reach %d tokens; the cache holds at most %d per request", end, limit);
         const int pages_to = (end + c.page_size - 1) / c.page_size;
         for (int g = 0; g < G; ++g) {
-            const int have = (int)r.pages[(size_t)g].ids.size();
+            const int have = r.pages[(size_t)g].end();
             if (pages_to > have) total[(size_t)g] += pages_to - have;
         }
     }
@@ -223,7 +223,7 @@ FBH_API int fbh_reserve_all(void* h, int n, const int* slots, const int* n_new, 
         const int pages_to = (end + c.page_size - 1) / c.page_size;
         for (int g = 0; g < G; ++g) {
             PageList& pl = r.pages[(size_t)g];
-            while ((int)pl.ids.size() < pages_to) pl.ids.push_back(c.pools[(size_t)g].take());
+            while (pl.end() < pages_to) pl.ids.push_back(c.pools[(size_t)g].take());
         }
         if (end > r.reserved_to) r.reserved_to = end;
     }
@@ -245,14 +245,15 @@ FBH_API int fbh_commit(void* h, int n, const int* slots, const int* n_new) {
             if (w <= 0) continue;
             const int first_live = r.length - w + 1;          // lowest position a future query can see
             PageList& pl = r.pages[(size_t)g];
-            int dead = (first_live > 0 ? first_live : 0) / c.page_size;
-            if (dead > (int)pl.ids.size()) dead = (int)pl.ids.size();
-            for (int p = pl.first_live; p < dead; ++p) {
-                if (pl.ids[(size_t)p] >= 0)
-                    if (int rc = c.pools[(size_t)g].give_back(pl.ids[(size_t)p])) return rc;
-                pl.ids[(size_t)p] = -1;
+            int dead = (first_live > 0 ? first_live : 0) / c.page_size;       // logical pages [0, dead) are dead
+            if (dead > pl.end()) dead = pl.end();
+            const int n_dead = dead - pl.base;
+            if (n_dead > 0) {
+                for (int i = 0; i < n_dead; ++i)
+                    if (int rc = c.pools[(size_t)g].give_back(pl.ids[(size_t)i])) return rc;
+                pl.ids.erase(pl.ids.begin(), pl.ids.begin() + n_dead);
+                pl.base = dead;
             }
-            if (dead > pl.first_live) pl.first_live = dead;
         }
     }
     return 0;
@@ -263,10 +264,17 @@ FBH_API int fbh_commit(void* h, int n, const int* slots, const int* n_new) {
 FBH_API int fbh_pages(void* h, int slot, int group, int* out, int cap) {
     Cache& c = *as_cache(h);
     if (int rc = check_slot(c, slot)) return rc;
-    const std::vector<int>& ids = c.records[(size_t)slot].pages[(size_t)group].ids;
-    const int n = (int)ids.size();
-    if (out && cap > 0) memcpy(out, ids.data(), sizeof(int) * (size_t)(n < cap ? n : cap));
+    const PageList& pl = c.records[(size_t)slot].pages[(size_t)group];
+    const int n = pl.end();
+    for (int i = 0; out && i < n && i < cap; ++i) out[i] = i < pl.base ? -1 : pl.ids[(size_t)(i - pl.base)];
     return n;
+}
+
+// The logical page index of the request's first live page in a group (what its table row starts at).
+FBH_API int fbh_first_live_page(void* h, int slot, int group) {
+    Cache& c = *as_cache(h);
+    if (int rc = check_slot(c, slot)) return rc;
+    return c.records[(size_t)slot].pages[(size_t)group].base;
 }
 
 // No page lost, held twice or free while in a table; no slot held twice.
@@ -279,8 +287,7 @@ FBH_API int fbh_check_invariants(void* h) {
         for (const Record& r : c.records) {
             if (!r.live) continue;
             for (int p : r.pages[(size_t)g].ids) {
-                if (p < 0) continue;
-                if (p >= pool.n_pages) return fail(ERR_STATE, "group %d: page %d is outside the pool", g, p);
+                if (p < 0 || p >= pool.n_pages) return fail(ERR_STATE, "group %d: page %d is outside the pool", g, p);
                 if (seen[(size_t)p]) return fail(ERR_STATE, "group %d: page %d is held twice", g, p);
                 if (!pool.held[(size_t)p]) return fail(ERR_STATE, "group %d: page %d is in a table but free in the pool", g, p);
                 seen[(size_t)p] = 1;
@@ -302,8 +309,9 @@ FBH_API int fbh_check_invariants(void* h) {
 // Packs the descriptor of one step.  Entry i: request in slots[i], its next q_len[i] tokens (tokens, concatenated),
 // wanted places among them (wants, concatenated, n_want[i] each).  Pages for the new tokens must be reserved.
 //   rows   [4][max_tokens]: token id, position, sequence of the row, rows whose logits are wanted
-//   seqs   [4][max_seqs]:   first row, rows, first position, slot
-//   tables [groups][max_seqs][max_pages]: page ids by logical page, -1 where there is none
+//   seqs   [4 + groups][max_seqs]: first row, rows, first position, slot, then for each group the logical page
+//          index that column 0 of the sequence's table row stands for (its first live page)
+//   tables [groups][max_seqs][max_pages]: the ids of the live pages, from the first live page on, -1 behind them
 //   fill   [groups][max_seqs]: how many entries of each table row were valid after the last call (kept by the caller)
 //   info   [4]: rows, wanted rows, longest entry, longest context
 FBH_API int fbh_build_step(void* h, int n_entries, const int* slots, const int* q_len, const int* tokens,
@@ -352,9 +360,11 @@ FBH_API int fbh_build_step(void* h, int n_entries, const int* slots, const int* 
         if (k > max_q) max_q = k;
         if (r.length + k > max_kv) max_kv = r.length + k;
         for (int g = 0; g < c.n_groups(); ++g) {
-            const std::vector<int>& ids = r.pages[(size_t)g].ids;
+            const PageList& pl = r.pages[(size_t)g];
+            const std::vector<int>& ids = pl.ids;
             const int have = (int)ids.size();
-            if (have > max_pages) return fail(ERR_BATCH, "entry %d holds %d pages; tables have %d", i, have, max_pages);
+            if (have > max_pages) return fail(ERR_BATCH, "entry %d holds %d live pages; tables have %d columns", i, have, max_pages);
+            seqs[(size_t)(4 + g) * max_seqs + i] = pl.base;
             int* trow = tables + ((size_t)g * max_seqs + (size_t)i) * max_pages;
             memcpy(trow, ids.data(), sizeof(int) * (size_t)have);
             int& f = fill[(size_t)g * max_seqs + i];

@@ -51,7 +51,8 @@ class StepBatch:
         # device tensors
         self.token_ids = self.positions = self.row_seq = self.out_rows = None
         self.seq_q_start_d = self.seq_q_len_d = self.seq_pos_start_d = self.seq_slot_d = None
-        self.tables: list = []
+        self.tables: list = []              # per cache group: block table [sequences, table columns]
+        self.table_bases: list = []         # per cache group: the logical page that column 0 of each row stands for
         self.h2d_bytes = 0
 
 
@@ -59,14 +60,15 @@ class BatchBuffers:
     """Pinned host staging and device storage for step descriptors, sized once."""
 
     ROW_FIELDS = 4      # token_ids, positions, row_seq, out_rows
-    SEQ_FIELDS = 4      # q_start, q_len, pos_start, slot
+    SEQ_FIELDS = 4      # q_start, q_len, pos_start, slot; then one row per cache group: the table rows' first page
 
     def __init__(self, device, max_tokens: int, max_seqs: int, n_groups: int, max_pages: int):
+        """max_pages: columns of a block-table row = the most live pages one request holds in any group."""
         self.device = device
         self.max_tokens, self.max_seqs, self.n_groups, self.max_pages = max_tokens, max_seqs, n_groups, max_pages
         pin = device.type == "cuda"
         self.h_rows = torch.zeros((self.ROW_FIELDS, max_tokens), dtype=torch.int32, pin_memory=pin)
-        self.h_seqs = torch.zeros((self.SEQ_FIELDS, max_seqs), dtype=torch.int32, pin_memory=pin)
+        self.h_seqs = torch.zeros((self.SEQ_FIELDS + n_groups, max_seqs), dtype=torch.int32, pin_memory=pin)
         self.h_tables = torch.full((max(n_groups, 1), max_seqs, max_pages), -1, dtype=torch.int32, pin_memory=pin)
         self.d_rows = torch.zeros_like(self.h_rows, device=device)
         self.d_seqs = torch.zeros_like(self.h_seqs, device=device)
@@ -119,11 +121,12 @@ class BatchBuffers:
         width = max(n, n_out)
         self.d_rows[:, :width].copy_(self.h_rows[:, :width], non_blocking=True)
         self.d_seqs[:, :S].copy_(self.h_seqs[:, :S], non_blocking=True)
-        b.h2d_bytes = 4 * (self.ROW_FIELDS * width + self.SEQ_FIELDS * S)
+        b.h2d_bytes = 4 * (self.ROW_FIELDS * width + (self.SEQ_FIELDS + self.n_groups) * S)
         if cache.n_groups:
             self.d_tables[:, :S].copy_(self.h_tables[:, :S], non_blocking=True)
             b.h2d_bytes += 4 * cache.n_groups * S * self.max_pages
         b.token_ids, b.positions, b.row_seq, b.out_rows = (self.d_rows[i] for i in range(4))
         b.seq_q_start_d, b.seq_q_len_d, b.seq_pos_start_d, b.seq_slot_d = (self.d_seqs[i] for i in range(4))
         b.tables = [self.d_tables[gi] for gi in range(cache.n_groups)]
+        b.table_bases = [self.d_seqs[self.SEQ_FIELDS + gi] for gi in range(cache.n_groups)]
         return b

@@ -64,19 +64,12 @@ class StepContext:
         self.pending_slabs = 1
         return x
 
-    def hint(self, weight) -> None:
-        """Tell the attention kernel that follows which matrix the product after it reads, so that it fetches the
-        start of that matrix into L2 when its own stream of cache ends (few rows only: a step of many rows is
-        bound by its products' arithmetic; bfloat16 kernels only).  It changes no result."""
-        if weight is not None and self.l2_hints and self.n_tokens <= 64:
-            ops.prefetch_hint(weight)
-
     def step_alloc(self, shape, dtype):
         """Scratch that lives until the step ends (ctx.ws allocations end with their scope)."""
         return self.engine.step_ws.alloc(shape, dtype)
 
     def cache(self, call: int):
-        return self.engine.cache.view(call, self.batch.tables)
+        return self.engine.cache.view(call, self.batch.tables, self.batch.table_bases)
 
     def logits(self, n_out: int, vocab: int):
         return self.engine.logits_buffer(n_out, vocab)
@@ -91,12 +84,15 @@ class Engine:
         self.runtime: Runtime = model.runtime
         rt = self.runtime
         limit = options.max_seq_len or min(options.cache_tokens, model.spec.max_positions or options.cache_tokens)
+        if model.spec.max_positions and limit > model.spec.max_positions:
+            raise ValueError(f"max_seq_len = {limit} is more than the {model.spec.max_positions} positions the "
+                             f"model's configuration allows")
         self.max_seq_len = int(limit)
         self.cache = CacheManager(model.cache_plans(), max_tokens=options.cache_tokens, page_size=rt.page_size,
                                   max_requests=options.max_requests, device=rt.device, dtype=rt.dtype,
-                                  max_seq_len=self.max_seq_len)
+                                  max_seq_len=self.max_seq_len, max_step_tokens=options.max_step_tokens)
         self.buffers = BatchBuffers(rt.device, options.max_step_tokens, options.max_requests, self.cache.n_groups,
-                                    self.cache.max_pages_per_request)
+                                    self.cache.table_pages)
         self.step_ws = Workspace(rt.device, 1 << 22)
         self._logits = None
         self._copied = torch.cuda.Event()
@@ -229,6 +225,9 @@ class Engine:
         cache = self.cache
         logits = None
         if entries:
+            if token_feed is not None and (any(len(e.tokens) != 1 for e in entries)
+                                           or token_feed.numel() < len(entries)):
+                raise BatchError("a token feed needs single-token entries and one id per entry")
             admitted = []
             try:
                 for e in entries:
@@ -244,18 +243,19 @@ class Engine:
                 if self._copy_pending:
                     self._copied.synchronize()      # the staging buffers are free to be rewritten
                 batch = self.buffers.build(entries, cache, self.model.vocab_size)
+                if token_feed is not None:
+                    self.buffers.d_rows[0, :batch.n_seqs].copy_(token_feed[:batch.n_seqs])
+                self._copied.record()
+                self._copy_pending = True
+                logits = self._run(batch)
             except Exception:
-                for rid in admitted:                # nothing ran: requests this step brought in leave again
+                # The step did not run to its end on the host (a bad entry, no pages, a launch that was refused):
+                # requests that this step brought in leave again, with what was reserved for them; lengths have
+                # not advanced, and pages reserved beyond a live request's length are taken by its next step.
+                for rid in admitted:
                     if rid in cache.requests:
                         cache.release(rid)
                 raise
-            if token_feed is not None:
-                if batch.n_tokens != batch.n_seqs or token_feed.numel() < batch.n_seqs:
-                    raise BatchError("a token feed needs single-token entries and one id per entry")
-                self.buffers.d_rows[0, :batch.n_seqs].copy_(token_feed[:batch.n_seqs])
-            self._copied.record()
-            self._copy_pending = True
-            logits = self._run(batch)
             cache.commit_all(needs)
             self.last_batch = batch
             self.steps_run += 1

@@ -23,22 +23,22 @@ _SIGNATURES = {
     "fb_set_pdl": (None, [I]),
     "fb_set_attention_tc": (None, [I]),
     "fb_set_gemm_pair": (None, [I]),
-    "fb_set_prefetch_hint": (None, [P, L, L, I]),
     # elementwise.cu
     "fb_embedding": (I, [P, I, P, P, I, I, I, P, STREAM]),
-    "fb_add_rmsnorm": (I, [P, P, I, I, L, P, I, P, I, P, I, I, F, STREAM]),
+    "fb_add_rmsnorm": (I, [P, P, I, I, L, P, I, P, I, P, I, I, F, F, STREAM]),
     "fb_rope_table": (I, [P, P, P, P, I, I, STREAM]),
-    "fb_rope_kv_write": (I, [P, L, I, L, P, L, P, L, P, L, I, I, P, P, I, P, P, P, I, P, P, I, I, I, I, I, I, I, P, STREAM]),
-    "fb_silu_mul": (I, [P, L, I, I, L, P, I, I, I, STREAM]),
+    "fb_rope_kv_write": (I, [P, L, I, L, P, L, P, L, P, L, I, I, P, P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P, STREAM]),
+    "fb_gate_mul": (I, [P, L, I, I, L, P, I, I, I, I, STREAM]),
     # gemm_simt.cu
     "fb_gemm_simt": (I, [P, I, L, P, I, L, P, I, L, I, I, I, STREAM]),
     # gemm_tc.cu
     "fb_gemm_tc": (I, [P, L, P, L, P, I, L, L, I, P, I, I, I, P, L, P, I, I, P, STREAM]),
-    "fb_gemm_tc_gated": (I, [P, L, P, L, P, I, L, I, I, I, P, L, P, I, P, STREAM]),
+    "fb_gemm_tc_gated": (I, [P, L, P, L, P, I, L, I, I, I, I, P, L, P, I, P, STREAM]),
     # attention_simt.cu
-    "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, I, I, I, I, I, F, P, STREAM]),
+    "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, P, I, I, I, I, I, F, P, STREAM]),
     # attention_mma.cu
-    "fb_paged_attention_mma": (I, [P, L, P, L, P, P, I, I, P, I, P, P, P, I, I, I, I, I, I, I, I, I, F, P, L, P, STREAM]),
+    "fb_paged_attention_mma": (I, [P, L, P, L, P, P, I, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, L, P, L, L, I,
+                                   P, STREAM]),
     # sampling.cu
     "fb_apply_penalties": (I, [P, L, I, P, P, P, P, P, P, I, STREAM]),
     "fb_apply_logit_bias": (I, [P, L, I, P, P, P, I, STREAM]),
@@ -59,6 +59,7 @@ _SIGNATURES = {
     "fbh_reserve_all": (I, [P, I, P, P, I]),
     "fbh_commit": (I, [P, I, P, P]),
     "fbh_pages": (I, [P, I, I, P, I]),
+    "fbh_first_live_page": (I, [P, I, I]),
     "fbh_check_invariants": (I, [P]),
     "fbh_build_step": (I, [P, I, P, P, P, P, P, I, I, I, I, P, P, P, P, P]),
 }

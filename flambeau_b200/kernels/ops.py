@@ -63,10 +63,11 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor, status: t
 
 
 def add_rms_norm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: torch.Tensor,
-                 rows=None, n_partials: int = 1, n_rows: int | None = None, partial_stride: int = 0) -> None:
-    """out[j] = rmsnorm(x[r] + sum_p delta_p[r]) * weight, r = rows[j] or j; without `rows` the sum is
-    also written back to x.  `delta` is [n, H]; with n_partials > 1 it is the first of that many slabs
-    `partial_stride` elements apart."""
+                 rows=None, n_partials: int = 1, n_rows: int | None = None, partial_stride: int = 0,
+                 weight_offset: float = 0.0) -> None:
+    """out[j] = rmsnorm(x[r] + sum_p delta_p[r]) * (weight + weight_offset), r = rows[j] or j; without `rows`
+    the sum is also written back to x.  `delta` is [n, H]; with n_partials > 1 it is the first of that many
+    slabs `partial_stride` elements apart.  weight_offset is 0 for a plain weight, 1 for a "1 + w" norm."""
     _cuda(x, delta, weight, out, rows)
     _i32(rows, "rows")
     H = x.shape[1]
@@ -84,7 +85,8 @@ def add_rms_norm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: 
                 raise KernelError("add_rms_norm: several slabs need their stride")
     check(lib().fb_add_rmsnorm(x.data_ptr(), _ptr(delta), dtype_code(delta) if delta is not None else 0,
                                n_partials, stride, weight.data_ptr(), dtype_code(weight), out.data_ptr(),
-                               dtype_code(out), _ptr(rows), n_out, H, float(eps), _stream()), "add_rms_norm")
+                               dtype_code(out), _ptr(rows), n_out, H, float(eps), float(weight_offset), _stream()),
+          "add_rms_norm")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
@@ -100,11 +102,13 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tenso
 
 def rope_kv_write(q_in, q_out, k, v, cos, sin, half: int, positions, row_seq, block_table, k_pool, v_pool,
                   page_size: int, nh: int, nkv: int, hd: int, write_kv: bool, status, n_partials: int = 1,
-                  partial_stride: int = 0) -> None:
+                  partial_stride: int = 0, table_base=None) -> None:
     """q_out = rotate(q_in) (q_out may be q_in); with write_kv, rotate k into the cache and copy v into it.
     q_in, k, v share one dtype (the projection's output); q_out and the cache share one dtype.  With
-    n_partials > 1 the inputs are split-K shares `partial_stride` elements apart and are added first."""
-    _cuda(q_in, q_out, k, v, cos, sin, positions, row_seq, block_table, k_pool, v_pool, status)
+    n_partials > 1 the inputs are split-K shares `partial_stride` elements apart and are added first.
+    table_base (int32 per sequence, optional): the logical page that column 0 of each table row stands for."""
+    _cuda(q_in, q_out, k, v, cos, sin, positions, row_seq, block_table, k_pool, v_pool, status, table_base)
+    _i32(table_base, "table_base")
     n = q_in.shape[0]
     if q_in.shape[1] != nh * hd or q_out.shape[1] != nh * hd or q_out.shape[0] != n:
         raise KernelError("rope_kv_write: q widths do not match the head counts")
@@ -122,21 +126,38 @@ def rope_kv_write(q_in, q_out, k, v, cos, sin, half: int, positions, row_seq, bl
         _rows(k) if k is not None else 0,
         _ptr(v), _rows(v) if v is not None else 0, dtype_code(q_in), dtype_code(q_out), _ptr(cos), _ptr(sin), half,
         _ptr(positions), _ptr(row_seq), _ptr(block_table),
-        block_table.stride(0) if block_table is not None else 0, _ptr(k_pool), _ptr(v_pool), page_size, n_pages,
-        n, nh, nkv if write_kv else 0, hd, 1 if write_kv else 0, status.data_ptr(), _stream()), "rope_kv_write")
+        block_table.stride(0) if block_table is not None else 0, _ptr(table_base), _ptr(k_pool), _ptr(v_pool),
+        page_size, n_pages, n, nh, nkv if write_kv else 0, hd, 1 if write_kv else 0, status.data_ptr(), _stream()),
+        "rope_kv_write")
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, n_partials: int = 1, partial_stride: int = 0) -> None:
-    """out[:, c] = silu(gate_up[:, 2c]) * gate_up[:, 2c+1] (gate and up alternate along a row); with
+ACTIVATIONS = {"silu": 1, "gelu_tanh": 2, "gelu_pytorch_tanh": 2}      # codes of the kernels' gate activations
+
+
+def activation_code(name: str) -> int:
+    try:
+        return ACTIVATIONS[name]
+    except KeyError:
+        raise KernelError(f"activation '{name}' is not implemented; known: {', '.join(sorted(ACTIVATIONS))}") from None
+
+
+def gate_mul(gate_up: torch.Tensor, out: torch.Tensor, n_partials: int = 1, partial_stride: int = 0,
+             activation: str = "silu") -> None:
+    """out[:, c] = act(gate_up[:, 2c]) * gate_up[:, 2c+1] (gate and up alternate along a row); with
     n_partials > 1, gate_up is the first of that many split-K shares `partial_stride` elements apart, which are
     added first."""
     _cuda(gate_up, out)
     n, two_i = gate_up.shape
     I = two_i // 2
     if tuple(out.shape) != (n, I) or not out.is_contiguous():
-        raise KernelError("silu_mul: bad output")
-    check(lib().fb_silu_mul(gate_up.data_ptr(), _rows(gate_up), dtype_code(gate_up), int(n_partials),
-                            int(partial_stride), out.data_ptr(), dtype_code(out), n, I, _stream()), "silu_mul")
+        raise KernelError("gate_mul: bad output")
+    check(lib().fb_gate_mul(gate_up.data_ptr(), _rows(gate_up), dtype_code(gate_up), int(n_partials),
+                            int(partial_stride), out.data_ptr(), dtype_code(out), n, I, activation_code(activation),
+                            _stream()), "gate_mul")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, n_partials: int = 1, partial_stride: int = 0) -> None:
+    gate_mul(gate_up, out, n_partials, partial_stride, "silu")
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -151,8 +172,9 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def paged_attention_simt(q, out, k_pool, v_pool, block_table, positions, row_seq, nh: int, nkv: int, hd: int,
-                         window: int, scale: float, status) -> None:
-    _cuda(q, out, k_pool, v_pool, block_table, positions, row_seq, status)
+                         window: int, scale: float, status, table_base=None) -> None:
+    _cuda(q, out, k_pool, v_pool, block_table, positions, row_seq, status, table_base)
+    _i32(table_base, "table_base")
     n = q.shape[0]
     n_pages, pool_kv, page_size, pool_hd = k_pool.shape
     if pool_kv != nkv or pool_hd != hd or q.shape[1] != nh * hd or out.shape[1] != nh * hd or out.shape[0] != n:
@@ -163,7 +185,7 @@ def paged_attention_simt(q, out, k_pool, v_pool, block_table, positions, row_seq
         raise KernelError("attention: cache pools must be contiguous")
     check(lib().fb_paged_attention_simt(
         q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), dtype_code(q), k_pool.data_ptr(), v_pool.data_ptr(),
-        page_size, n_pages, block_table.data_ptr(), block_table.stride(0), positions.data_ptr(),
+        page_size, n_pages, block_table.data_ptr(), block_table.stride(0), _ptr(table_base), positions.data_ptr(),
         row_seq.data_ptr(), n, nh, nkv, hd, int(window), float(scale), status.data_ptr(), _stream()),
         "paged_attention_simt")
 
@@ -252,8 +274,9 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.T
     return _SPLITS_USED.value if slabs is not None else 1
 
 
-def gemm_tc_gated(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
-    """out[M, N/2] = silu(g) * u where (g_0, u_0, g_1, u_1, ...) = a @ w^T: w stacks gate and up rows alternately
+def gemm_tc_gated(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+                  activation: str = "silu") -> None:
+    """out[M, N/2] = act(g) * u where (g_0, u_0, g_1, u_1, ...) = a @ w^T: w stacks gate and up rows alternately
     and the activation runs in the product's epilogue."""
     _cuda(a, w, out, status)
     M, K = a.shape
@@ -262,8 +285,9 @@ def gemm_tc_gated(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: t
         raise KernelError(f"gated gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
     partials, counters = _SplitScratch.get(a.device)
     check(lib().fb_gemm_tc_gated(a.data_ptr(), _rows(a), w.data_ptr(), _rows(w), out.data_ptr(), dtype_code(out),
-                                 _rows(out), M, N, K, partials.data_ptr(), partials.numel(), counters.data_ptr(),
-                                 counters.numel(), status.data_ptr(), _stream()), "gemm_tc_gated")
+                                 _rows(out), M, N, K, activation_code(activation), partials.data_ptr(),
+                                 partials.numel(), counters.data_ptr(), counters.numel(), status.data_ptr(),
+                                 _stream()), "gemm_tc_gated")
 
 
 def linear_slabs(a: torch.Tensor, w: torch.Tensor, slabs: torch.Tensor, ctx) -> int:
@@ -308,19 +332,21 @@ class _AttentionScratch:
         return hit
 
 
-def prefetch_hint(weight: torch.Tensor, budget_bytes: int = 16 << 20) -> None:
-    """The next bfloat16 attention launch also fetches the first bytes of every row of `weight` ([rows, K], the
-    matrix of the product that follows) into L2 when its split-key kernel's stream of cache ends, `budget_bytes`
-    in all: the product starts on data that is already on the chip.  A hint: results do not depend on it.
+def prefetch_arguments(weight, budget_bytes: int = 16 << 20) -> tuple:
+    """(base, rows, row stride in bytes, bytes per row) for the attention launcher's L2 hint: the first bytes of
+    every row of `weight` ([rows, K], the matrix of the product that follows), `budget_bytes` in all, which the
+    split-key kernel fetches into L2 when its stream of cache ends, so that the product starts on data that is
+    already on the chip.  A hint: results do not depend on it; a matrix the kernel cannot take gives no hint.
     (Measured for the row-wise kernels between the products and for the products' own tails as well: there it
     costs more than it brings.)"""
-    if weight.dim() != 2 or weight.stride(1) != 1:
-        return
+    if weight is None or weight.dim() != 2 or weight.stride(1) != 1:
+        return (0, 0, 0, 0)
     rows = weight.shape[0]
     row_bytes = weight.shape[1] * weight.element_size()
     per_row = min(row_bytes, max(512, (budget_bytes // max(rows, 1)) // 512 * 512)) // 16 * 16
-    if per_row >= 16:
-        lib().fb_set_prefetch_hint(weight.data_ptr(), rows, weight.stride(0) * weight.element_size(), per_row)
+    if per_row < 16:
+        return (0, 0, 0, 0)
+    return (weight.data_ptr(), rows, weight.stride(0) * weight.element_size(), per_row)
 
 
 def set_gemm_pair(on: bool) -> None:
@@ -342,11 +368,14 @@ def mma_attention_supported(q: torch.Tensor, nh: int, nkv: int, hd: int) -> bool
 
 def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, n_seqs: int,
                         max_q_len: int, max_kv_len: int, any_short: bool, any_long: bool, nh: int, nkv: int,
-                        hd: int, window: int, scale: float, status) -> None:
+                        hd: int, window: int, scale: float, status, table_base=None, prefetch=None) -> None:
     """bfloat16 attention on the tensor cores over the paged cache; sequences are described per entry of the
     step (first row, rows, first position).  any_short / any_long say whether the step holds sequences with
-    rows * (nh/nkv) <= 16 / > 16, which run in different arrangements of the kernel."""
-    _cuda(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, status)
+    rows * (nh/nkv) <= 16 / > 16, which run in different arrangements of the kernel.  table_base (int32 per
+    sequence, optional): the logical page that column 0 of each table row stands for.  prefetch (optional): the
+    weight matrix of the product that follows (see prefetch_arguments)."""
+    _cuda(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, status, table_base)
+    _i32(table_base, "table_base")
     n_pages, pool_kv, page_size, pool_hd = k_pool.shape
     if pool_kv != nkv or pool_hd != hd or q.shape[1] != nh * hd or out.shape[1] != nh * hd:
         raise KernelError("attention: shapes do not match the head counts")
@@ -357,23 +386,25 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
     scratch = _AttentionScratch.get(q.device, n_seqs, nkv, hd)
     check(lib().fb_paged_attention_mma(
         q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), k_pool.data_ptr(), v_pool.data_ptr(), page_size, n_pages,
-        block_table.data_ptr(), block_table.stride(0), seq_q_start.data_ptr(), seq_q_len.data_ptr(),
-        seq_pos_start.data_ptr(), n_seqs, max_q_len, max_kv_len, 1 if any_short else 0, 1 if any_long else 0,
-        nh, nkv, hd, int(window), float(scale), scratch.data_ptr(), scratch.numel(), status.data_ptr(), _stream()),
-        "paged_attention_mma")
+        block_table.data_ptr(), block_table.stride(0), _ptr(table_base), seq_q_start.data_ptr(),
+        seq_q_len.data_ptr(), seq_pos_start.data_ptr(), n_seqs, max_q_len, max_kv_len, 1 if any_short else 0,
+        1 if any_long else 0, nh, nkv, hd, int(window), float(scale), scratch.data_ptr(), scratch.numel(),
+        *prefetch_arguments(prefetch), status.data_ptr(), _stream()), "paged_attention_mma")
 
 
-def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int, scale: float) -> None:
+def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int, scale: float,
+                    next_weight=None) -> None:
     """Attention of every row of the step over its request's cached keys: the tensor-core kernel for bfloat16
-    and head sizes it takes, the float32 CUDA-core kernel otherwise (all of the 32-bit mode)."""
+    and head sizes it takes, the float32 CUDA-core kernel otherwise (all of the 32-bit mode).  next_weight: the
+    matrix of the product that follows, whose start the bfloat16 kernel may fetch into L2 (a hint)."""
     b = ctx.batch
     if mma_attention_supported(q, nh, nkv, hd):
         G = nh // nkv
         short = [ql * G <= 16 for ql in b.seq_q_len]
         paged_attention_mma(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.seq_q_start_d, b.seq_q_len_d,
                             b.seq_pos_start_d, b.n_seqs, b.max_q_len, b.max_kv_len, any(short), not all(short),
-                            nh, nkv, hd, window, scale, ctx.runtime.status)
+                            nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,
+                            prefetch=next_weight)
     else:
-        lib().fb_set_prefetch_hint(None, 0, 0, 0)          # this kernel takes no hint: none stays behind
         paged_attention_simt(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.positions, b.row_seq,
-                             nh, nkv, hd, window, scale, ctx.runtime.status)
+                             nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base)

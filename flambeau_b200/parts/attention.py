@@ -19,12 +19,17 @@ class PagedAttention(Mixer):
     crates/forward/src/core/composites/standard_attn.rs:197-286 (projections),
     :355-399 (rotary), :418-420 (scale), :1261-1302 (output projection).
 
-    Sizes are parameters: `num_heads * head_dim` need not equal `width`."""
+    Sizes are parameters: `num_heads * head_dim` need not equal `width`.
+    `qk_norm` (optional, a norm PartSpec of width head_dim): a norm over every
+    head of q and of k between the projection and the rotation, with weights
+    `<prefix>q_norm.weight` and `<prefix>k_norm.weight` (the optional
+    attn_q_norm / attn_k_norm of crates/forward/src/ctx.rs:368-369; the
+    architecture built here has none)."""
     graph_safe = True
 
     def __init__(self, runtime=None, prefix="", *, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  window: int = 0, position: PartSpec | None = None, scale: float | None = None,
-                 init_std: float = 0.02):
+                 init_std: float = 0.02, qk_norm: PartSpec | None = None):
         super().__init__(runtime, prefix)
         self.width, self.nh, self.nkv, self.hd = int(width), int(num_heads), int(num_kv_heads), int(head_dim)
         if self.nh % self.nkv:
@@ -32,12 +37,16 @@ class PagedAttention(Mixer):
         self.window = int(window or 0)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.hd)
         self.position = build_part(position, runtime) if position is not None else None
+        self.q_norm = self.k_norm = None
+        if qk_norm is not None:
+            self.q_norm = build_part(PartSpec(qk_norm.category, qk_norm.kind, qk_norm.params, prefix + "q_norm."), runtime)
+            self.k_norm = build_part(PartSpec(qk_norm.category, qk_norm.kind, qk_norm.params, prefix + "k_norm."), runtime)
         self.init_std = init_std
         self.qw, self.kvw = self.nh * self.hd, self.nkv * self.hd
         self.qkv = self.o = None
 
     def children(self):
-        return [self.position] if self.position is not None else []
+        return [p for p in (self.position, self.q_norm, self.k_norm) if p is not None]
 
     def cache_requirement(self):
         return KVRequirement(self.nkv, self.hd, self.window)
@@ -70,13 +79,27 @@ class PagedAttention(Mixer):
             fused = pos is None or getattr(pos, "fused_with_cache_write", False)
             # the fused rotary kernel adds split-K shares of the projection itself; a position encoding with a
             # rotate() of its own gets whole rows
-            qkv_slabs = ctx.ws.alloc((ctx.max_slabs if fused else 1, n, self.qw + 2 * self.kvw), torch.float32)
-            parts = self.qkv.slabs(ctx, h, qkv_slabs)
-            stride = qkv_slabs.stride(0)
-            qkv = qkv_slabs[0]
-            q_in = qkv[:, :self.qw]
-            k = qkv[:, self.qw:self.qw + self.kvw]
-            v = qkv[:, self.qw + self.kvw:]
+            if self.q_norm is None:
+                qkv_slabs = ctx.ws.alloc((ctx.max_slabs if fused else 1, n, self.qw + 2 * self.kvw), torch.float32)
+                parts = self.qkv.slabs(ctx, h, qkv_slabs)
+                stride = qkv_slabs.stride(0)
+                qkv = qkv_slabs[0]
+                q_in = qkv[:, :self.qw]
+                k = qkv[:, self.qw:self.qw + self.kvw]
+                v = qkv[:, self.qw + self.kvw:]
+            else:
+                # un-fused: three products from row slices of the stacked weight, so that the heads of q and of k
+                # lie as rows of their own; each head is normalised, then everything goes on as before
+                parts, stride = 1, 0
+                w = self.qkv.weight
+                qn, kn = ctx.ws.alloc((n, self.qw), torch.float32), ctx.ws.alloc((n, self.kvw), torch.float32)
+                q_in, k = ctx.ws.alloc((n, self.qw), torch.float32), ctx.ws.alloc((n, self.kvw), torch.float32)
+                v = ctx.ws.alloc((n, self.kvw), torch.float32)
+                ops.linear(h, w[:self.qw], qn, ctx)
+                ops.linear(h, w[self.qw:self.qw + self.kvw], kn, ctx)
+                ops.linear(h, w[self.qw + self.kvw:], v, ctx)
+                self.q_norm.normalize(ctx, qn.view(n * self.nh, self.hd), q_in.view(n * self.nh, self.hd))
+                self.k_norm.normalize(ctx, kn.view(n * self.nkv, self.hd), k.view(n * self.nkv, self.hd))
             q = ctx.ws.alloc((n, self.qw), rt.dtype)
             b = ctx.batch
             if fused:
@@ -84,15 +107,18 @@ class PagedAttention(Mixer):
                 half = pos.half if pos is not None else 0
                 ops.rope_kv_write(q_in, q, k, v, cos, sin, half, b.positions, b.row_seq, cache.block_table,
                                   cache.k_pool, cache.v_pool, cache.page_size, self.nh, self.nkv, self.hd,
-                                  cache.writable, rt.status, n_partials=parts, partial_stride=stride)
+                                  cache.writable, rt.status, n_partials=parts, partial_stride=stride,
+                                  table_base=cache.table_base)
             else:
                 pos.rotate(ctx, q_in, k if cache.writable else None)
                 ops.rope_kv_write(q_in, q, k, v, None, None, 0, b.positions, b.row_seq, cache.block_table,
                                   cache.k_pool, cache.v_pool, cache.page_size, self.nh, self.nkv, self.hd,
-                                  cache.writable, rt.status)
+                                  cache.writable, rt.status, table_base=cache.table_base)
             a = ctx.ws.alloc((n, self.qw), rt.dtype)
-            ctx.hint(self.o.weight)
-            ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale)
+            # few rows: the attention kernel fetches the start of the output projection's weights into L2 at its end
+            hint = self.o.weight if ctx.l2_hints and n <= 64 else None
+            ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale,
+                                next_weight=hint)
             ctx.pending_slabs = self.o.slabs(ctx, a, ctx.delta_slabs)
 
 

@@ -12,6 +12,7 @@ Categories and the method each must have:
   norm           add_norm(ctx, x, delta, out, rows=None, n_partials=1)
                  x: float32 stream [n, width], updated in place with delta when
                  rows is None; out: normalised rows in the engine dtype.
+                 normalize(ctx, x, out): the norm of every row of x alone.
   position       prepare(ctx) -> per-step tables (memoised in ctx.shared);
                  rotate(ctx, q, k) in place on [n, heads*head_dim] views.
   mixer          forward(ctx, h, out, call); cache_requirement() -> KVRequirement | None;
@@ -119,6 +120,11 @@ class Norm(Part):
     category = "norm"
 
     def add_norm(self, ctx, x, delta, out, rows=None, n_partials: int = 1) -> None:
+        raise NotImplementedError
+
+    def normalize(self, ctx, x, out) -> None:
+        """out = the norm of every row of x (float32 [rows, width], contiguous), nothing added, x unchanged:
+        what a mixer's query/key norm calls with rows = tokens x heads and width = the head size."""
         raise NotImplementedError
 
 

@@ -1,4 +1,4 @@
-"""SiLU-gated dense feed-forward."""
+"""Gated dense feed-forward (SiLU-gated in the architecture built here)."""
 from __future__ import annotations
 
 import torch
@@ -10,17 +10,21 @@ from .spec import register_part
 
 
 class GatedMLP(FeedForward):
-    """d = (silu(h Wg^T) * (h Wu^T)) Wd^T, no bias, no routing
-    (crates/forward/src/core/composites/dense_ffn.rs:116-186).  Gate and up
-    weights are stacked at load, row by row alternately, so one product yields
-    both and its epilogue can apply the activation to neighbouring outputs."""
+    """d = (act(h Wg^T) * (h Wu^T)) Wd^T, no bias, no routing
+    (crates/forward/src/core/composites/dense_ffn.rs:116-186; act = SiLU
+    there).  Gate and up weights are stacked at load, row by row alternately,
+    so one product yields both and its epilogue can apply the activation to
+    neighbouring outputs.  `activation` names one of the kernels' gate
+    activations (kernels.ops.ACTIVATIONS)."""
     graph_safe = True
 
     def __init__(self, runtime=None, prefix="", *, width: int, inner: int, activation: str = "silu",
                  init_std: float = 0.02):
         super().__init__(runtime, prefix)
-        if activation != "silu":
-            raise ValueError(f"gated feed-forward: activation '{activation}' is not implemented (silu)")
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: activation '{activation}' is not implemented "
+                             f"({', '.join(sorted(ops.ACTIVATIONS))})")
+        self.activation = activation
         self.width, self.inner, self.init_std = int(width), int(inner), init_std
         self.gate_up = self.down = None
 
@@ -47,13 +51,13 @@ class GatedMLP(FeedForward):
             if n <= 64:                   # few rows: float32 split-K shares, added by the activation kernel
                 gu = ctx.ws.alloc((ctx.max_slabs, n, 2 * self.inner), torch.float32)
                 parts = self.gate_up.slabs(ctx, h, gu)
-                ops.silu_mul(gu[0], a, n_partials=parts, partial_stride=gu.stride(0))
+                ops.gate_mul(gu[0], a, n_partials=parts, partial_stride=gu.stride(0), activation=self.activation)
             elif ops.tc_supported(h, self.gate_up.weight, a):
-                ops.gemm_tc_gated(h, self.gate_up.weight, a, self.runtime.status)   # activation in the epilogue
+                ops.gemm_tc_gated(h, self.gate_up.weight, a, self.runtime.status, self.activation)   # in the epilogue
             else:
                 gu = ctx.ws.alloc((n, 2 * self.inner), self.runtime.dtype)
                 self.gate_up(ctx, h, gu)
-                ops.silu_mul(gu, a)
+                ops.gate_mul(gu, a, activation=self.activation)
             ctx.pending_slabs = self.down.slabs(ctx, a, ctx.delta_slabs)
 
 

@@ -7,14 +7,18 @@ from .spec import register_part
 
 
 class RMSNorm(Norm):
-    """y = v * w / sqrt(mean(v^2) + eps) with v = x + delta; plain weight, no 1+w
-    (crates/kernels-hip/src/kernels/rmsnorm_f16.cu:41-85).  The sum, the mean
-    and the product are float32; the stream x stays float32."""
+    """y = v * (w + weight_offset) / sqrt(mean(v^2) + eps) with v = x + delta.  The
+    architecture built here uses the plain weight (weight_offset 0,
+    crates/kernels-hip/src/kernels/rmsnorm_f16.cu:41-85); weight_offset 1 is
+    the "1 + w" form some architectures store.  The sum, the mean and the
+    product are float32; the stream x stays float32."""
     graph_safe = True
 
-    def __init__(self, runtime=None, prefix="", *, width: int, eps: float, init=("one_plus_normal", 0.02)):
+    def __init__(self, runtime=None, prefix="", *, width: int, eps: float, init=("one_plus_normal", 0.02),
+                 weight_offset: float = 0.0):
         super().__init__(runtime, prefix)
         self.width, self.eps, self.init = int(width), float(eps), tuple(init)
+        self.weight_offset = float(weight_offset)
         self.weight = None
 
     def own_tensor_specs(self):
@@ -29,7 +33,10 @@ class RMSNorm(Norm):
     def add_norm(self, ctx, x, delta, out, rows=None, n_partials: int = 1):
         stride = ctx.delta_slabs.stride(0) if n_partials > 1 else 0
         ops.add_rms_norm(x, delta, self.weight, self.eps, out, rows=rows, n_partials=n_partials,
-                         n_rows=ctx.n_tokens, partial_stride=stride)
+                         n_rows=ctx.n_tokens, partial_stride=stride, weight_offset=self.weight_offset)
+
+    def normalize(self, ctx, x, out):
+        ops.add_rms_norm(x, None, self.weight, self.eps, out, n_rows=x.shape[0], weight_offset=self.weight_offset)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -76,17 +76,21 @@ def write_random_model(folder, config, seed: int = 0, dtype: str = "bfloat16", f
 
 
 def fill_random_on_device(model, seed: int = 0) -> None:
-    """Bind random weights generated on the model's device (no file).  Same distributions as the file mode;
-    the values differ from the file mode's because the device generator is another one."""
+    """Bind random weights generated on the model's device (no file), part by part.  Same distributions as the
+    file mode; the values differ from the file mode's because the device generator is another one."""
     rt = model.runtime
-    specs = model.tensor_specs()
-    tensors = {}
-    for name, ts in specs.items():
-        if ts.alias_of is not None and ts.alias_of in specs:
-            continue
-        t = draw(ts, seed, name, device=rt.device)
-        tensors[name] = t.to(torch.int32 if ts.kind == "int" else rt.dtype)
-    for name, ts in specs.items():
-        if name not in tensors:
-            tensors[name] = tensors[ts.alias_of]
-    model.bind(tensors)
+    all_specs = model.tensor_specs()
+    shared: dict = {}                              # tensors that stand for another name too (a tied head)
+    targets = {ts.alias_of for ts in all_specs.values() if ts.alias_of is not None and ts.alias_of in all_specs}
+    for part in model.parts():
+        tensors = {}
+        for name, ts in part.tensor_specs().items():
+            src = ts.alias_of if ts.alias_of is not None and ts.alias_of in all_specs else name
+            t = shared.get(src)
+            if t is None:
+                t = draw(all_specs[src], seed, src, device=rt.device)
+                t = t.to(torch.int32 if all_specs[src].kind == "int" else rt.dtype)
+                if src in targets:
+                    shared[src] = t
+            tensors[name] = t
+        part.bind(tensors)

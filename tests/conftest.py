@@ -14,6 +14,14 @@ def pytest_configure(config):
 
 
 def pytest_collection_modifyitems(config, items):
-    """GPU tests fail loudly rather than skip when the marker is selected without a device; when the marker
-    is not selected they are deselected by -m "not gpu" as usual."""
-    return
+    """GPU tests fail loudly rather than skip: when tests marked `gpu` are selected and there is no CUDA device,
+    the run is stopped with an error before the first test.  With -m "not gpu" they are deselected as usual and
+    nothing here looks for a device."""
+    markexpr = config.getoption("markexpr", "") or ""
+    if "not gpu" in markexpr:
+        return
+    if any(item.get_closest_marker("gpu") for item in items) and "gpu" in markexpr:
+        import torch
+        if not torch.cuda.is_available():
+            raise pytest.UsageError("tests marked 'gpu' were selected but no CUDA device is available; "
+                                    "run them on a B200, or select -m \"not gpu\"")

@@ -145,6 +145,24 @@ def attention_causal_window(q, k, v, positions, window: int, scale: float):
     return out
 
 
+def attention_causal_window_dense(q, k, v, positions, window: int, scale: float):
+    """The formula of attention_causal_window with a mask over the whole score matrix instead of a loop over
+    queries, for sequences of thousands of tokens (tests/test_plain.py holds the two against each other).
+    Keys outside [max(0, p-W+1), p] get a weight of exactly zero."""
+    T, nh, hd = q.shape
+    rep = nh // k.shape[1]
+    pos = positions.to(torch.long)
+    seen = pos[None, :] <= pos[:, None]
+    if window > 0:
+        seen &= pos[None, :] >= (pos[:, None] - window + 1)
+    out = torch.zeros_like(q)
+    for g in range(nh):
+        scores = scale * (q[:, g, :] @ k[:, g // rep, :].T)
+        scores = scores.masked_fill(~seen, -math.inf)
+        out[:, g, :] = torch.softmax(scores, dim=-1) @ v[:, g // rep, :]
+    return out
+
+
 def gated_mlp(h, w_gate, w_up, w_down):
     """g = h Wg^T, u = h Wu^T, a = g/(1+exp(-g)) * u, d = a Wd^T; no bias.
     crates/forward/src/core/composites/dense_ffn.rs:116-186;
@@ -155,7 +173,7 @@ def gated_mlp(h, w_gate, w_up, w_down):
     return a @ w_down.T
 
 
-def attention_block(x, W, prefix, c, positions):
+def attention_block(x, W, prefix, c, positions, dense: bool = False):
     """h = norm(x); q,k,v = h Wq^T, h Wk^T, h Wv^T (no bias); rope on q and k
     after projection and before use; attention; o = a Wo^T.
     crates/forward/src/core/composites/standard_attn.rs:130-158, 197-286,
@@ -167,16 +185,17 @@ def attention_block(x, W, prefix, c, positions):
     v = (h @ W[prefix + "self_attn.v_proj.weight"].T).reshape(T, c["nkv"], c["hd"])
     q = rope_split_half(q, positions, c["theta"])
     k = rope_split_half(k, positions, c["theta"])
-    a = attention_causal_window(q, k, v, positions, c["window"], 1.0 / math.sqrt(c["hd"]))
+    attend = attention_causal_window_dense if dense else attention_causal_window
+    a = attend(q, k, v, positions, c["window"], 1.0 / math.sqrt(c["hd"]))
     return a.reshape(T, c["nh"] * c["hd"]) @ W[prefix + "self_attn.o_proj.weight"].T
 
 
-def decoder_block(x, W, layer: int, c, positions):
+def decoder_block(x, W, layer: int, c, positions, dense: bool = False):
     """x = x + attention(norm(x)); x = x + mlp(norm(x)).
     crates/models/qwen35-v2/src/model.rs:25-42;
     crates/forward/src/core/composites/residual_add.rs:26-29."""
     prefix = f"model.layers.{layer}."
-    x = x + attention_block(x, W, prefix, c, positions)
+    x = x + attention_block(x, W, prefix, c, positions, dense)
     h = rms_norm(x, W[prefix + "post_attention_layernorm.weight"], c["eps"])
     x = x + gated_mlp(h, W[prefix + "mlp.gate_proj.weight"],
                       W[prefix + "mlp.up_proj.weight"],
@@ -198,15 +217,18 @@ def lm_head(x, W, c):
 # whole model
 # --------------------------------------------------------------------------
 
-def forward_logits(cfg: dict, W: dict, tokens) -> torch.Tensor:
-    """Logits [T, V] (float64) for one whole sequence at positions 0..T-1.
+def forward_logits(cfg: dict, W: dict, tokens, dense: bool = False, rows=None) -> torch.Tensor:
+    """Logits [T, V] (float64) for one whole sequence at positions 0..T-1 (for the positions in `rows` only,
+    if given; `dense` takes the masked-matrix form of the attention, for long sequences).
     crates/forward/README.md:18-39 gives the order of the parts."""
     c = _cfg(cfg)
     W = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in W.items()}
     positions = torch.arange(len(tokens))
     x = embedding(W["model.embed_tokens.weight"], tokens)
     for layer in range(c["L"]):
-        x = decoder_block(x, W, layer, c, positions)
+        x = decoder_block(x, W, layer, c, positions, dense)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
     return lm_head(x, W, c)
 
 

@@ -6,8 +6,56 @@ import pytest
 import torch
 
 from flambeau_b200.cache.manager import CacheManager, CallPlan
-from flambeau_b200.cache.pages import OutOfPages, PageError, PagePool
+from flambeau_b200.cache.pages import Books, OutOfPages, PageError
 from flambeau_b200.parts.base import KVRequirement, StateRequirement
+
+
+class PagePool:
+    """A pool on its own, driven through the books (one group, one request slot per held page, pages of one
+    token): what the cache manager's groups are made of."""
+
+    def __init__(self, n_pages: int):
+        if n_pages <= 0:
+            raise ValueError("a page pool needs at least one page")
+        self.n_pages = int(n_pages)
+        # one request slot per possible holder of a single page; page_size 1 makes a token a page
+        self._books = Books([self.n_pages], [0], 1, self.n_pages + 1, self.n_pages)
+        self._holder: dict = {}              # page id -> slot that holds it
+
+    @property
+    def n_free(self) -> int:
+        return self._books.free_pages()[0]
+
+    @property
+    def n_held(self) -> int:
+        return self.n_pages - self.n_free
+
+    def take(self, count: int) -> list:
+        """`count` page ids, or OutOfPages with nothing taken."""
+        if count < 0:
+            raise ValueError("negative page count")
+        if count > self.n_free:
+            raise OutOfPages(count, self.n_free, self.n_pages)
+        out = []
+        for _ in range(count):
+            slot = self._books.admit()
+            self._books.reserve_all([slot], [1])
+            page = self._books.pages(slot, 0)[0]
+            self._holder[page] = slot
+            out.append(page)
+        return out
+
+    def give_back(self, pages) -> None:
+        for p in pages:
+            if not 0 <= p < self.n_pages:
+                raise PageError(f"page id {p} is outside the pool of {self.n_pages}")
+            slot = self._holder.pop(p, None)
+            if slot is None:
+                raise PageError(f"page {p} is given back but is not held")
+            self._books.release(slot)
+
+    def is_held(self, page: int) -> bool:
+        return self._books.is_held(0, page)
 
 
 def test_pool_is_fifo_and_all_or_nothing():
@@ -82,6 +130,7 @@ def test_window_gives_pages_back_as_they_die():
     first_live = rec.length - 16 + 1
     for j, p in enumerate(rec.pages[0]):
         assert (p < 0) == ((j + 1) * 16 <= first_live), "exactly the pages wholly below the window are given back"
+    assert cm.first_live_page("a", 0) == first_live // 16
     cm.release("a")
     assert cm.free_pages() == [4]
 
@@ -146,3 +195,34 @@ def test_random_orders_never_lose_or_double_a_page(window, seed):
         assert held + cm.free_pages()[0] == cm.groups[0].pool.n_pages
     cm.release_all()
     assert cm.free_pages() == [12]
+
+
+def test_a_reader_may_not_look_further_back_than_the_cache_it_reads_keeps():
+    """Pages are given back by the owner's window; a call that reads that cache with no window, or a wider one,
+    would ask for keys whose pages are gone."""
+    def build(owner_window, reader_window):
+        return CacheManager([CallPlan(kv=KVRequirement(2, 16, owner_window)),
+                             CallPlan(kv=KVRequirement(2, 16, reader_window), cache_from=0)],
+                            max_tokens=64, page_size=16, max_requests=1, device="cpu", dtype=torch.float32)
+    for owner, reader in ((16, 0), (16, 32)):
+        with pytest.raises(ValueError, match="keeps only"):
+            build(owner, reader)
+    for owner, reader in ((0, 0), (0, 8), (32, 32), (32, 8)):
+        build(owner, reader)
+
+
+def test_a_windowed_request_outlives_its_table_row():
+    """A block-table row holds live pages only, so a request under a window runs on far past the number of
+    tokens that the row's columns could address from position 0."""
+    plans = [CallPlan(kv=KVRequirement(1, 8, 24))]
+    cm = CacheManager(plans, max_tokens=128, page_size=8, max_requests=2, device="cpu", dtype=torch.float32,
+                      max_seq_len=100000, max_step_tokens=16)
+    assert cm.table_pages == -(-(24 + 16) // 8) + 2
+    cm.admit("a")
+    for _ in range(300):                          # 4,800 tokens through a row of 7 columns and a pool of 16 pages
+        cm.reserve("a", 16)
+        live = [p for p in cm.requests["a"].pages[0] if p >= 0]
+        assert len(live) <= cm.table_pages
+        cm.commit("a", 16)
+        cm.check_invariants()
+    assert cm.length("a") == 4800 and cm.first_live_page("a", 0) == (4800 - 24 + 1) // 8

@@ -57,19 +57,23 @@ def test_generation_under_page_pressure_gives_the_same_tokens(model):
     from flambeau_b200.sampling.params import SamplingParams
     if model["dtype"] != "float32":
         pytest.skip("token-for-token equality is a float32 property")
-    prompts = list(tiny.random_requests(model["cfg"], [20, 33, 18, 27], seed=9).values())
+    # A pool that the requests outgrow while they decode.  Without a window every request keeps growing.  Under
+    # a window a request holds two pages at most, so the prompts are short enough to be admitted side by side on
+    # one page each, and the pool has five pages for the eight they come to need.
+    windowed = model["cfg"]["sliding_window"] is not None
+    lengths, tight_tokens = ([5, 9, 7, 12], 80) if windowed else ([20, 33, 18, 27], 112)
+    prompts = list(tiny.random_requests(model["cfg"], lengths, seed=9).values())
     params = SamplingParams(max_tokens=30)
     roomy = Engine.from_folder(model["folder"], EngineOptions(dtype="float32", cache_tokens=512, max_requests=4,
                                                               max_step_tokens=64, max_seq_len=128))
     want = Generator(roomy, prefill_chunk_tokens=16).generate(prompts, params)
-    tight = Engine.from_folder(model["folder"], EngineOptions(dtype="float32", cache_tokens=112, max_requests=4,
+    tight = Engine.from_folder(model["folder"], EngineOptions(dtype="float32", cache_tokens=tight_tokens, max_requests=4,
                                                               max_step_tokens=64, max_seq_len=128))
     gen = Generator(tight, prefill_chunk_tokens=16)
     got = gen.generate(prompts, params)
     assert got == want
     sched = gen.last_scheduler
-    if model["cfg"]["sliding_window"] is None:
-        assert sum(r.preemptions for r in sched.finished) > 0, "the pool was meant to be too small"
+    assert sum(r.preemptions for r in sched.finished) > 0, "the pool was meant to be too small"
     assert all(r.finish_reason == "length" for r in sched.finished)
     tight.cache.check_invariants()
     assert not tight.cache.requests

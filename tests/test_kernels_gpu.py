@@ -233,16 +233,73 @@ def test_cache_write_flags_a_missing_page():
     assert int(st.item()) == 2
 
 
+def gate_times(activation, g, u):
+    """The gate activations of the kernels, in float64."""
+    if activation == "silu":
+        return g / (1 + torch.exp(-g)) * u
+    return 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3))) * u
+
+
 @pytest.mark.parametrize("n,I", [(1, 7), (5, 160), (3, 14336), (2, 1002)])
 @pytest.mark.parametrize("di,do,slabs", [("f", "f", 1), ("b", "b", 1), ("f", "b", 5), ("f", "b", 9)])
-def test_silu_mul(n, I, di, do, slabs):
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
+def test_gate_mul(n, I, di, do, slabs, activation):
     from flambeau_b200.kernels import ops
     parts = torch.randn(slabs, n, 2 * I, device=DEV).to(DT[di])
     out = torch.empty(n, I, device=DEV, dtype=DT[do])
-    ops.silu_mul(parts[0], out, n_partials=slabs, partial_stride=parts.stride(0))
+    ops.gate_mul(parts[0], out, n_partials=slabs, partial_stride=parts.stride(0), activation=activation)
     gu = parts.double().sum(0)
     g, u = gu[:, 0::2], gu[:, 1::2]                         # gate and up alternate along a row
-    close(out, g / (1 + torch.exp(-g)) * u, 3e-6 if do == "f" else 6e-3)
+    close(out, gate_times(activation, g, u), 3e-6 if do == "f" else 6e-3)
+
+
+def test_an_unknown_activation_is_refused():
+    from flambeau_b200.kernels import ops
+    from flambeau_b200.kernels.library import KernelError
+    gu = torch.randn(2, 8, device=DEV)
+    with pytest.raises(KernelError, match="not implemented"):
+        ops.gate_mul(gu, torch.empty(2, 4, device=DEV), activation="relu")
+
+
+@pytest.mark.parametrize("n,H,od", [(3, 96, "f"), (5, 4096, "b"), (300, 1024, "b"), (2, 20000, "f")])
+def test_add_rms_norm_with_a_weight_offset(n, H, od):
+    """The "1 + w" form of the norm: the stored weight plus an offset, in each of the kernel's forms."""
+    from flambeau_b200.kernels import ops
+    eps = 1e-6
+    x = torch.randn(n, H, device=DEV)
+    delta = torch.randn(n, H, device=DEV) * 0.5
+    w = (0.1 * torch.randn(H, device=DEV)).to(DT[od])
+    out = torch.empty(n, H, device=DEV, dtype=DT[od])
+    x0 = x.clone()
+    ops.add_rms_norm(x, delta, w, eps, out, weight_offset=1.0)
+    v = x0.double() + delta.double()
+    close(out, pm.rms_norm(v, 1.0 + w.double(), eps), 3e-6 if od == "f" else 6e-3)
+
+
+def test_cache_write_through_a_table_that_starts_at_a_later_page():
+    """A table row holds live pages only: column 0 stands for the logical page given in table_base."""
+    from flambeau_b200.kernels import ops
+    ps, nkv, hd, nh = 8, 2, 16, 2
+    positions = torch.tensor([100, 101, 7, 103], dtype=torch.int32, device=DEV)
+    row_seq = torch.tensor([0, 0, 1, 0], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[5, 3, -1], [9, -1, -1]], dtype=torch.int32, device=DEV)
+    base = torch.tensor([11, 0], dtype=torch.int32, device=DEV)          # sequence 0: columns are pages 11, 12, 13
+    qkv = torch.randn(4, (nh + 2 * nkv) * hd, device=DEV)
+    kp = torch.zeros(12, nkv, ps, hd, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.empty(4, nh * hd, device=DEV)
+    st = status()
+    ops.rope_kv_write(qkv[:, :nh * hd], q_out, qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:], None, None,
+                      0, positions, row_seq, table, kp, vp, ps, nh, nkv, hd, True, st, table_base=base)
+    assert int(st.item()) == 0
+    k = qkv[:, nh * hd:(nh + nkv) * hd].reshape(4, nkv, hd)
+    for r, (page, slot) in enumerate([(3, 4), (3, 5), (9, 7), (3, 7)]):
+        assert torch.equal(kp[page, :, slot], k[r])
+    # a position below the row's first page has no column: flagged, nothing written
+    positions[0] = 80
+    ops.rope_kv_write(qkv[:, :nh * hd], q_out, qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:], None, None,
+                      0, positions, row_seq, table, kp, vp, ps, nh, nkv, hd, True, st, table_base=base)
+    assert int(st.item()) == 2
 
 
 # ---- sampler -------------------------------------------------------------------------------------------------

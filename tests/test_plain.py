@@ -41,6 +41,26 @@ def test_window_limits_what_a_query_sees():
     assert torch.allclose(w1, v.repeat_interleave(1, dim=1))
 
 
+@pytest.mark.parametrize("window", [0, 1, 5, 40])
+def test_the_masked_matrix_form_of_the_attention_equals_the_loop(window):
+    g = torch.Generator().manual_seed(window)
+    T = 37
+    q = torch.randn(T, 6, 8, generator=g, dtype=torch.float64)
+    k, v = (torch.randn(T, 3, 8, generator=g, dtype=torch.float64) for _ in range(2))
+    pos = torch.arange(T)
+    loop = pm.attention_causal_window(q, k, v, pos, window, 0.35)
+    dense = pm.attention_causal_window_dense(q, k, v, pos, window, 0.35)
+    assert torch.allclose(loop, dense, atol=1e-13, rtol=0)
+
+
+def test_whole_model_with_the_masked_matrix_form_and_chosen_rows(model):
+    cfg, W = model
+    toks = tiny.random_requests(cfg, [45], seed=5)["r0"]
+    full = pm.forward_logits(cfg, W, toks)
+    some = pm.forward_logits(cfg, W, toks, dense=True, rows=[0, 17, 44])
+    assert torch.allclose(full[[0, 17, 44]], some, atol=1e-11, rtol=0)
+
+
 def test_rope_rotates_pairs_and_keeps_norms():
     x = torch.randn(5, 3, 16, dtype=torch.float64)
     pos = torch.tensor([0, 1, 2, 50, 1000])

@@ -17,8 +17,8 @@ VOCAB = 500
 def make(tokens=256, window=24, max_requests=4, page_size=8, max_step=64):
     cache = CacheManager([CallPlan(kv=KVRequirement(1, 8, 0)), CallPlan(kv=KVRequirement(2, 8, window))],
                          max_tokens=tokens, page_size=page_size, max_requests=max_requests, device="cpu",
-                         dtype=torch.float32, max_seq_len=tokens)
-    buffers = BatchBuffers(torch.device("cpu"), max_step, max_requests, cache.n_groups, cache.max_pages_per_request)
+                         dtype=torch.float32, max_seq_len=tokens, max_step_tokens=max_step)
+    buffers = BatchBuffers(torch.device("cpu"), max_step, max_requests, cache.n_groups, cache.table_pages)
     return cache, buffers
 
 
@@ -83,14 +83,19 @@ def test_descriptor_of_random_steps(seed):
         assert b.max_kv_len >= max(p + q for p, q in zip(seqs["pos0"], seqs["qlen"]))
         for gi in range(cache.n_groups):
             for s, e in enumerate(entries):
-                pages = list(cache.table_row(e.request_id, gi))
+                pages = list(cache.table_row(e.request_id, gi))      # by logical page, -1 = given back
+                base = cache.first_live_page(e.request_id, gi)
                 got = b.tables[gi][s].tolist()
-                assert got[:len(pages)] == pages, f"group {gi} sequence {s}"
+                # the row holds the live pages only, from the first live page on
+                assert all(p < 0 for p in pages[:base]) and all(p >= 0 for p in pages[base:])
+                assert int(b.table_bases[gi][s]) == base
+                assert got[:len(pages) - base] == pages[base:], f"group {gi} sequence {s}"
+                assert all(p == -1 for p in got[len(pages) - base:]), "what an earlier request left in the row"
                 # every position a query of this step can see has a page
                 window = cache.groups[gi].req.window
                 first_q, last_q = seqs["pos0"][s], seqs["pos0"][s] + seqs["qlen"][s] - 1
                 lo = max(0, first_q - window + 1) if window else 0
-                assert all(got[p // 8] >= 0 for p in range(lo, last_q + 1))
+                assert all(got[p // 8 - base] >= 0 for p in range(lo, last_q + 1))
         cache.commit_all([(e.request_id, len(e.tokens)) for e in entries])
         cache.check_invariants()
         for e in entries:

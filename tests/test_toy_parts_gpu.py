@@ -1,6 +1,8 @@
 """Generality of the parts framework, shown with toy parts that are defined here and never become a model:
 a mixer with state of its own (no keys or values), a feed-forward that routes each token to two of four experts,
-a position encoding with a rotate() of its own, a run order that names a layer twice and lets a call read another call's cache.  They are registered, built, loaded from a
+a position encoding with a rotate() of its own, a query/key norm of the "1 + w" kind hooked into the attention
+mixer, a feed-forward gated by another activation, a run order that names a layer twice and lets a call read
+another call's cache.  They are registered, built, loaded from a
 random model folder and stepped through the engine (whole, in portions, mixed with page reuse, decoded one by
 one) without a change to the framework's files, and compared with a plain computation written here."""
 import json
@@ -152,15 +154,16 @@ def toy_spec(cfg: ToyConfig):
     def norm(prefix):
         return PartSpec("norm", "rmsnorm", dict(width=H, eps=cfg.eps), prefix)
 
-    def ffn(prefix):
-        return PartSpec("feed_forward", "gated_mlp", dict(width=H, inner=cfg.inner), prefix)
+    def ffn(prefix, activation="silu"):
+        return PartSpec("feed_forward", "gated_mlp", dict(width=H, inner=cfg.inner, activation=activation), prefix)
 
     def routed(prefix):
         return PartSpec("feed_forward", "toy_routed", dict(width=H, inner=cfg.expert_inner, experts=cfg.experts), prefix)
 
     def block(i, mixer):
         p = f"layers.{i}."
-        return PartSpec("block", "pre_norm", dict(mixer=mixer, feed_forward=(routed if i == 1 else ffn)(p + "ffn."),
+        feed_forward = routed(p + "ffn.") if i == 1 else ffn(p + "ffn.", "gelu_tanh" if i == 2 else "silu")
+        return PartSpec("block", "pre_norm", dict(mixer=mixer, feed_forward=feed_forward,
                                                   mixer_norm=norm(p + "norm1."), feed_forward_norm=norm(p + "norm2.")), p)
 
     attn0 = PartSpec("mixer", "attention", dict(
@@ -170,7 +173,10 @@ def toy_spec(cfg: ToyConfig):
     decay = PartSpec("mixer", "toy_decay", dict(width=H, decay=cfg.decay), "layers.1.mix.")
     attn2 = PartSpec("mixer", "attention", dict(
         width=H, num_heads=cfg.heads, num_kv_heads=cfg.heads, head_dim=cfg.head_dim, window=0, init_std=cfg.attn_std,
-        position=PartSpec("position", "toy_shifted_rotary", dict(head_dim=cfg.head_dim, theta=cfg.theta, shift=5))),
+        position=PartSpec("position", "toy_shifted_rotary", dict(head_dim=cfg.head_dim, theta=cfg.theta, shift=5)),
+        # a norm over every head of q and k before the rotation, stored as w with 1 + w applied
+        qk_norm=PartSpec("norm", "rmsnorm", dict(width=cfg.head_dim, eps=cfg.eps, weight_offset=1.0,
+                                                 init=("normal", 0.2)))),
         "layers.2.attn.")
     return ModelSpec(
         hidden_size=H, vocab_size=cfg.vocab_size,
@@ -208,6 +214,9 @@ def plain_toy_logits(cfg: ToyConfig, W, tokens):
             if layer == 0:
                 q, k = pm.rope_split_half(q, pos, cfg.theta), pm.rope_split_half(k, pos, cfg.theta)
             else:
+                q = pm.rms_norm(q, 1.0 + W[a + "q_norm.weight"], cfg.eps)
+                k = pm.rms_norm(k, 1.0 + W[a + "k_norm.weight"], cfg.eps)
+
                 def interleaved(t):
                     i = torch.arange(cfg.head_dim // 2, dtype=torch.float64)
                     ang = (pos.double() + 5)[:, None] * (cfg.theta ** (-2.0 * i / cfg.head_dim))[None, :]
@@ -229,6 +238,10 @@ def plain_toy_logits(cfg: ToyConfig, W, tokens):
             weights = routing_weights(h @ W[p + "ffn.router"].T)
             for e in range(cfg.experts):
                 x = x + weights[:, e:e + 1] * (torch.relu(h @ W[p + "ffn.up"][e].T) @ W[p + "ffn.down"][e].T)
+        elif layer == 2:
+            g, u = h @ W[p + "ffn.gate_proj.weight"].T, h @ W[p + "ffn.up_proj.weight"].T
+            act = 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3)))
+            x = x + (act * u) @ W[p + "ffn.down_proj.weight"].T
         else:
             x = x + pm.gated_mlp(h, W[p + "ffn.gate_proj.weight"], W[p + "ffn.up_proj.weight"],
                                  W[p + "ffn.down_proj.weight"])
