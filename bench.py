@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--shape 7b|nemo12b|small24b] [--only headline|mixed|shapes] ...
 
 Default run: the layer sizes of the Mistral-7B-v0.1 shape with random weights in bfloat16, a batch of 8
 sequences that each hold 8,192 tokens of context (4,096 live keys under the sliding window), 16-token pages.
@@ -10,24 +11,35 @@ A "step" is one decode step.  It prints ONE JSON line:
   value      decoded tokens a second, timed on the device with CUDA events over exactly K steps
   e2e        the same through the Python entry point's own loop (scheduler step -> engine step -> sampler):
              host token ids in from pinned memory, sampled token ids back to the host, every step
-  prefill    one step of 2,048 prompt tokens: tokens a second, ms, and flops / time / bf16 peak
+  prefill    one step of 2,048 prompt tokens: tokens a second, ms, and flops / time / bf16 peak; beside it the
+             same prompt through the entry point as time to the first token (`ttft_ms`, the scheduler cutting it
+             into portions of 512, the default, and of 2,048) and one bare step of 512 tokens
   roofline   bytes the decode step has to read (every weight it uses once + the live cache) / time / HBM peak
-  points     decode tokens a second at batch 1 and 64
+  points     decode tokens a second at batch 1 and 64, and the other shapes' figures as flat numbers
+  kernels    per kernel class of the decode step and of the 2,048-token step: launches and microseconds per layer
+             call (CUDA events around every launcher call of an eager step: serialised kernels), and the
+             fraction of the measured peak that bounds the class
+  check      outside the timed regions: the decode attention at the benchmarked geometry against a float32
+             softmax over the same pages, and whether the step's logits are finite
+  mixed      the Mistral-Nemo-12B shape: 32 requests with seeded prompts of 128 to 4,096 tokens, portions of
+             512, 256 sampled tokens each at temperature 0.7, through the scheduler with a page pool smaller
+             than the requests' sum; prefill as prompt tokens / time to first token and decode as
+             (n - 1) / (last - first token time), the reference's conventions (doc/PERF_MATRIX.md:4-8); and one
+             mixed step's host time against its device time
+  shapes     the Mistral-Small-24B shape: decode at batch 1 / 8 / 64 with 4,096-token contexts and a 2,048-token
+             prefill, each with its roofline fraction
 
-The cache of the timed sequences is laid out by the cache manager exactly as a real 8,192-token request leaves
-it (pages taken and, under the window, given back), but its keys and values are random numbers rather than the
-result of 8 x 8,192 tokens of prefill; weights are random too ("data": "synthetic").
-Every decode step reads all weights (14 GB), far more than the 126 MB L2, so no L2 flush is needed.
+The cache of the timed sequences is laid out by the cache manager exactly as a real request of that length
+leaves it (pages taken and, under the window, given back), but its keys and values are random numbers rather than
+the result of a prefill; weights are random too ("data": "synthetic").  Every decode step reads all weights
+(14 GB and more), far more than the 126 MB L2, so no L2 flush is needed.
 """
 from __future__ import annotations
 
 import argparse
+import gc
 import json
-import os
-import statistics
-import subprocess
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -35,11 +47,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
-
-MISTRAL_7B = dict(architectures=["MistralForCausalLM"], hidden_size=4096, num_hidden_layers=32,
-                  num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
-                  vocab_size=32000, rope_theta=10000.0, sliding_window=4096, rms_norm_eps=1e-5,
-                  tie_word_embeddings=False, max_position_embeddings=32768)
+PAGE = 16
 
 
 def peaks() -> dict:
@@ -64,59 +72,20 @@ def peaks() -> dict:
     return dict(FALLBACK_PEAKS)
 
 
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int = 0):
-        self.rows, self.proc, self.index = [], None, index
-
-    def __enter__(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
-        return self
-
-    def _read(self):
-        for line in self.proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) >= 6:
-                self.rows.append(parts)
-
-    def __exit__(self, *exc):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
-
-    def summary(self) -> dict:
-        mhz = [int(r[0]) for r in self.rows if r[0].isdigit()]
-        mx = [int(r[1]) for r in self.rows if r[1].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(self.rows)}
-
-
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--shape", default="7b", help="the shape of the headline run: 7b, nemo12b or small24b")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the 32 of the shape (sizes unchanged)")
+    ap.add_argument("--context", type=int, default=None, help="tokens per sequence (default: the shape's)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (sizes unchanged)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true", help="do not measure batch 1 and 64")
+    ap.add_argument("--only", choices=["all", "headline", "mixed", "shapes"], default="all",
+                    help="headline: the shape's own line only; mixed / shapes: that part only")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -134,175 +103,165 @@ def main(argv=None) -> int:
     import torch
     from flambeau_b200.config.mistral import MistralConfig
     from flambeau_b200.engine.batch import Entry
-    from flambeau_b200.engine.generate import EngineExecutor
-    from flambeau_b200.engine.scheduler import Request, Scheduler
     from flambeau_b200.engine.step import Engine, EngineOptions
-    from flambeau_b200.kernels import library
-    from flambeau_b200.sampling.params import SamplingParams
+    from flambeau_b200.measure import work, workloads
+    from flambeau_b200.measure.shapes import shape as shape_of
+    from flambeau_b200.measure.timers import ClockSampler
 
     pk = peaks()
-    layers_full = MISTRAL_7B["num_hidden_layers"]
-    layers = args.layers or layers_full
-    cfg = MistralConfig.from_dict({**MISTRAL_7B, "num_hidden_layers": layers})
-    window = cfg.sliding_window or 0
-    page = 16
-    max_batch = args.batch if args.skip_points else max(args.batch, 64)
-    live_per_seq = min(args.context, window + page) if window else args.context
-    per_seq_pool = -(-(live_per_seq + 2 * page + args.steps + args.warmup + 64) // page) * page
-    cache_tokens = max(max_batch * per_seq_pool + 512, args.prefill_tokens + page)
-    engine = Engine.from_config(cfg, seed=0, options=EngineOptions(
-        dtype="bfloat16", page_size=page, cache_tokens=cache_tokens, max_requests=max_batch,
-        max_step_tokens=max(args.prefill_tokens, max_batch), max_seq_len=args.context + 4096))
-    dev = engine.runtime.device
-    for g in engine.cache.groups:                       # random keys and values stand in for a real prefill
-        for c in g.owners:
-            g.k[c].normal_(0.0, 1.0)
-            g.v[c].normal_(0.0, 1.0)
-    vocab = cfg.vocab_size
+    tag = "of measured" if pk["source"] == "measured" else "of fallback"
     gen = torch.Generator().manual_seed(1)
 
-    def seat(batch: int, context: int) -> list:
-        """`batch` requests whose cache holds context-1 tokens (bookkeeping only: pages taken and released as a
-        real request of that length would have them)."""
-        engine.cache.release_all()
-        ids = []
-        for i in range(batch):
-            rid = f"seq{i}"
-            engine.cache.admit(rid)
-            left = context - 1
-            while left > 0:
-                k = min(left, 256)
-                engine.cache.reserve(rid, k)
-                engine.cache.commit(rid, k)
-                left -= k
-            ids.append(rid)
-        return ids
+    def build(shape, layers, max_batch, context, prefill_tokens, steps):
+        cfg = MistralConfig.from_dict({**shape.config, "num_hidden_layers": layers})
+        window = cfg.sliding_window or 0
+        live = min(context, window + PAGE) if window else context
+        per_seq = -(-(live + 2 * PAGE + steps + 64) // PAGE) * PAGE
+        cache_tokens = max(max_batch * per_seq + 512, prefill_tokens + PAGE)
+        engine = Engine.from_config(cfg, seed=0, options=EngineOptions(
+            dtype="bfloat16", page_size=PAGE, cache_tokens=cache_tokens, max_requests=max_batch,
+            max_step_tokens=max(prefill_tokens, max_batch), max_seq_len=min(context + 4096, cfg.max_position_embeddings)))
+        workloads.randomise_cache(engine)
+        return cfg, engine
 
-    def decode_device(batch: int, steps: int, warmup: int) -> tuple:
-        """(ms per step, launches per step) of engine.step + on-device sampling with fixed input tokens."""
-        ids = seat(batch, args.context)
-        tok = torch.randint(0, vocab, (batch,), generator=gen).tolist()
-        entries = [Entry(r, [t], [0]) for r, t in zip(ids, tok)]
-        from flambeau_b200.kernels import ops
-        chosen = torch.zeros(batch, dtype=torch.int32, device=dev)
-        for _ in range(warmup):
-            ops.sample(engine.step(entries), chosen, n=batch)
-        torch.cuda.synchronize()
-        l0 = library.LAUNCHES[0]
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for _ in range(steps):
-            ops.sample(engine.step(entries), chosen, n=batch)
-        t1.record()
-        torch.cuda.synchronize()
-        engine.runtime.check_status("bench decode")
-        return t0.elapsed_time(t1) / steps, (library.LAUNCHES[0] - l0) / steps
+    def drop(engine):
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
 
-    def decode_e2e(batch: int, steps: int, warmup: int) -> tuple:
-        """Tokens a second through the scheduler loop that generate() runs: host ids in, host ids out."""
-        ids = seat(batch, args.context)
-        ex = EngineExecutor(engine)
-        sched = Scheduler(ex, token_budget=max(batch, 1), prefill_chunk=512, max_running=batch)
-        for i, rid in enumerate(ids):
-            r = Request(rid, prompt=[0] * (args.context - 1), params=SamplingParams(max_tokens=steps + warmup + 8),
-                        generated=[int(torch.randint(0, vocab, (1,), generator=gen))], arrival=i)
-            r.fed = args.context - 1
-            sched.running.append(r)
-        ahead = sched.run_ahead
+    def decode_point(engine, cfg, batch, context, steps, warmup):
+        ms, launches = workloads.decode_device(engine, batch, context, steps, warmup, gen)
+        nbytes = work.decode_step_bytes(engine.model.step_weight_bytes(), engine.cache.kv_bytes_per_token(),
+                                        [context] * batch, cfg.sliding_window or 0)
+        gbs = nbytes / (ms / 1e3) / 1e9
+        return dict(ms=ms, launches=launches, tok_s=batch / (ms / 1e3), bytes=nbytes, gbs=gbs,
+                    frac=gbs / pk["hbm_gbs"])
 
-        def run_steps(n: int) -> None:
-            # the scheduler queues each step before it reads the tokens of the one before; the last step of a
-            # region queues nothing, so the region holds exactly the device work of the tokens it delivers
-            for i in range(n):
-                sched.run_ahead = ahead and i < n - 1
-                assert len(sched.step()) == batch
+    def prefill_point(engine, cfg, layers, tokens):
+        ms = workloads.prefill_step(engine, tokens, gen)
+        flops = work.step_flops(cfg, layers, range(tokens), 1)
+        tflops = flops / (ms / 1e3) / 1e12
+        return dict(ms=ms, tok_s=tokens / (ms / 1e3), tflops=tflops, frac=tflops / pk["bf16_tflops"])
 
-        run_steps(warmup)
-        torch.cuda.synchronize()
-        h0, d0 = ex.h2d_bytes, ex.d2h_bytes
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        w0 = time.perf_counter()
-        t0.record()
-        run_steps(steps)
-        t1.record()
-        torch.cuda.synchronize()
-        wall = time.perf_counter() - w0
-        ms = max(t0.elapsed_time(t1), wall * 1e3)
-        for rid in ids:
-            engine.cache.release(rid)
-        return batch * steps / (ms / 1e3), (ex.h2d_bytes - h0) / steps, (ex.d2h_bytes - d0) / steps
+    line: dict = {}
+    clock_summary = None
+    head = shape_of(args.shape)
+    context = args.context or head.context
+    layers_full = head.config["num_hidden_layers"]
+    layers = args.layers or layers_full
 
-    def prefill(tokens: int) -> float:
-        engine.cache.release_all()
-        toks = torch.randint(0, vocab, (tokens,), generator=gen).tolist()
-        times = []
-        for i in range(8):                              # 3 warm-up steps, then the median of 5
-            torch.cuda.synchronize()
-            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            t0.record()
-            engine.step([Entry("prompt", toks, [tokens - 1])], end=["prompt"])
-            t1.record()
-            torch.cuda.synchronize()
-            if i >= 3:
-                times.append(t0.elapsed_time(t1))
-        engine.runtime.check_status("bench prefill")
-        return statistics.median(times)
-
-    # ---- measurements ----------------------------------------------------------
-    with ClockSampler(dev.index or 0) as clocks:        # clocks and throttle reasons while the timed regions run
+    with ClockSampler(0) as clocks:                     # clocks and throttle reasons while the timed regions run
         time.sleep(0.3)                                 # let nvidia-smi start reporting before the first region
-        ms_step, launches = decode_device(args.batch, args.steps, args.warmup)
-        e2e_value, h2d, d2h = decode_e2e(args.batch, args.steps, args.warmup)
-        points = {}
-        if not args.skip_points:
-            for b in (1, 64):
-                ms_b, _ = decode_device(b, max(8, args.steps // 2), 3)
-                points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
-        pre_ms = prefill(args.prefill_tokens)
-    clock_summary = clocks.summary()
+        # ---- the headline shape -------------------------------------------------------------------
+        if args.only in ("all", "headline"):
+            max_batch = args.batch if args.skip_points else max(args.batch, 64)
+            cfg, engine = build(head, layers, max_batch, context, args.prefill_tokens, args.steps + args.warmup)
+            d = decode_point(engine, cfg, args.batch, context, args.steps, args.warmup)
+            e2e_value, h2d, d2h = workloads.decode_e2e(engine, args.batch, context, args.steps, args.warmup, gen)
+            points = {}
+            if not args.skip_points:
+                for b in (1, 64):
+                    points[f"decode_b{b}"] = round(decode_point(engine, cfg, b, context, max(8, args.steps // 2), 3)["tok_s"], 1)
+            T = args.prefill_tokens
+            pre = prefill_point(engine, cfg, layers, T)
+            prefill = {"value": round(pre["tok_s"], 1), "tokens": T, "ms": round(pre["ms"], 3),
+                       "frac": round(pre["frac"], 4), "tflops": round(pre["tflops"], 1),
+                       "peak_tflops": pk["bf16_tflops"], "peak": tag}
+            if args.only == "all":
+                pre512 = prefill_point(engine, cfg, layers, 512)
+                prefill["step_512_ms"] = round(pre512["ms"], 3)
+                prefill["step_512_tok_s"] = round(pre512["tok_s"], 1)
+                for chunk in (512, T):
+                    ms = workloads.time_to_first(engine, T, chunk, gen)
+                    prefill[f"ttft_ms_chunk{chunk}"] = round(ms, 3)
+                    prefill[f"ttft_tok_s_chunk{chunk}"] = round(T / (ms / 1e3), 1)
+            # ---- outside the timed regions: correctness of the benchmarked geometry, per-kernel times ----
+            check = workloads.attention_check(engine, args.batch, context, gen)
+            kernels = {}
+            if args.only == "all":
+                ids = workloads.seat(engine, [context] * args.batch)
+                entries = [Entry(r, [int(torch.randint(0, cfg.vocab_size, (1,), generator=gen))], [0]) for r in ids]
+                sections = workloads.kernel_sections(engine, entries, cfg)
+                kernels[f"decode_b{args.batch}"] = workloads.roofline_of_sections(
+                    cfg, sections, args.batch, [context] * args.batch, layers, pk)
+                engine.cache.release_all()
+                toks = torch.randint(0, cfg.vocab_size, (T,), generator=gen).tolist()
+                sections = workloads.kernel_sections(engine, [Entry("prompt", toks, [T - 1])], cfg, end=["prompt"])
+                kernels[f"prefill_{T}"] = workloads.roofline_of_sections(cfg, sections, T, [T], layers, pk)
+            window = cfg.sliding_window or 0
+            line = {
+                "metric": f"decode tok/s @ batch {args.batch} ({head.name}, {context} context); "
+                          f"prefill tok/s @ {T}; % of roofline",
+                "value": round(d["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": round(d["ms"], 4), "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+                "config": {
+                    "model": f"{head.name}, random weights", "global_batch": args.batch, "seq_len": context,
+                    "parallelism": "single GPU", "layers": layers, "layers_of_shape": layers_full,
+                    "hidden_size": cfg.hidden_size, "heads": cfg.num_attention_heads,
+                    "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                    "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,
+                    "sliding_window": window, "page_size": PAGE, "kv_dtype": "bf16",
+                    "l2": "inputs larger than L2 (every step reads all weights)",
+                    "cache_state": f"pages laid out by the cache manager for {context - 1}-token requests; K/V values random",
+                },
+                "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+                        "d2h_bytes_per_step": int(d2h)},
+                "gpu_launches": int(round(d["launches"] * args.steps)),
+                "prefill": prefill,
+                "roofline": {"bound": "hbm", "achieved": round(d["gbs"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                             "frac": round(d["frac"], 4), "bytes_per_step": int(d["bytes"]), "peak_source": tag},
+                "points": points, "check": check, "kernels": kernels,
+            }
+            drop(engine)
+            del engine
 
-    # ---- accounting --------------------------------------------------------------
-    weight_bytes = engine.model.step_weight_bytes()
-    live_keys = min(args.context, window) if window else args.context
-    kv_bytes = args.batch * live_keys * engine.cache.kv_bytes_per_token()
-    step_bytes = weight_bytes + kv_bytes
-    achieved_gbs = step_bytes / (ms_step / 1e3) / 1e9
-    H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
-    qw, kvw = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
-    T = args.prefill_tokens
-    linear_flops = 2.0 * T * layers * (H * (qw + 2 * kvw) + qw * H + 3 * H * I) + 2.0 * V * H
-    # causal attention within the window: query i sees min(i+1, W) keys; QK^T and PV, 2 flops per multiply-add
-    seen = sum(min(i + 1, window) if window else i + 1 for i in range(T))
-    attn_flops = 2.0 * 2.0 * seen * qw * layers
-    pre_flops = linear_flops + attn_flops
-    pre_tflops = pre_flops / (pre_ms / 1e3) / 1e12
-    value = args.batch / (ms_step / 1e3)
-    tag = "of measured" if pk["source"] == "measured" else "of fallback"
-    line = {
-        "metric": "decode tok/s @ batch 8 (Mistral-7B shape, 8192 context); prefill tok/s @ 2048; % of roofline",
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {
-            "model": "Mistral-7B-v0.1 shape, random weights", "global_batch": args.batch, "seq_len": args.context,
-            "parallelism": "single GPU", "layers": layers, "layers_of_shape": layers_full, "hidden_size": H,
-            "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
-            "intermediate_size": I, "vocab_size": V, "sliding_window": window, "page_size": page,
-            "kv_dtype": "bf16", "l2": "inputs larger than L2 (every step reads all weights)",
-            "cache_state": "pages laid out by the cache manager for 8191-token requests; K/V values random",
-        },
-        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
-                "d2h_bytes_per_step": int(d2h)},
-        "gpu_launches": int(round(launches * args.steps)),
-        "prefill": {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
-                    "frac": round(pre_tflops / pk["bf16_tflops"], 4), "tflops": round(pre_tflops, 1),
-                    "peak_tflops": pk["bf16_tflops"], "peak": tag},
-        "roofline": {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved_gbs / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes),
-                     "peak_source": tag},
-        "points": points,
-        "clocks": clock_summary,
-    }
+        # ---- the Mistral-Nemo-12B mixed workload through the scheduler -----------------------------------
+        if args.only in ("all", "mixed"):
+            nemo = shape_of("nemo12b")
+            ncfg = MistralConfig.from_dict(nemo.config if args.layers is None else
+                                           {**nemo.config, "num_hidden_layers": args.layers})
+            n_req, lo, hi, chunk, new = 32, 128, 4096, 512, 256
+            ubatch = 2 * chunk + n_req                        # two portions beside every decoded token
+            demand = n_req * ((lo + hi) // 2 + new)           # about what the requests come to hold together
+            engine = Engine.from_config(ncfg, seed=0, options=EngineOptions(
+                dtype="bfloat16", page_size=PAGE, cache_tokens=int(0.75 * demand) // PAGE * PAGE, max_requests=n_req,
+                max_step_tokens=ubatch, max_seq_len=hi + new + PAGE))
+            workloads.mixed_requests(engine, n_requests=4, prompt_range=(lo, 600), chunk=chunk, ubatch=ubatch,
+                                     decode_tokens=8, temperature=0.7, seed=99)        # warm-up
+            mixed = workloads.mixed_requests(engine, n_requests=n_req, prompt_range=(lo, hi), chunk=chunk,
+                                             ubatch=ubatch, decode_tokens=new, temperature=0.7, seed=7)
+            mixed.update(model=nemo.name, layers=ncfg.num_hidden_layers, layers_of_shape=nemo.config["num_hidden_layers"],
+                         chunk=chunk, ubatch=ubatch, temperature=0.7, pool_tokens=engine.options.cache_tokens)
+            workloads.randomise_cache(engine)
+            mixed["one_step"] = workloads.step_host_device(engine, decoding=24, context=2048, portion=chunk, gen=gen)
+            line["mixed"] = mixed
+            drop(engine)
+            del engine
+
+        # ---- the Mistral-Small-24B shape ------------------------------------------------------------------
+        if args.only in ("all", "shapes"):
+            big = shape_of("small24b")
+            blayers = args.layers or big.config["num_hidden_layers"]
+            bcfg, engine = build(big, blayers, 64, big.context, 2048, args.steps + args.warmup)
+            rec = {"model": big.name, "layers": blayers, "layers_of_shape": big.config["num_hidden_layers"],
+                   "context": big.context, "peak": tag}
+            for b in (1, 8, 64):
+                d = decode_point(engine, bcfg, b, big.context, max(8, args.steps // 2), 3)
+                rec[f"decode_b{b}"] = {"value": round(d["tok_s"], 1), "ms": round(d["ms"], 3),
+                                       "gbs": round(d["gbs"], 1), "frac": round(d["frac"], 4)}
+                line.setdefault("points", {})[f"small24b_decode_b{b}"] = round(d["tok_s"], 1)
+            pre = prefill_point(engine, bcfg, blayers, 2048)
+            rec["prefill_2048"] = {"value": round(pre["tok_s"], 1), "ms": round(pre["ms"], 3),
+                                   "tflops": round(pre["tflops"], 1), "frac": round(pre["frac"], 4)}
+            ms = workloads.time_to_first(engine, 2048, 512, gen)
+            rec["prefill_2048"]["ttft_ms_chunk512"] = round(ms, 3)
+            line.setdefault("points", {})["small24b_prefill_2048"] = round(pre["tok_s"], 1)
+            line["shapes"] = {"small24b": rec}
+            drop(engine)
+            del engine
+    clock_summary = clocks.summary()
+    line["clocks"] = clock_summary
     print(json.dumps(line))
     return 0
 

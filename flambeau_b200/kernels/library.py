@@ -103,9 +103,15 @@ def library_path() -> str:
 
 LAUNCHES = [0]          # launcher calls that reached the device queue (each is at least one kernel launch)
 
+# A section timer (measure.timers.SectionTimer) sets this to be told of every launcher call, after the call has
+# queued its kernels: on_launch(what, note), `note` being what the wrapper knows of the call's shape.
+ON_LAUNCH = [None]
 
-def check(code: int, what: str) -> None:
+
+def check(code: int, what: str, note=None) -> None:
     LAUNCHES[0] += 1
     if code != 0:
         msg = lib().fb_last_error().decode(errors="replace")
         raise KernelError(f"{what}: {msg or 'error code %d' % code}")
+    if ON_LAUNCH[0] is not None:
+        ON_LAUNCH[0](what, note)

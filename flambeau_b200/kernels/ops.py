@@ -168,7 +168,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
         raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
     check(lib().fb_gemm_simt(a.data_ptr(), dtype_code(a), _rows(a), w.data_ptr(), dtype_code(w), _rows(w),
-                             out.data_ptr(), dtype_code(out), _rows(out), M, N, K, _stream()), "gemm_simt")
+                             out.data_ptr(), dtype_code(out), _rows(out), M, N, K, _stream()), "gemm_simt", (M, N, K))
 
 
 def paged_attention_simt(q, out, k_pool, v_pool, block_table, positions, row_seq, nh: int, nkv: int, hd: int,
@@ -270,7 +270,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.T
     check(lib().fb_gemm_tc(a.data_ptr(), _rows(a), w.data_ptr(), _rows(w), out.data_ptr(), dtype_code(out),
                            _rows(out), slab_stride, max_slabs, ctypes.byref(_SPLITS_USED), M, N, K,
                            partials.data_ptr(), partials.numel(), counters.data_ptr(), counters.numel(),
-                           int(splits), status.data_ptr(), _stream()), "gemm_tc")
+                           int(splits), status.data_ptr(), _stream()), "gemm_tc", (M, N, K))
     return _SPLITS_USED.value if slabs is not None else 1
 
 
@@ -287,7 +287,7 @@ def gemm_tc_gated(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: t
     check(lib().fb_gemm_tc_gated(a.data_ptr(), _rows(a), w.data_ptr(), _rows(w), out.data_ptr(), dtype_code(out),
                                  _rows(out), M, N, K, activation_code(activation), partials.data_ptr(),
                                  partials.numel(), counters.data_ptr(), counters.numel(), status.data_ptr(),
-                                 _stream()), "gemm_tc_gated")
+                                 _stream()), "gemm_tc_gated", (M, N, K))
 
 
 def linear_slabs(a: torch.Tensor, w: torch.Tensor, slabs: torch.Tensor, ctx) -> int:

@@ -26,7 +26,9 @@ class Scene:
         total_pages = sum(-(-(a + b) // page_size) for a, b in seqs) + extra_pages
         ids = list(range(total_pages))
         rnd.shuffle(ids)
-        max_pages = max(-(-(a + b) // page_size) for a, b in seqs) + 2
+        def first_page(cached):                     # the first page the cache manager still holds
+            return (max(0, cached - window + 1) // page_size) if (window and compact) else 0
+        max_pages = max(-(-(a + b) // page_size) - first_page(a) for a, b in seqs) + 2
         self.k_pool = torch.full((total_pages, nkv, page_size, hd), float("nan"))   # unwritten slots are poison
         self.v_pool = torch.full((total_pages, nkv, page_size, hd), float("nan"))
         self.table = torch.full((len(seqs), max_pages), -1, dtype=torch.int32)

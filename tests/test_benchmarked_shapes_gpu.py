@@ -5,9 +5,10 @@
     and decoded tokens cross the window's edge and the leading pages are given back.  Width, inner size and
     vocabulary are cut down (they are covered at full size by test_large_shape_gpu.py), which keeps the float64
     oracle to a few seconds.
-  * The 7B shape itself at depth: the first 8 of its 32 layers at full sizes, a 64-token prompt whole, in
-    portions, and with its last tokens one by one, in 32-bit and in bfloat16; the error that bfloat16 reaches at
-    that depth is printed.
+  * The 7B shape itself at depth: 8 of its 32 layers at full sizes, a 64-token prompt whole, in portions, and
+    with its last tokens one by one.  In 32-bit the bound is the 1e-4 of every other test; in bfloat16 it is the
+    tiny models' 2e-2 scaled by the square root of the depth (tiny.tol_at_depth says why), and the error that is
+    reached is printed.
   * Head sizes that are even but no multiple of 8, which take the kernels' scalar forms.
   * Peak device memory while a model is loaded.
 """
@@ -34,7 +35,7 @@ SEVEN_B_LAYERS_OF_SHAPE = 32
 @pytest.fixture(scope="module")
 def windowed(tmp_path_factory):
     folder = tiny.make_folder(tmp_path_factory.mktemp("window4096"), WINDOW_GEOMETRY, seed=11, dtype="bfloat16",
-                              sharp=0.03)
+                              sharp=0.02)
     pcfg, W = pm.read_model_folder(folder)
     toks = tiny.random_requests(WINDOW_GEOMETRY, [4208], seed=6)["r0"]
     # rows that are checked: around the first portion's end, around the window's edge (queries 4095..4097 are the
@@ -50,7 +51,7 @@ def test_prompt_in_portions_of_512_across_the_real_window(windowed, dtype, tmp_p
     from flambeau_b200.engine.trace import replay
     toks, rows = windowed["tokens"], windowed["rows"]
     # pool: the window, a portion, and the pages a portion's first and last tokens share with their neighbours
-    engine = Engine.from_folder(windowed["folder"], EngineOptions(dtype=dtype, cache_tokens=4096 + 512 + 64,
+    engine = Engine.from_folder(windowed["folder"], EngineOptions(dtype=dtype, cache_tokens=4096 + 512 + 128,
                                                                   max_requests=1, max_step_tokens=512,
                                                                   max_seq_len=8192))
     assert engine.cache.table_pages < 8192 // 16, "a table row holds live pages only"
@@ -93,6 +94,8 @@ def test_the_7b_shape_at_depth(seven_b, dtype, tmp_path):
     reqs = seven_b["requests"]
     engine = Engine.from_folder(seven_b["folder"], EngineOptions(dtype=dtype, cache_tokens=128, max_requests=1,
                                                                  max_step_tokens=64, max_seq_len=128))
+    layers = SEVEN_B["num_hidden_layers"]
+    tol = tiny.tol_at_depth(dtype, layers)       # float32: 1e-4 at any depth; bfloat16: 2e-2 * sqrt(layers / 3)
     worst = 0.0
     for name, sched in (("whole", tiny.schedule_whole(reqs)), ("portions", tiny.schedule_portions(reqs)),
                         ("tail", tiny.schedule_tail(reqs, 32))):
@@ -100,10 +103,9 @@ def test_the_7b_shape_at_depth(seven_b, dtype, tmp_path):
         replay(engine, sched.lines(), out)
         engine.runtime.check_status(name)
         got = tiny.read_rows(out, sched, SEVEN_B["vocab_size"])
-        worst = max(worst, tiny.compare_rows(got, seven_b["want"], tiny.TOL[dtype],
-                                             f"7B shape, {SEVEN_B['num_hidden_layers']} of "
-                                             f"{SEVEN_B_LAYERS_OF_SHAPE} layers, {dtype}, {name}"))
-    print(f"[depth] 7B shape at {SEVEN_B['num_hidden_layers']} layers, {dtype}: worst error {worst:.3e}")
+        worst = max(worst, tiny.compare_rows(got, seven_b["want"], tol,
+                                             f"7B shape, {layers} of {SEVEN_B_LAYERS_OF_SHAPE} layers, {dtype}, {name}"))
+    print(f"[depth] 7B shape at {layers} layers, {dtype}: worst error {worst:.3e} (bound {tol:.2e})")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

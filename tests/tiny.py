@@ -26,6 +26,16 @@ CONFIGS = {"A": CONFIG_A, "B": CONFIG_B}
 TOL = {"float32": 1e-4, "bfloat16": 2e-2}
 
 
+def tol_at_depth(dtype: str, layers: int) -> float:
+    """The bound for a model of `layers` layers.  float32: the same 1e-4 at any depth.  bfloat16: the bound above
+    is set for the tiny models (two and three layers); every layer rounds its normalised input, its queries, keys,
+    values, attention output and feed-forward activation to 8 bits of mantissa, independent roundings whose effect
+    on the logits adds in quadrature, so the bound grows with the square root of the depth beyond three layers."""
+    if dtype == "float32":
+        return TOL["float32"]
+    return TOL["bfloat16"] * max(1.0, layers / 3.0) ** 0.5
+
+
 def make_folder(folder, cfg: dict, seed: int, dtype: str, sharp: float | None = 0.2) -> Path:
     """A model folder with seeded random weights.  `sharp` redraws the query and key projections with that
     standard deviation, so that attention scores spread over several units and a wrong, missing or extra key
