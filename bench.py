@@ -100,6 +100,10 @@ def main(argv=None) -> int:
     if args.warmup < 3:
         args.warmup = 3
 
+    import os
+    if os.environ.get("FLAMBEAU_BENCH_STACKS"):          # where the host is after that many seconds (diagnosis)
+        import faulthandler
+        faulthandler.dump_traceback_later(float(os.environ["FLAMBEAU_BENCH_STACKS"]), repeat=False, file=sys.stderr)
     import torch
     from flambeau_b200.config.mistral import MistralConfig
     from flambeau_b200.engine.batch import Entry
@@ -111,6 +115,10 @@ def main(argv=None) -> int:
     pk = peaks()
     tag = "of measured" if pk["source"] == "measured" else "of fallback"
     gen = torch.Generator().manual_seed(1)
+    started = time.time()
+
+    def say(msg: str) -> None:                           # progress on stderr; stdout carries the JSON line alone
+        print(f"[bench {time.time() - started:6.1f} s] {msg}", file=sys.stderr, flush=True)
 
     def build(shape, layers, max_batch, context, prefill_tokens, steps):
         cfg = MistralConfig.from_dict({**shape.config, "num_hidden_layers": layers})
@@ -124,8 +132,7 @@ def main(argv=None) -> int:
         workloads.randomise_cache(engine)
         return cfg, engine
 
-    def drop(engine):
-        del engine
+    def free_device_memory():
         gc.collect()
         torch.cuda.empty_cache()
 
@@ -155,14 +162,18 @@ def main(argv=None) -> int:
         # ---- the headline shape -------------------------------------------------------------------
         if args.only in ("all", "headline"):
             max_batch = args.batch if args.skip_points else max(args.batch, 64)
+            say(f"building {head.name}, {layers} layers")
             cfg, engine = build(head, layers, max_batch, context, args.prefill_tokens, args.steps + args.warmup)
+            say(f"decode at batch {args.batch}")
             d = decode_point(engine, cfg, args.batch, context, args.steps, args.warmup)
+            say(f"{d['ms']:.3f} ms a step; the same through the scheduler loop")
             e2e_value, h2d, d2h = workloads.decode_e2e(engine, args.batch, context, args.steps, args.warmup, gen)
             points = {}
             if not args.skip_points:
                 for b in (1, 64):
                     points[f"decode_b{b}"] = round(decode_point(engine, cfg, b, context, max(8, args.steps // 2), 3)["tok_s"], 1)
             T = args.prefill_tokens
+            say(f"prefill of {T} tokens")
             pre = prefill_point(engine, cfg, layers, T)
             prefill = {"value": round(pre["tok_s"], 1), "tokens": T, "ms": round(pre["ms"], 3),
                        "frac": round(pre["frac"], 4), "tflops": round(pre["tflops"], 1),
@@ -172,10 +183,12 @@ def main(argv=None) -> int:
                 prefill["step_512_ms"] = round(pre512["ms"], 3)
                 prefill["step_512_tok_s"] = round(pre512["tok_s"], 1)
                 for chunk in (512, T):
+                    say(f"time to first token, portions of {chunk}")
                     ms = workloads.time_to_first(engine, T, chunk, gen)
                     prefill[f"ttft_ms_chunk{chunk}"] = round(ms, 3)
                     prefill[f"ttft_tok_s_chunk{chunk}"] = round(T / (ms / 1e3), 1)
             # ---- outside the timed regions: correctness of the benchmarked geometry, per-kernel times ----
+            say("attention check and kernel sections")
             check = workloads.attention_check(engine, args.batch, context, gen)
             kernels = {}
             if args.only == "all":
@@ -213,8 +226,8 @@ def main(argv=None) -> int:
                              "frac": round(d["frac"], 4), "bytes_per_step": int(d["bytes"]), "peak_source": tag},
                 "points": points, "check": check, "kernels": kernels,
             }
-            drop(engine)
-            del engine
+            engine = None
+            free_device_memory()
 
         # ---- the Mistral-Nemo-12B mixed workload through the scheduler -----------------------------------
         if args.only in ("all", "mixed"):
@@ -224,29 +237,35 @@ def main(argv=None) -> int:
             n_req, lo, hi, chunk, new = 32, 128, 4096, 512, 256
             ubatch = 2 * chunk + n_req                        # two portions beside every decoded token
             demand = n_req * ((lo + hi) // 2 + new)           # about what the requests come to hold together
+            say(f"building {nemo.name}, {ncfg.num_hidden_layers} layers")
             engine = Engine.from_config(ncfg, seed=0, options=EngineOptions(
                 dtype="bfloat16", page_size=PAGE, cache_tokens=int(0.75 * demand) // PAGE * PAGE, max_requests=n_req,
                 max_step_tokens=ubatch, max_seq_len=hi + new + PAGE))
+            say("mixed workload: warm-up")
             workloads.mixed_requests(engine, n_requests=4, prompt_range=(lo, 600), chunk=chunk, ubatch=ubatch,
                                      decode_tokens=8, temperature=0.7, seed=99)        # warm-up
+            say(f"mixed workload: {n_req} requests")
             mixed = workloads.mixed_requests(engine, n_requests=n_req, prompt_range=(lo, hi), chunk=chunk,
                                              ubatch=ubatch, decode_tokens=new, temperature=0.7, seed=7)
             mixed.update(model=nemo.name, layers=ncfg.num_hidden_layers, layers_of_shape=nemo.config["num_hidden_layers"],
                          chunk=chunk, ubatch=ubatch, temperature=0.7, pool_tokens=engine.options.cache_tokens)
+            say(f"{mixed['wall_s']} s; one mixed step, host against device")
             workloads.randomise_cache(engine)
             mixed["one_step"] = workloads.step_host_device(engine, decoding=24, context=2048, portion=chunk, gen=gen)
             line["mixed"] = mixed
-            drop(engine)
-            del engine
+            engine = None
+            free_device_memory()
 
         # ---- the Mistral-Small-24B shape ------------------------------------------------------------------
         if args.only in ("all", "shapes"):
             big = shape_of("small24b")
             blayers = args.layers or big.config["num_hidden_layers"]
+            say(f"building {big.name}, {blayers} layers")
             bcfg, engine = build(big, blayers, 64, big.context, 2048, args.steps + args.warmup)
             rec = {"model": big.name, "layers": blayers, "layers_of_shape": big.config["num_hidden_layers"],
                    "context": big.context, "peak": tag}
             for b in (1, 8, 64):
+                say(f"decode at batch {b}")
                 d = decode_point(engine, bcfg, b, big.context, max(8, args.steps // 2), 3)
                 rec[f"decode_b{b}"] = {"value": round(d["tok_s"], 1), "ms": round(d["ms"], 3),
                                        "gbs": round(d["gbs"], 1), "frac": round(d["frac"], 4)}
@@ -258,8 +277,9 @@ def main(argv=None) -> int:
             rec["prefill_2048"]["ttft_ms_chunk512"] = round(ms, 3)
             line.setdefault("points", {})["small24b_prefill_2048"] = round(pre["tok_s"], 1)
             line["shapes"] = {"small24b": rec}
-            drop(engine)
-            del engine
+            engine = None
+            free_device_memory()
+    say("done")
     clock_summary = clocks.summary()
     line["clocks"] = clock_summary
     print(json.dumps(line))

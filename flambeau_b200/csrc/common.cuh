@@ -68,6 +68,7 @@ __device__ __forceinline__ float fb_gate_times(int act, float g, float u) {
 // fb_pdl_wait() returns once all earlier kernels of the stream have completed and their writes are visible, so
 // the order of results is that of ordinary stream launches; only launch latency and prologues overlap.
 extern int g_fb_pdl;        // 1: launch with the programmatic-serialization attribute; 0: plain launches
+extern long g_fb_pdl_max_smem;   // kernels that ask for more dynamic shared memory than this are launched plainly
 
 __device__ __forceinline__ void fb_pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -83,7 +84,7 @@ inline void fb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
-    if (g_fb_pdl) {
+    if (g_fb_pdl && (long)smem <= g_fb_pdl_max_smem) {
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;

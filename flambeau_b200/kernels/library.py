@@ -21,6 +21,7 @@ _SIGNATURES = {
     "fb_last_error": (c_char_p, []),
     "fb_abi_version": (I, []),
     "fb_set_pdl": (None, [I]),
+    "fb_set_pdl_max_smem": (None, [L]),
     "fb_set_attention_tc": (None, [I]),
     "fb_set_gemm_pair": (None, [I]),
     # elementwise.cu
@@ -93,6 +94,8 @@ def lib():
         declare(handle, _SIGNATURES)
         if os.environ.get("FLAMBEAU_PDL", "1") == "0":
             handle.fb_set_pdl(0)                # plain stream-ordered launches (for debugging and A/B timing)
+        if os.environ.get("FLAMBEAU_PDL_MAX_SMEM"):
+            handle.fb_set_pdl_max_smem(int(os.environ["FLAMBEAU_PDL_MAX_SMEM"]))
         _LIB = handle
     return _LIB
 

@@ -16,9 +16,10 @@ leaves it (pages taken and, under a window, given back) but filled with random n
 of a prefill ("seated" requests)."""
 from __future__ import annotations
 
-import math
+import os
 import random
 import statistics
+import sys
 import time
 
 import torch
@@ -239,11 +240,17 @@ def mixed_requests(engine, *, n_requests: int, prompt_range: tuple, chunk: int, 
     reqs = [sched.add(i, p, SamplingParams(temperature=temperature, seed=seed + i, max_tokens=decode_tokens,
                                            ignore_eos=True)) for i, p in enumerate(prompts)]
     first, last, step_rows = {}, {}, []
+    trace = os.environ.get("FLAMBEAU_BENCH_TRACE")          # one line per step on stderr
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     while not sched.idle:
         out = sched.step()
         now = time.perf_counter() - t0
+        if trace:
+            b = engine.last_batch
+            print(f"[mixed {now:8.3f} s] step {sched.steps}: {b.n_tokens} rows of {b.n_seqs} sequences, "
+                  f"{len(out)} tokens out, {len(sched.running)} running, {len(sched.waiting)} waiting",
+                  file=sys.stderr, flush=True)
         for r, _tok in out:
             first.setdefault(r.request_id, now)
             last[r.request_id] = now
