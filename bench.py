@@ -199,8 +199,10 @@ def main(argv=None) -> int:
                     cfg, sections, args.batch, [context] * args.batch, layers, pk)
                 engine.cache.release_all()
                 toks = torch.randint(0, cfg.vocab_size, (T,), generator=gen).tolist()
-                sections = workloads.kernel_sections(engine, [Entry("prompt", toks, [T - 1])], cfg, end=["prompt"])
-                kernels[f"prefill_{T}"] = workloads.roofline_of_sections(cfg, sections, T, [T], layers, pk)
+                for rows in (T, 512):
+                    sections = workloads.kernel_sections(engine, [Entry("prompt", toks[:rows], [rows - 1])], cfg,
+                                                         end=["prompt"])
+                    kernels[f"prefill_{rows}"] = workloads.roofline_of_sections(cfg, sections, rows, [rows], layers, pk)
             window = cfg.sliding_window or 0
             line = {
                 "metric": f"decode tok/s @ batch {args.batch} ({head.name}, {context} context); "

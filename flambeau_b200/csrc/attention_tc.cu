@@ -418,7 +418,7 @@ int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream)
     }
     const int TQ = RT * BM / (a.nh / a.nkv);
     const dim3 grid(((max_q_len + TQ - 1) / TQ) * a.nkv * n_seqs);
-    fb_launch((kern), grid, tc_threads(RT), (size_t)SM::BYTES, stream, a);
+    fb_launch_class(FB_LAUNCH_ATTENTION_TC, (kern), grid, tc_threads(RT), (size_t)SM::BYTES, stream, a);
     return fb_check_launch("attention_tc");
 }
 

@@ -68,7 +68,9 @@ __device__ __forceinline__ float fb_gate_times(int act, float g, float u) {
 // fb_pdl_wait() returns once all earlier kernels of the stream have completed and their writes are visible, so
 // the order of results is that of ordinary stream launches; only launch latency and prologues overlap.
 extern int g_fb_pdl;        // 1: launch with the programmatic-serialization attribute; 0: plain launches
-extern long g_fb_pdl_max_smem;   // kernels that ask for more dynamic shared memory than this are launched plainly
+// Kernel classes that are launched plainly even while programmatic dependent launch is on (a bit set of FbLaunchClass).
+enum FbLaunchClass : int { FB_LAUNCH_OTHER = 0, FB_LAUNCH_GEMM_PAIR = 1, FB_LAUNCH_ATTENTION_TC = 2, FB_LAUNCH_GEMM_WIDE = 4 };
+extern int g_fb_plain_classes;
 
 __device__ __forceinline__ void fb_pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -76,21 +78,26 @@ __device__ __forceinline__ void fb_pdl_launch_dependents() {
 __device__ __forceinline__ void fb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 template <typename... KArgs, typename... Args>
-inline void fb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                      Args... args) {
+inline void fb_launch_class(int launch_class, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                            cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
-    if (g_fb_pdl && (long)smem <= g_fb_pdl_max_smem) {
+    if (g_fb_pdl && !(launch_class & g_fb_plain_classes)) {
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);     // an error shows in fb_check_launch()
+}
+template <typename... KArgs, typename... Args>
+inline void fb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                      Args... args) {
+    fb_launch_class(FB_LAUNCH_OTHER, kernel, grid, block, smem, stream, args...);
 }
 
 // ---- a running start for the product that follows ---------------------------

@@ -8,20 +8,20 @@
 static thread_local char g_last_error[1024] = "";
 
 int g_fb_pdl = 1;
-// Kernels that fill a multiprocessor by themselves (the two-SM product, the tcgen05 attention and the 256-token
-// tile of the one-SM product: about 193 KB of shared memory and all of tensor memory) are launched plainly.  With
-// hundreds of launches queued ahead of the device (a deep model's step of several hundred rows), programmatic
-// launches of these kernels stopped the device: no kernel of the queue made progress any more, although no wait
-// of any kernel here depends on a later one; launched plainly they run.  They run for tens of microseconds and
-// more, so the overlap of their prologue with the tail of the kernel before them is what they give up.
-long g_fb_pdl_max_smem = 128 * 1024;
+// The two-SM product (a cluster kernel) is launched plainly, and with it the 256-token tile of the one-SM product,
+// its stand-in.  With hundreds of launches queued ahead of the device (a deep model's step of several hundred rows
+// whose products do not fill every SM pair), programmatic launches of the cluster kernel stopped the device: no
+// kernel of the queue made progress any more, although no wait in any kernel here depends on a later kernel;
+// with that one kernel launched plainly the same queue runs.  The tcgen05 attention kernel and everything else
+// keep their programmatic launches.  The products concerned run for tens of microseconds and more; what they give
+// up is the overlap of their prologue with the tail of the kernel before them.
+int g_fb_plain_classes = FB_LAUNCH_GEMM_PAIR | FB_LAUNCH_GEMM_WIDE;
 
 // Switches programmatic dependent launch on (1, the default) or off (0) for all later launches.
 FB_API void fb_set_pdl(int on) { g_fb_pdl = on ? 1 : 0; }
 
-// Kernels that ask for more than `bytes` of dynamic shared memory are launched plainly (they wait for all earlier
-// work and are not overlapped with the kernel before them) even while programmatic dependent launch is on.
-FB_API void fb_set_pdl_max_smem(long long bytes) { g_fb_pdl_max_smem = (long)bytes; }
+// Which kernel classes (a bit set of FbLaunchClass) are launched plainly while programmatic dependent launch is on.
+FB_API void fb_set_plain_launch_classes(int classes) { g_fb_plain_classes = classes; }
 
 FbPrefetch fb_make_prefetch(const void* base, long long rows, long long row_stride_bytes, int bytes_per_row) {
     FbPrefetch pf = {nullptr, 0, 0, 0};

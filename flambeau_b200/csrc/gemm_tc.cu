@@ -370,7 +370,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
         fb_setup_done(configured);
     }
     const int grid = (int)(n_units < slots ? n_units : slots);
-    fb_launch((kern), grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, partials,
+    fb_launch_class(BN >= 256 ? FB_LAUNCH_GEMM_WIDE : FB_LAUNCH_OTHER, (kern), grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, partials,
               counters, M, N, K, splits, tiles_m, tiles_n, (int)n_units, gated, status);
     return fb_check_launch("gemm_tc");
 }

@@ -290,7 +290,7 @@ int launch_pair(const void* X, long lda, const void* W, long ldw, void* out, lon
     const long n_units = tiles * splits;
     if (n_units > 2000000000L) return fb_fail(-1, "gemm_tc_pair: too many tiles (M=%d N=%d)", M, N);
     const int pairs = (int)(n_units < pair_slots() ? n_units : pair_slots());
-    fb_launch((kern), 2 * pairs, P_THREADS, P_SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, M, N, K,
+    fb_launch_class(FB_LAUNCH_GEMM_PAIR, (kern), 2 * pairs, P_THREADS, P_SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, M, N, K,
               tiles_m, (int)tiles, splits, (int)n_units, gated, status);
     return fb_check_launch("gemm_tc_pair");
 }

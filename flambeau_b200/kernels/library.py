@@ -21,7 +21,7 @@ _SIGNATURES = {
     "fb_last_error": (c_char_p, []),
     "fb_abi_version": (I, []),
     "fb_set_pdl": (None, [I]),
-    "fb_set_pdl_max_smem": (None, [L]),
+    "fb_set_plain_launch_classes": (None, [I]),
     "fb_set_attention_tc": (None, [I]),
     "fb_set_gemm_pair": (None, [I]),
     # elementwise.cu
@@ -94,8 +94,9 @@ def lib():
         declare(handle, _SIGNATURES)
         if os.environ.get("FLAMBEAU_PDL", "1") == "0":
             handle.fb_set_pdl(0)                # plain stream-ordered launches (for debugging and A/B timing)
-        if os.environ.get("FLAMBEAU_PDL_MAX_SMEM"):
-            handle.fb_set_pdl_max_smem(int(os.environ["FLAMBEAU_PDL_MAX_SMEM"]))
+        if os.environ.get("FLAMBEAU_PDL_PLAIN"):
+            # bit set of kernel classes launched plainly: 1 two-SM product, 2 tcgen05 attention, 4 256-token one-SM product
+            handle.fb_set_plain_launch_classes(int(os.environ["FLAMBEAU_PDL_PLAIN"]))
         _LIB = handle
     return _LIB
 

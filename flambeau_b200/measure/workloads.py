@@ -162,7 +162,7 @@ def classify(cfg, what: str, note) -> str:
             "paged_attention_simt": "attention"}.get(what, what)
 
 
-def kernel_sections(engine, entries, cfg, reps: int = 3, end=()) -> dict:
+def kernel_sections(engine, entries, cfg, reps: int = 3, end=(), ahead_ms: float = 40.0) -> dict:
     """class -> (launches per step, milliseconds per step) of one eager step of `entries`.  The step is run
     `reps + 1` times in a row, so the entries must stay valid: decoded tokens are; a whole prompt is when `end`
     names its request, which then gives back what it holds after every run."""
@@ -172,6 +172,9 @@ def kernel_sections(engine, entries, cfg, reps: int = 3, end=()) -> dict:
         engine.step(entries, end=end)                          # warm
         totals: dict = {}
         for _ in range(reps):
+            # a long kernel ahead of the step lets the host queue every launch before the device starts on the
+            # first: the sections then hold the kernels' own times, not the host's time between two launches
+            torch.cuda._sleep(int(ahead_ms * 2.0e6))
             with SectionTimer() as t:
                 logits = engine.step(entries, end=end)
                 if logits is not None:

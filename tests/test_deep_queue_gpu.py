@@ -23,11 +23,16 @@ def test_a_mixed_step_of_a_deep_model_queued_ahead_of_the_device():
     engine = Engine.from_config(cfg, seed=1, options=EngineOptions(
         dtype="bfloat16", cache_tokens=24 * 320 + 2048, max_requests=25, max_step_tokens=600, max_seq_len=2048,
         cuda_graphs=False))
-    workloads.randomise_cache(engine)
     gen = torch.Generator().manual_seed(3)
     tokens = torch.randint(0, cfg.vocab_size, (24 + 512,), generator=gen).tolist()
+    # every page of a pool holds the same random keys and values, put back before each run: what a request sees of
+    # its "earlier tokens" then does not depend on which pages the pool hands out, nor on what a run before wrote
+    pools = [t for g in engine.cache.groups for c in g.owners for t in (g.k[c], g.v[c])]
+    protos = [torch.randn_like(t[:1]) for t in pools]
 
     def entries():
+        for t, proto in zip(pools, protos):
+            t.copy_(proto.expand_as(t))
         ids = workloads.seat(engine, [300] * 24 + [513], prefix="q")
         e = [Entry(r, [tokens[i]], [0]) for i, r in enumerate(ids[:-1])]
         e.append(Entry(ids[-1], tokens[24:], [0, 511]))
