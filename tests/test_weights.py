@@ -112,3 +112,38 @@ def test_one_error_lists_missing_unexpected_and_misshapen(tmp_path):
     msg = str(err)
     for needle in ("missing (2)", "unexpected (1)", "wrong shape or type (2)", "[16, 64]", "[32, 64]"):
         assert needle in msg
+
+
+def test_linear_weights_stored_in_32_bit_are_kept_and_warned_about(tmp_path):
+    """A tensor stored in 32-bit stays so in bfloat16 mode.  For norm weights that is wanted; a linear map kept in
+    float32 runs on the FMA kernel, so the loader says so once."""
+    import warnings
+    cfg = MistralConfig.from_dict(tiny.CONFIGS["A"])
+    write_random_model(tmp_path / "f32", cfg, seed=1, dtype="float32")
+    write_random_model(tmp_path / "mixed", cfg, seed=1, dtype="bfloat16", float32_names=("layernorm", "model.norm"))
+    specs = model_tensor_specs(cfg)
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        got = load_tensors(tmp_path / "f32", specs, FakeRuntime())
+    assert all(t.dtype == torch.float32 for t in got.values())
+    assert sum("32-bit" in str(w.message) for w in seen) == 1, "one warning, not one per tensor"
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        got = load_tensors(tmp_path / "mixed", specs, FakeRuntime())
+    assert not seen, "norm weights in 32-bit are the usual case and need no warning"
+    assert got["model.norm.weight"].dtype == torch.float32
+    assert got["model.layers.0.self_attn.q_proj.weight"].dtype == torch.bfloat16
+
+
+def test_model_is_bound_part_by_part_and_a_tied_head_is_one_tensor(tmp_path):
+    from flambeau_b200.weights.loader import FolderTensors
+    cfg = MistralConfig.from_dict(tiny.CONFIGS["B"])                    # tied
+    write_random_model(tmp_path / "m", cfg, seed=2, dtype="bfloat16")
+    specs = model_tensor_specs(cfg)
+    ft = FolderTensors(tmp_path / "m", specs, FakeRuntime())
+    emb = ft.fetch(["model.embed_tokens.weight"])["model.embed_tokens.weight"]
+    layer = ft.fetch([n for n in specs if n.startswith("model.layers.1.")])
+    head = ft.fetch(["lm_head.weight"])["lm_head.weight"]
+    ft.close()
+    assert head.data_ptr() == emb.data_ptr(), "a tied head is the embedding tensor under a second name"
+    assert len(layer) == 9
