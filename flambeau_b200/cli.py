@@ -93,8 +93,8 @@ def main(argv=None) -> int:
     p.add_argument("--stop-token-id", type=int, action="append")
     p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     p.add_argument("--inflight-slots", type=int, default=4)
-    p.add_argument("--prefill-ubatch", type=int, default=512)
-    p.add_argument("--prefill-chunk-tokens", type=int, default=512)
+    p.add_argument("--prefill-ubatch", type=int, default=2048, help="most rows of one step")
+    p.add_argument("--prefill-chunk-tokens", type=int, default=2048, help="longest portion of a prompt in one step")
     p.add_argument("--paged-kv", type=int, help="number of cache pages (16 tokens each)")
     p.add_argument("--ctx-cap", type=int)
     p.set_defaults(fn=cmd_infer)

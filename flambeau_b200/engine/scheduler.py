@@ -88,7 +88,7 @@ class PlannedStep:
 
 
 class Scheduler:
-    def __init__(self, executor, *, token_budget: int = 512, prefill_chunk: int = 512, max_running: int = 4,
+    def __init__(self, executor, *, token_budget: int = 2048, prefill_chunk: int = 2048, max_running: int = 4,
                  run_ahead: bool = True):
         """`executor` has .cache (a CacheManager), .run(entries, sampled_requests) -> list of token ids, and
         .finish(request_id); for running ahead also .launch(entries, sampled, feed, pending) -> handle,
