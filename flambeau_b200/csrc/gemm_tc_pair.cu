@@ -72,9 +72,11 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
 }
 
 // One unit of work: output tile (nt, mt) and share `split` of its K range.  Token tiles vary fastest, so pairs
-// that run together share weight tiles through L2; shares of K vary slowest.
-struct PairUnit { int mt, nt, split, kb_begin, n_kb; };
-__device__ __forceinline__ PairUnit pair_unit(int u, int tiles_m, int tiles, int splits, int kb_total) {
+// that run together share weight tiles through L2; shares of K vary slowest.  The last token tile of a product
+// whose rows do not fill it is multiplied at its own width: n_tok = the tile's rows rounded up to 32 (the N of
+// the MMA; each CTA supplies n_tok / 2 tokens), so a step of 2,048 + 32 rows pays for 32 rows more, not for 256.
+struct PairUnit { int mt, nt, split, kb_begin, n_kb, n_tok; };
+__device__ __forceinline__ PairUnit pair_unit(int u, int tiles_m, int tiles, int splits, int kb_total, int M) {
     PairUnit w;
     const int t = u % tiles;
     w.split = u / tiles;
@@ -82,6 +84,8 @@ __device__ __forceinline__ PairUnit pair_unit(int u, int tiles_m, int tiles, int
     w.nt = t / tiles_m;
     w.kb_begin = (int)((long)w.split * kb_total / splits);
     w.n_kb = (int)((long)(w.split + 1) * kb_total / splits) - w.kb_begin;
+    const int rows_left = M - w.mt * PBN;
+    w.n_tok = rows_left >= PBN ? PBN : ((rows_left + 31) / 32) * 32;
     return w;
 }
 
@@ -134,9 +138,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             uint32_t it = 0;
             bool first = true;
             for (int u = pair; u < n_units && !*(volatile int*)bail; u += n_pairs) {
-                const PairUnit w = pair_unit(u, tiles_m, tiles, splits, kb_total);
+                const PairUnit w = pair_unit(u, tiles_m, tiles, splits, kb_total, M);
                 const int n0 = w.nt * (2 * PBM) + (int)rank * PBM;
-                const int m0 = w.mt * PBN + (int)rank * PBNH;
+                const int m0 = w.mt * PBN + (int)rank * (w.n_tok / 2);    // this CTA's half of the tile's tokens
                 int i = 0;
                 if (first) {
                     // weights do not depend on the kernel before this one; the activations do
@@ -171,11 +175,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else if (warp == 1) {
         // ---------------- MMA: the even CTA issues for the pair ----------------
         if (rank == 0 && elect_one()) {
-            constexpr uint32_t idesc = umma_idesc(PBN, false, 2 * PBM);
             uint32_t it = 0;
             int j = 0;
             for (int u = pair; u < n_units && !*(volatile int*)bail; u += n_pairs, ++j) {
-                const int n_kb = pair_unit(u, tiles_m, tiles, splits, kb_total).n_kb;
+                const PairUnit w = pair_unit(u, tiles_m, tiles, splits, kb_total, M);
+                const int n_kb = w.n_kb;
+                const uint32_t idesc = umma_idesc(w.n_tok, false, 2 * PBM);
                 const int b = j & 1;
                 const uint32_t use = (uint32_t)(j >> 1);
                 // both CTAs' epilogues must have drained this accumulator (two units ago)
@@ -211,7 +216,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int row_local = quarter * 32 + lane;
         int j = 0;
         for (int u = pair; u < n_units; u += n_pairs, ++j) {
-            const PairUnit w = pair_unit(u, tiles_m, tiles, splits, kb_total);
+            const PairUnit w = pair_unit(u, tiles_m, tiles, splits, kb_total, M);
             const int m0 = w.mt * PBN;
             const int n = w.nt * (2 * PBM) + (int)rank * PBM + row_local;
             TO* dst = out + (size_t)w.split * (size_t)slab_stride;     // this share's slab (the whole sum: slab 0)
@@ -223,7 +228,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * PBN);
             if (got) {
 #pragma unroll 1
-                for (int c = half_id * 16; c < PBN; c += 32) {
+                for (int c = half_id * 16; c < w.n_tok; c += 32) {
                     if (m0 + c >= M) break;
                     float v[16];
                     if (w.n_kb > 0) {

@@ -61,9 +61,11 @@ def test_tensor_core_product(M, N, K, out_dtype, splits):
     assert torch.equal(out, out2), "the product is not reproducible"
 
 
-@pytest.mark.parametrize("M,N,K", [(300, 10000, 200), (2048, 6144, 1024), (1000, 9999, 136)])
+@pytest.mark.parametrize("M,N,K", [(300, 10000, 200), (2048, 6144, 1024), (1000, 9999, 136), (257, 1024, 128),
+                                   (536, 3000, 264), (1056, 2048, 512), (400, 4100, 72), (2080, 1536, 256)])
 def test_two_sm_product_equals_the_one_sm_product(M, N, K):
-    """Both kernels add the same products in the same order, so they agree to the bit."""
+    """Both kernels add the same products in the same order, so they agree to the bit.  Row counts that leave a
+    last token tile of 1, 24, 32, 44, 144 and 232 rows: the two-SM kernel multiplies that tile at its own width."""
     from flambeau_b200.kernels import ops
     g = torch.Generator(device="cuda").manual_seed(M + N)
     a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
@@ -149,3 +151,21 @@ def test_gated_epilogue(M, I, K, out_dtype):
     want = gate / (1 + torch.exp(-gate)) * up
     assert int(status.item()) == 0 and torch.isfinite(out).all()
     assert rel_err(out, want) < (3e-5 if out_dtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("M,I,K", [(5, 100, 136), (300, 160, 96), (1056, 512, 256)])
+def test_gated_epilogue_with_another_activation(M, I, K):
+    """The activation of the epilogue is an argument: gelu (tanh form) beside silu, in the one-SM and the two-SM kernel."""
+    import math
+    from flambeau_b200.kernels import ops
+    g = torch.Generator(device="cuda").manual_seed(M + I)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, device="cuda", generator=g) / 8).to(torch.bfloat16)
+    out = torch.full((M, I), float("nan"), device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.gemm_tc_gated(a, w, out, status, activation="gelu_tanh")
+    y = a.double() @ w.double().T
+    gate, up = y[:, 0::2], y[:, 1::2]
+    want = 0.5 * gate * (1 + torch.tanh(math.sqrt(2 / math.pi) * (gate + 0.044715 * gate ** 3))) * up
+    assert int(status.item()) == 0 and torch.isfinite(out).all()
+    assert rel_err(out, want) < 3e-5
