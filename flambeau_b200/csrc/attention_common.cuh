@@ -40,6 +40,8 @@ struct AttnArgs {
     const int* table_base;             // per sequence: the logical page that column 0 of its table row stands for
                                        // (nullptr: page 0); released leading pages are not in the table
     const int* seq_q_start; const int* seq_q_len; const int* seq_pos_start;
+    const int* multi_seqs; int n_multi;   // the sequences that bring more than one token, in step order: the grid of
+                                          // the arrangements for portions covers only these (nullptr: all n_seqs)
     int nh, nkv, hd, window;
     float scale_log2e;
     float* part_o; float* part_ml;     // split-key: partial results, [slot][16 rows][HD_MAX] and [slot][16][2]
@@ -59,6 +61,9 @@ __device__ __forceinline__ int table_page(const AttnArgs& a, const int* table, i
     return (e >= 0 && e < a.table_stride) ? table[e] : -1;
 }
 __device__ __forceinline__ int table_base_of(const AttnArgs& a, int seq) { return a.table_base ? a.table_base[seq] : 0; }
+// Sequences that the arrangements for portions lay their grid over, and the j-th of them.
+__host__ __device__ __forceinline__ int portion_seqs(const AttnArgs& a) { return a.multi_seqs ? a.n_multi : a.n_seqs; }
+__device__ __forceinline__ int portion_seq(const AttnArgs& a, int j) { return a.multi_seqs ? a.multi_seqs[j] : j; }
 
 // The keys a group of consecutive query tokens [first, last] of a sequence can see, and where tiles start.
 struct KeyRange { int t_lo, t_hi, tile_lo; };

@@ -71,9 +71,9 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     // ---- what this CTA has to do: query tokens [tok0, tok0 + ntok) of a sequence, one key/value head ----
     // CTAs are numbered heaviest first over the whole step: the last tokens of every sequence and head (they see
     // the most keys) get the first SMs, whatever head or sequence they belong to
-    const int pairs = a.nkv * a.n_seqs;
+    const int pairs = a.nkv * portion_seqs(a);
     const int rank = blockIdx.x / pairs, pair = blockIdx.x - rank * pairs;
-    const int seq = pair / a.nkv, kvh = pair - seq * a.nkv;
+    const int seq = portion_seq(a, pair / a.nkv), kvh = pair % a.nkv;
     const int q_tiles = gridDim.x / pairs;
     const int q_len = a.seq_q_len[seq];
     if (q_len * G <= a.short_rows) return;                      // the split-key arrangement's
@@ -387,7 +387,7 @@ int launch_long(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t strea
         fb_setup_done(configured);
     }
     const int TQ = 64 * long_row_blocks(HD_MAX) / (a.nh / a.nkv);
-    const dim3 grid(((max_q_len + TQ - 1) / TQ) * a.nkv * n_seqs);
+    const dim3 grid(((max_q_len + TQ - 1) / TQ) * a.nkv * portion_seqs(a));
     fb_launch((kern), grid, LONG_THREADS, smem, stream, a);
     return fb_check_launch("attention_mma");
 }
@@ -422,7 +422,8 @@ FB_API void fb_set_attention_tc(int on) { g_attention_tc = on ? 1 : 0; }
 
 // q, out: bfloat16 [rows, heads*hd]; pools bfloat16 [pages][kv heads][page size][hd].
 // seq_*: per sequence of the step (device int32); table_base (may be null): the logical page that column 0 of each
-// sequence's table row stands for.  max_q_len / max_kv_len / any_short / any_long come from the host's copy of the
+// sequence's table row stands for; multi_seqs (may be null: all sequences): the n_multi sequences that bring more
+// than one token, which is all that the arrangements for portions lay their grid over.  max_q_len / max_kv_len / any_short / any_long come from the host's copy of the
 // step descriptor.  `scratch` holds the arrival counters and partial results of the split-key arrangement.
 // prefetch_*: the first prefetch_bytes_per_row bytes of each of prefetch_rows rows (prefetch_row_stride bytes
 // apart, from prefetch_base) are fetched into L2 when the split-key kernel's stream of cache ends: the matrix of
@@ -430,12 +431,13 @@ FB_API void fb_set_attention_tc(int on) { g_attention_tc = on ? 1 : 0; }
 FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, long long out_stride,
                                   const void* k_pool, const void* v_pool, int page_size, int n_pages,
                                   const int* block_table, int table_stride, const int* table_base,
-                                  const int* seq_q_start, const int* seq_q_len, const int* seq_pos_start, int n_seqs,
-                                  int max_q_len, int max_kv_len, int any_short, int any_long, int nh, int nkv, int hd,
+                                  const int* seq_q_start, const int* seq_q_len, const int* seq_pos_start,
+                                  const int* multi_seqs, int n_multi, int n_seqs, int max_q_len, int max_kv_len, int any_short, int any_long, int nh, int nkv, int hd,
                                   int window, float scale, float* scratch, long long scratch_floats,
                                   const void* prefetch_base, long long prefetch_rows, long long prefetch_row_stride,
                                   int prefetch_bytes_per_row, int* status, cudaStream_t stream) {
     FB_REQUIRE(n_seqs >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention_mma: bad sizes");
+    FB_REQUIRE(!multi_seqs || (n_multi >= 0 && n_multi <= n_seqs), "attention_mma: bad list of multi-token sequences");
     FB_REQUIRE(nh % nkv == 0, "attention_mma: %d query heads are not a multiple of %d key/value heads", nh, nkv);
     FB_REQUIRE(hd % 8 == 0 && hd <= 256, "attention_mma: head size %d must be a multiple of 8 and at most 256", hd);
     const int G = nh / nkv;
@@ -452,11 +454,16 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     a.page_size = page_size; a.n_pages = n_pages;
     a.block_table = block_table; a.table_stride = table_stride; a.table_base = table_base;
     a.seq_q_start = seq_q_start; a.seq_q_len = seq_q_len; a.seq_pos_start = seq_pos_start;
+    a.multi_seqs = multi_seqs; a.n_multi = n_multi;
     a.nh = nh; a.nkv = nkv; a.hd = hd; a.window = window;
     a.scale_log2e = scale * 1.4426950408889634f;
     a.status = status;
     a.short_rows = G <= 16 ? 16 : 0;               // with more than 16 heads per group even one token is "long"
-    if (a.short_rows == 0) { any_long = any_long || any_short; any_short = 0; }
+    if (a.short_rows == 0) {                       // then single tokens run in the arrangement for portions as well,
+        any_long = any_long || any_short;          // whose grid must cover every sequence
+        any_short = 0;
+        a.multi_seqs = nullptr;
+    }
     // whole pages fetched by tensor-map copies when a 64-key tile is a whole number of pages and the head a whole
     // number of 64-column blocks; single rows by bulk copies otherwise
     const bool tma = hd % 64 == 0 && page_size >= 8 && page_size <= KT && KT % page_size == 0;

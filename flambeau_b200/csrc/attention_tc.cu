@@ -89,9 +89,9 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     // ---- what this CTA has to do: query tokens [tok0, tok0 + ntok) of a sequence, one key/value head ----
     // CTAs are numbered heaviest first over the whole step: the last tokens of every sequence and head (they see
     // the most keys) get the first SMs, whatever head or sequence they belong to
-    const int pairs = a.nkv * a.n_seqs;
+    const int pairs = a.nkv * portion_seqs(a);
     const int rank = blockIdx.x / pairs, pair = blockIdx.x - rank * pairs;
-    const int seq = pair / a.nkv, kvh = pair - seq * a.nkv;
+    const int seq = portion_seq(a, pair / a.nkv), kvh = pair % a.nkv;
     const int q_tiles = gridDim.x / pairs;
     const int q_len = a.seq_q_len[seq];
     if (q_len * G <= a.short_rows) return;                      // the split-key arrangement's
@@ -417,7 +417,7 @@ int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream)
         fb_setup_done(configured);
     }
     const int TQ = RT * BM / (a.nh / a.nkv);
-    const dim3 grid(((max_q_len + TQ - 1) / TQ) * a.nkv * n_seqs);
+    const dim3 grid(((max_q_len + TQ - 1) / TQ) * a.nkv * portion_seqs(a));
     fb_launch_class(FB_LAUNCH_ATTENTION_TC, (kern), grid, tc_threads(RT), (size_t)SM::BYTES, stream, a);
     return fb_check_launch("attention_tc");
 }
@@ -427,7 +427,7 @@ template <int HD>
 int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream) {
     const int sms = fb_sm_count();
     const int TQ2 = 2 * BM / (a.nh / a.nkv);
-    const long ctas2 = (long)((max_q_len + TQ2 - 1) / TQ2) * a.nkv * n_seqs;      // an upper bound: short sequences leave early
+    const long ctas2 = (long)((max_q_len + TQ2 - 1) / TQ2) * a.nkv * portion_seqs(a);   // an upper bound: short ones leave early
     return ctas2 >= sms ? launch_tc<HD, 2>(a, n_seqs, max_q_len, stream) : launch_tc<HD, 1>(a, n_seqs, max_q_len, stream);
 }
 

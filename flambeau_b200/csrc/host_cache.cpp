@@ -309,11 +309,12 @@ FBH_API int fbh_check_invariants(void* h) {
 // Packs the descriptor of one step.  Entry i: request in slots[i], its next q_len[i] tokens (tokens, concatenated),
 // wanted places among them (wants, concatenated, n_want[i] each).  Pages for the new tokens must be reserved.
 //   rows   [4][max_tokens]: token id, position, sequence of the row, rows whose logits are wanted
-//   seqs   [4 + groups][max_seqs]: first row, rows, first position, slot, then for each group the logical page
-//          index that column 0 of the sequence's table row stands for (its first live page)
+//   seqs   [5 + groups][max_seqs]: first row, rows, first position, slot, then for each group the logical page
+//          index that column 0 of the sequence's table row stands for (its first live page), then the list of the
+//          sequences that bring more than one token (info[4] of them)
 //   tables [groups][max_seqs][max_pages]: the ids of the live pages, from the first live page on, -1 behind them
 //   fill   [groups][max_seqs]: how many entries of each table row were valid after the last call (kept by the caller)
-//   info   [4]: rows, wanted rows, longest entry, longest context
+//   info   [5]: rows, wanted rows, longest entry, longest context, sequences with more than one token
 FBH_API int fbh_build_step(void* h, int n_entries, const int* slots, const int* q_len, const int* tokens,
                            const int* n_want, const int* wants, int vocab, int max_tokens, int max_seqs, int max_pages,
                            int* rows, int* seqs, int* tables, int* fill, int* info) {
@@ -333,7 +334,8 @@ FBH_API int fbh_build_step(void* h, int n_entries, const int* slots, const int* 
     int* pos = rows + max_tokens;
     int* row_seq = rows + 2 * (size_t)max_tokens;
     int* out_rows = rows + 3 * (size_t)max_tokens;
-    int row = 0, n_out = 0, w = 0, max_q = 0, max_kv = 0;
+    int row = 0, n_out = 0, w = 0, max_q = 0, max_kv = 0, n_multi = 0;
+    int* multi = seqs + (size_t)(4 + c.n_groups()) * max_seqs;
     for (int i = 0; i < n_entries; ++i) {
         const Record& r = c.records[(size_t)slots[i]];
         const int k = q_len[i];
@@ -359,6 +361,7 @@ FBH_API int fbh_build_step(void* h, int n_entries, const int* slots, const int* 
         seqs[3 * max_seqs + i] = slots[i];
         if (k > max_q) max_q = k;
         if (r.length + k > max_kv) max_kv = r.length + k;
+        if (k > 1) multi[n_multi++] = i;
         for (int g = 0; g < c.n_groups(); ++g) {
             const PageList& pl = r.pages[(size_t)g];
             const std::vector<int>& ids = pl.ids;
@@ -377,5 +380,6 @@ FBH_API int fbh_build_step(void* h, int n_entries, const int* slots, const int* 
     info[1] = n_out;
     info[2] = max_q;
     info[3] = max_kv;
+    info[4] = n_multi;
     return 0;
 }

@@ -53,6 +53,8 @@ class StepBatch:
         self.seq_q_start_d = self.seq_q_len_d = self.seq_pos_start_d = self.seq_slot_d = None
         self.tables: list = []              # per cache group: block table [sequences, table columns]
         self.table_bases: list = []         # per cache group: the logical page that column 0 of each row stands for
+        self.multi_seqs_d = None            # device: the sequences that bring more than one token, in step order
+        self.n_multi = 0
         self.h2d_bytes = 0
 
 
@@ -60,7 +62,8 @@ class BatchBuffers:
     """Pinned host staging and device storage for step descriptors, sized once."""
 
     ROW_FIELDS = 4      # token_ids, positions, row_seq, out_rows
-    SEQ_FIELDS = 4      # q_start, q_len, pos_start, slot; then one row per cache group: the table rows' first page
+    SEQ_FIELDS = 4      # q_start, q_len, pos_start, slot; then one row per cache group (the table rows' first
+                        # page) and one with the list of the sequences that bring more than one token
 
     def __init__(self, device, max_tokens: int, max_seqs: int, n_groups: int, max_pages: int):
         """max_pages: columns of a block-table row = the most live pages one request holds in any group."""
@@ -68,7 +71,7 @@ class BatchBuffers:
         self.max_tokens, self.max_seqs, self.n_groups, self.max_pages = max_tokens, max_seqs, n_groups, max_pages
         pin = device.type == "cuda"
         self.h_rows = torch.zeros((self.ROW_FIELDS, max_tokens), dtype=torch.int32, pin_memory=pin)
-        self.h_seqs = torch.zeros((self.SEQ_FIELDS + n_groups, max_seqs), dtype=torch.int32, pin_memory=pin)
+        self.h_seqs = torch.zeros((self.SEQ_FIELDS + n_groups + 1, max_seqs), dtype=torch.int32, pin_memory=pin)
         self.h_tables = torch.full((max(n_groups, 1), max_seqs, max_pages), -1, dtype=torch.int32, pin_memory=pin)
         self.d_rows = torch.zeros_like(self.h_rows, device=device)
         self.d_seqs = torch.zeros_like(self.h_seqs, device=device)
@@ -77,7 +80,7 @@ class BatchBuffers:
         self.np_seqs = self.h_seqs.numpy()
         self.np_tables = self.h_tables.numpy()
         self._fill = np.zeros((max(n_groups, 1), max_seqs), dtype=np.int32)   # valid entries last written per table row
-        self._info = np.zeros(4, dtype=np.int32)
+        self._info = np.zeros(8, dtype=np.int32)
         from ..kernels.library import lib
         self._lib = lib()
 
@@ -117,11 +120,12 @@ class BatchBuffers:
         b.seq_slot = slots.tolist()
         b.max_q_len, b.max_kv_len = int(info[2]), int(info[3])
         b.n_tokens, b.n_seqs, b.n_out = n, S, n_out
+        b.n_multi = int(info[4])
         # ---- three copies to the device ----
         width = max(n, n_out)
         self.d_rows[:, :width].copy_(self.h_rows[:, :width], non_blocking=True)
         self.d_seqs[:, :S].copy_(self.h_seqs[:, :S], non_blocking=True)
-        b.h2d_bytes = 4 * (self.ROW_FIELDS * width + (self.SEQ_FIELDS + self.n_groups) * S)
+        b.h2d_bytes = 4 * (self.ROW_FIELDS * width + (self.SEQ_FIELDS + self.n_groups + 1) * S)
         if cache.n_groups:
             self.d_tables[:, :S].copy_(self.h_tables[:, :S], non_blocking=True)
             b.h2d_bytes += 4 * cache.n_groups * S * self.max_pages
@@ -129,4 +133,5 @@ class BatchBuffers:
         b.seq_q_start_d, b.seq_q_len_d, b.seq_pos_start_d, b.seq_slot_d = (self.d_seqs[i] for i in range(4))
         b.tables = [self.d_tables[gi] for gi in range(cache.n_groups)]
         b.table_bases = [self.d_seqs[self.SEQ_FIELDS + gi] for gi in range(cache.n_groups)]
+        b.multi_seqs_d = self.d_seqs[self.SEQ_FIELDS + self.n_groups]
         return b

@@ -368,14 +368,18 @@ def mma_attention_supported(q: torch.Tensor, nh: int, nkv: int, hd: int) -> bool
 
 def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, n_seqs: int,
                         max_q_len: int, max_kv_len: int, any_short: bool, any_long: bool, nh: int, nkv: int,
-                        hd: int, window: int, scale: float, status, table_base=None, prefetch=None) -> None:
+                        hd: int, window: int, scale: float, status, table_base=None, prefetch=None,
+                        multi_seqs=None, n_multi: int = 0) -> None:
     """bfloat16 attention on the tensor cores over the paged cache; sequences are described per entry of the
     step (first row, rows, first position).  any_short / any_long say whether the step holds sequences with
     rows * (nh/nkv) <= 16 / > 16, which run in different arrangements of the kernel.  table_base (int32 per
     sequence, optional): the logical page that column 0 of each table row stands for.  prefetch (optional): the
-    weight matrix of the product that follows (see prefetch_arguments)."""
-    _cuda(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, status, table_base)
+    weight matrix of the product that follows (see prefetch_arguments).  multi_seqs (int32, optional): the
+    n_multi sequences of the step that bring more than one token; the kernels for portions then lay their grid over
+    these instead of over every sequence."""
+    _cuda(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, status, table_base, multi_seqs)
     _i32(table_base, "table_base")
+    _i32(multi_seqs, "multi_seqs")
     n_pages, pool_kv, page_size, pool_hd = k_pool.shape
     if pool_kv != nkv or pool_hd != hd or q.shape[1] != nh * hd or out.shape[1] != nh * hd:
         raise KernelError("attention: shapes do not match the head counts")
@@ -387,7 +391,8 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
     check(lib().fb_paged_attention_mma(
         q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), k_pool.data_ptr(), v_pool.data_ptr(), page_size, n_pages,
         block_table.data_ptr(), block_table.stride(0), _ptr(table_base), seq_q_start.data_ptr(),
-        seq_q_len.data_ptr(), seq_pos_start.data_ptr(), n_seqs, max_q_len, max_kv_len, 1 if any_short else 0,
+        seq_q_len.data_ptr(), seq_pos_start.data_ptr(), _ptr(multi_seqs), int(n_multi), n_seqs, max_q_len, max_kv_len,
+        1 if any_short else 0,
         1 if any_long else 0, nh, nkv, hd, int(window), float(scale), scratch.data_ptr(), scratch.numel(),
         *prefetch_arguments(prefetch), status.data_ptr(), _stream()), "paged_attention_mma")
 
@@ -404,7 +409,7 @@ def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int,
         paged_attention_mma(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.seq_q_start_d, b.seq_q_len_d,
                             b.seq_pos_start_d, b.n_seqs, b.max_q_len, b.max_kv_len, any(short), not all(short),
                             nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,
-                            prefetch=next_weight)
+                            prefetch=next_weight, multi_seqs=b.multi_seqs_d, n_multi=b.n_multi)
     else:
         paged_attention_simt(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.positions, b.row_seq,
                              nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base)

@@ -106,10 +106,13 @@ class Scene:
             G = self.nh // self.nkv
             short = [n * G <= 16 for _, n in self.seqs]
             assert ops.mma_attention_supported(q, self.nh, self.nkv, self.hd)
+            multi = [s for s, (_, n) in enumerate(self.seqs) if n > 1]      # as the engine's descriptor lists them
+            multi_d = torch.tensor(multi + [0], dtype=torch.int32, device=dev)
             ops.paged_attention_mma(q, out, kp, vp, table, self.seq_q_start.to(dev), self.seq_q_len.to(dev),
                                     self.seq_pos_start.to(dev), len(self.seqs), max(n for _, n in self.seqs),
                                     max(c + n for c, n in self.seqs), any(short), not all(short), self.nh, self.nkv,
-                                    self.hd, self.window, scale, status, table_base=base, prefetch=prefetch)
+                                    self.hd, self.window, scale, status, table_base=base, prefetch=prefetch,
+                                    multi_seqs=multi_d, n_multi=len(multi))
         torch.cuda.synchronize()
         assert int(status.item()) == 0, "the kernel flagged a fault (missing page or timed-out wait)"
         return out.float().cpu()
@@ -125,7 +128,8 @@ def check(scene, kernel, tol=None):
 
 
 KERNELS = [("simt", torch.float32), ("simt", torch.bfloat16), ("mma", torch.bfloat16)]
-GEOMETRY = [(4, 4, 16), (4, 2, 24), (8, 2, 64), (8, 1, 80), (32, 8, 128), (6, 3, 40), (2, 1, 256), (16, 2, 32)]
+GEOMETRY = [(4, 4, 16), (4, 2, 24), (8, 2, 64), (8, 1, 80), (32, 8, 128), (6, 3, 40), (2, 1, 256), (16, 2, 32),
+            (32, 1, 64)]       # the last: 32 query heads on one key/value head, where even a single token is "long"
 
 
 @pytest.mark.parametrize("kernel,dtype", KERNELS)

@@ -80,6 +80,7 @@ def test_descriptor_of_random_steps(seed):
         assert b.seq_pos_start_d[:S].tolist() == seqs["pos0"] == b.seq_pos_start
         assert b.seq_slot_d[:S].tolist() == seqs["slot"] == b.seq_slot
         assert b.max_q_len == max(seqs["qlen"])
+        assert b.multi_seqs_d[:b.n_multi].tolist() == [s for s, q in enumerate(seqs["qlen"]) if q > 1]
         assert b.max_kv_len >= max(p + q for p, q in zip(seqs["pos0"], seqs["qlen"]))
         for gi in range(cache.n_groups):
             for s, e in enumerate(entries):
