@@ -128,6 +128,20 @@ class CacheGroup:
         return 2 * len(self.owners) * self.req.kv_heads * self.req.head_dim * any_pool.element_size()
 
 
+@dataclass
+class Snapshot:
+    """What a request holds, copied to the host: its length, per group the first live page and the contents of
+    the live pages of every layer call that owns a cache, and its fixed-size state."""
+    length: int
+    first_pages: list                          # per group
+    k: dict = field(default_factory=dict)      # owner call -> host tensor [live pages, kv heads, page size, head size]
+    v: dict = field(default_factory=dict)
+    state: dict = field(default_factory=dict)  # call -> host tensor [*shape]
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for d in (self.k, self.v, self.state) for t in d.values())
+
+
 class CacheManager:
     def __init__(self, plans: list, *, max_tokens: int, page_size: int, max_requests: int, device, dtype,
                  max_seq_len: int | None = None, max_step_tokens: int | None = None):
@@ -251,6 +265,50 @@ class CacheManager:
     def release_all(self) -> None:
         for rid in list(self.requests):
             self.release(rid)
+
+    # ---- snapshot and restore ------------------------------------------------
+    def snapshot(self, request_id) -> Snapshot:
+        """Copy what the request holds to the host (the copies are complete when this returns).  The request
+        stays live; release it to give its pages to others.  The reference snapshots contiguous slots only and
+        refuses paged ones (crates/forward/src/core/scratch.rs:1575-1581)."""
+        rec = self.requests[request_id]
+        snap = Snapshot(length=rec.length, first_pages=[self.books.first_live_page(rec.slot, g.index)
+                                                        for g in self.groups])
+        for g in self.groups:
+            ids = [p for p in rec.pages[g.index] if p >= 0]
+            # only pages that hold committed tokens (pages reserved ahead of the length hold nothing yet)
+            ids = ids[:max(0, -(-rec.length // self.page_size) - snap.first_pages[g.index])]
+            index = torch.tensor(ids, dtype=torch.long, device=self.device)
+            for c in g.owners:
+                snap.k[c] = g.k[c].index_select(0, index).cpu()
+                snap.v[c] = g.v[c].index_select(0, index).cpu()
+        for c, t in self.state.items():
+            snap.state[c] = t[rec.slot].to("cpu", copy=True)
+        return snap
+
+    def restore(self, request_id, snap: Snapshot) -> RequestRecord:
+        """Bring a snapshot back as a live request under `request_id`: a slot and fresh pages are taken (all or
+        nothing, OutOfPages otherwise) and filled with the snapshot's contents; the request then continues at
+        position snap.length as if it had never left."""
+        if request_id in self.requests:
+            raise PageError(f"request {request_id!r} is already live")
+        if len(snap.first_pages) != self.n_groups:
+            raise PageError("the snapshot was taken from a cache with other groups")
+        slot = self.books.admit_at(snap.length, snap.first_pages)
+        rec = RequestRecord(request_id, slot, self.books)
+        self.requests[request_id] = rec
+        for g in self.groups:
+            ids = [p for p in rec.pages[g.index] if p >= 0]
+            index = torch.tensor(ids, dtype=torch.long, device=self.device)
+            for c in g.owners:
+                if snap.k[c].shape[0] != len(ids):
+                    self.release(request_id)
+                    raise PageError("the snapshot does not fit this cache's page size")
+                g.k[c].index_copy_(0, index, snap.k[c].to(self.device))
+                g.v[c].index_copy_(0, index, snap.v[c].to(self.device))
+        for c, t in self.state.items():
+            t[slot].copy_(snap.state[c])
+        return rec
 
     # ---- what a step needs ---------------------------------------------------
     def table_row(self, request_id, group: int) -> list:

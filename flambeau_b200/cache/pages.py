@@ -78,6 +78,11 @@ class Books:
     def admit(self) -> int:
         return self._ok(self._lib.fbh_admit(self._h))
 
+    def admit_at(self, length: int, first_pages) -> int:
+        """A slot for a request of `length` tokens whose group g holds its pages from first_pages[g] on."""
+        fp = _ints(first_pages if len(first_pages) else [0])
+        return self._ok(self._lib.fbh_admit_at(self._h, int(length), _ptr(fp)))
+
     def release(self, slot: int) -> None:
         self._ok(self._lib.fbh_release(self._h, slot))
 

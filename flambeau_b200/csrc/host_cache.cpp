@@ -139,6 +139,38 @@ FBH_API int fbh_admit(void* h) {
     return slot;
 }
 
+// A request that comes back from a snapshot: `length` tokens whose keys are to be put back, the pages below
+// first_pages[g] of each group already given back when the snapshot was taken.  Takes a slot and the pages for
+// logical pages [first_pages[g], ceil(length / page_size)) of every group, or nothing at all; returns the slot.
+FBH_API int fbh_admit_at(void* h, int length, const int* first_pages) {
+    Cache& c = *as_cache(h);
+    if (c.free_slots.empty()) return fail(ERR_STATE, "all %d request slots are taken", c.max_requests);
+    const int limit = c.max_pages_per_request * c.page_size;
+    if (length < 0 || length > limit)
+        return fail(ERR_LIMIT, "a request of %d tokens; the cache holds at most %d per request", length, limit);
+    const int pages_to = (length + c.page_size - 1) / c.page_size;
+    for (int g = 0; g < c.n_groups(); ++g) {
+        if (first_pages[g] < 0 || first_pages[g] > pages_to)
+            return fail(ERR_STATE, "group %d: first live page %d of a request of %d pages", g, first_pages[g], pages_to);
+        const int want = pages_to - first_pages[g];
+        if (want > c.pools[(size_t)g].n_free())
+            return fail(ERR_PAGES, "%d cache pages wanted, %d of %d free", want, c.pools[(size_t)g].n_free(),
+                        c.pools[(size_t)g].n_pages);
+    }
+    const int slot = c.free_slots.back();
+    c.free_slots.pop_back();
+    Record& r = c.records[(size_t)slot];
+    r.live = true;
+    r.length = r.reserved_to = length;
+    r.pages.assign((size_t)c.n_groups(), PageList());
+    for (int g = 0; g < c.n_groups(); ++g) {
+        PageList& pl = r.pages[(size_t)g];
+        pl.base = first_pages[g];
+        while (pl.end() < pages_to) pl.ids.push_back(c.pools[(size_t)g].take());
+    }
+    return slot;
+}
+
 FBH_API int fbh_release(void* h, int slot) {
     Cache& c = *as_cache(h);
     if (int rc = check_slot(c, slot)) return rc;

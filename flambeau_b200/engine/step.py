@@ -209,6 +209,14 @@ class Engine:
     def is_live(self, request_id) -> bool:
         return request_id in self.cache.requests
 
+    def snapshot(self, request_id):
+        """What the request holds in the cache (keys, values, fixed-size state, length) as host tensors."""
+        return self.cache.snapshot(request_id)
+
+    def restore(self, request_id, snapshot) -> None:
+        """Make `request_id` live again from a snapshot; its next step continues at the snapshot's length."""
+        self.cache.restore(request_id, snapshot)
+
     # ---- the step ------------------------------------------------------------------
     def step(self, entries: list, end=(), token_feed: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run `entries` (Entry or (request_id, tokens, want) tuples) as one batch.

@@ -50,6 +50,7 @@ _SIGNATURES = {
     "fbh_cache_free": (None, [P]),
     "fbh_has_slot": (I, [P]),
     "fbh_admit": (I, [P]),
+    "fbh_admit_at": (I, [P, I, P]),
     "fbh_release": (I, [P, I]),
     "fbh_length": (I, [P, I]),
     "fbh_reserved_to": (I, [P, I]),

@@ -226,3 +226,55 @@ def test_a_windowed_request_outlives_its_table_row():
         cm.commit("a", 16)
         cm.check_invariants()
     assert cm.length("a") == 4800 and cm.first_live_page("a", 0) == (4800 - 24 + 1) // 8
+
+
+@pytest.mark.parametrize("window", [0, 24])
+def test_snapshot_and_restore_bring_a_request_back(window):
+    """What a request holds goes to the host and comes back into other pages and another slot: same length, same
+    first live page, same contents by logical page, same state; all or nothing when pages are short."""
+    plans = [CallPlan(kv=KVRequirement(2, 4, window), state=StateRequirement((3,))), CallPlan(kv=KVRequirement(2, 4, window))]
+    cm = CacheManager(plans, max_tokens=128, page_size=8, max_requests=4, device="cpu", dtype=torch.float32,
+                      max_seq_len=512)
+    g = cm.groups[0]
+    for t in list(g.k.values()) + list(g.v.values()):
+        t.copy_(torch.arange(t.numel(), dtype=torch.float32).view_as(t))     # every element names its place
+    cm.admit("a")
+    for _ in range(9):
+        cm.reserve("a", 7)
+        cm.commit("a", 7)                                                      # 63 tokens; under the window pages go back
+    cm.state[0][cm.requests["a"].slot] = torch.tensor([1.0, 2.0, 3.0])
+    before_pages = [p for p in cm.requests["a"].pages[0]]
+    live = [p for p in before_pages if p >= 0]
+    snap = cm.snapshot("a")
+    assert snap.length == 63 and snap.first_pages == [cm.first_live_page("a", 0)]
+    assert snap.k[0].shape[0] == len(live) and torch.equal(snap.k[1], g.k[1][live])
+    cm.release("a")
+    cm.admit("other")
+    cm.reserve("other", 20)                                                    # takes the pages that came back first
+    cm.commit("other", 20)
+    for t in list(g.k.values()) + list(g.v.values()):
+        t.zero_()
+    cm.restore("b", snap)
+    cm.check_invariants()
+    rec = cm.requests["b"]
+    assert rec.length == 63 and cm.first_live_page("b", 0) == snap.first_pages[0]
+    after = [p for p in rec.pages[0]]
+    assert [p < 0 for p in after] == [p < 0 for p in before_pages]
+    now_live = [p for p in after if p >= 0]
+    assert now_live != live, "the request came back into other pages"
+    for c in (0, 1):
+        assert torch.equal(g.k[c][now_live], snap.k[c]) and torch.equal(g.v[c][now_live], snap.v[c])
+    assert cm.state[0][rec.slot].tolist() == [1.0, 2.0, 3.0]
+    cm.reserve("b", 5)                                                         # and goes on
+    cm.commit("b", 5)
+    assert cm.length("b") == 68
+    with pytest.raises(PageError):
+        cm.restore("b", snap)                                                  # already live
+    free = cm.free_pages()
+    big = cm.snapshot("b")
+    cm.admit("hog")
+    cm.reserve("hog", free[0] * 8)
+    with pytest.raises(OutOfPages):
+        cm.restore("c", big)
+    assert cm.free_pages() == [0] and "c" not in cm.requests
+    cm.check_invariants()

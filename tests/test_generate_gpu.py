@@ -185,3 +185,35 @@ def test_errors_are_raised_before_anything_runs(model):
     logits = e.step([("a", [1, 2, 3], [2])], end=["a"])
     assert logits.shape == (1, model["cfg"]["vocab_size"]) and torch.isfinite(logits).all()
     assert not e.cache.requests
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_a_request_comes_back_from_a_snapshot(name, tmp_path):
+    """Thirty tokens in, snapshot, release, other requests through the same pages, restore under another id,
+    ten more tokens: the logits are those of the request that never left, bit for bit."""
+    from flambeau_b200.engine.batch import Entry
+    from flambeau_b200.engine.step import Engine, EngineOptions
+    cfg = tiny.CONFIGS[name]
+    folder = tiny.make_folder(tmp_path / "m", cfg, seed=6, dtype="float32")
+    toks = tiny.random_requests(cfg, [40, 25], seed=12)
+    a, other = toks["r0"], toks["r1"]
+    engine = Engine.from_folder(folder, EngineOptions(dtype="float32", cache_tokens=96, max_requests=2,
+                                                      max_step_tokens=64, max_seq_len=64, cuda_graphs=False))
+    engine.step([Entry("stay", a[:30], [])])
+    want = [engine.step([Entry("stay", [t], [0])]).clone() for t in a[30:]]
+    engine.finish("stay")
+    engine.step([Entry("go", a[:30], [])])
+    snap = engine.snapshot("go")
+    assert snap.length == 30 and snap.nbytes() > 0
+    engine.finish("go")
+    engine.step([Entry("other", other, [len(other) - 1])], end=["other"])      # the freed pages are written over
+    engine.step([Entry("other2", other[:9], [])])                               # and some are held by someone else
+    engine.restore("back", snap)
+    got = [engine.step([Entry("back", [t], [0])]).clone() for t in a[30:]]
+    engine.runtime.check_status("restore")
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+    engine.finish("back")
+    engine.finish("other2")
+    engine.cache.check_invariants()
+    assert not engine.cache.requests
