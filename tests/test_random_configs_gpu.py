@@ -87,3 +87,32 @@ def test_random_mid_size_configuration(seed, dtype, tmp_path):
         got = tiny.read_rows(tmp_path / name, sched, cfg["vocab_size"])
         tiny.compare_rows(got, want, tiny.TOL[dtype], f"seed {seed} {dtype} {name} {cfg}")
         del engine
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("page_size", [8, 32, 64])
+def test_other_page_sizes(page_size, dtype, tmp_path):
+    """The page size is an option of the engine (16 by default, as in the reference): pages of 8, 32 and 64 tokens
+    under a window that is no multiple of any of them, with heads of 128 so that the bfloat16 kernels fetch whole
+    pages by tensor-map copies, through a mixed schedule with page reuse."""
+    from flambeau_b200.engine.step import Engine, EngineOptions
+    from flambeau_b200.engine.trace import replay
+    cfg = dict(architectures=["MistralForCausalLM"], hidden_size=192, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=128, intermediate_size=256, vocab_size=300, rope_theta=1e4,
+               sliding_window=70, rms_norm_eps=1e-5, tie_word_embeddings=False, hidden_act="silu")
+    sharp = (0.2 if dtype == "float32" else 0.1) * (64.0 / 192) ** 0.5 * (16.0 / 128) ** 0.25
+    folder = tiny.make_folder(tmp_path / "model", cfg, seed=page_size, dtype=dtype, sharp=sharp)
+    requests = tiny.random_requests(cfg, [150, 37, 200, 21, 90], seed=page_size)
+    pcfg, W = pm.read_model_folder(folder)
+    want = {rid: pm.forward_logits(pcfg, W, toks) for rid, toks in requests.items()}
+    sched = tiny.schedule_mixed(requests, seed=page_size)
+    tokens = sched.max_live_tokens(requests)
+    engine = Engine.from_folder(folder, EngineOptions(dtype=dtype, page_size=page_size, cache_tokens=tokens,
+                                                       max_requests=4, max_step_tokens=256, max_seq_len=256))
+    assert engine.cache.page_size == page_size
+    replay(engine, sched.lines(), tmp_path / "out")
+    engine.runtime.check_status("replay")
+    engine.cache.check_invariants()
+    assert all(g.pool.n_free == g.pool.n_pages for g in engine.cache.groups), "pages lost"
+    got = tiny.read_rows(tmp_path / "out", sched, cfg["vocab_size"])
+    tiny.compare_rows(got, want, tiny.TOL[dtype], f"page size {page_size} {dtype}")
