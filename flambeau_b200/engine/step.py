@@ -58,7 +58,8 @@ class StepContext:
         n = self.n_tokens
         x = self.step_alloc((n, width), torch.float32)
         self.normed = self.step_alloc((n, width), self.runtime.dtype)
-        self.max_slabs = 16 if n <= 16 else (8 if n <= 64 else 4)
+        self.max_slabs = 8 if n <= 64 else 4       # (16 for the fewest rows was measured: the kernels that add the
+                                                   # shares take them four at a time, and a ninth costs a round trip)
         self.delta_slabs = self.step_alloc((self.max_slabs, n, width), torch.float32)
         self.delta = self.delta_slabs[0]
         self.pending_slabs = 1
