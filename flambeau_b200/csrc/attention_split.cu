@@ -618,7 +618,7 @@ int launch_split(AttnArgs& a, int n_seqs, long long scratch_floats, cudaStream_t
     static int min_tiles = 0;
     if (!min_tiles) {
         const char* env = getenv("FLAMBEAU_ATTN_MIN_TILES");
-        min_tiles = env && atoi(env) > 0 ? atoi(env) : 2;
+        min_tiles = env && atoi(env) > 0 ? atoi(env) : 3;
     }
     a.min_tiles = min_tiles;
     const long slots = a.short_ctas + (long)n_seqs * a.nkv;                 // CTA index + pair index < slots
