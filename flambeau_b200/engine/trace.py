@@ -74,7 +74,7 @@ def main(argv=None) -> int:
     try:
         engine = Engine.from_folder(args.model, EngineOptions(
             dtype=args.dtype, page_size=args.page_size, cache_tokens=tokens, max_requests=args.max_requests,
-            max_step_tokens=tokens, max_seq_len=tokens))
+            max_step_tokens=tokens))           # a request may grow to the pool's size or the model's position limit
         replay(engine, sys.stdin, args.out, report)
     except USER_ERRORS as e:                       # what the input or the model folder can cause: one line, no trace
         sys.stderr.write(f"trace_run: error: {type(e).__name__}: {e}\n")
