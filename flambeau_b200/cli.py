@@ -7,6 +7,7 @@
   flambeau replay --model DIR --dtype ... --out DIR --max-tokens N      (steps as JSON lines on stdin)
   flambeau random-model --config CONFIG.json --out DIR --seed S --dtype bfloat16|float32
   flambeau inspect --model DIR
+  flambeau bench [--shape 7b|nemo12b|small24b] [--only headline|mixed|shapes] [--steps K] ...   (one JSON line)
 
 The reference's `infer` takes text and a tokenizer from its model file; this engine takes token ids, so
 `--prompt` is a list of ids (commas or spaces) and the completion is printed as ids.
@@ -73,6 +74,10 @@ def cmd_inspect(a) -> int:
 
 
 def main(argv=None) -> int:
+    argv = sys.argv[1:] if argv is None else list(argv)
+    if argv and argv[0] == "bench":                # the benchmark parses its own options
+        from .measure.bench import main as bench_main
+        return bench_main(argv[1:])
     ap = argparse.ArgumentParser(prog="flambeau", description="B200-native single-GPU inference engine")
     sub = ap.add_subparsers(dest="cmd", required=True)
 
@@ -116,6 +121,9 @@ def main(argv=None) -> int:
     p = sub.add_parser("inspect", help="print the configuration and the tensor list of a model folder")
     p.add_argument("--model", required=True)
     p.set_defaults(fn=cmd_inspect)
+
+    sub.add_parser("bench", help="decode and prefill throughput with rooflines, as one JSON line "
+                                 "(`flambeau bench --help` lists its options)")
 
     a = ap.parse_args(argv)
     from .errors import USER_ERRORS

@@ -48,3 +48,16 @@ def test_flambeau_answers_mistakes_in_one_line(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(bad))
     p = run(ROOT / "bin" / "flambeau", "random-model", "--config", tmp_path / "config.json", "--out", tmp_path / "m")
     assert p.returncode == 1 and "hidden_act" in p.stderr and "Traceback" not in p.stderr
+
+
+def test_bench_subcommand_keeps_the_contract_for_more_than_one_gpu(capsys):
+    """`flambeau bench` is bench.py: for more than one GPU it says so in one line and exits with 2; the reference
+    arm answers with its `unavailable` line."""
+    import json
+    from flambeau_b200.cli import main
+    assert main(["bench", "--gpus", "4"]) == 2
+    out = capsys.readouterr().out.strip().splitlines()
+    assert len(out) == 1 and "one GPU" in out[0]
+    assert main(["bench", "--impl", "reference"]) == 0
+    line = json.loads(capsys.readouterr().out)
+    assert line["impl"] == "reference" and "unavailable" in line
