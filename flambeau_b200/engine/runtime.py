@@ -31,6 +31,10 @@ class NoDeviceError(RuntimeError):
     """The engine was asked to run where there is no CUDA device."""
 
 
+_ELEMENT_SIZE = {torch.float32: 4, torch.bfloat16: 2, torch.float16: 2, torch.int32: 4, torch.int64: 8,
+                 torch.float64: 8, torch.uint8: 1, torch.int8: 1, torch.bool: 1}
+
+
 class Workspace:
     """A bump arena for the activations of one step.
 
@@ -54,7 +58,7 @@ class Workspace:
         n = 1
         for s in shape:
             n *= s
-        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        nbytes = n * _ELEMENT_SIZE[dtype]
         start = (self.top + self.ALIGN - 1) // self.ALIGN * self.ALIGN
         end = start + nbytes
         if end > self.buffer.numel():
