@@ -16,11 +16,12 @@
 // O is rescaled only when a row's maximum has grown by more than 2^8 since the exponentials' reference point was
 // last moved (the sum l is kept against the same reference, so O / l is exact either way); the first tile sets
 // the reference.  Warps: 0 fetches K and V pages with tensor-map copies through four-slot rings of their own (page
-// ids read from the block table 32 at a time), 1 owns tensor memory and issues the MMAs, 2..5 and 6..9 are the
-// softmax of the two row tiles (a warp reads the quarter of the lanes given by its index modulo 4).  A wait names a
-// phase of an mbarrier only by its parity, so every barrier here is waited on for the phase that is current or
-// just completed: one barrier per buffer, and one of its own for the last product.  Every wait is bounded in
-// time; when one runs out the kernel flags it, leaves its loops, frees its tensor memory and returns.
+// ids read from the block table 32 at a time); 1 owns tensor memory; 1 and 2 issue the MMAs of row tiles 0 and 1;
+// 4..7 and 8..11 are the softmax of the two row tiles (a warp reads the quarter of the lanes given by its index
+// modulo 4).  A wait names a phase of an mbarrier only by its parity, so every barrier here is waited on for the
+// phase that is current or just completed: one barrier per buffer, and one of its own for the last product.  Every
+// wait is bounded in time; when one runs out the kernel flags it, leaves its loops, frees its tensor memory and
+// returns.
 //
 // Formulas: crates/kernels-hip/src/kernels/attention_prefill_flash_tile_f16.cu:73-213 (tile + online softmax).
 #include "attention_common.cuh"
@@ -32,9 +33,9 @@ using namespace fb_attn;
 
 constexpr int BM = 128;            // query rows per row tile (the M of the MMAs)
 constexpr int BN = 64;             // keys per tile
-// Threads of a CTA with RT row tiles: warp 0 fetches, warp 1 issues the MMAs, warps 2..5 (and 6..9) are the softmax
-// of row tile 0 (and 1).
-__host__ __device__ constexpr int tc_threads(int rt) { return 64 + BM * rt; }
+// Threads of a CTA with RT row tiles: warp 0 fetches, warps 1 and 2 issue the MMAs of row tiles 0 and 1 (warp 3 has no
+// work), warps 4..7 (and 8..11) are the softmax of row tile 0 (and 1).
+__host__ __device__ constexpr int tc_threads(int rt) { return 128 + BM * rt; }
 constexpr int NKV = 4;             // K slots and V slots
 constexpr int TMEM_COLS = 512;     // S/P buffer b of row tile t at (2t + b) * 64; O of row tile t at RT * 128 + t * 128
 constexpr float RESCALE_STEP = 8.0f;
@@ -80,7 +81,8 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     uint64_t* pv_done = bars + 4 * NKV + 4 * RT;                // [RT]  O of a row tile holds the key tile's product
     uint64_t* o_done = bars + 4 * NKV + 5 * RT;                 // [RT]  O of a row tile holds all products (used once)
     uint64_t* q_full = bars + 4 * NKV + 6 * RT;                 //       Q is staged
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * NKV + 6 * RT + 1);
+    uint64_t* v_clean = bars + 4 * NKV + 6 * RT + 1;            //       row tile 0 has cleared a V tile's unseen rows (at most twice)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * NKV + 6 * RT + 2);
     int* bail = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -109,13 +111,24 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
     const int* table = a.block_table + (size_t)seq * a.table_stride;
     const int pages_per_tile = BN / a.page_size;
     const int n_ops = pages_per_tile * CB;                      // copies per K or V tile: (page, column block)
+    // Value rows no query of the CTA sees: pages of the first tile wholly before the window, keys of the last tile
+    // behind the last position.  Whole pages arrive, the slots behind the last position included, and what a page
+    // holds there was never written by this request; pages wholly before the window or behind the last position do
+    // not arrive at all, and their slots hold whatever was there.  The probabilities of such keys are 0, but
+    // 0 * NaN is NaN: the softmax of row tile 0 clears those rows, 128 bytes per key and column block, before it
+    // lets its product start, and says so on a barrier that the thread of row tile 1's products waits for.
+    const int dead_lo_first = ((t_lo - k_begin) / a.page_size) * a.page_size;      // rows [0, dead_lo_first) of tile 0
+    const int dead_hi_last = k_end - (k_begin + (n_tiles - 1) * BN);               // rows [dead_hi_last, BN) of the last tile
+    auto dead_lo_of = [&](int j) { return j == 0 ? dead_lo_first : 0; };
+    auto dead_hi_of = [&](int j) { return j == n_tiles - 1 ? dead_hi_last : BN; };
+    auto has_dead = [&](int j) { return dead_lo_of(j) > 0 || dead_hi_of(j) < BN; };
 
     if (tid == 0) {
         for (int s = 0; s < NKV; ++s) {
             mbar_init(smem_u32(&k_full[s]), n_ops);
-            mbar_init(smem_u32(&k_empty[s]), 1);
+            mbar_init(smem_u32(&k_empty[s]), RT);
             mbar_init(smem_u32(&v_full[s]), n_ops);
-            mbar_init(smem_u32(&v_empty[s]), 1);
+            mbar_init(smem_u32(&v_empty[s]), RT);
         }
         for (int t = 0; t < RT; ++t) {
             mbar_init(smem_u32(&s_full[2 * t]), 1);
@@ -126,6 +139,7 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
             mbar_init(smem_u32(&o_done[t]), 1);
         }
         mbar_init(smem_u32(q_full), RT * BM);
+        mbar_init(smem_u32(v_clean), BM);
         *bail = 0;
         mbar_fence_init();
     }
@@ -138,6 +152,7 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
 
     // a wait that ran out anywhere ends every loop of the CTA
     auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+        if (mbar_try_wait(smem_u32(bar), parity)) return true;  // a wait that passes costs one round trip to shared memory
         if (*(volatile int*)bail) return false;
         if (mbar_wait(smem_u32(bar), parity, a.status)) return true;
         *(volatile int*)bail = 1;
@@ -194,16 +209,23 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
             issue(Vs + s * SM::KV_BYTES, &a.map_v, &v_full[s], page);
             page = lookup(j + 1);                               // in flight while this warp waits for the next slot
         }
-    } else if (warp == 1) {
-        // ================= MMA issue =================
+    } else if (warp < 4) {
+        // ================= MMA issue: warp 1 for row tile 0, warp 2 for row tile 1 =================
         // Scores run two key tiles ahead of the softmax (two buffers per row tile), so a row tile's softmax never
-        // waits for the tensor pipe.  Per key tile and row tile: O += P V, then the scores of the tile after next
-        // into the columns P lay in (the MMAs run in the order of their issue, so the product has read P by then).
-        if (elect_one()) {
+        // waits for the tensor pipe.  Per key tile: O += P V, then the scores of the tile after next into the
+        // columns P lay in (the MMAs of one thread run in the order of their issue, so the product has read P by
+        // then), then every commit of the step at one point.  Measured on one SM with back-to-back instructions:
+        // a thread that issues MMAs runs in step with the tensor pipe (its queue is a few instructions deep), so
+        // the pipe stands still while that thread waits for a barrier, and every point of the instruction stream
+        // where tcgen05.commit stands costs the pipe about 170 cycles, however many commits stand there.  Hence a
+        // thread for each row tile (the pipe has the other's MMAs meanwhile), the waits for K and V ahead of the
+        // wait for P (they pass at once unless the cache is late), and one point of commits per key tile.
+        const int t = warp - 1;
+        if (t < RT && elect_one()) {
             constexpr uint32_t idesc_s = umma_idesc(BN);
             constexpr uint32_t idesc_o = umma_idesc(HD, true);
-            auto issue_s = [&](int j, int t) {                  // S buffer j & 1 of row tile t = Q_t K_j^T
-                const uint32_t q_addr = smem_u32(Qs + t * SM::Q_BYTES);
+            const uint32_t q_addr = smem_u32(Qs + t * SM::Q_BYTES);
+            auto issue_s = [&](int j) {                         // S buffer j & 1 of the row tile = Q_t K_j^T
                 const uint32_t k_addr = smem_u32(Ks + (j % NKV) * SM::KV_BYTES);
                 const uint32_t d = tmem_base + (uint32_t)((2 * t + (j & 1)) * BN);
 #pragma unroll
@@ -211,47 +233,48 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
                     umma_bf16(d, umma_desc(q_addr + (uint32_t)((kk / 4) * (BM * 128) + (kk % 4) * 32)),
                               umma_desc(k_addr + (uint32_t)((kk / 4) * (BN * 128) + (kk % 4) * 32)), idesc_s,
                               kk > 0 ? 1u : 0u);
-                umma_commit(smem_u32(&s_full[2 * t + (j & 1)]));
-                if (t == RT - 1) umma_commit(smem_u32(&k_empty[j % NKV]));
             };
             bool ok = wait(q_full, 0);
             for (int j = 0; ok && j < 2 && j < n_tiles; ++j) {
                 ok = wait(&k_full[j % NKV], (uint32_t)(j / NKV) & 1u);
                 if (!ok) break;
                 tmem_fence_after();
-                for (int t = 0; t < RT; ++t) issue_s(j, t);
+                issue_s(j);
+                umma_commit(smem_u32(&s_full[2 * t + (j & 1)]));
+                umma_commit(smem_u32(&k_empty[j % NKV]));
             }
             for (int j = 0; ok && j < n_tiles; ++j) {
-                for (int t = 0; ok && t < RT; ++t) {
-                    ok = wait(&p_full[2 * t + (j & 1)], (uint32_t)(j >> 1) & 1u);
-                    if (ok && t == 0) ok = wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u);
-                    if (!ok) break;
-                    tmem_fence_after();
-                    const uint32_t v_addr = smem_u32(Vs + (j % NKV) * SM::KV_BYTES);
-                    const uint32_t p_addr = tmem_base + (uint32_t)((2 * t + (j & 1)) * BN);   // bf16 pairs over the scores
-                    const uint32_t d = tmem_base + (uint32_t)(RT * 128 + t * 128);
+                const bool more = j + 2 < n_tiles;              // there are scores left to compute
+                ok = wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u);
+                if (ok && more) ok = wait(&k_full[(j + 2) % NKV], (uint32_t)((j + 2) / NKV) & 1u);
+                // (the barrier's first phase is tile 0's clearing if tile 0 has rows to clear, else the last tile's)
+                if (ok && t > 0 && has_dead(j)) ok = wait(v_clean, (j > 0 && has_dead(0)) ? 1u : 0u);
+                if (ok) ok = wait(&p_full[2 * t + (j & 1)], (uint32_t)(j >> 1) & 1u);
+                if (!ok) break;
+                tmem_fence_after();
+                const uint32_t v_addr = smem_u32(Vs + (j % NKV) * SM::KV_BYTES);
+                const uint32_t p_addr = tmem_base + (uint32_t)((2 * t + (j & 1)) * BN);     // bf16 pairs over the scores
+                const uint32_t d = tmem_base + (uint32_t)(RT * 128 + t * 128);
 #pragma unroll
-                    for (int kk = 0; kk < BN / UMMA_K; ++kk) {  // 16 keys = 8 columns of P each
-                        const uint64_t db = umma_desc_mn(v_addr + (uint32_t)(kk * 16 * 128), BN * 128, 1024);
-                        umma_bf16_ts(d, p_addr + (uint32_t)(kk * 8), db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-                    }
-                    umma_commit(smem_u32(&pv_done[t]));
-                    if (j == n_tiles - 1) umma_commit(smem_u32(&o_done[t]));
-                    if (t == RT - 1) umma_commit(smem_u32(&v_empty[j % NKV]));
-                    if (j + 2 < n_tiles) {
-                        if (t == 0) ok = wait(&k_full[(j + 2) % NKV], (uint32_t)((j + 2) / NKV) & 1u);
-                        if (!ok) break;
-                        tmem_fence_after();
-                        issue_s(j + 2, t);
-                    }
+                for (int kk = 0; kk < BN / UMMA_K; ++kk) {      // 16 keys = 8 columns of P each
+                    const uint64_t db = umma_desc_mn(v_addr + (uint32_t)(kk * 16 * 128), BN * 128, 1024);
+                    umma_bf16_ts(d, p_addr + (uint32_t)(kk * 8), db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                if (more) issue_s(j + 2);
+                umma_commit(smem_u32(&pv_done[t]));
+                if (j == n_tiles - 1) umma_commit(smem_u32(&o_done[t]));
+                umma_commit(smem_u32(&v_empty[j % NKV]));
+                if (more) {
+                    umma_commit(smem_u32(&s_full[2 * t + (j & 1)]));
+                    umma_commit(smem_u32(&k_empty[(j + 2) % NKV]));
                 }
             }
         }
         __syncwarp();
     } else {
-        // ================= softmax: thread = query row = tensor-memory lane; warps 2..5 row tile 0, 6..9 row tile 1 =====
+        // ================= softmax: thread = query row = tensor-memory lane; warps 4..7 row tile 0, 8..11 row tile 1 =====
         const int quarter = warp & 3;                           // the lanes this warp may read
-        const int t = (warp - 2) >> 2;                          // its row tile
+        const int t = (warp - 4) >> 2;                          // its row tile
         const int r = t * BM + quarter * 32 + lane;             // row of the CTA
         const bool valid = r < rows_valid;
         const int token = q_start + tok0 + r / G, head = kvh * G + r % G;
@@ -346,26 +369,19 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
                 tmem_st16(s_addr + (uint32_t)(c * 16), pk);
             }
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            // Whole pages arrive, the slots behind the last position included, and what a page holds there was never
-            // written by this request; pages wholly before the window or behind the last position do not arrive at
-            // all, and their slots hold whatever was there.  The probabilities of such keys are 0, but 0 * NaN is
-            // NaN: row tile 0 (whose product is issued first) clears those value rows, 128 bytes per key and
-            // column block, before the products read them.
-            if (t == 0) {
-                const int dead_lo = tile_start < t_lo ? ((t_lo - tile_start) / a.page_size) * a.page_size : 0;   // rows [0, dead_lo)
-                const int dead_hi = min(max(t_hi + 1 - tile_start, 0), BN);                                       // rows [dead_hi, BN)
-                if (dead_lo > 0 || dead_hi < BN) {
-                    ok = __all_sync(0xffffffffu, wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u));
-                    if (!ok) continue;
-                    uint8_t* vt = Vs + (j % NKV) * SM::KV_BYTES;
-                    const int n_dead = dead_lo + (BN - dead_hi);
-                    for (int idx = tid - 64; idx < n_dead * 8 * CB; idx += BM) {
-                        const int cb = idx / (n_dead * 8), rest = idx - cb * (n_dead * 8);
-                        const int k = rest / 8, row = k < dead_lo ? k : dead_hi + (k - dead_lo);
-                        *reinterpret_cast<uint4*>(vt + cb * (BN * 128) + row * 128 + (rest & 7) * 16) = make_uint4(0, 0, 0, 0);
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            if (t == 0 && has_dead(j)) {                        // (only the first and the last tile can)
+                const int dead_lo = dead_lo_of(j), dead_hi = dead_hi_of(j);
+                ok = __all_sync(0xffffffffu, wait(&v_full[j % NKV], (uint32_t)(j / NKV) & 1u));
+                if (!ok) continue;
+                uint8_t* vt = Vs + (j % NKV) * SM::KV_BYTES;
+                const int n_dead = dead_lo + (BN - dead_hi);
+                for (int idx = tid - 128; idx < n_dead * 8 * CB; idx += BM) {
+                    const int cb = idx / (n_dead * 8), rest = idx - cb * (n_dead * 8);
+                    const int k = rest / 8, row = k < dead_lo ? k : dead_hi + (k - dead_lo);
+                    *reinterpret_cast<uint4*>(vt + cb * (BN * 128) + row * 128 + (rest & 7) * 16) = make_uint4(0, 0, 0, 0);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (RT > 1) mbar_arrive(smem_u32(v_clean));
             }
             tmem_wait_st();
             tmem_fence_before();
