@@ -82,8 +82,11 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (sizes unchanged)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true", help="do not measure batch 1 and 64")
-    ap.add_argument("--only", choices=["all", "headline", "mixed", "shapes"], default="all",
-                    help="headline: the shape's own line only; mixed / shapes: that part only")
+    ap.add_argument("--only", choices=["all", "headline", "mixed", "shapes", "timeline", "mma-issue"], default="all",
+                    help="headline: the shape's own line only; mixed / shapes: that part only; timeline: the kernels "
+                         "of one decode step at --batch as the device ran them (a table on stderr, 4 layers unless "
+                         "--layers says otherwise); mma-issue: cycles per tcgen05.mma of one SM for the attention "
+                         "kernel's instruction streams (a table on stderr)")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -154,6 +157,31 @@ def main(argv=None) -> int:
     context = args.context or head.context
     layers_full = head.config["num_hidden_layers"]
     layers = args.layers or layers_full
+
+    if args.only == "mma-issue":
+        from flambeau_b200.measure.probes import run_probe
+        table = run_probe("mma_issue_rate")
+        print(table, file=sys.stderr)
+        rows = [ln.rsplit(None, 4) for ln in table.splitlines()[1:] if ln.strip()]
+        print(json.dumps({"impl": "ours", "mma_issue_cycles_each": {r[0].strip(): float(r[3]) for r in rows}}))
+        return 0
+    if args.only == "timeline":
+        layers = args.layers or 4
+        say(f"building {head.name}, {layers} layers")
+        cfg, engine = build(head, layers, args.batch, context, args.batch, 64)
+        rows = workloads.decode_timeline(engine, args.batch, context, gen)
+        last_end, costs = 0.0, {}
+        print(f"{'start us':>9} {'end us':>9} {'alone us':>9} {'costs us':>9}  kernel", file=sys.stderr)
+        for start, end, name in rows:
+            short = name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0]
+            cost = max(end - last_end, 0.0)
+            print(f"{start:9.2f} {end:9.2f} {end - start:9.2f} {cost:9.2f}  {short}", file=sys.stderr)
+            costs[short] = costs.get(short, 0.0) + cost
+            last_end = max(last_end, end)
+        print(json.dumps({"impl": "ours", "timeline": {"model": head.name, "layers": layers, "batch": args.batch,
+                          "context": context, "step_us": round(last_end, 2),
+                          "cost_us_by_kernel": {k: round(v, 2) for k, v in costs.items()}}}))
+        return 0
 
     with ClockSampler(0) as clocks:                     # clocks and throttle reasons while the timed regions run
         time.sleep(0.3)                                 # let nvidia-smi start reporting before the first region

@@ -189,6 +189,35 @@ def kernel_sections(engine, entries, cfg, reps: int = 3, end=(), ahead_ms: float
         engine.use_graphs = was
 
 
+def decode_timeline(engine, batch: int, context: int, gen, warmup: int = 8) -> list:
+    """The kernels of one decode step as the device ran them, from the driver's activity records (torch.profiler):
+    [(start us, end us, name)] in order of start, times from the step's first kernel.  Unlike the section timer this
+    leaves the step as it is (a replayed graph with programmatic dependent launches), so a kernel's start lies before
+    the end of the one ahead of it; what a kernel costs the step is its end minus the end of the kernel before it."""
+    from torch.profiler import ProfilerActivity, profile
+    ids = seat(engine, [context] * batch)
+    tok = torch.randint(0, engine.model.vocab_size, (batch,), generator=gen).tolist()
+    entries = [Entry(r, [t], [0]) for r, t in zip(ids, tok)]
+    chosen = torch.zeros(batch, dtype=torch.int32, device=engine.runtime.device)
+    for _ in range(warmup):
+        ops.sample(engine.step(entries), chosen, n=batch)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            ops.sample(engine.step(entries), chosen, n=batch)
+        torch.cuda.synchronize()
+    rows = sorted(((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                   if "cuda" in str(e.device_type).lower() and "Memcpy" not in e.name and "Memset" not in e.name),
+                  key=lambda r: r[0])
+    firsts = [i for i, r in enumerate(rows) if "embedding" in r[2]]
+    if len(firsts) < 3:
+        raise RuntimeError("the profiler returned no kernel records for the step")
+    a, b = firsts[1], firsts[2]                          # the second of the three steps
+    t0 = rows[a][0]
+    engine.cache.release_all()
+    return [(s - t0, e - t0, n) for s, e, n in rows[a:b]]
+
+
 def attention_check(engine, batch: int, context: int, gen) -> dict:
     """Relative error of the bfloat16 decode attention over the cache of `batch` seated requests (layer call 0,
     a random query) against a float32 softmax over the same pages, for the first and the last sequence."""
