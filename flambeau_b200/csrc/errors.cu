@@ -66,6 +66,17 @@ int fb_check_launch(const char* what) {
     return 0;
 }
 
+// `rows` rows of `width_bytes` from pinned host memory to the device, each side with its own distance between rows
+// (one asynchronous 2-d copy on the stream: a step's descriptor is a few rows of a wider staging buffer).
+FB_API int fb_copy_rows_to_device(void* dst, long long dst_pitch, const void* src, long long src_pitch,
+                                  long long width_bytes, long long rows, cudaStream_t stream) {
+    if (width_bytes <= 0 || rows <= 0) return 0;
+    const cudaError_t e = cudaMemcpy2DAsync(dst, (size_t)dst_pitch, src, (size_t)src_pitch, (size_t)width_bytes,
+                                            (size_t)rows, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return fb_fail(-2, "copy of a step's descriptor to the device failed: %s", cudaGetErrorString(e));
+    return 0;
+}
+
 FB_API const char* fb_last_error() { return g_last_error; }
 
 // Version stamp checked by the Python loader against the sources it compiled.

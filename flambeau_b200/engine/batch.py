@@ -84,6 +84,20 @@ class BatchBuffers:
         from ..kernels.library import lib
         self._lib = lib()
 
+    def _to_device(self, dst: torch.Tensor, src: torch.Tensor, rows: int, width: int, pitch: int) -> None:
+        """The first `width` int32 of each of the first `rows` rows (rows `pitch` int32 apart on both sides), on
+        torch's current stream.  On the GPU one asynchronous 2-d copy from the pinned buffer; torch's own copy of
+        such a slice goes through a temporary and a kernel."""
+        if not width or not rows:
+            return
+        if self.device.type != "cuda":
+            dst.view(-1, pitch)[:rows, :width].copy_(src.view(-1, pitch)[:rows, :width])
+            return
+        from ..kernels.ops import _stream
+        if self._lib.fb_copy_rows_to_device(dst.data_ptr(), 4 * pitch, src.data_ptr(), 4 * pitch, 4 * width, rows,
+                                            _stream()) != 0:
+            raise BatchError(self._lib.fb_last_error().decode(errors="replace"))
+
     def build(self, entries: list, cache, vocab_size: int) -> StepBatch:
         """Validate the entries against the cache manager's books and pack them (in the C++ host code,
         csrc/host_cache.cpp: fbh_build_step).  Pages for the new tokens must have been reserved already."""
@@ -121,13 +135,15 @@ class BatchBuffers:
         b.max_q_len, b.max_kv_len = int(info[2]), int(info[3])
         b.n_tokens, b.n_seqs, b.n_out = n, S, n_out
         b.n_multi = int(info[4])
-        # ---- three copies to the device ----
+        # ---- three copies to the device: the used part of each staging buffer, as one 2-d copy each ----
         width = max(n, n_out)
-        self.d_rows[:, :width].copy_(self.h_rows[:, :width], non_blocking=True)
-        self.d_seqs[:, :S].copy_(self.h_seqs[:, :S], non_blocking=True)
+        self._to_device(self.d_rows, self.h_rows, self.ROW_FIELDS, width, self.max_tokens)
+        self._to_device(self.d_seqs, self.h_seqs, self.SEQ_FIELDS + self.n_groups + 1, S, self.max_seqs)
         b.h2d_bytes = 4 * (self.ROW_FIELDS * width + (self.SEQ_FIELDS + self.n_groups + 1) * S)
         if cache.n_groups:
-            self.d_tables[:, :S].copy_(self.h_tables[:, :S], non_blocking=True)
+            # every group's table rows of the step's sequences: S * max_pages entries a group, contiguous
+            self._to_device(self.d_tables, self.h_tables, cache.n_groups, S * self.max_pages,
+                            self.max_seqs * self.max_pages)
             b.h2d_bytes += 4 * cache.n_groups * S * self.max_pages
         b.token_ids, b.positions, b.row_seq, b.out_rows = (self.d_rows[i] for i in range(4))
         b.seq_q_start_d, b.seq_q_len_d, b.seq_pos_start_d, b.seq_slot_d = (self.d_seqs[i] for i in range(4))

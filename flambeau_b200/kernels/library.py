@@ -20,6 +20,7 @@ STREAM = c_void_p
 _SIGNATURES = {
     "fb_last_error": (c_char_p, []),
     "fb_abi_version": (I, []),
+    "fb_copy_rows_to_device": (I, [P, L, P, L, L, L, STREAM]),
     "fb_set_pdl": (None, [I]),
     "fb_set_plain_launch_classes": (None, [I]),
     "fb_set_attention_tc": (None, [I]),
