@@ -44,6 +44,9 @@ struct AttnArgs {
                                           // the arrangements for portions covers only these (nullptr: all n_seqs)
     int nh, nkv, hd, window;
     float scale_log2e;
+    const float* score_slopes;         // per query head, or nullptr: slope * (key position - query position) is added
+                                       // to the scaled score (a linear penalty on distance; <= 0 for the keys a
+                                       // query sees when the slope is >= 0)
     float* part_o; float* part_ml;     // split-key: partial results, [slot][16 rows][HD_MAX] and [slot][16][2]
     int* part_cnt;                     // split-key: per (sequence, key/value head), segments that have arrived; 0 at rest
     int n_seqs;                        // sequences of the step

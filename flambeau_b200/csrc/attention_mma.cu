@@ -193,11 +193,13 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     const int row_base = warp * (16 * R);           // first row of this warp within the CTA
     // per-thread rows of row block rb: row_base + 16*rb + lane/4 and that + 8
     int p_row[R][2], t0_row[R][2];
+    float slope_row[R][2];                          // the row's head's penalty on distance, in base-2 units
 #pragma unroll
     for (int rb = 0; rb < R; ++rb)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r = row_base + 16 * rb + (lane >> 2) + 8 * h;
+            slope_row[rb][h] = a.score_slopes && r < rows_valid ? a.score_slopes[kvh * G + r % G] * 1.4426950408889634f : 0.0f;
             if (r < rows_valid) {
                 p_row[rb][h] = pos0 + tok0 + r / G;
                 t0_row[rb][h] = (a.window > 0 && p_row[rb][h] - a.window + 1 > 0) ? p_row[rb][h] - a.window + 1 : 0;
@@ -287,7 +289,7 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
                     const int h = e >> 1;
                     const int t = tile_start + nb * 8 + 2 * (lane & 3) + (e & 1);
                     const bool ok = t >= t0_row[rb][h] && t <= p_row[rb][h] && t < k_end;
-                    const float v = ok ? s[rb][nb][e] * a.scale_log2e : -INFINITY;
+                    const float v = ok ? fmaf(slope_row[rb][h], (float)(t - p_row[rb][h]), s[rb][nb][e] * a.scale_log2e) : -INFINITY;
                     s[rb][nb][e] = v;
                     tile_max[h] = fmaxf(tile_max[h], v);
                 }
@@ -433,7 +435,8 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
                                   const int* block_table, int table_stride, const int* table_base,
                                   const int* seq_q_start, const int* seq_q_len, const int* seq_pos_start,
                                   const int* multi_seqs, int n_multi, int n_seqs, int max_q_len, int max_kv_len, int any_short, int any_long, int nh, int nkv, int hd,
-                                  int window, float scale, float* scratch, long long scratch_floats,
+                                  int window, float scale, const float* score_slopes, float* scratch,
+                                  long long scratch_floats,
                                   const void* prefetch_base, long long prefetch_rows, long long prefetch_row_stride,
                                   int prefetch_bytes_per_row, int* status, cudaStream_t stream) {
     FB_REQUIRE(n_seqs >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention_mma: bad sizes");
@@ -457,6 +460,7 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     a.multi_seqs = multi_seqs; a.n_multi = n_multi;
     a.nh = nh; a.nkv = nkv; a.hd = hd; a.window = window;
     a.scale_log2e = scale * 1.4426950408889634f;
+    a.score_slopes = score_slopes;
     a.status = status;
     a.short_rows = G <= 16 ? 16 : 0;               // with more than 16 heads per group even one token is "long"
     if (a.short_rows == 0) {                       // then single tokens run in the arrangement for portions as well,

@@ -21,7 +21,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
                             int n_pages, const int* __restrict__ block_table, int table_stride,
                             const int* __restrict__ table_base,
                             const int* __restrict__ positions, const int* __restrict__ row_seq, int n, int nh,
-                            int nkv, int hd, int window, float scale, int* status) {
+                            int nkv, int hd, int window, float scale, const float* __restrict__ score_slopes,
+                            int* status) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     extern __shared__ float q_sh[];                    // [4 warps][hd]
@@ -40,6 +41,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
     if (!active) return;
 
     const int p = positions[row];
+    const float slope = score_slopes ? score_slopes[head] : 0.0f;
     const int t0 = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int* table = block_table + (size_t)row_seq[row] * table_stride;
     const int base_page = table_base ? table_base[row_seq[row]] : 0;     // the table row starts at this logical page
@@ -64,7 +66,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
                 const T* kr = k_pool + (((size_t)my_page * nkv + kvh) * page_size + (t % page_size)) * hd;
                 float dot = 0.0f;
                 for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], fb_to_float(kr[d]), dot);
-                s = dot * scale;
+                s = dot * scale + slope * (float)(t - p);
             }
         }
         const float tile_max = fb_warp_max(s);
@@ -104,12 +106,13 @@ static int launch_attention_simt(const void* q, long q_stride, void* out, long o
                                  const void* v_pool, int page_size, int n_pages, const int* block_table,
                                  int table_stride, const int* table_base, const int* positions, const int* row_seq,
                                  int n, int nh,
-                                 int nkv, int hd, int window, float scale, int* status, cudaStream_t stream) {
+                                 int nkv, int hd, int window, float scale, const float* score_slopes, int* status,
+                                 cudaStream_t stream) {
     const long items = (long)n * nh;
     const unsigned blocks = (unsigned)((items + 3) / 4);
     fb_launch((paged_attention_simt_kernel<T, NDR>), blocks, 128, 4 * hd * sizeof(float), stream, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, page_size, n_pages,
-        block_table, table_stride, table_base, positions, row_seq, n, nh, nkv, hd, window, scale, status);
+        block_table, table_stride, table_base, positions, row_seq, n, nh, nkv, hd, window, scale, score_slopes, status);
     return fb_check_launch("paged_attention_simt");
 }
 
@@ -117,7 +120,8 @@ FB_API int fb_paged_attention_simt(const void* q, long long q_stride, void* out,
                                    const void* k_pool, const void* v_pool, int page_size, int n_pages,
                                    const int* block_table, int table_stride, const int* table_base,
                                    const int* positions, const int* row_seq, int n, int nh, int nkv, int hd,
-                                   int window, float scale, int* status, cudaStream_t stream) {
+                                   int window, float scale, const float* score_slopes, int* status,
+                                   cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention: bad sizes n=%d heads=%d kv=%d hd=%d", n, nh, nkv, hd);
     FB_REQUIRE(nh % nkv == 0, "attention: %d query heads are not a multiple of %d key/value heads", nh, nkv);
     FB_REQUIRE(hd <= 512, "attention: head size %d is larger than 512", hd);
@@ -126,7 +130,7 @@ FB_API int fb_paged_attention_simt(const void* q, long long q_stride, void* out,
 #define FB_ATTN_CASE(NDR)                                                                                      \
     FB_DISPATCH_DTYPE(dtype, T, return (launch_attention_simt<T, NDR>(q, (long)q_stride, out, (long)out_stride,     \
         k_pool, v_pool, page_size, n_pages, block_table, table_stride, table_base, positions, row_seq, n, nh, \
-        nkv, hd, window, scale, status, stream)))
+        nkv, hd, window, scale, score_slopes, status, stream)))
     if (hd <= 32) { FB_ATTN_CASE(1); }
     else if (hd <= 64) { FB_ATTN_CASE(2); }
     else if (hd <= 128) { FB_ATTN_CASE(4); }

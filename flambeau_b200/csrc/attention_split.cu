@@ -369,9 +369,11 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
         }
         // this thread's rows: lane/4 and that + 8
         int p_row[2], t0_row[2];
+        float slope_row[2];                           // the row's head's penalty on distance, in base-2 units
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r = (lane >> 2) + 8 * h;
+            slope_row[h] = a.score_slopes && r < rows_valid ? a.score_slopes[kvh * G + r % G] * 1.4426950408889634f : 0.0f;
             if (r < rows_valid) {
                 p_row[h] = pos0 + r / G;
                 t0_row[h] = (a.window > 0 && p_row[h] - a.window + 1 > 0) ? p_row[h] - a.window + 1 : 0;
@@ -445,7 +447,7 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
                         const int h = e >> 1;
                         const int t = tile_start + key0 + nb * 8 + 2 * (lane & 3) + (e & 1);
                         const bool ok = t >= t0_row[h] && t <= p_row[h] && t < k_end;
-                        const float v = ok ? s[nb][e] * a.scale_log2e : -INFINITY;
+                        const float v = ok ? fmaf(slope_row[h], (float)(t - p_row[h]), s[nb][e] * a.scale_log2e) : -INFINITY;
                         s[nb][e] = v;
                         tile_max[h] = fmaxf(tile_max[h], v);
                     }

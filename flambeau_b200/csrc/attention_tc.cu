@@ -451,7 +451,8 @@ int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream)
 
 bool fb_attention_tc_takes(const AttnArgs& a, bool tma) {
     const int G = a.nh / a.nkv;
-    return tma && (a.hd == 64 || a.hd == 128) && G <= BM && BN % a.page_size == 0 && a.out_stride % 8 == 0 &&
+    return tma && !a.score_slopes && (a.hd == 64 || a.hd == 128) && G <= BM && BN % a.page_size == 0 &&
+           a.out_stride % 8 == 0 &&
            (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
 }
 

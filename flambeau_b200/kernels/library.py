@@ -37,10 +37,10 @@ _SIGNATURES = {
     "fb_gemm_tc": (I, [P, L, P, L, P, I, L, L, I, P, I, I, I, P, L, P, I, I, P, STREAM]),
     "fb_gemm_tc_gated": (I, [P, L, P, L, P, I, L, I, I, I, I, P, L, P, I, P, STREAM]),
     # attention_simt.cu
-    "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, P, I, I, I, I, I, F, P, STREAM]),
+    "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, P, I, I, I, I, I, F, P, P, STREAM]),
     # attention_mma.cu
-    "fb_paged_attention_mma": (I, [P, L, P, L, P, P, I, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, L, P, L, L,
-                                   I, P, STREAM]),
+    "fb_paged_attention_mma": (I, [P, L, P, L, P, P, I, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P, L, P, L,
+                                   L, I, P, STREAM]),
     # sampling.cu
     "fb_apply_penalties": (I, [P, L, I, P, P, P, P, P, P, I, STREAM]),
     "fb_apply_logit_bias": (I, [P, L, I, P, P, P, I, STREAM]),

@@ -180,8 +180,20 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                              out.data_ptr(), dtype_code(out), _rows(out), M, N, K, _stream()), "gemm_simt", (M, N, K))
 
 
+def _slopes(score_slopes, nh: int) -> int:
+    """The address of the per-head slopes (float32 [nh], contiguous, on the GPU), or 0 for none."""
+    if score_slopes is None:
+        return 0
+    if not score_slopes.is_cuda or score_slopes.dtype != torch.float32 or score_slopes.numel() != nh \
+            or not score_slopes.is_contiguous():
+        raise KernelError(f"attention: score slopes must be {nh} contiguous float32 on the GPU, one per query head")
+    return score_slopes.data_ptr()
+
+
 def paged_attention_simt(q, out, k_pool, v_pool, block_table, positions, row_seq, nh: int, nkv: int, hd: int,
-                         window: int, scale: float, status, table_base=None) -> None:
+                         window: int, scale: float, status, table_base=None, score_slopes=None) -> None:
+    """score_slopes (float32 per query head, optional): slope * (key position - query position) is added to every
+    scaled score, a linear penalty on distance."""
     _cuda(q, out, k_pool, v_pool, block_table, positions, row_seq, status, table_base)
     _i32(table_base, "table_base")
     n = q.shape[0]
@@ -195,8 +207,8 @@ def paged_attention_simt(q, out, k_pool, v_pool, block_table, positions, row_seq
     check(lib().fb_paged_attention_simt(
         q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), dtype_code(q), k_pool.data_ptr(), v_pool.data_ptr(),
         page_size, n_pages, block_table.data_ptr(), block_table.stride(0), _ptr(table_base), positions.data_ptr(),
-        row_seq.data_ptr(), n, nh, nkv, hd, int(window), float(scale), status.data_ptr(), _stream()),
-        "paged_attention_simt")
+        row_seq.data_ptr(), n, nh, nkv, hd, int(window), float(scale), _slopes(score_slopes, nh), status.data_ptr(),
+        _stream()), "paged_attention_simt")
 
 
 def apply_penalties(logits, rows, tokens, counts, repetition, presence, frequency) -> None:
@@ -378,14 +390,15 @@ def mma_attention_supported(q: torch.Tensor, nh: int, nkv: int, hd: int) -> bool
 def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, n_seqs: int,
                         max_q_len: int, max_kv_len: int, any_short: bool, any_long: bool, nh: int, nkv: int,
                         hd: int, window: int, scale: float, status, table_base=None, prefetch=None,
-                        multi_seqs=None, n_multi: int = 0) -> None:
+                        multi_seqs=None, n_multi: int = 0, score_slopes=None) -> None:
     """bfloat16 attention on the tensor cores over the paged cache; sequences are described per entry of the
     step (first row, rows, first position).  any_short / any_long say whether the step holds sequences with
     rows * (nh/nkv) <= 16 / > 16, which run in different arrangements of the kernel.  table_base (int32 per
     sequence, optional): the logical page that column 0 of each table row stands for.  prefetch (optional): the
     weight matrix of the product that follows (see prefetch_arguments).  multi_seqs (int32, optional): the
     n_multi sequences of the step that bring more than one token; the kernels for portions then lay their grid over
-    these instead of over every sequence."""
+    these instead of over every sequence.  score_slopes (float32 per query head, optional): slope * (key position -
+    query position) is added to every scaled score; portions then run on the mma.sync kernel."""
     _cuda(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, status, table_base, multi_seqs)
     _i32(table_base, "table_base")
     _i32(multi_seqs, "multi_seqs")
@@ -402,12 +415,13 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
         block_table.data_ptr(), block_table.stride(0), _ptr(table_base), seq_q_start.data_ptr(),
         seq_q_len.data_ptr(), seq_pos_start.data_ptr(), _ptr(multi_seqs), int(n_multi), n_seqs, max_q_len, max_kv_len,
         1 if any_short else 0,
-        1 if any_long else 0, nh, nkv, hd, int(window), float(scale), scratch.data_ptr(), scratch.numel(),
+        1 if any_long else 0, nh, nkv, hd, int(window), float(scale), _slopes(score_slopes, nh), scratch.data_ptr(),
+        scratch.numel(),
         *prefetch_arguments(prefetch), status.data_ptr(), _stream()), "paged_attention_mma")
 
 
 def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int, scale: float,
-                    next_weight=None) -> None:
+                    next_weight=None, score_slopes=None) -> None:
     """Attention of every row of the step over its request's cached keys: the tensor-core kernel for bfloat16
     and head sizes it takes, the float32 CUDA-core kernel otherwise (all of the 32-bit mode).  next_weight: the
     matrix of the product that follows, whose start the bfloat16 kernel may fetch into L2 (a hint)."""
@@ -418,7 +432,9 @@ def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int,
         paged_attention_mma(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.seq_q_start_d, b.seq_q_len_d,
                             b.seq_pos_start_d, b.n_seqs, b.max_q_len, b.max_kv_len, any(short), not all(short),
                             nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,
-                            prefetch=next_weight, multi_seqs=b.multi_seqs_d, n_multi=b.n_multi)
+                            prefetch=next_weight, multi_seqs=b.multi_seqs_d, n_multi=b.n_multi,
+                            score_slopes=score_slopes)
     else:
         paged_attention_simt(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.positions, b.row_seq,
-                             nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base)
+                             nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,
+                             score_slopes=score_slopes)

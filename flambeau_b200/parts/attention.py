@@ -24,12 +24,17 @@ class PagedAttention(Mixer):
     head of q and of k between the projection and the rotation, with weights
     `<prefix>q_norm.weight` and `<prefix>k_norm.weight` (the optional
     attn_q_norm / attn_k_norm of crates/forward/src/ctx.rs:368-369; the
-    architecture built here has none)."""
+    architecture built here has none).
+    `distance_slopes` (optional, one number per query head): slope * (key
+    position - query position) is added to every scaled score, a linear
+    penalty on distance that a position scheme without rotation can be built
+    from (the architecture built here has none; portions of prompts then run
+    on the mma.sync kernel, which has the hook)."""
     graph_safe = True
 
     def __init__(self, runtime=None, prefix="", *, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  window: int = 0, position: PartSpec | None = None, scale: float | None = None,
-                 init_std: float = 0.02, qk_norm: PartSpec | None = None):
+                 init_std: float = 0.02, qk_norm: PartSpec | None = None, distance_slopes=None):
         super().__init__(runtime, prefix)
         self.width, self.nh, self.nkv, self.hd = int(width), int(num_heads), int(num_kv_heads), int(head_dim)
         if self.nh % self.nkv:
@@ -42,6 +47,13 @@ class PagedAttention(Mixer):
             self.q_norm = build_part(PartSpec(qk_norm.category, qk_norm.kind, qk_norm.params, prefix + "q_norm."), runtime)
             self.k_norm = build_part(PartSpec(qk_norm.category, qk_norm.kind, qk_norm.params, prefix + "k_norm."), runtime)
         self.init_std = init_std
+        self.distance_slopes = None
+        if distance_slopes is not None:
+            slopes = [float(x) for x in distance_slopes]
+            if len(slopes) != self.nh:
+                raise ValueError(f"{len(slopes)} distance slopes for {self.nh} query heads")
+            self.distance_slopes = torch.tensor(slopes, dtype=torch.float32,
+                                                device=runtime.device if runtime is not None else "cpu")
         self.qw, self.kvw = self.nh * self.hd, self.nkv * self.hd
         self.qkv = self.o = None
 
@@ -118,7 +130,7 @@ class PagedAttention(Mixer):
             # few rows: the attention kernel fetches the start of the output projection's weights into L2 at its end
             hint = self.o.weight if ctx.l2_hints and n <= 64 else None
             ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale,
-                                next_weight=hint)
+                                next_weight=hint, score_slopes=self.distance_slopes)
             ctx.pending_slabs = self.o.slabs(ctx, a, ctx.delta_slabs)
 
 

@@ -22,6 +22,7 @@ class Scene:
         g = torch.Generator().manual_seed(seed)
         rnd = random.Random(seed)
         self.nh, self.nkv, self.hd, self.window, self.dtype, self.ps = nh, nkv, hd, window, dtype, page_size
+        self.slopes = None            # per query head: slope * (key position - query position) added to the scores
         self.seqs = seqs
         total_pages = sum(-(-(a + b) // page_size) for a, b in seqs) + extra_pages
         ids = list(range(total_pages))
@@ -80,6 +81,8 @@ class Scene:
                 t0 = max(0, p - self.window + 1) if self.window else 0
                 for h in range(self.nh):
                     sc = scale * (k[t0:p + 1, h // G] @ q[j, h])
+                    if self.slopes is not None:
+                        sc = sc + float(self.slopes[h]) * (torch.arange(t0, p + 1, dtype=torch.float64) - p)
                     w = torch.softmax(sc, dim=0)
                     out[i, h] = w @ v[t0:p + 1, h // G]
                 i += 1
@@ -99,9 +102,11 @@ class Scene:
         status = torch.zeros(1, dtype=torch.int32, device=dev)
         table = self.table.to(dev)
         base = self.table_base.to(dev) if self.table_base is not None else None
+        slopes = self.slopes.to(dev, torch.float32) if self.slopes is not None else None
         if kernel == "simt":
             ops.paged_attention_simt(q, out, kp, vp, table, self.positions.to(dev), self.row_seq.to(dev),
-                                     self.nh, self.nkv, self.hd, self.window, scale, status, table_base=base)
+                                     self.nh, self.nkv, self.hd, self.window, scale, status, table_base=base,
+                                     score_slopes=slopes)
         else:
             G = self.nh // self.nkv
             short = [n * G <= 16 for _, n in self.seqs]
@@ -112,7 +117,7 @@ class Scene:
                                     self.seq_pos_start.to(dev), len(self.seqs), max(n for _, n in self.seqs),
                                     max(c + n for c, n in self.seqs), any(short), not all(short), self.nh, self.nkv,
                                     self.hd, self.window, scale, status, table_base=base, prefetch=prefetch,
-                                    multi_seqs=multi_d, n_multi=len(multi))
+                                    multi_seqs=multi_d, n_multi=len(multi), score_slopes=slopes)
         torch.cuda.synchronize()
         assert int(status.item()) == 0, "the kernel flagged a fault (missing page or timed-out wait)"
         return out.float().cpu()
@@ -138,6 +143,33 @@ GEOMETRY = [(4, 4, 16), (4, 2, 24), (8, 2, 64), (8, 1, 80), (32, 8, 128), (6, 3,
 def test_portions_beside_decoded_tokens(kernel, dtype, nh, nkv, hd, window):
     seqs = [(0, 37), (50, 1), (3, 2), (129, 1), (17, 70), (0, 1), (64, 3), (200, 1)]
     check(Scene(seqs, nh, nkv, hd, window, dtype, seed=nh * 100 + hd + window), kernel)
+
+
+@pytest.mark.parametrize("kernel,dtype", KERNELS)
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 24), (8, 2, 64), (32, 8, 128), (32, 1, 64)])
+@pytest.mark.parametrize("window", [0, 40])
+def test_a_penalty_on_distance_per_head(kernel, dtype, nh, nkv, hd, window):
+    """slope_h * (key position - query position) added to the scores: slopes that differ from head to head and are
+    steep enough to change which keys count (the nearest few for the steepest head, all of them for slope 0);
+    decoded tokens at several depths beside portions, so the split-key and the portion arrangements both run."""
+    sc = Scene([(300, 1), (0, 37), (130, 1), (75, 20), (11, 1)], nh, nkv, hd, window, dtype, seed=nh + hd + window,
+               spread=0.5)
+    sc.slopes = torch.tensor([0.0 if h == 0 else 2.0 ** (-8.0 * h / nh) for h in range(nh)], dtype=torch.float64)
+    check(sc, kernel)
+    plain = Scene([(300, 1), (0, 37), (130, 1), (75, 20), (11, 1)], nh, nkv, hd, window, dtype, seed=nh + hd + window,
+                  spread=0.5)
+    scale = 1.0 / math.sqrt(hd)
+    moved = (sc.reference(scale) - plain.reference(scale)).abs().max() / plain.reference(scale).abs().max()
+    assert moved > 0.05, "the slopes of this test do not move the result: it could not fail"
+
+
+def test_slopes_must_be_one_float_per_head():
+    from flambeau_b200.kernels import ops
+    from flambeau_b200.kernels.library import KernelError
+    sc = Scene([(20, 1)], 4, 2, 32, 0, torch.bfloat16)
+    sc.slopes = torch.zeros(3, dtype=torch.float64)
+    with pytest.raises(KernelError, match="one per query head"):
+        sc.run("mma", 0.1)
 
 
 @pytest.mark.parametrize("kernel,dtype", KERNELS)

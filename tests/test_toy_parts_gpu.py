@@ -143,8 +143,14 @@ class ToyConfig:
 
 # run order: attention (rotary split-half, window) | decay mixer | decay mixer again (same weights, its own
 # state) | attention with the toy position encoding, full context | a call of layer 0 again that reads the cache
-# of the first call instead of writing one
-ORDER = [(0, None), (1, None), (1, None), (2, None), (0, 0)]
+# of the first call instead of writing one | attention without any rotation, whose positions act through a per-head
+# penalty on distance added to the scores
+ORDER = [(0, None), (1, None), (1, None), (2, None), (0, 0), (3, None)]
+
+
+def toy_slopes(cfg):
+    """Per query head: 0 for the first (it sees all keys alike), then steeper and steeper."""
+    return [0.0 if h == 0 else 2.0 ** (-3.0 * h / cfg.heads) for h in range(cfg.heads)]
 
 
 def toy_spec(cfg: ToyConfig):
@@ -178,10 +184,13 @@ def toy_spec(cfg: ToyConfig):
         qk_norm=PartSpec("norm", "rmsnorm", dict(width=cfg.head_dim, eps=cfg.eps, weight_offset=1.0,
                                                  init=("normal", 0.2)))),
         "layers.2.attn.")
+    attn3 = PartSpec("mixer", "attention", dict(
+        width=H, num_heads=cfg.heads, num_kv_heads=cfg.kv_heads, head_dim=cfg.head_dim, window=cfg.window,
+        init_std=cfg.attn_std, position=None, distance_slopes=toy_slopes(cfg)), "layers.3.attn.")
     return ModelSpec(
         hidden_size=H, vocab_size=cfg.vocab_size,
         embedding=PartSpec("embedding", "token_embedding", dict(vocab=cfg.vocab_size, width=H, init_std=0.5), "embed."),
-        layers=[block(0, attn0), block(1, decay), block(2, attn2)],
+        layers=[block(0, attn0), block(1, decay), block(2, attn2), block(3, attn3)],
         order=[LayerCall(l, c) for l, c in ORDER],
         final_norm=norm("final_norm."),
         head=PartSpec("head", "lm_head", dict(vocab=cfg.vocab_size, width=H, init_std=0.1), "head."))
@@ -206,14 +215,14 @@ def plain_toy_logits(cfg: ToyConfig, W, tokens):
             x = x + out
         else:
             nh = cfg.heads
-            nkv = cfg.kv_heads if layer == 0 else cfg.heads
+            nkv = cfg.heads if layer == 2 else cfg.kv_heads
             a = p + "attn."
             q = (h @ W[a + "q_proj.weight"].T).reshape(T, nh, cfg.head_dim)
             k = (h @ W[a + "k_proj.weight"].T).reshape(T, nkv, cfg.head_dim)
             v = (h @ W[a + "v_proj.weight"].T).reshape(T, nkv, cfg.head_dim)
             if layer == 0:
                 q, k = pm.rope_split_half(q, pos, cfg.theta), pm.rope_split_half(k, pos, cfg.theta)
-            else:
+            elif layer == 2:
                 q = pm.rms_norm(q, 1.0 + W[a + "q_norm.weight"], cfg.eps)
                 k = pm.rms_norm(k, 1.0 + W[a + "k_norm.weight"], cfg.eps)
 
@@ -230,8 +239,18 @@ def plain_toy_logits(cfg: ToyConfig, W, tokens):
                 kv[c] = (k, v)
             else:
                 k, v = kv[cache_from]
-            window = cfg.window if layer == 0 else 0
-            att = pm.attention_causal_window(q, k, v, pos, window, 1.0 / math.sqrt(cfg.head_dim))
+            window = 0 if layer == 2 else cfg.window
+            if layer == 3:                              # no rotation: slope * (key position - query position) on the scores
+                att = torch.zeros(T, nh, cfg.head_dim, dtype=torch.float64)
+                slopes = toy_slopes(cfg)
+                for t in range(T):
+                    t0 = max(0, t - window + 1)
+                    for hh in range(nh):
+                        sc = (k[t0:t + 1, hh // (nh // nkv)] @ q[t, hh]) / math.sqrt(cfg.head_dim) \
+                            + slopes[hh] * (torch.arange(t0, t + 1, dtype=torch.float64) - t)
+                        att[t, hh] = torch.softmax(sc, dim=0) @ v[t0:t + 1, hh // (nh // nkv)]
+            else:
+                att = pm.attention_causal_window(q, k, v, pos, window, 1.0 / math.sqrt(cfg.head_dim))
             x = x + att.reshape(T, nh * cfg.head_dim) @ W[a + "o_proj.weight"].T
         h = pm.rms_norm(x, W[p + "norm2.weight"], cfg.eps)
         if layer == 1:
