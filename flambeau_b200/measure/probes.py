@@ -14,8 +14,9 @@ from ..kernels import build
 PROBES = build.CSRC / "probes"
 
 
-def run_probe(name: str) -> str:
-    """Compiles csrc/probes/<name>.cu (if its binary is older than the source) and returns what it prints."""
+def build_probe(name: str):
+    """Compiles csrc/probes/<name>.cu for sm_100a into the build folder (if its binary is older than the source or
+    the shared headers) and returns the program's path."""
     src = PROBES / f"{name}.cu"
     if not src.is_file():
         raise build.BuildError(f"no probe '{name}' under {PROBES}")
@@ -25,6 +26,16 @@ def run_probe(name: str) -> str:
         flags = [f for f in build.NVCC_FLAGS if f not in ("-Xcompiler", "-fPIC", "-fvisibility=hidden")]
         build._run_with_heartbeat([build.find_nvcc(), *flags, "-I", str(build.CSRC), "-o", str(exe), str(src)],
                                   src.name)
+    return exe
+
+
+def probe_names() -> list:
+    return sorted(p.stem for p in PROBES.glob("*.cu"))
+
+
+def run_probe(name: str) -> str:
+    """Builds the probe if need be, runs it and returns what it prints."""
+    exe = build_probe(name)
     done = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
     if done.returncode != 0:
         raise RuntimeError(f"probe {name} failed: {done.stderr.strip() or done.stdout.strip()}")
