@@ -93,9 +93,9 @@ class BatchBuffers:
         if self.device.type != "cuda":
             dst.view(-1, pitch)[:rows, :width].copy_(src.view(-1, pitch)[:rows, :width])
             return
-        from ..kernels.ops import _stream
+        from ..kernels.ops import current_stream
         if self._lib.fb_copy_rows_to_device(dst.data_ptr(), 4 * pitch, src.data_ptr(), 4 * pitch, 4 * width, rows,
-                                            _stream()) != 0:
+                                            current_stream()) != 0:
             raise BatchError(self._lib.fb_last_error().decode(errors="replace"))
 
     def build(self, entries: list, cache, vocab_size: int) -> StepBatch:

@@ -28,11 +28,14 @@ except AttributeError:                 # a torch without it: the public way, a f
     _raw_stream = None
 
 
-def _stream() -> int:
+def current_stream() -> int:
     """The CUDA stream the kernels are queued on: torch's current stream of the current device."""
     if _raw_stream is not None:
         return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
+
+
+_stream = current_stream
 
 
 def _cuda(*tensors) -> None:
