@@ -55,10 +55,41 @@ def read_safetensors(path) -> dict[str, torch.Tensor]:
     return out
 
 
-def read_model_folder(folder):
+class LazyWeights:
+    """name -> float64 tensor like read_safetensors, but every tensor is read and converted when it is asked for and
+    not kept: for models whose weights in float64 would not fit the host's memory at once."""
+
+    def __init__(self, path):
+        self.path = Path(path)
+        with open(self.path, "rb") as f:
+            (hlen,) = struct.unpack("<Q", f.read(8))
+            self.header = {k: v for k, v in json.loads(f.read(hlen)).items() if k != "__metadata__"}
+        self.base = 8 + hlen
+
+    def __contains__(self, name):
+        return name in self.header
+
+    def keys(self):
+        return self.header.keys()
+
+    def __getitem__(self, name):
+        info = self.header[name]
+        lo, hi = info["data_offsets"]
+        with open(self.path, "rb") as f:
+            f.seek(self.base + lo)
+            buf = f.read(hi - lo)
+        if info["dtype"] == "BF16":
+            arr = (np.frombuffer(buf, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+        else:
+            arr = np.frombuffer(buf, dtype=_NP_DTYPES[info["dtype"]])
+            arr = arr.astype(np.float64) if arr.dtype.kind == "f" else arr.copy()
+        return torch.from_numpy(arr.reshape(info["shape"]))
+
+
+def read_model_folder(folder, lazy: bool = False):
     folder = Path(folder)
     cfg = json.loads((folder / "config.json").read_text())
-    weights = read_safetensors(folder / "model.safetensors")
+    weights = LazyWeights(folder / "model.safetensors") if lazy else read_safetensors(folder / "model.safetensors")
     return cfg, weights
 
 
@@ -222,7 +253,8 @@ def forward_logits(cfg: dict, W: dict, tokens, dense: bool = False, rows=None) -
     if given; `dense` takes the masked-matrix form of the attention, for long sequences).
     crates/forward/README.md:18-39 gives the order of the parts."""
     c = _cfg(cfg)
-    W = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in W.items()}
+    if not isinstance(W, LazyWeights):
+        W = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in W.items()}
     positions = torch.arange(len(tokens))
     x = embedding(W["model.embed_tokens.weight"], tokens)
     for layer in range(c["L"]):

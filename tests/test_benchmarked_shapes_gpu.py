@@ -5,13 +5,15 @@
     and decoded tokens cross the window's edge and the leading pages are given back.  Width, inner size and
     vocabulary are cut down (they are covered at full size by test_large_shape_gpu.py), which keeps the float64
     oracle to a few seconds.
-  * The 7B shape itself at depth: 8 of its 32 layers at full sizes, a 64-token prompt whole, in portions, and
-    with its last tokens one by one.  In 32-bit the bound is the 1e-4 of every other test; in bfloat16 it is the
+  * The 7B shape itself, all 32 layers at full sizes: a 64-token prompt whole, in portions, and with its last
+    tokens one by one.  In 32-bit the bound is the 1e-4 of every other test; in bfloat16 it is the
     tiny models' 2e-2 scaled by the square root of the depth (tiny.tol_at_depth says why), and the error that is
     reached is printed.
   * Head sizes that are even but no multiple of 8, which take the kernels' scalar forms.
   * Peak device memory while a model is loaded.
 """
+import os
+
 import pytest
 import torch
 
@@ -25,7 +27,11 @@ WINDOW_GEOMETRY = dict(architectures=["MistralForCausalLM"], hidden_size=1024, n
                        vocab_size=2000, rope_theta=10000.0, sliding_window=4096, rms_norm_eps=1e-5,
                        tie_word_embeddings=False, hidden_act="silu", max_position_embeddings=32768)
 
-SEVEN_B = dict(architectures=["MistralForCausalLM"], hidden_size=4096, num_hidden_layers=8, num_attention_heads=32,
+# The whole shape: 14.5 GB of weights on disk (removed when the module's tests are through), 29 GB on the device in
+# 32-bit, a minute and a half in all; the oracle reads its float64 weights tensor by tensor.
+# FLAMBEAU_TEST_7B_LAYERS=8 runs a quarter of it where disk or time is short.
+SEVEN_B_LAYERS = int(os.environ.get("FLAMBEAU_TEST_7B_LAYERS", "32"))
+SEVEN_B = dict(architectures=["MistralForCausalLM"], hidden_size=4096, num_hidden_layers=SEVEN_B_LAYERS, num_attention_heads=32,
                num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=32000, rope_theta=10000.0,
                sliding_window=4096, rms_norm_eps=1e-5, tie_word_embeddings=False, hidden_act="silu",
                max_position_embeddings=32768)
@@ -77,18 +83,21 @@ def test_prompt_in_portions_of_512_across_the_real_window(windowed, dtype, tmp_p
 def seven_b(tmp_path_factory):
     from flambeau_b200.config.mistral import MistralConfig
     from flambeau_b200.weights.random_init import write_random_model
-    folder = tmp_path_factory.mktemp("sevenb8")
-    write_random_model(folder, MistralConfig.from_dict(SEVEN_B), seed=3, dtype="bfloat16")
-    pcfg, W = pm.read_model_folder(folder)
-    reqs = tiny.random_requests(SEVEN_B, [64], seed=4)
-    want = {rid: pm.forward_logits(pcfg, W, toks, dense=True) for rid, toks in reqs.items()}
-    del W
-    return dict(folder=folder, requests=reqs, want=want)
+    import shutil
+    folder = tmp_path_factory.mktemp("sevenb")
+    try:
+        write_random_model(folder, MistralConfig.from_dict(SEVEN_B), seed=3, dtype="bfloat16")
+        pcfg, W = pm.read_model_folder(folder, lazy=True)
+        reqs = tiny.random_requests(SEVEN_B, [64], seed=4)
+        want = {rid: pm.forward_logits(pcfg, W, toks, dense=True) for rid, toks in reqs.items()}
+        yield dict(folder=folder, requests=reqs, want=want)
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)              # gigabytes: not left to pytest's own clean-up
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_the_7b_shape_at_depth(seven_b, dtype, tmp_path):
-    """8 of the 32 layers of the 7B shape, all at full size."""
+    """The 7B shape, all 32 layers at full size (or as many as FLAMBEAU_TEST_7B_LAYERS says)."""
     from flambeau_b200.engine.step import Engine, EngineOptions
     from flambeau_b200.engine.trace import replay
     reqs = seven_b["requests"]

@@ -113,3 +113,15 @@ def test_sampling_oracle():
     assert pm.filtered_support(p, min_p=float(p[2] / p[0]) + 1e-9) == [0, 1]
     pen = pm.apply_penalties(torch.tensor([2.0, -2.0, 1.0]), [0, 1, 1], repetition=2.0, presence=0.5, frequency=0.25)
     assert torch.allclose(pen, torch.tensor([2.0 / 2 - 0.5 - 0.25, -2.0 * 2 - 0.5 - 0.5, 1.0], dtype=torch.float64))
+
+
+def test_weights_read_one_at_a_time_give_the_same_logits(tmp_path):
+    """The reader that converts a tensor when it is asked for (for models too large for the host in float64) and the
+    reader that converts everything at once are the same numbers."""
+    import tiny
+    folder = tiny.make_folder(tmp_path / "m", tiny.CONFIG_B, seed=1, dtype="bfloat16")
+    cfg, eager = pm.read_model_folder(folder)
+    _, lazy = pm.read_model_folder(folder, lazy=True)
+    assert set(lazy.keys()) == set(eager.keys())
+    tokens = [1, 5, 9, 200, 3, 7, 8]
+    assert torch.equal(pm.forward_logits(cfg, eager, tokens), pm.forward_logits(cfg, lazy, tokens))
