@@ -264,6 +264,22 @@ def forward_logits(cfg: dict, W: dict, tokens, dense: bool = False, rows=None) -
     return lm_head(x, W, c)
 
 
+def forward_logits_many(cfg: dict, W, sequences: dict, dense: bool = False) -> dict:
+    """forward_logits for several whole sequences {name: tokens}, layer by layer over all of them, so that weights
+    which are read when asked for (LazyWeights) are read once per layer and not once per sequence."""
+    c = _cfg(cfg)
+    emb = W["model.embed_tokens.weight"].to(F64)
+    xs = {name: embedding(emb, toks) for name, toks in sequences.items()}
+    del emb
+    for layer in range(c["L"]):
+        prefix = f"model.layers.{layer}."
+        here = {k: W[k].to(F64) for k in W.keys() if k.startswith(prefix)}
+        for name, toks in sequences.items():
+            xs[name] = decoder_block(xs[name], here, layer, c, torch.arange(len(toks)), dense)
+    tail = {k: W[k].to(F64) for k in ("model.norm.weight", "model.embed_tokens.weight", "lm_head.weight") if k in W}
+    return {name: lm_head(x, tail, c) for name, x in xs.items()}
+
+
 def argmax_lowest(row: torch.Tensor) -> int:
     """Strict '>' scan, so the lowest index wins a tie.
     crates/runtime/src/sampling.rs:486-496."""

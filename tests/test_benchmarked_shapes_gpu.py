@@ -5,8 +5,8 @@
     and decoded tokens cross the window's edge and the leading pages are given back.  Width, inner size and
     vocabulary are cut down (they are covered at full size by test_large_shape_gpu.py), which keeps the float64
     oracle to a few seconds.
-  * The 7B shape itself, all 32 layers at full sizes: a 64-token prompt whole, in portions, and with its last
-    tokens one by one.  In 32-bit the bound is the 1e-4 of every other test; in bfloat16 it is the
+  * The 7B shape itself, all 32 layers at full sizes: three prompts whole, in portions, with their last
+    tokens one by one, and mixed (portions of some beside decoded tokens of others in a pool no larger than needed).  In 32-bit the bound is the 1e-4 of every other test; in bfloat16 it is the
     tiny models' 2e-2 scaled by the square root of the depth (tiny.tol_at_depth says why), and the error that is
     reached is printed.
   * Head sizes that are even but no multiple of 8, which take the kernels' scalar forms.
@@ -88,8 +88,8 @@ def seven_b(tmp_path_factory):
     try:
         write_random_model(folder, MistralConfig.from_dict(SEVEN_B), seed=3, dtype="bfloat16")
         pcfg, W = pm.read_model_folder(folder, lazy=True)
-        reqs = tiny.random_requests(SEVEN_B, [64], seed=4)
-        want = {rid: pm.forward_logits(pcfg, W, toks, dense=True) for rid, toks in reqs.items()}
+        reqs = tiny.random_requests(SEVEN_B, [64, 21, 37], seed=4)
+        want = pm.forward_logits_many(pcfg, W, reqs, dense=True)
         yield dict(folder=folder, requests=reqs, want=want)
     finally:
         shutil.rmtree(folder, ignore_errors=True)              # gigabytes: not left to pytest's own clean-up
@@ -101,13 +101,14 @@ def test_the_7b_shape_at_depth(seven_b, dtype, tmp_path):
     from flambeau_b200.engine.step import Engine, EngineOptions
     from flambeau_b200.engine.trace import replay
     reqs = seven_b["requests"]
-    engine = Engine.from_folder(seven_b["folder"], EngineOptions(dtype=dtype, cache_tokens=128, max_requests=1,
-                                                                 max_step_tokens=64, max_seq_len=128))
+    mixed = tiny.schedule_mixed(reqs, seed=5, max_live=3)
+    engine = Engine.from_folder(seven_b["folder"], EngineOptions(dtype=dtype, cache_tokens=mixed.max_live_tokens(reqs),
+                                                                 max_requests=3, max_step_tokens=128, max_seq_len=128))
     layers = SEVEN_B["num_hidden_layers"]
     tol = tiny.tol_at_depth(dtype, layers)       # float32: 1e-4 at any depth; bfloat16: 2e-2 * sqrt(layers / 3)
     worst = 0.0
     for name, sched in (("whole", tiny.schedule_whole(reqs)), ("portions", tiny.schedule_portions(reqs)),
-                        ("tail", tiny.schedule_tail(reqs, 32))):
+                        ("tail", tiny.schedule_tail(reqs, 16)), ("mixed", mixed)):
         out = tmp_path / name
         replay(engine, sched.lines(), out)
         engine.runtime.check_status(name)

@@ -125,3 +125,6 @@ def test_weights_read_one_at_a_time_give_the_same_logits(tmp_path):
     assert set(lazy.keys()) == set(eager.keys())
     tokens = [1, 5, 9, 200, 3, 7, 8]
     assert torch.equal(pm.forward_logits(cfg, eager, tokens), pm.forward_logits(cfg, lazy, tokens))
+    many = pm.forward_logits_many(cfg, lazy, {"a": tokens, "b": tokens[:3]})
+    assert torch.equal(many["a"], pm.forward_logits(cfg, eager, tokens))
+    assert torch.equal(many["b"], pm.forward_logits(cfg, eager, tokens[:3]))
