@@ -29,8 +29,21 @@ WINDOW_GEOMETRY = dict(architectures=["MistralForCausalLM"], hidden_size=1024, n
 
 # The whole shape: 14.5 GB of weights on disk (removed when the module's tests are through), 29 GB on the device in
 # 32-bit, a minute and a half in all; the oracle reads its float64 weights tensor by tensor.
-# FLAMBEAU_TEST_7B_LAYERS=8 runs a quarter of it where disk or time is short.
-SEVEN_B_LAYERS = int(os.environ.get("FLAMBEAU_TEST_7B_LAYERS", "32"))
+# FLAMBEAU_TEST_7B_LAYERS=8 runs a quarter of it where disk or time is short; so does a temporary folder with less
+# than 30 GB free, or a device with less than 60 GB free (the 32-bit engine holds 29 GB of weights).
+def _seven_b_layers() -> int:
+    asked = os.environ.get("FLAMBEAU_TEST_7B_LAYERS")
+    if asked:
+        return int(asked)
+    import shutil
+    import tempfile
+    room = shutil.disk_usage(tempfile.gettempdir()).free >= 30 << 30
+    if room and torch.cuda.is_available():
+        room = torch.cuda.mem_get_info()[0] >= 60 << 30
+    return 32 if room else 8
+
+
+SEVEN_B_LAYERS = _seven_b_layers()
 SEVEN_B = dict(architectures=["MistralForCausalLM"], hidden_size=4096, num_hidden_layers=SEVEN_B_LAYERS, num_attention_heads=32,
                num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=32000, rope_theta=10000.0,
                sliding_window=4096, rms_norm_eps=1e-5, tie_word_embeddings=False, hidden_act="silu",
