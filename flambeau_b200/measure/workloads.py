@@ -189,6 +189,10 @@ def kernel_sections(engine, entries, cfg, reps: int = 3, end=(), ahead_ms: float
         engine.use_graphs = was
 
 
+class TimelineUnavailable(RuntimeError):
+    """The driver's activity records (CUPTI) cannot be had here: another profiler holds them, or the process may not."""
+
+
 def decode_timeline(engine, batch: int, context: int, gen, warmup: int = 8) -> list:
     """The kernels of one decode step as the device ran them, from the driver's activity records (torch.profiler):
     [(start us, end us, name)] in order of start, times from the step's first kernel.  Unlike the section timer this
@@ -202,16 +206,22 @@ def decode_timeline(engine, batch: int, context: int, gen, warmup: int = 8) -> l
     for _ in range(warmup):
         ops.sample(engine.step(entries), chosen, n=batch)
     torch.cuda.synchronize()
-    with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        for _ in range(3):
-            ops.sample(engine.step(entries), chosen, n=batch)
-        torch.cuda.synchronize()
-    rows = sorted(((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+    try:
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                ops.sample(engine.step(entries), chosen, n=batch)
+            torch.cuda.synchronize()
+        events = list(prof.events())
+    except RuntimeError as exc:                          # the profiler could not start
+        engine.cache.release_all()
+        raise TimelineUnavailable(str(exc)) from None
+    rows = sorted(((e.time_range.start, e.time_range.end, e.name) for e in events
                    if "cuda" in str(e.device_type).lower() and "Memcpy" not in e.name and "Memset" not in e.name),
                   key=lambda r: r[0])
     firsts = [i for i, r in enumerate(rows) if "embedding" in r[2]]
     if len(firsts) < 3:
-        raise RuntimeError("the profiler returned no kernel records for the step")
+        engine.cache.release_all()
+        raise TimelineUnavailable("the profiler returned no kernel records for the step")
     a, b = firsts[1], firsts[2]                          # the second of the three steps
     t0 = rows[a][0]
     engine.cache.release_all()

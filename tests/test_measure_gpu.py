@@ -16,7 +16,10 @@ def test_decode_timeline_lists_the_steps_kernels_in_order(tmp_path):
     engine = Engine.from_folder(folder, EngineOptions(dtype="bfloat16", cache_tokens=512, max_requests=2,
                                                       max_step_tokens=8, max_seq_len=256))
     workloads.randomise_cache(engine)
-    rows = workloads.decode_timeline(engine, 2, 100, torch.Generator().manual_seed(0))
+    try:
+        rows = workloads.decode_timeline(engine, 2, 100, torch.Generator().manual_seed(0))
+    except workloads.TimelineUnavailable as exc:         # an instrument, not the engine: its absence fails nothing
+        pytest.skip(f"no activity records here: {exc}")
     names = [n for _, _, n in rows]
     assert "embedding" in names[0] and any("sample" in n for n in names[-2:])
     layers = tiny.CONFIG_A["num_hidden_layers"]
