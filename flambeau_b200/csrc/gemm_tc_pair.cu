@@ -30,7 +30,11 @@ constexpr int P_STAGES = 6;
 constexpr int P_A_BYTES = PBM * PBK * 2;
 constexpr int P_STAGE_BYTES = P_A_BYTES + PBNH * PBK * 2;
 constexpr int P_TMEM_COLS = 2 * PBN;
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+// The epilogue's way out: 16 tokens x this CTA's 128 features (float32 at most), two buffers for each of its two
+// groups of four warps (one is filled while a tensor-map store empties the other).
+constexpr int P_OUT_TOKENS = 16;
+constexpr int P_OUT_BYTES = P_OUT_TOKENS * PBM * 4;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256 + 4 * P_OUT_BYTES;
 // Pairs that run at a time: one per two SMs of the current device.
 inline int pair_slots() { return fb_sm_count() / 2 > 0 ? fb_sm_count() / 2 : 1; }
 
@@ -67,6 +71,17 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
+// One box of an output map (x = feature, y = token, z = slab) from shared memory to global memory; the store joins
+// the thread's current bulk group.
+__device__ __forceinline__ void tma_store_3d(const void* map, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until all but the last of this thread's groups of stores have read their shared memory (which may then be written
+// again) / until all of them are complete.
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
@@ -92,6 +107,7 @@ __device__ __forceinline__ PairUnit pair_unit(int u, int tiles_m, int tiles, int
 template <typename TO>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const __grid_constant__ CUtensorMap map_o, int boxed_out,
                     TO* __restrict__ out, long ldo, long slab_stride, int M, int N, int K, int tiles_m, int tiles,
                     int splits, int n_units, int gated, int* status) {
     constexpr int S = P_STAGES;
@@ -102,6 +118,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // [2S+2..2S+4): accumulator empty (even CTA's are used)
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 4);
     int* bail = (int*)(tmem_slot + 1);
+    uint8_t* out_stage = smem + S * P_STAGE_BYTES + 256;     // [2 groups of warps][2 buffers][16 tokens][128 features]
 
     fb_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -214,6 +231,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int quarter = warp & 3;
         const int half_id = (warp - 2) >> 2;
         const int row_local = quarter * 32 + lane;
+        uint32_t boxes = 0;                                     // boxes this group of warps has staged: the buffers take turns
         int j = 0;
         for (int u = pair; u < n_units; u += n_pairs, ++j) {
             const PairUnit w = pair_unit(u, tiles_m, tiles, splits, kb_total, M);
@@ -222,20 +240,36 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             TO* dst = out + (size_t)w.split * (size_t)slab_stride;     // this share's slab (the whole sum: slab 0)
             const int b = j & 1;
             const uint32_t use = (uint32_t)(j >> 1);
-            const bool got = !*(volatile int*)bail && mbar_wait(smem_u32(&bars[2 * S + b]), use & 1u, status);
-            if (!got) *bail = 1;
+            const bool mine = !*(volatile int*)bail && mbar_wait(smem_u32(&bars[2 * S + b]), use & 1u, status);
+            if (!mine) *bail = 1;
+            // all or none: the turns below meet at barriers of their own
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const bool got = !*(volatile int*)bail;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * PBN);
             if (got) {
+                // Sixteen tokens of the CTA's 128 features a turn, by each of the two groups of four warps.  Where the
+                // output's strides allow a tensor map the values go to shared memory as [token][feature] and one
+                // thread sends the box on its way (rows and columns beyond the output's edge are not written): a
+                // thousand 128-byte stores a tile from the warps themselves keep the epilogue waiting for the memory
+                // system's acknowledgements (7 us a tile against 2 to 3 us this way).
+                const int width = gated ? PBM / 2 : PBM;        // features of a staged row
+                const bool leader = quarter == 0 && lane == 0;
 #pragma unroll 1
                 for (int c = half_id * 16; c < w.n_tok; c += 32) {
                     if (m0 + c >= M) break;
+                    TO* stage = reinterpret_cast<TO*>(out_stage + (half_id * 2 + (boxes & 1)) * P_OUT_BYTES);
+                    ++boxes;
                     float v[16];
                     if (w.n_kb > 0) {
                         tmem_ld16(taddr + (uint32_t)c, v);
                     } else {
 #pragma unroll
                         for (int q = 0; q < 16; ++q) v[q] = 0.0f;
+                    }
+                    if (boxed_out) {
+                        if (leader) bulk_wait_read();           // the box sent from this buffer, the one before last, has left it
+                        asm volatile("bar.sync %0, 128;" ::"r"(2 + half_id) : "memory");
                     }
                     if (gated) {
                         // features alternate gate, up: the even lane writes act(gate) * up to column n / 2
@@ -245,15 +279,34 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                             const float up = __shfl_xor_sync(0xffffffffu, v[q], 1);
                             r[q] = fb_gate_times(gated, v[q], up);
                         }
-                        const bool writes = !(lane & 1) && n + 1 < N;
+                        if (boxed_out) {
+                            if (!(lane & 1)) {
 #pragma unroll
-                        for (int q = 0; q < 16; ++q)
-                            if (writes && m0 + c + q < M)
-                                dst[(size_t)(m0 + c + q) * ldo + (n >> 1)] = fb_from_float<TO>(r[q]);
+                                for (int q = 0; q < 16; ++q) stage[q * width + (row_local >> 1)] = fb_from_float<TO>(r[q]);
+                            }
+                        } else {
+                            const bool writes = !(lane & 1) && n + 1 < N;
+#pragma unroll
+                            for (int q = 0; q < 16; ++q)
+                                if (writes && m0 + c + q < M)
+                                    dst[(size_t)(m0 + c + q) * ldo + (n >> 1)] = fb_from_float<TO>(r[q]);
+                        }
+                    } else if (boxed_out) {
+#pragma unroll
+                        for (int q = 0; q < 16; ++q) stage[q * width + row_local] = fb_from_float<TO>(v[q]);
                     } else if (n < N) {
 #pragma unroll
                         for (int q = 0; q < 16; ++q)
                             if (m0 + c + q < M) dst[(size_t)(m0 + c + q) * ldo + n] = fb_from_float<TO>(v[q]);
+                    }
+                    if (boxed_out) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        asm volatile("bar.sync %0, 128;" ::"r"(2 + half_id) : "memory");
+                        if (leader) {
+                            const int x = (w.nt * (2 * PBM) + (int)rank * PBM) >> (gated ? 1 : 0);
+                            tma_store_3d(&map_o, smem_u32(stage), x, m0 + c, w.split);
+                            bulk_commit();
+                        }
                     }
                 }
             }
@@ -264,6 +317,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (*(volatile int*)bail) break;
         }
     }
+    if (warp >= 2 && (warp & 3) == 0 && lane == 0) bulk_wait_all();   // the boxes this thread sent are in memory
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     cluster_sync_all();                          // neither CTA leaves while the other may still reach into it
@@ -282,6 +336,11 @@ int launch_pair(const void* X, long lda, const void* W, long ldw, void* out, lon
     if (rc) return rc;
     rc = fb_tensor_map_bf16(&mx, X, M, K, lda, PBK, PBNH);
     if (rc) return rc;
+    // the output as boxes of 16 tokens x a CTA's features (half as many where the epilogue folds gate and up)
+    CUtensorMap mo;
+    const int boxed = fb_tensor_map_out(&mo, out, (int)sizeof(TO), M, gated ? N / 2 : N, ldo, splits, slab_stride,
+                                        gated ? PBM / 2 : PBM, P_OUT_TOKENS);
+    if (boxed < 0) return boxed;
     auto kern = gemm_tc_pair_kernel<TO>;
     static bool configured[FB_MAX_DEVICES] = {};
     if (fb_needs_setup(configured)) {
@@ -295,8 +354,9 @@ int launch_pair(const void* X, long lda, const void* W, long ldw, void* out, lon
     const long n_units = tiles * splits;
     if (n_units > 2000000000L) return fb_fail(-1, "gemm_tc_pair: too many tiles (M=%d N=%d)", M, N);
     const int pairs = (int)(n_units < pair_slots() ? n_units : pair_slots());
-    fb_launch_class(FB_LAUNCH_GEMM_PAIR, (kern), 2 * pairs, P_THREADS, P_SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, M, N, K,
-              tiles_m, (int)tiles, splits, (int)n_units, gated, status);
+    fb_launch_class(FB_LAUNCH_GEMM_PAIR, (kern), 2 * pairs, P_THREADS, P_SMEM_BYTES, stream, mw, mx, mo,
+                    boxed == 0 ? 1 : 0, (TO*)out, ldo, slab_stride, M, N, K, tiles_m, (int)tiles, splits, (int)n_units,
+                    gated, status);
     return fb_check_launch("gemm_tc_pair");
 }
 

@@ -5,6 +5,7 @@
 #include "common.cuh"
 
 #include <mutex>
+#include <stdint.h>
 #include <unordered_map>
 
 namespace {
@@ -86,5 +87,30 @@ int fb_tensor_map_bf16_uncached(CUtensorMap* out, const void* ptr, long rows, lo
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fb_fail(-3, "tensor map: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+// An output of a product: [slabs][rows][cols] of float32 or bfloat16 (row stride ld, slab stride slab_stride, in
+// elements), written in boxes of box_rows x box_cols elements of one slab as they lie in shared memory (no swizzle).
+// Not cached: outputs are workspace views that differ from call to call more often than not, and the encoder takes
+// no memory.  Returns 1 if such a map cannot be made for these strides and this address (the caller then stores
+// without it), 0 if it was made, a negative code after fb_fail() if the driver refused it.
+int fb_tensor_map_out(CUtensorMap* out, void* ptr, int elem_bytes, long rows, long cols, long ld, long slabs,
+                      long slab_stride, int box_cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return 1;
+    if (slabs < 1) slabs = 1;
+    if (slabs == 1) slab_stride = rows * ld;
+    const bool ok = ((uintptr_t)ptr & 15) == 0 && (ld * elem_bytes) % 16 == 0 && (slab_stride * elem_bytes) % 16 == 0 &&
+                    (box_cols * elem_bytes) % 16 == 0 && box_cols <= 256 && box_rows <= 256 && rows > 0 && cols > 0;
+    if (!ok) return 1;
+    const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)slabs};
+    const cuuint64_t strides[2] = {(cuuint64_t)ld * elem_bytes, (cuuint64_t)slab_stride * elem_bytes};
+    const cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = fn(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, ptr,
+                    dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fb_fail(-3, "tensor map: cuTensorMapEncodeTiled failed with code %d for an output", (int)r);
     return 0;
 }

@@ -10,3 +10,9 @@ int fb_tensor_map_bf16(CUtensorMap* out, const void* ptr, long rows, long cols, 
 // As above, but nothing is cached and no host memory is taken.
 int fb_tensor_map_bf16_uncached(CUtensorMap* out, const void* ptr, long rows, long cols, long ld, int box_cols,
                                 int box_rows);
+
+// The output of a product, [slabs][rows][cols] of float32 (elem_bytes 4) or bfloat16 (2), for stores of boxes of
+// box_rows x box_cols elements of one slab from shared memory (no swizzle).  0: made; 1: these strides or this
+// address do not allow one (store without it); negative: refused by the driver, after fb_fail().
+int fb_tensor_map_out(CUtensorMap* out, void* ptr, int elem_bytes, long rows, long cols, long ld, long slabs,
+                      long slab_stride, int box_cols, int box_rows);
