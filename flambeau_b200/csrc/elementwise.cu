@@ -164,10 +164,11 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
     }
 }
 
-// Many rows with one delta each (a prompt's portion): R rows per CTA and V vectors per thread and row, every
-// load of the CTA's rows issued before the first use.  One row per CTA leaves too few loads in flight to fill
-// the memory pipe when each thread has only one vector of the row.
-template <typename TD, typename TW, typename TO, int R, int V>
+// Many rows with one delta each, or with none (a prompt's portion): R rows per CTA and V vectors per thread and row,
+// every load of the CTA's rows issued before the first use.  One row per CTA leaves too few loads in flight to fill
+// the memory pipe when each thread has only one vector of the row.  Without a delta (the stream already holds the
+// sum) nothing is written back to the stream.
+template <typename TD, typename TW, typename TO, int R, int V, bool HAS_DELTA>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta, const TW* __restrict__ w,
                         TO* __restrict__ out, int n, int H, float eps, float w_offset) {
@@ -187,15 +188,17 @@ add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta, con
         for (int v = 0; v < V; ++v) {
             const size_t at = (size_t)min(r0 + r, n - 1) * H + 4 * (threadIdx.x + v * blockDim.x);
             a[r][v] = Vec4<float>::load(x + at);
-            d[r][v] = Vec4<TD>::load(delta + at);
+            if (HAS_DELTA) d[r][v] = Vec4<TD>::load(delta + at);
         }
+    if (HAS_DELTA) {
 #pragma unroll
-    for (int r = 0; r < R; ++r)
+        for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int v = 0; v < V; ++v) {
-            a[r][v].x += d[r][v].x; a[r][v].y += d[r][v].y; a[r][v].z += d[r][v].z; a[r][v].w += d[r][v].w;
-            if (r0 + r < n) Vec4<float>::store(x + (size_t)(r0 + r) * H + 4 * (threadIdx.x + v * blockDim.x), a[r][v]);
-        }
+            for (int v = 0; v < V; ++v) {
+                a[r][v].x += d[r][v].x; a[r][v].y += d[r][v].y; a[r][v].z += d[r][v].z; a[r][v].w += d[r][v].w;
+                if (r0 + r < n) Vec4<float>::store(x + (size_t)(r0 + r) * H + 4 * (threadIdx.x + v * blockDim.x), a[r][v]);
+            }
+    }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     float ss[R];
 #pragma unroll
@@ -232,11 +235,18 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_partials, size_
     const bool aligned = H % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
                          ((uintptr_t)out % 16 == 0) && (!delta || ((uintptr_t)delta % 16 == 0 && partial_stride % 4 == 0));
     const int nvec4 = H / 4, per_thread = (nvec4 + 1023) / 1024;
-    if (aligned && delta && !rows && n_partials == 1 && n_out > 256 && per_thread <= 2 && nvec4 % (32 * per_thread) == 0) {
+    if (aligned && !rows && (delta ? n_partials == 1 : true) && n_out > 256 && per_thread <= 2 &&
+        nvec4 % (32 * per_thread) == 0) {
         const int threads = nvec4 / per_thread;
 #define FB_NORM_ROWS(R_, V_)                                                                                  \
-        fb_launch((add_rmsnorm_rows_kernel<TD, TW, TO, R_, V_>), (n_out + R_ - 1) / R_, threads, 0, stream, x, \
-                  (const TD*)delta, (const TW*)w, (TO*)out, n_out, H, eps, w_offset)
+        do {                                                                                                  \
+            if (delta)                                                                                        \
+                fb_launch((add_rmsnorm_rows_kernel<TD, TW, TO, R_, V_, true>), (n_out + R_ - 1) / R_, threads, 0, \
+                          stream, x, (const TD*)delta, (const TW*)w, (TO*)out, n_out, H, eps, w_offset);      \
+            else                                                                                              \
+                fb_launch((add_rmsnorm_rows_kernel<TD, TW, TO, R_, V_, false>), (n_out + R_ - 1) / R_, threads, 0, \
+                          stream, x, (const TD*)delta, (const TW*)w, (TO*)out, n_out, H, eps, w_offset);      \
+        } while (0)
         if (per_thread == 2) FB_NORM_ROWS(1, 2); else if (nvec4 <= 256) FB_NORM_ROWS(4, 1); else FB_NORM_ROWS(2, 1);
 #undef FB_NORM_ROWS
         return fb_check_launch("add_rmsnorm");

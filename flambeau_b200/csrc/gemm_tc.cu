@@ -402,7 +402,7 @@ FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw
         if (const int shares = fb_gemm_pair_plan(M, N, K, slabs)) {
             if (splits_used) *splits_used = shares;
             return fb_launch_gemm_pair(X, (long)lda, W, (long)ldw, out, o_dtype, (long)ldo, (long)slab_stride, shares,
-                                       M, N, K, 0, status, stream);
+                                       M, N, K, 0, 0, status, stream);
         }
     }
     CUtensorMap mw, mx;
@@ -432,6 +432,24 @@ FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw
     return fb_fail(-1, "gemm_tc: unknown output dtype code %d", o_dtype);
 }
 
+// acc[M,N] += X[M,K] * W[N,K]^T in float32 where the product is one that leaves in whole tiles through the two-SM
+// kernel (hundreds of rows, and no shares of K would be chosen although the caller has `max_slabs` slabs for them):
+// each element gets one float32 add, so a residual stream takes a part's output without a pass of its own.
+// Returns 1 if the product was added, 0 if this is not such a product (nothing was done: the caller takes the
+// other way), negative on an error.
+FB_API int fb_gemm_tc_add(const void* X, long long lda, const void* W, long long ldw, float* acc, long long ldacc,
+                          int max_slabs, int M, int N, int K, int* status, cudaStream_t stream) {
+    FB_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc_add: bad sizes M=%d N=%d K=%d", M, N, K);
+    FB_REQUIRE(lda >= K && ldw >= K && ldacc >= N, "gemm_tc_add: a row stride is shorter than its row");
+    FB_REQUIRE(lda % 8 == 0 && ldw % 8 == 0, "gemm_tc_add: row strides must be multiples of 8 elements (16 bytes)");
+    FB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tc_add: operands must be 16-byte aligned");
+    if (M <= 128) return 0;
+    if (fb_gemm_pair_plan(M, N, K, max_slabs < 1 ? 1 : max_slabs) != 1) return 0;
+    const int rc = fb_launch_gemm_pair(X, (long)lda, W, (long)ldw, acc, FB_F32, (long)ldacc, 0, 1, M, N, K, 0, 1, status,
+                                       stream);
+    return rc ? rc : 1;
+}
+
 // out[M, N/2] = act(g) * u with [g_0, u_0, g_1, u_1, ...] = X[M,K] * W[N,K]^T: W stacks gate and up rows
 // alternately, and the activation `act` (an FbAct code) is applied in the epilogue (the whole sum in one CTA, so
 // K is not split).
@@ -446,7 +464,7 @@ FB_API int fb_gemm_tc_gated(const void* X, long long lda, const void* W, long lo
     if (M == 0) return 0;
     const int BN = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     if (BN == 256 && (o_dtype == FB_F32 || o_dtype == FB_BF16) && fb_gemm_pair_plan(M, N, K, 1))
-        return fb_launch_gemm_pair(X, (long)lda, W, (long)ldw, out, o_dtype, (long)ldo, 0, 1, M, N, K, act, status,
+        return fb_launch_gemm_pair(X, (long)lda, W, (long)ldw, out, o_dtype, (long)ldo, 0, 1, M, N, K, act, 0, status,
                                    stream);
     CUtensorMap mw, mx;
     int rc = fb_tensor_map_bf16(&mw, W, N, K, (long)ldw, BK, BM);

@@ -77,6 +77,12 @@ __device__ __forceinline__ void tma_store_3d(const void* map, uint32_t src, int 
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
                  ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
 }
+// The same, added to what global memory holds (float32 adds, done by the memory system: each element of the output
+// gets exactly one such add from this kernel, so the result does not depend on any order).
+__device__ __forceinline__ void tma_add_3d(const void* map, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Until all but the last of this thread's groups of stores have read their shared memory (which may then be written
 // again) / until all of them are complete.
@@ -109,7 +115,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_o, int boxed_out,
                     TO* __restrict__ out, long ldo, long slab_stride, int M, int N, int K, int tiles_m, int tiles,
-                    int splits, int n_units, int gated, int* status) {
+                    int splits, int n_units, int gated, int accumulate, int* status) {
     constexpr int S = P_STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -297,14 +303,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     } else if (n < N) {
 #pragma unroll
                         for (int q = 0; q < 16; ++q)
-                            if (m0 + c + q < M) dst[(size_t)(m0 + c + q) * ldo + n] = fb_from_float<TO>(v[q]);
+                            if (m0 + c + q < M) {
+                                TO* at = dst + (size_t)(m0 + c + q) * ldo + n;     // (no other thread has this element)
+                                *at = fb_from_float<TO>(accumulate ? fb_to_float(*at) + v[q] : v[q]);
+                            }
                     }
                     if (boxed_out) {
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         asm volatile("bar.sync %0, 128;" ::"r"(2 + half_id) : "memory");
                         if (leader) {
                             const int x = (w.nt * (2 * PBM) + (int)rank * PBM) >> (gated ? 1 : 0);
-                            tma_store_3d(&map_o, smem_u32(stage), x, m0 + c, w.split);
+                            if (accumulate) tma_add_3d(&map_o, smem_u32(stage), x, m0 + c, w.split);
+                            else tma_store_3d(&map_o, smem_u32(stage), x, m0 + c, w.split);
                             bulk_commit();
                         }
                     }
@@ -330,7 +340,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
 template <typename TO>
 int launch_pair(const void* X, long lda, const void* W, long ldw, void* out, long ldo, long slab_stride, int splits,
-                int M, int N, int K, int gated, int* status, cudaStream_t stream) {
+                int M, int N, int K, int gated, int accumulate, int* status, cudaStream_t stream) {
     CUtensorMap mw, mx;
     int rc = fb_tensor_map_bf16(&mw, W, N, K, ldw, PBK, PBM);
     if (rc) return rc;
@@ -356,7 +366,7 @@ int launch_pair(const void* X, long lda, const void* W, long ldw, void* out, lon
     const int pairs = (int)(n_units < pair_slots() ? n_units : pair_slots());
     fb_launch_class(FB_LAUNCH_GEMM_PAIR, (kern), 2 * pairs, P_THREADS, P_SMEM_BYTES, stream, mw, mx, mo,
                     boxed == 0 ? 1 : 0, (TO*)out, ldo, slab_stride, M, N, K, tiles_m, (int)tiles, splits, (int)n_units,
-                    gated, status);
+                    gated, accumulate, status);
     return fb_check_launch("gemm_tc_pair");
 }
 
@@ -395,13 +405,16 @@ int fb_gemm_pair_plan(int M, int N, int K, int max_slabs) {
 }
 
 int fb_launch_gemm_pair(const void* X, long lda, const void* W, long ldw, void* out, int o_dtype, long ldo,
-                        long slab_stride, int splits, int M, int N, int K, int gated, int* status,
+                        long slab_stride, int splits, int M, int N, int K, int gated, int accumulate, int* status,
                         cudaStream_t stream) {
     if (splits < 1 || (splits > 1 && (slab_stride <= 0 || o_dtype != FB_F32 || gated)))
         return fb_fail(-1, "gemm_tc_pair: %d shares of K need float32 slabs", splits);
+    if (accumulate && (o_dtype != FB_F32 || splits != 1 || gated))
+        return fb_fail(-1, "gemm_tc_pair: only a whole float32 product can be added to its output");
     if (o_dtype == FB_F32)
-        return launch_pair<float>(X, lda, W, ldw, out, ldo, slab_stride, splits, M, N, K, gated, status, stream);
+        return launch_pair<float>(X, lda, W, ldw, out, ldo, slab_stride, splits, M, N, K, gated, accumulate, status,
+                                  stream);
     if (o_dtype == FB_BF16)
-        return launch_pair<__nv_bfloat16>(X, lda, W, ldw, out, ldo, 0, 1, M, N, K, gated, status, stream);
+        return launch_pair<__nv_bfloat16>(X, lda, W, ldw, out, ldo, 0, 1, M, N, K, gated, 0, status, stream);
     return fb_fail(-1, "gemm_tc_pair: unknown output dtype code %d", o_dtype);
 }

@@ -47,6 +47,7 @@ class StepContext:
         self.normed = self.delta = self.delta_slabs = None
         self.max_slabs = 1                  # how many split-K slabs a product may leave for the next kernel to add
         self.pending_slabs = 1
+        self.stream_x = None                # the residual stream of the block that is running (set by the block)
         self.l2_hints = engine.l2_hints
 
     def open_stream(self, width: int):
@@ -64,6 +65,15 @@ class StepContext:
         self.delta = self.delta_slabs[0]
         self.pending_slabs = 1
         return x
+
+    def to_stream(self, linear, a) -> None:
+        """The last product of a mixer or a feed-forward, whose result belongs on the residual stream: added to
+        the stream by the product's own epilogue where that is possible (ctx.pending_slabs = 0: nothing is left to
+        add), else left in ctx.delta_slabs for the next norm to add (ctx.pending_slabs = how many slabs)."""
+        if self.stream_x is not None and linear.add_into(self, a, self.stream_x):
+            self.pending_slabs = 0
+        else:
+            self.pending_slabs = linear.slabs(self, a, self.delta_slabs)
 
     def step_alloc(self, shape, dtype):
         """Scratch that lives until the step ends (ctx.ws allocations end with their scope)."""

@@ -34,6 +34,7 @@ _SIGNATURES = {
     # gemm_simt.cu
     "fb_gemm_simt": (I, [P, I, L, P, I, L, P, I, L, I, I, I, STREAM]),
     # gemm_tc.cu
+    "fb_gemm_tc_add": (I, [P, L, P, L, P, L, I, I, I, I, P, STREAM]),
     "fb_gemm_tc": (I, [P, L, P, L, P, I, L, L, I, P, I, I, I, P, L, P, I, I, P, STREAM]),
     "fb_gemm_tc_gated": (I, [P, L, P, L, P, I, L, I, I, I, I, P, L, P, I, P, STREAM]),
     # attention_simt.cu

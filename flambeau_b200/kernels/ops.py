@@ -298,6 +298,26 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.T
     return _SPLITS_USED.value if slabs is not None else 1
 
 
+def gemm_tc_add(a: torch.Tensor, w: torch.Tensor, acc: torch.Tensor, status: torch.Tensor, max_slabs: int = 1) -> bool:
+    """acc[M,N] += a[M,K] @ w[N,K]^T in float32, where the product is one the two-SM tensor-core kernel takes in
+    whole tiles (hundreds of rows, and no split of K would be chosen although `max_slabs` slabs could be had): each
+    element of acc gets one float32 add from the kernel's epilogue.  Returns False, having done nothing, for any
+    other product: the caller then leaves the output where another kernel adds it."""
+    _cuda(a, w, acc, status)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or acc.shape[0] < M or acc.shape[1] != N:
+        raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} acc{tuple(acc.shape)} do not agree")
+    if acc.dtype != torch.float32 or not tc_supported(a, w, acc) or M <= 128:
+        return False
+    rc = lib().fb_gemm_tc_add(a.data_ptr(), _rows(a), w.data_ptr(), _rows(w), acc.data_ptr(), _rows(acc),
+                              int(max_slabs), M, N, K, status.data_ptr(), _stream())
+    if rc == 0:
+        return False                         # nothing was launched
+    check(0 if rc == 1 else rc, "gemm_tc_add", (M, N, K))
+    return True
+
+
 def gemm_tc_gated(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
                   activation: str = "silu") -> None:
     """out[M, N/2] = act(g) * u where (g_0, u_0, g_1, u_1, ...) = a @ w^T: w stacks gate and up rows alternately

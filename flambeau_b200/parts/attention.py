@@ -131,7 +131,7 @@ class PagedAttention(Mixer):
             hint = self.o.weight if ctx.l2_hints and n <= 64 else None
             ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale,
                                 next_weight=hint, score_slopes=self.distance_slopes)
-            ctx.pending_slabs = self.o.slabs(ctx, a, ctx.delta_slabs)
+            ctx.to_stream(self.o, a)
 
 
 register_part("mixer", "attention", PagedAttention)

@@ -10,7 +10,9 @@ class ResidualStream:
     not been added yet (`pending`): the next norm adds it while it normalises,
     so the add costs no pass of its own.  `pending_slabs` > 1 says that the
     output is a sum of that many float32 slabs (split-K shares of the part's last
-    product, ctx.delta_slabs[0..k)), which the norm adds as well."""
+    product, ctx.delta_slabs[0..k)), which the norm adds as well; 0 says that the
+    part's last product has added its result to x itself (ctx.to_stream), so the
+    norm has nothing to add."""
 
     def __init__(self, x, pending=None, pending_slabs: int = 1):
         self.x, self.pending, self.pending_slabs = x, pending, pending_slabs
@@ -35,6 +37,7 @@ class PreNormBlock(Part):
 
     def forward(self, ctx, stream: ResidualStream, call) -> None:
         h, delta = ctx.normed, ctx.delta
+        ctx.stream_x = stream.x
         self.mixer_norm.add_norm(ctx, stream.x, stream.pending, h, n_partials=stream.pending_slabs)
         ctx.pending_slabs = 1                 # a part that leaves split-K shares in ctx.delta_slabs says how many
         self.mixer.forward(ctx, h, delta, call)

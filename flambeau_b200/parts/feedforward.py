@@ -72,7 +72,7 @@ class GatedMLP(FeedForward):
                 gu = ctx.ws.alloc((n, 2 * self.inner), self.runtime.dtype)
                 self.gate_up(ctx, h, gu)
                 ops.gate_mul(gu, a, activation=self.activation)
-            ctx.pending_slabs = self.down.slabs(ctx, a, ctx.delta_slabs)
+            ctx.to_stream(self.down, a)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

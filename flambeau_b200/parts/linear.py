@@ -22,6 +22,11 @@ class Linear:
         """The product as a sum of float32 slabs (split-K shares that the next kernel adds); returns how many."""
         return ops.linear_slabs(a, self.weight, slabs, ctx)
 
+    def add_into(self, ctx, a: torch.Tensor, acc: torch.Tensor) -> bool:
+        """acc += a W^T where the product's own epilogue can do the add (see ops.gemm_tc_add); False, with nothing
+        done, where it cannot."""
+        return ops.gemm_tc_add(a, self.weight, acc, ctx.runtime.status, ctx.max_slabs)
+
 
 def interleave_rows(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """Rows a_0, b_0, a_1, b_1, ...: two maps of one input whose outputs are wanted side by side."""

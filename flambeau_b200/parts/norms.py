@@ -31,6 +31,8 @@ class RMSNorm(Norm):
         return [self.weight]
 
     def add_norm(self, ctx, x, delta, out, rows=None, n_partials: int = 1):
+        if n_partials == 0:                  # the stream already holds the sum
+            delta = None
         stride = ctx.delta_slabs.stride(0) if n_partials > 1 else 0
         ops.add_rms_norm(x, delta, self.weight, self.eps, out, rows=rows, n_partials=n_partials,
                          n_rows=ctx.n_tokens, partial_stride=stride, weight_offset=self.weight_offset)

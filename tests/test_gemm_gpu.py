@@ -85,6 +85,40 @@ def test_two_sm_product_equals_the_one_sm_product(M, N, K):
     assert rel_err(outs[0], a.double() @ w.double().T) < 2e-5
 
 
+@pytest.mark.parametrize("M,N,K,taken", [(2048, 4096, 4096, True), (2048, 4096, 14336, True), (600, 5000, 264, True),
+                                         (2080, 1536, 520, True), (257, 10000, 128, True), (64, 4096, 4096, False),
+                                         (128, 1024, 512, False), (512, 1024, 16384, False)])
+def test_product_added_to_its_output(M, N, K, taken):
+    """acc += a w^T from the two-SM kernel's epilogue: one float32 add per element, edges of the output clipped,
+    twice in a row for the second add, reproducible; and products that the kernel does not take in whole tiles (few
+    rows; a long K on few tiles, which wants shares) are declined with the output untouched."""
+    from flambeau_b200.kernels import ops
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    acc0 = torch.randn(M + 3, N, device="cuda", generator=g)           # rows beyond M belong to someone else
+    acc = acc0.clone()
+    assert ops.gemm_tc_add(a, w, acc, status, max_slabs=4) == taken
+    if not taken:
+        assert torch.equal(acc, acc0)
+        return
+    exact = a.double() @ w.double().T
+    assert int(status.item()) == 0
+    assert torch.equal(acc[M:], acc0[M:])
+    assert rel_err(acc[:M], acc0[:M].double() + exact) < 2e-5
+    again = acc0.clone()
+    assert ops.gemm_tc_add(a, w, again, status, max_slabs=4)
+    assert torch.equal(acc, again), "the sum is not reproducible"
+    assert ops.gemm_tc_add(a, w, acc, status, max_slabs=4)
+    assert rel_err(acc[:M], acc0[:M].double() + 2 * exact) < 2e-5
+    # an output whose rows are not 16 bytes apart has no tensor map: the warps add for themselves
+    wide = torch.randn(M, N + 1, device="cuda", generator=g)
+    view0 = wide[:, :N].clone()
+    assert ops.gemm_tc_add(a, w, wide[:, :N], status, max_slabs=4)
+    assert rel_err(wide[:, :N], view0.double() + exact) < 2e-5 and int(status.item()) == 0
+
+
 @pytest.mark.parametrize("M,N,K,P", [(8, 4096, 4096, 16), (64, 512, 8192, 8), (40, 1000, 264, 4), (512, 4096, 14336, 8),
                                      (300, 1000, 8192, 4), (1024, 2048, 4096, 8), (2048, 4096, 1024, 4)])
 def test_shares_of_k_left_in_slabs(M, N, K, P):

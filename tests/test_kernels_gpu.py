@@ -119,6 +119,12 @@ def test_add_rms_norm_many_rows(n, H, dd, od):
     v = x0.double() + delta.double()
     close(x, v, 1e-6)
     close(out, pm.rms_norm(v, w.double(), eps), 3e-6 if od == "f" else 6e-3)
+    # nothing to add (the stream holds the sum already): the same rows, normalised, the stream untouched
+    x1 = x.clone()
+    out.fill_(float("nan"))
+    ops.add_rms_norm(x, None, w, eps, out)
+    assert torch.equal(x, x1)
+    close(out, pm.rms_norm(x1.double(), w.double(), eps), 3e-6 if od == "f" else 6e-3)
 
 
 @pytest.mark.parametrize("half,theta", [(8, 1e4), (12, 1e6), (64, 1e4)])

@@ -15,14 +15,14 @@ pytestmark = pytest.mark.gpu
 class Bench:
     """A runtime, a cache manager for the given call plans and a step context: what a part needs to run."""
 
-    def __init__(self, dtype, plans=(), cache_tokens=256):
+    def __init__(self, dtype, plans=(), cache_tokens=256, max_step_tokens=256):
         from flambeau_b200.engine.runtime import Runtime
         from flambeau_b200.engine.step import Engine, EngineOptions
         self.rt = Runtime("cuda:0", dtype, 16)
         stub = SimpleNamespace(runtime=self.rt, spec=SimpleNamespace(max_positions=None), vocab_size=1000,
                                cache_plans=lambda: list(plans), graph_safe=lambda: False)
         self.engine = Engine(stub, EngineOptions(dtype=dtype, cache_tokens=cache_tokens, max_requests=4,
-                                                 max_step_tokens=256, max_seq_len=cache_tokens))
+                                                 max_step_tokens=max_step_tokens, max_seq_len=cache_tokens))
 
     def begin(self, entries, width):
         from flambeau_b200.engine.batch import Entry
@@ -208,3 +208,35 @@ def test_pre_norm_block(dtype):
     c = dict(nh=nh, nkv=nkv, hd=hd, theta=1e4, window=0, eps=eps)
     want = pm.decoder_block(x0.double(), Wm, 0, c, torch.arange(T))
     assert rel(got, want) < TOL[dtype]
+
+
+def test_pre_norm_block_whose_products_add_to_the_stream():
+    """A portion of hundreds of rows in bfloat16: the output projection and the down projection add their results
+    to the stream in their own epilogues (nothing is left pending for the next norm), and the block is the plain
+    computation's all the same."""
+    from flambeau_b200.cache.manager import CallPlan
+    from flambeau_b200.parts.base import KVRequirement
+    from flambeau_b200.parts.block import PreNormBlock, ResidualStream
+    from flambeau_b200.parts.spec import PartSpec
+    dtype = "bfloat16"
+    width, nh, nkv, hd, inner, eps = 72, 3, 1, 16, 64, 1e-5    # K of 64 at most: no split of K is worth its slab
+    T = 333
+    b = Bench(dtype, plans=[CallPlan(kv=KVRequirement(nkv, hd, 0))], cache_tokens=512, max_step_tokens=512)
+    norm = lambda p: PartSpec("norm", "rmsnorm", dict(width=width, eps=eps), p)
+    block = PreNormBlock(b.rt, "L.", mixer=PartSpec("mixer", "attention", dict(
+        width=width, num_heads=nh, num_kv_heads=nkv, head_dim=hd, init_std=0.1,
+        position=PartSpec("position", "rotary_half", dict(head_dim=hd, theta=1e4))), "L.self_attn."),
+        feed_forward=PartSpec("feed_forward", "gated_mlp", dict(width=width, inner=inner, init_std=0.1), "L.mlp."),
+        mixer_norm=norm("L.input_layernorm."), feed_forward_norm=norm("L.post_attention_layernorm."))
+    W = bind_random(block, DT[dtype])
+    ctx, x = b.begin([("a", [1] * T, [])], width)
+    x0 = torch.randn(T, width)
+    x.copy_(x0)
+    stream = ResidualStream(x)
+    block.forward(ctx, stream, 0)
+    b.end()
+    assert stream.pending_slabs == 0, "the down projection left its result for the norm to add"
+    Wm = {k.replace("L.", "model.layers.0."): v for k, v in W.items()}
+    c = dict(nh=nh, nkv=nkv, hd=hd, theta=1e4, window=0, eps=eps)
+    want = pm.decoder_block(x0.double(), Wm, 0, c, torch.arange(T))
+    assert rel(x, want) < TOL[dtype]
