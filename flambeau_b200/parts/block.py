@@ -46,6 +46,7 @@ class PreNormBlock(Part):
         ctx.pending_slabs = 1
         self.feed_forward.forward(ctx, h, delta)
         stream.pending, stream.pending_slabs = delta, ctx.pending_slabs
+        ctx.stream_x = None                   # another kind of block decides for itself whether parts may add to its stream
 
 
 register_part("block", "pre_norm", PreNormBlock)
