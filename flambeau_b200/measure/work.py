@@ -36,7 +36,7 @@ def decode_step_bytes(weight_bytes: int, kv_bytes_per_token: int, contexts, wind
     return weight_bytes + sum(live_keys(c, window) for c in contexts) * kv_bytes_per_token
 
 
-def kernel_classes(cfg, rows: int, contexts, elem: int = 2) -> dict:
+def kernel_classes(cfg, rows: int, contexts, elem: int = 2, to_stream=None) -> dict:
     """For one layer call (and the head) of a step with `rows` rows whose sequences hold `contexts` tokens:
     class name -> dict(bytes, flops, matrix=(N, K) for the products).  `elem`: bytes of a weight or cache element.
     A step of decoded tokens has one row per context; a portion of a prompt has one context and `rows` rows that
@@ -57,14 +57,21 @@ def kernel_classes(cfg, rows: int, contexts, elem: int = 2) -> dict:
         seen = keys_seen(positions, W)
         first_key = max(0, ctx - rows - W + 1) if W else 0
         attn_bytes = (ctx - first_key) * 2 * kvw * elem + 2 * rows * qw * elem
+    # Over a portion in bfloat16 the output and down projections add to the residual stream themselves (read and
+    # write it once, 8 bytes an element) and the norm after them reads the stream and writes the normalised rows;
+    # else the projection writes float32, and the norm reads stream and projection and writes both.
+    # (to_stream: whether they did; None: as the engine does for the benchmarked shapes at this row count)
+    if to_stream is None:
+        to_stream = rows > 512 and elem == 2
+    norm_bytes = rows * H * ((4 + elem) if to_stream else (4 + 4 + 4 + elem))
     return {
         "qkv_proj": product(qw + 2 * kvw, H),
         "rotary_cache_write": dict(bytes=rows * (qw + 2 * kvw) * (4 + elem), flops=0.0),
         "attention": dict(bytes=attn_bytes, flops=4.0 * seen * qw),
-        "o_proj": product(H, qw),
-        "add_norm": dict(bytes=rows * H * (4 + 4 + 4 + elem), flops=0.0),
+        "o_proj": product(H, qw, out_elem=8 if to_stream else 4),
+        "add_norm": dict(bytes=norm_bytes, flops=0.0),
         "gate_up_proj": dict(**product(2 * I, H, out_elem=elem), fused_activation=True),
         "gate_mul": dict(bytes=rows * I * (2 * 4 + elem), flops=0.0),
-        "down_proj": product(H, I),
+        "down_proj": product(H, I, out_elem=8 if to_stream else 4),
         "lm_head": dict(bytes=V * H * elem, flops=0.0, matrix=(V, H)),
     }

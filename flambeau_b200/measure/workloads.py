@@ -162,6 +162,11 @@ def classify(cfg, what: str, note) -> str:
             "paged_attention_simt": "attention"}.get(what, what)
 
 
+class Sections(dict):
+    """class -> (launches per step, milliseconds per step), and in `ops` the launcher calls that were seen."""
+    ops: frozenset = frozenset()
+
+
 def kernel_sections(engine, entries, cfg, reps: int = 3, end=(), ahead_ms: float = 40.0) -> dict:
     """class -> (launches per step, milliseconds per step) of one eager step of `entries`.  The step is run
     `reps + 1` times in a row, so the entries must stay valid: decoded tokens are; a whole prompt is when `end`
@@ -171,6 +176,7 @@ def kernel_sections(engine, entries, cfg, reps: int = 3, end=(), ahead_ms: float
     try:
         engine.step(entries, end=end)                          # warm
         totals: dict = {}
+        seen = set()
         for _ in range(reps):
             # a long kernel ahead of the step lets the host queue every launch before the device starts on the
             # first: the sections then hold the kernels' own times, not the host's time between two launches
@@ -182,9 +188,12 @@ def kernel_sections(engine, entries, cfg, reps: int = 3, end=(), ahead_ms: float
                     ops.sample(logits, chosen)
             for what, note, ms in t.sections():
                 c = classify(cfg, what, note)
+                seen.add(what)
                 n, total = totals.get(c, (0, 0.0))
                 totals[c] = (n + 1, total + ms)
-        return {c: (n / reps, total / reps) for c, (n, total) in totals.items()}
+        out = Sections({c: (n / reps, total / reps) for c, (n, total) in totals.items()})
+        out.ops = frozenset(seen)
+        return out
     finally:
         engine.use_graphs = was
 
@@ -366,7 +375,9 @@ def roofline_of_sections(cfg, sections: dict, rows: int, contexts, layers: int, 
     layer call (per step for the head and the sampler), the work, and the fraction of the measured peak that
     bounds it (memory for few rows and for the row-wise kernels, the tensor cores for products and attention over
     hundreds of rows)."""
-    classes = work.kernel_classes(cfg, rows, contexts)
+    # (whether the projections added to the residual stream themselves is what the step did, where that is known)
+    ops_seen = getattr(sections, "ops", None)
+    classes = work.kernel_classes(cfg, rows, contexts, to_stream=None if ops_seen is None else "gemm_tc_add" in ops_seen)
     out = {}
     for name, (launches, ms) in sections.items():
         per = 1 if name in ("lm_head", "sample", "embedding", "rope_table") else layers
