@@ -247,6 +247,13 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_partials, size_
                 fb_launch((add_rmsnorm_rows_kernel<TD, TW, TO, R_, V_, false>), (n_out + R_ - 1) / R_, threads, 0, \
                           stream, x, (const TD*)delta, (const TW*)w, (TO*)out, n_out, H, eps, w_offset);      \
         } while (0)
+        if (!delta && nvec4 >= 512 && nvec4 % 128 == 0) {
+            // Nothing to add: half the loads a row, and CTAs of a quarter of the threads with four vectors each keep
+            // more of them in flight (2,048 x 4,096: 8.6 us against 11.8 us with 1,024 threads a row).
+            fb_launch((add_rmsnorm_rows_kernel<TD, TW, TO, 2, 4, false>), (n_out + 1) / 2, nvec4 / 4, 0, stream, x,
+                      (const TD*)delta, (const TW*)w, (TO*)out, n_out, H, eps, w_offset);
+            return fb_check_launch("add_rmsnorm");
+        }
         if (per_thread == 2) FB_NORM_ROWS(1, 2); else if (nvec4 <= 256) FB_NORM_ROWS(4, 1); else FB_NORM_ROWS(2, 1);
 #undef FB_NORM_ROWS
         return fb_check_launch("add_rmsnorm");
