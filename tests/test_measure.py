@@ -52,3 +52,11 @@ def test_launcher_calls_fold_into_classes():
     assert classes["attention"]["bytes"] >= 8 * 4096 * 2 * 1024 * 2
     portion = work.kernel_classes(cfg, 2048, [2048])
     assert portion["attention"]["flops"] == 4.0 * work.keys_seen(range(2048), 0) * 4096
+    # projections that add to the residual stream themselves read and write it; the norm after them moves less
+    assert classify(cfg, "gemm_tc_add", (2048, 5120, 4096)) == "o_proj"
+    added = work.kernel_classes(cfg, 2048, [2048], to_stream=True)
+    left = work.kernel_classes(cfg, 2048, [2048], to_stream=False)
+    H = 5120
+    assert left["add_norm"]["bytes"] - added["add_norm"]["bytes"] == 2048 * H * 8
+    assert added["o_proj"]["bytes"] - left["o_proj"]["bytes"] == 2048 * H * 4
+    assert added["down_proj"]["bytes"] - left["down_proj"]["bytes"] == 2048 * H * 4
