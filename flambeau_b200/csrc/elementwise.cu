@@ -261,6 +261,9 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_partials, size_
     if (aligned && H <= 16384) {
         const int nvec = H / 4;
         int threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
+        // hundreds of rows (a portion whose product left shares of K): a quarter of the threads with four vectors
+        // each, as for the rows kernel above; a few rows (decoding) keep one vector a thread
+        if (n_out >= 128 && nvec >= 512 && nvec <= 4096 && nvec % 128 == 0) threads = nvec / 4;
         const int vpt = (nvec + threads - 1) / threads;
 #define FB_NORM_VEC(V)                                                                                        \
         fb_launch((add_rmsnorm_vec_kernel<TD, TW, TO, V>), n_out, threads, 0, stream, x, (const TD*)delta, n_partials,  \

@@ -76,10 +76,12 @@ def test_add_rms_norm_rows_and_slabs():
     close(x, x0.double() + slabs.double().sum(0), 2e-6)
 
 
-@pytest.mark.parametrize("n,H,P", [(1, 1024, 1), (8, 4096, 16), (3, 2048, 5), (64, 4096, 8), (8, 5120, 20)])
+@pytest.mark.parametrize("n,H,P", [(1, 1024, 1), (8, 4096, 16), (3, 2048, 5), (64, 4096, 8), (8, 5120, 20),
+                                   (300, 4096, 3), (200, 5120, 2), (130, 2048, 5), (150, 8192, 2), (129, 16384, 2)])
 @pytest.mark.parametrize("od", ["f", "b"])
 def test_add_rms_norm_few_wide_rows(n, H, P, od):
-    """The widths of real models with the row counts of decoding, and as many split-K slabs as the products leave."""
+    """The widths of real models with the row counts of decoding, and as many split-K slabs as the products leave;
+    and the same over the hundreds of rows of a portion whose product left shares (a launch shape of its own)."""
     from flambeau_b200.kernels import ops
     eps = 1e-5
     g = torch.Generator(device=DEV).manual_seed(n * H + P)
